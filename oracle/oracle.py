@@ -1,0 +1,309 @@
+"""ctypes driver for the CPU oracle (oracle/d3gs_oracle.cpp).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and by the
+``cpu_baseline`` / ``--impl reference`` legs of bench.py.  The product package never imports it.
+
+All functions take and return numpy arrays.  ``Scene`` bundles the Gaussian parameters in the
+reference's layout (d3sim/algos/d3gs/origin/model.py:36-44) and ``run_iteration`` chains the
+stages in the order of the reference's training step (d3sim/algos/d3gs/train.py:162-217).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "libd3gs_oracle.so")
+_SRC = os.path.join(_HERE, "d3gs_oracle.cpp")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with g++ (OpenMP when the compiler has it)."""
+    if not force and os.path.exists(_SO) and os.path.getmtime(_SO) >= os.path.getmtime(_SRC):
+        return _SO
+    os.makedirs(os.path.dirname(_SO), exist_ok=True)
+    base = ["-O2", "-fPIC", "-shared", "-std=c++17", "-ffp-contract=off", "-fno-fast-math",
+            "-Wno-unknown-pragmas", "-o", _SO, _SRC]
+    errs = []
+    for cxx in ("/usr/bin/g++", "g++"):
+        for omp in (["-fopenmp"], []):
+            r = subprocess.run([cxx] + omp + base, capture_output=True, text=True)
+            if r.returncode == 0:
+                return _SO
+            errs.append(r.stderr[-400:])
+    raise RuntimeError("could not build the CPU oracle:\n" + "\n".join(errs))
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(_SO)
+        _lib.oracle_scan_inclusive.restype = ctypes.c_int64
+        _lib.oracle_num_threads.restype = ctypes.c_int
+        for f in ("oracle_expf", "oracle_logf", "oracle_exp_blend"):
+            getattr(_lib, f).restype = ctypes.c_float
+            getattr(_lib, f).argtypes = [ctypes.c_float]
+    return _lib
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+def _p(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+@dataclass
+class OpConfig:
+    """Scalar options of the splat operator (defaults: config_def.py:77-161)."""
+    width: int = 256
+    height: int = 256
+    tile: int = 16
+    near: float = 0.2
+    far: float = 10000.0
+    eps: float = 1e-6
+    eigen_eps: float = 0.1
+    clamp_factor: float = 1.3
+    sigma: float = 3.0
+    lowpass: float = 0.3
+    alpha_eps: float = 1.0 / 255.0
+    t_eps: float = 0.0001
+    early_filter: int = 0          # EarlyFilterAlgo value
+    sh_degree: int = 3
+    training: bool = True
+    scale_global: float = 1.0
+    clamp_mask_reference_order: bool = True
+
+    def vec(self) -> np.ndarray:
+        return np.array([self.width, self.height, self.tile, self.near, self.far, self.eps, self.eigen_eps,
+                         self.clamp_factor, self.sigma, self.lowpass, self.alpha_eps, self.t_eps,
+                         self.early_filter, self.sh_degree, int(self.training), self.scale_global,
+                         int(self.clamp_mask_reference_order), 0, 0, 0], dtype=np.float32)
+
+    @property
+    def tiles_xy(self):
+        return (self.width + self.tile - 1) // self.tile, (self.height + self.tile - 1) // self.tile
+
+
+@dataclass
+class Scene:
+    xyz: np.ndarray
+    quat: np.ndarray
+    scale: np.ndarray
+    opacity: np.ndarray
+    sh_base: np.ndarray
+    sh_rest: np.ndarray          # [N,15,3]
+    cams: np.ndarray             # [B,16]
+
+    @property
+    def n(self):
+        return self.xyz.shape[0]
+
+    @property
+    def b(self):
+        return self.cams.shape[0]
+
+
+def bit_length(n: int) -> int:
+    """DeviceSort.get_higher_msb (csrc/devsort.py:129-149)."""
+    return int(n).bit_length()
+
+
+def preprocess_fwd(cfg: OpConfig, sc: Scene, mask=None):
+    BN = sc.b * sc.n
+    out = dict(
+        tiles_touched=np.zeros(BN, np.int32), radii=np.zeros(BN, np.int32),
+        depths=np.zeros(BN, np.float32), uvs=np.zeros((BN, 2), np.float32),
+        conic_opacity=np.zeros((BN, 4), np.float32), rgb=np.zeros((BN, 3), np.float32),
+        cov2d=np.zeros((BN, 3), np.float32), ne0=np.zeros(BN, np.uint8))
+    cv = cfg.vec()
+    lib().oracle_preprocess_fwd(_p(cv), ctypes.c_int(sc.b), ctypes.c_int(sc.n), _p(sc.cams), _p(sc.xyz), _p(sc.quat),
+                                _p(sc.scale), _p(sc.opacity), _p(sc.sh_base), _p(sc.sh_rest), _p(mask),
+                                _p(out["tiles_touched"]), _p(out["radii"]), _p(out["depths"]), _p(out["uvs"]),
+                                _p(out["conic_opacity"]), _p(out["rgb"]), _p(out["cov2d"]), _p(out["ne0"]))
+    return out
+
+
+def scan_inclusive(tiles_touched):
+    out = np.empty_like(tiles_touched)
+    total = lib().oracle_scan_inclusive(ctypes.c_int64(tiles_touched.size), _p(tiles_touched), _p(out))
+    return out, int(total)
+
+
+def duplicate_keys(cfg: OpConfig, b: int, n: int, scan, total, prep):
+    keys = np.zeros(total, np.uint64)
+    vals = np.zeros(total, np.int32)
+    cv = cfg.vec()
+    lib().oracle_duplicate_keys(_p(cv), ctypes.c_int(b), ctypes.c_int(n), _p(scan), _p(prep["radii"]),
+                                _p(prep["depths"]), _p(prep["uvs"]), _p(prep["conic_opacity"]), _p(keys), _p(vals))
+    return keys, vals
+
+
+def sort_pairs(keys, vals, end_bit: int):
+    ko = np.empty_like(keys)
+    vo = np.empty_like(vals)
+    lib().oracle_sort_pairs(ctypes.c_int64(keys.size), ctypes.c_int(end_bit), _p(keys), _p(vals), _p(ko), _p(vo))
+    return ko, vo
+
+
+def tile_ranges(sorted_keys, num_tiles: int):
+    r = np.zeros((num_tiles, 2), np.int32)
+    lib().oracle_tile_ranges(ctypes.c_int64(sorted_keys.size), _p(sorted_keys), _p(r))
+    return r
+
+
+def raster_fwd(cfg: OpConfig, b: int, ranges, sorted_ids, prep, bg=None):
+    H, W = cfg.height, cfg.width
+    color = np.zeros((b, H, W, 3), np.float32)
+    T = np.zeros((b, H, W), np.float32)
+    nc = np.zeros((b, H, W), np.int32)
+    bg = _f32(np.zeros(3) if bg is None else bg)
+    cv = cfg.vec()
+    lib().oracle_raster_fwd(_p(cv), ctypes.c_int(b), _p(ranges), _p(sorted_ids), _p(prep["uvs"]),
+                            _p(prep["conic_opacity"]), _p(prep["rgb"]), _p(bg), _p(color), _p(T), _p(nc))
+    return color, T, nc
+
+
+def raster_bwd(cfg: OpConfig, b: int, bn: int, ranges, sorted_ids, prep, color, T, nc, drgb, dT=None):
+    duv = np.zeros((bn, 2), np.float32)
+    dconic = np.zeros((bn, 3), np.float32)
+    dop = np.zeros(bn, np.float32)
+    dcol = np.zeros((bn, 3), np.float32)
+    cv = cfg.vec()
+    drgb = _f32(drgb)
+    dT = None if dT is None else _f32(dT)
+    lib().oracle_raster_bwd(_p(cv), ctypes.c_int(b), ctypes.c_int64(bn), _p(ranges), _p(sorted_ids), _p(prep["uvs"]),
+                            _p(prep["conic_opacity"]), _p(prep["rgb"]), _p(color), _p(T), _p(nc), _p(drgb), _p(dT),
+                            _p(duv), _p(dconic), _p(dop), _p(dcol))
+    return dict(duv=duv, dconic=dconic, dopacity=dop, dcolor=dcol)
+
+
+def preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg):
+    n = sc.n
+    g = dict(xyz=np.zeros((n, 3), np.float32), quat=np.zeros((n, 4), np.float32),
+             scale=np.zeros((n, 3), np.float32), opacity=np.zeros(n, np.float32),
+             sh_base=np.zeros((n, 3), np.float32), sh_rest=np.zeros((n, 15, 3), np.float32))
+    cv = cfg.vec()
+    lib().oracle_preprocess_bwd(_p(cv), ctypes.c_int(sc.b), ctypes.c_int(n), _p(sc.cams), _p(sc.xyz), _p(sc.quat),
+                                _p(sc.scale), _p(sc.opacity), _p(sc.sh_rest), _p(prep["radii"]), _p(prep["cov2d"]),
+                                _p(prep["ne0"]), _p(rg["duv"]), _p(rg["dconic"]), _p(rg["dopacity"]),
+                                _p(rg["dcolor"]), _p(g["xyz"]), _p(g["quat"]), _p(g["scale"]), _p(g["opacity"]),
+                                _p(g["sh_base"]), _p(g["sh_rest"]))
+    return g
+
+
+def l1_dssim(x_nhwc, y_nchw, lambda_dssim: float = 0.2, want_grad: bool = True):
+    b, h, w, _ = x_nhwc.shape
+    out = np.zeros(3, np.float32)
+    dx = np.zeros_like(x_nhwc) if want_grad else None
+    lib().oracle_l1_dssim(ctypes.c_int(b), ctypes.c_int(h), ctypes.c_int(w), ctypes.c_float(lambda_dssim),
+                          _p(x_nhwc), _p(y_nchw), _p(out), _p(dx))
+    return out, dx
+
+
+def adam(p, g, m, v, lr, beta1, beta2, eps, step):
+    lib().oracle_adam(ctypes.c_int64(p.size), _p(p), _p(g), _p(m), _p(v), ctypes.c_float(lr), ctypes.c_float(beta1),
+                      ctypes.c_float(beta2), ctypes.c_float(eps), ctypes.c_int(step))
+
+
+def densify_stats(b, n, width, height, need_max_radii, duv, radii, duv_ndc_length, count, max_radii):
+    lib().oracle_densify_stats(ctypes.c_int(b), ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(height),
+                               ctypes.c_int(int(need_max_radii)), _p(duv), _p(radii), _p(duv_ndc_length),
+                               _p(count), _p(max_radii))
+
+
+# Per-tensor Adam learning rates of the reference's optimizer factory (tools.py:146-173).
+ADAM_LRS = dict(xyz=1.6e-4, sh_base=2.5e-3, sh_rest=2.5e-3 / 20.0, opacity=0.05, scale=5e-3, quat=1e-3)
+
+
+@dataclass
+class IterationResult:
+    prep: dict
+    scan: np.ndarray
+    num_rendered: int
+    keys: np.ndarray
+    vals: np.ndarray
+    sorted_keys: np.ndarray
+    sorted_ids: np.ndarray
+    ranges: np.ndarray
+    color: np.ndarray
+    T: np.ndarray
+    n_contrib: np.ndarray
+    loss: np.ndarray | None = None
+    drgb: np.ndarray | None = None
+    raster_grads: dict | None = None
+    grads: dict | None = None
+    timings: dict = field(default_factory=dict)
+
+
+def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None) -> IterationResult:
+    """preprocess -> scan -> keys -> sort -> ranges -> raster (render.py:169-1015)."""
+    tm = {} if timings is None else timings
+    tx, ty = cfg.tiles_xy
+    t0 = time.perf_counter()
+    prep = preprocess_fwd(cfg, sc)
+    t1 = time.perf_counter()
+    scan, total = scan_inclusive(prep["tiles_touched"])
+    keys, vals = duplicate_keys(cfg, sc.b, sc.n, scan, total, prep)
+    t2 = time.perf_counter()
+    end_bit = 32 + bit_length(sc.b * tx * ty)
+    sk, sv = sort_pairs(keys, vals, end_bit)
+    t3 = time.perf_counter()
+    ranges = tile_ranges(sk, sc.b * tx * ty)
+    t4 = time.perf_counter()
+    color, T, nc = raster_fwd(cfg, sc.b, ranges, sv, prep)
+    t5 = time.perf_counter()
+    tm.update(preprocess=t1 - t0, scan_keys=t2 - t1, sort=t3 - t2, ranges=t4 - t3, raster_fwd=t5 - t4)
+    return IterationResult(prep, scan, total, keys, vals, sk, sv, ranges, color, T, nc, timings=tm)
+
+
+def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None) -> IterationResult:
+    """raster backward -> preprocess backward (render.py:2779-3374)."""
+    t0 = time.perf_counter()
+    res.drgb = _f32(drgb)
+    res.raster_grads = raster_bwd(cfg, sc.b, sc.b * sc.n, res.ranges, res.sorted_ids, res.prep, res.color, res.T,
+                                  res.n_contrib, res.drgb, dT)
+    t1 = time.perf_counter()
+    res.grads = preprocess_bwd(cfg, sc, res.prep, res.raster_grads)
+    t2 = time.perf_counter()
+    res.timings.update(raster_bwd=t1 - t0, preprocess_bwd=t2 - t1)
+    return res
+
+
+def run_iteration(cfg: OpConfig, sc: Scene, target_nchw, lambda_dssim: float, adam_state: dict | None = None,
+                  step: int = 1, betas=(0.9, 0.999), eps: float = 1e-15, lrs: dict | None = None,
+                  stats: dict | None = None) -> IterationResult:
+    """One full training iteration on the CPU: forward, loss, backward, Adam, densify statistics."""
+    res = forward(cfg, sc)
+    t0 = time.perf_counter()
+    loss, drgb = l1_dssim(res.color, _f32(target_nchw), lambda_dssim)
+    res.loss = loss
+    res.timings["loss"] = time.perf_counter() - t0
+    backward(cfg, sc, res, drgb)
+    if adam_state is not None:
+        t0 = time.perf_counter()
+        lrs = ADAM_LRS if lrs is None else lrs
+        for name in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest"):
+            p = getattr(sc, name)
+            adam(p, res.grads[name], adam_state[name][0], adam_state[name][1], lrs[name], betas[0], betas[1], eps, step)
+        res.timings["adam"] = time.perf_counter() - t0
+    if stats is not None:
+        duv = res.raster_grads["duv"]
+        densify_stats(sc.b, sc.n, cfg.width, cfg.height, stats.get("need_max_radii", False), duv, res.prep["radii"],
+                      stats["duv_ndc_length"], stats["count"], stats["max_radii"])
+    return res
