@@ -1,0 +1,134 @@
+"""ctypes binding of libd3gs_b200.so (declarations mirror include/d3gs_b200.h).
+
+The library is the only compute path of this package: there is no CPU or torch fallback.
+``load()`` raises if the shared object is missing, and every wrapper raises ``RuntimeError`` with
+the library's message when an entry point reports an error -- the same way the reference's native
+sort module surfaces ``TV_THROW_RT_ERR`` as a Python exception (d3sim/csrc/devsort.py:36, 90).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libd3gs_b200.so")
+MAX_VIEWS = 8
+
+_lib = None
+
+
+class Camera(C.Structure):
+    _fields_ = [("cam2world_T", C.c_float * 12), ("fx", C.c_float), ("fy", C.c_float), ("cx", C.c_float),
+                ("cy", C.c_float)]
+
+
+class OpConfig(C.Structure):
+    _fields_ = [("width", C.c_int32), ("height", C.c_int32), ("tile_x", C.c_int32), ("tile_y", C.c_int32),
+                ("near_plane", C.c_float), ("far_plane", C.c_float), ("eps", C.c_float),
+                ("cov2d_radii_eigen_eps", C.c_float), ("projected_clamp_factor", C.c_float),
+                ("gaussian_std_sigma", C.c_float), ("gaussian_lowpass_filter", C.c_float), ("alpha_eps", C.c_float),
+                ("transmittance_eps", C.c_float), ("scale_global", C.c_float), ("early_filter_algo", C.c_int32),
+                ("sh_degree", C.c_int32), ("training", C.c_int32), ("clamp_mask_reference_order", C.c_int32),
+                ("fused_activations", C.c_int32),
+                ("bg_color", C.c_float * 3), ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS)]
+
+
+class Model(C.Structure):
+    _fields_ = [("num", C.c_int64), ("xyz", C.c_void_p), ("quaternion_xyzw", C.c_void_p), ("scale", C.c_void_p),
+                ("opacity", C.c_void_p), ("sh_base", C.c_void_p), ("sh_rest", C.c_void_p),
+                ("sh_base_stride", C.c_int32), ("sh_rest_stride", C.c_int32)]
+
+
+class ModelGrad(C.Structure):
+    _fields_ = [("xyz", C.c_void_p), ("quaternion_xyzw", C.c_void_p), ("scale", C.c_void_p), ("opacity", C.c_void_p),
+                ("sh_base", C.c_void_p), ("sh_rest", C.c_void_p), ("sh_base_stride", C.c_int32),
+                ("sh_rest_stride", C.c_int32), ("sh_rest_floats", C.c_int32), ("reserved", C.c_int32)]
+
+
+class SplatContext(C.Structure):
+    _fields_ = [("tiles_touched", C.c_void_p), ("radii", C.c_void_p), ("depths", C.c_void_p), ("uvs", C.c_void_p),
+                ("conic_opacity", C.c_void_p), ("rgb_gaussian", C.c_void_p), ("cov2d_vecs", C.c_void_p),
+                ("sh_to_rgb_ne_0", C.c_void_p)]
+
+
+class AdamSegment(C.Structure):
+    _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p),
+                ("count", C.c_int64), ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
+                ("bias_correction1", C.c_float), ("bias_correction2_sqrt", C.c_float), ("grad_scale", C.c_float),
+                ("weight_decay", C.c_float)]
+
+
+class DensifyStats(C.Structure):
+    _fields_ = [("duv", C.c_void_p), ("radii", C.c_void_p), ("duv_ndc_length", C.c_void_p), ("count", C.c_void_p),
+                ("max_radii", C.c_void_p), ("num", C.c_int64), ("batch", C.c_int32), ("width", C.c_int32),
+                ("height", C.c_int32), ("need_max_radii", C.c_int32), ("loss_batch", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+_STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats]
+
+_P, _I32, _I64, _F, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/d3gs_b200.h declares
+SIGNATURES = {
+    "d3gs_version": (C.c_char_p, []),
+    "d3gs_last_error": (_SZ, [C.c_char_p, _SZ]),
+    "d3gs_bit_length": (_I32, [C.c_uint32]),
+    "d3gs_struct_size": (_SZ, [_I32]),
+    "d3gs_preprocess_forward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), _P, C.POINTER(SplatContext), _P]),
+    "d3gs_scan_workspace_bytes": (_SZ, [_I64]),
+    "d3gs_scan_tiles": (_I32, [_P, _P, _I64, _P, _P, _SZ, _P, _P]),
+    "d3gs_duplicate_keys": (_I32, [C.POINTER(OpConfig), _I64, _P, C.POINTER(SplatContext), _P, _P, _P]),
+    "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
+    "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
+    "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _P]),
+    "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
+    "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P, _P, _P,
+                                        _P, C.POINTER(ModelGrad), _P]),
+    "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
+    "d3gs_ssim_backward": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P]),
+    "d3gs_l1_dssim_scratch_bytes": (_SZ, [_I32, _I32, _I32]),
+    "d3gs_l1_dssim_forward_backward": (_I32, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P, _SZ, _P]),
+    "d3gs_adam_stats_step": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), _P]),
+    "d3gs_densify_stats": (_I32, [C.POINTER(DensifyStats), _P]),
+}
+
+
+def load():
+    """Load the shared library once; raise loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -c \"import __graft_entry__ as g; g.build()\"` "
+            "(nvcc, sm_100a). This package has no fallback path.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    for k, st in enumerate(_STRUCTS):
+        native = lib.d3gs_struct_size(k)
+        if native != C.sizeof(st):
+            raise RuntimeError(f"ABI mismatch for {st.__name__}: library {native} bytes, binding {C.sizeof(st)} bytes")
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    load().d3gs_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {last_error()}")
+
+
+def ptr(t):
+    """Device pointer of a torch tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()

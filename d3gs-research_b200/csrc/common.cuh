@@ -1,0 +1,169 @@
+// Shared device/host helpers for the d3gs_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "d3gs_b200.h"
+
+namespace d3gs {
+
+// ---- host-side error plumbing ------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what);
+
+#define D3GS_REQUIRE(cond, ...)                 \
+    do {                                        \
+        if (!(cond)) {                          \
+            ::d3gs::set_error(__VA_ARGS__);     \
+            return D3GS_ERR_INVALID_ARGUMENT;   \
+        }                                       \
+    } while (0)
+
+#define D3GS_CUDA(expr)                                          \
+    do {                                                         \
+        cudaError_t e__ = (expr);                                \
+        if (e__ != cudaSuccess) return ::d3gs::cuda_fail(e__, #expr); \
+    } while (0)
+
+#define D3GS_LAUNCH_CHECK(name)                                  \
+    do {                                                         \
+        cudaError_t e__ = cudaGetLastError();                    \
+        if (e__ != cudaSuccess) return ::d3gs::cuda_fail(e__, name); \
+    } while (0)
+
+inline int64_t div_up64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device math with a defined bit pattern -----------------------------------------------
+// The integer results of the binning stages (radius, tile rect, culling compares, sort keys)
+// and n_contrib depend on a handful of float expressions.  Those expressions are written with
+// explicit round-to-nearest intrinsics / fmaf so that the compiler can neither contract nor
+// reorder them; a host program using IEEE float arithmetic and fmaf reproduces every bit.
+
+__device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float f_add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float f_sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float f_fma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float f_sqrt(float a) { return __fsqrt_rn(a); }
+
+// exp(x) of the fused "exponential"/"sigmoid" activations (origin/model.py:453-462): Cephes-style
+// reduction, degree-5 polynomial.
+__device__ __forceinline__ float act_exp(float x) {
+    x = fminf(fmaxf(x, -87.0f), 88.0f);
+    float n = rintf(f_mul(x, 1.44269504088896341f));
+    float r = f_fma(n, -0.693359375f, x);
+    r = f_fma(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = f_fma(p, r, 1.3981999507e-3f);
+    p = f_fma(p, r, 8.3334519073e-3f);
+    p = f_fma(p, r, 4.1665795894e-2f);
+    p = f_fma(p, r, 1.6666665459e-1f);
+    p = f_fma(p, r, 5.0000001201e-1f);
+    float y = f_add(f_fma(p, f_mul(r, r), r), 1.0f);
+    int ni = (int)n;
+    return f_mul(y, __uint_as_float((uint32_t)(ni + 127) << 23));
+}
+
+// log(x), x > 0 finite (early-filter bound, render.py:1020): Cephes logf.
+__device__ __forceinline__ float act_log(float x) {
+    uint32_t u = __float_as_uint(x);
+    int e = (int)((u >> 23) & 0xff) - 126;
+    float m = __uint_as_float((u & 0x007fffffu) | 0x3f000000u);
+    if (m < 0.707106781186547524f) { e -= 1; m = f_sub(f_add(m, m), 1.0f); } else { m = f_sub(m, 1.0f); }
+    float z = f_mul(m, m);
+    float p = 7.0376836292e-2f;
+    p = f_fma(p, m, -1.1514610310e-1f);
+    p = f_fma(p, m, 1.1676998740e-1f);
+    p = f_fma(p, m, -1.2420140846e-1f);
+    p = f_fma(p, m, 1.4249322787e-1f);
+    p = f_fma(p, m, -1.6668057665e-1f);
+    p = f_fma(p, m, 2.0000714765e-1f);
+    p = f_fma(p, m, -2.4999993993e-1f);
+    p = f_fma(p, m, 3.3333331174e-1f);
+    float y = f_mul(f_mul(m, z), p);
+    float fe = (float)e;
+    y = f_fma(fe, -2.12194440e-4f, y);
+    y = f_fma(-0.5f, z, y);
+    float r = f_add(m, y);
+    return f_fma(fe, 0.693359375f, r);
+}
+
+// exp(power) of the blend loop (`fast_exp`, render.py:1768): 2^t by magic-number rounding and a
+// degree-5 minimax polynomial (max rel. error 2.2e-7), ten FP32-pipe operations, no SFU.
+__device__ __forceinline__ float blend_exp(float power) {
+    float t = fmaxf(f_mul(power, 1.44269504088896341f), -125.0f);
+    t = fminf(t, 125.0f);
+    float m = f_add(t, 12582912.0f);
+    float n = f_sub(m, 12582912.0f);
+    float f = f_sub(t, n);
+    float p = 0.001327647129073739f;
+    p = f_fma(p, f, 0.009675540961325169f);
+    p = f_fma(p, f, 0.05550713092088699f);
+    p = f_fma(p, f, 0.24022120237350464f);
+    p = f_fma(p, f, 0.6931469440460205f);
+    p = f_fma(p, f, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(m) << 23));
+}
+
+// power = -0.5(a dx^2 + c dy^2) - b dx dy evaluated as dx*(ha*dx + nb*dy) + (hc*dy)*dy with
+// ha=-0.5a, nb=-b, hc=-0.5c (render.py:1765-1767).
+__device__ __forceinline__ float blend_power(float ha, float nb, float hc, float dx, float dy) {
+    float t = f_fma(nb, dy, f_mul(ha, dx));
+    float u = f_mul(hc, dy);
+    return f_fma(t, dx, f_mul(u, dy));
+}
+
+__device__ __forceinline__ int f2i_sat(float v) {
+    v = fminf(fmaxf(v, -2.0e9f), 2.0e9f);
+    return (int)v;
+}
+__device__ __forceinline__ int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+// ---- mbarrier + bulk async copy (TMA engine, non-tensor form), own memory only ---------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// global -> shared bulk copy; dst/src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (seconds), returns false so the caller can flag
+// D3GS_STATUS_COPY_TIMEOUT and leave instead of hanging the device.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 64) __nanosleep(64);
+    }
+    return false;
+}
+
+}  // namespace d3gs

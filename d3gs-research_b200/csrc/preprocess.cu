@@ -1,0 +1,412 @@
+// K1 preprocess forward and K3 key duplication.
+//
+// This translation unit is compiled with -fmad=false: every float expression below is evaluated
+// exactly as written (IEEE add/mul/div/sqrt, explicit fmaf only), because the integer outputs of
+// these stages -- radii, tile rectangles, tiles_touched, culling decisions, and the depth bits
+// inside the sort keys -- must be reproducible bit for bit by a host program.
+//
+// Reference semantics: d3sim/algos/d3gs/render.py:250-681 (proxy branch 421-476, 569-619),
+// 739-840, 1017-1327; math from d3sim/csrc/gs3d.py and d3sim/csrc/camera.py:307-333.
+#include "common.cuh"
+
+namespace d3gs {
+namespace {
+
+struct TileGeom {
+    int tiles_x, tiles_y;
+    float ts;
+};
+
+__device__ __forceinline__ void tile_rect(const TileGeom& tg, float u, float v, float radius, int* rmin, int* rmax) {
+    // render.py:472-473: clamp(int((uv -/+ r (+ 15)) / 16), 0, tiles); max is exclusive
+    rmin[0] = clampi(f2i_sat((u - radius) / tg.ts), 0, tg.tiles_x);
+    rmin[1] = clampi(f2i_sat((v - radius) / tg.ts), 0, tg.tiles_y);
+    rmax[0] = clampi(f2i_sat((u + radius + tg.ts - 1.0f) / tg.ts), 0, tg.tiles_x);
+    rmax[1] = clampi(f2i_sat((v + radius + tg.ts - 1.0f) / tg.ts), 0, tg.tiles_y);
+}
+
+struct Obb {
+    float w, h, s, c;
+};
+
+// gs3d.py:710-742
+__device__ __forceinline__ void ellipse_bound_aabb(float ca, float cb, float cc, float bound, float* half) {
+    float det = ca * cc - cb * cb;
+    float vx = (-bound * cc) * det, vy = (-bound * ca) * det;
+    float sx = sqrtf(fmaxf(0.0f, vx)) / det, sy = sqrtf(fmaxf(0.0f, vy)) / det;
+    half[0] = fabsf(vx > 0.0f ? sx : 0.0f);
+    half[1] = fabsf(vy > 0.0f ? sy : 0.0f);
+}
+
+// gs3d.py:744-793, 968-989
+__device__ __forceinline__ Obb ellipse_bound_obb(float ca, float cb, float cc, float bound) {
+    float A = -ca / bound, C = -cc / bound, Bh = -cb / bound;
+    float det = A * C - Bh * Bh;
+    float mid = 0.5f * (A + C);
+    float sq = sqrtf(fmaxf(0.0f, mid * mid - det));
+    float e1 = mid + sq, e2 = mid - sq;
+    float s1 = e1 > 0.0f ? 1.0f : -1.0f, s2 = e2 > 0.0f ? 1.0f : -1.0f;
+    float vx = e2 - C, vy = Bh;
+    float vn = sqrtf(vx * vx + vy * vy);
+    vx = vx / vn;
+    vy = vy / vn;
+    float minor = 1.0f / sqrtf(e1 * s1), major = 1.0f / sqrtf(e2 * s2);
+    float mx = vx * major, my = vy * major;
+    float mn = sqrtf(mx * mx + my * my);
+    Obb r;
+    r.w = major * 2.0f;
+    r.h = minor * 2.0f;
+    r.s = my / mn;
+    r.c = mx / mn;
+    return r;
+}
+
+// gs3d.py:1254-1322: separating-axis test, touching boxes do not overlap
+__device__ __forceinline__ bool aabb_overlap_obb(float minx, float miny, float maxx, float maxy, const Obb& o,
+                                                 float cx, float cy) {
+    float l1x = (maxx - minx) / 2.0f, l1y = (maxy - miny) / 2.0f;
+    float l2x = o.w / 2.0f, l2y = o.h / 2.0f;
+    float lx = (maxx + minx) / 2.0f - cx, ly = (maxy + miny) / 2.0f - cy;
+    const float ax[4][2] = {{1.0f, 0.0f}, {0.0f, 1.0f}, {o.c, o.s}, {-o.s, o.c}};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float ux = ax[k][0], uy = ax[k][1];
+        float r1 = l1x * fabsf(ax[0][0] * ux + ax[0][1] * uy);
+        float r2 = l1y * fabsf(ax[1][0] * ux + ax[1][1] * uy);
+        float r3 = l2x * fabsf(ax[2][0] * ux + ax[2][1] * uy);
+        float r4 = l2y * fabsf(ax[3][0] * ux + ax[3][1] * uy);
+        if (((r1 + r2) + r3) + r4 <= fabsf(lx * ux + ly * uy)) return false;
+    }
+    return true;
+}
+
+// Visits every tile that the early filter keeps (render.py:1017-1327) intersected with the
+// 3-sigma rect (render.py:594, 814-817).  filter: 0 NONE, 1 AABB, 3 OBB; OBB_DFVT (4) is mapped
+// to OBB by the host (same tile set by construction of the traversal).
+template <class F>
+__device__ __forceinline__ void for_each_tile(int filter, const TileGeom& tg, int tile_px, float alpha_eps, float u,
+                                              float v, float ca, float cb, float cc, float opacity, const int* rmin,
+                                              const int* rmax, F fn) {
+    if (filter == 0) {
+        for (int y = rmin[1]; y < rmax[1]; ++y)
+            for (int x = rmin[0]; x < rmax[0]; ++x) fn(x, y);
+        return;
+    }
+    float bound = 2.0f * act_log(alpha_eps / opacity);
+    float half[2];
+    ellipse_bound_aabb(ca, cb, cc, bound, half);
+    int bmin[2], bmax[2];
+    bmin[0] = clampi(f2i_sat((u - half[0]) / tg.ts), 0, tg.tiles_x);
+    bmin[1] = clampi(f2i_sat((v - half[1]) / tg.ts), 0, tg.tiles_y);
+    bmax[0] = clampi(f2i_sat(ceilf((u + half[0]) / tg.ts)), 0, tg.tiles_x);
+    bmax[1] = clampi(f2i_sat(ceilf((v + half[1]) / tg.ts)), 0, tg.tiles_y);
+    float ox = u - (float)bmin[0] * tg.ts, oy = v - (float)bmin[1] * tg.ts;
+    Obb obb = ellipse_bound_obb(ca, cb, cc, bound);
+    for (int y = bmin[1]; y < bmax[1]; ++y) {
+        float py0 = (float)((y - bmin[1]) * tile_px), py1 = py0 + tg.ts;
+        for (int x = bmin[0]; x < bmax[0]; ++x) {
+            float px0 = (float)((x - bmin[0]) * tile_px), px1 = px0 + tg.ts;
+            bool ok;
+            if (filter == 1) {
+                bool xo = (ox - half[0]) <= px1 && (ox + half[0]) >= px0;
+                bool yo = (oy - half[1]) <= py1 && (oy + half[1]) >= py0;
+                ok = xo && yo;
+            } else {
+                ok = aabb_overlap_obb(px0, py0, px1, py1, obb, ox, oy);
+            }
+            ok = ok && x >= rmin[0] && x < rmax[0] && y >= rmin[1] && y < rmax[1];
+            if (ok) fn(x, y);
+        }
+    }
+}
+
+__constant__ float kShC2[5] = {1.0925484305920792f, -1.0925484305920792f, 0.31539156525252005f,
+                               -1.0925484305920792f, 0.5462742152960396f};
+__constant__ float kShC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.4570457994644658f, 0.3731763325901154f,
+                               -0.4570457994644658f, 1.445305721320277f,  -0.5900435899266435f};
+
+// gs3d.py:151-201: basis values, bs[0] = C0
+__device__ __forceinline__ void sh_basis(int deg, float x, float y, float z, float* bs) {
+    const float C1 = 0.4886025119029199f;
+    bs[0] = 0.28209479177387814f;
+    if (deg > 0) {
+        bs[1] = -C1 * y;
+        bs[2] = C1 * z;
+        bs[3] = -C1 * x;
+        if (deg > 1) {
+            float xx = x * x, yy = y * y, zz = z * z, xy = x * y, yz = y * z, xz = x * z;
+            bs[4] = kShC2[0] * xy;
+            bs[5] = kShC2[1] * yz;
+            bs[6] = kShC2[2] * (2.0f * zz - xx - yy);
+            bs[7] = kShC2[3] * xz;
+            bs[8] = kShC2[4] * (xx - yy);
+            if (deg > 2) {
+                bs[9] = kShC3[0] * y * (3.0f * xx - yy);
+                bs[10] = kShC3[1] * xy * z;
+                bs[11] = kShC3[2] * y * (4.0f * zz - xx - yy);
+                bs[12] = kShC3[3] * z * (2.0f * zz - 3.0f * xx - 3.0f * yy);
+                bs[13] = kShC3[4] * x * (4.0f * zz - xx - yy);
+                bs[14] = kShC3[5] * z * (xx - yy);
+                bs[15] = kShC3[6] * x * (xx - 3.0f * yy);
+            }
+        }
+    }
+}
+
+struct PrepArgs {
+    D3gsOpConfig cfg;
+    D3gsModel model;
+    D3gsSplatContext ctx;
+    const uint8_t* mask;
+};
+
+template <int DEG>
+__global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+    const int64_t N = a.model.num;
+    const int64_t total = N * a.cfg.num_views;
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int b = (int)(i / N);
+    const int64_t g = i - (int64_t)b * N;
+    const D3gsOpConfig& cf = a.cfg;
+    const D3gsCamera& cam = cf.cameras[b];
+    const float* Rt = cam.cam2world_T;   // Rt[k*3 + j]: k-th column of R_c2w
+    TileGeom tg;
+    tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
+    tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
+    tg.ts = (float)cf.tile_x;
+
+    bool valid = true;
+    const float px = a.model.xyz[g * 3], py = a.model.xyz[g * 3 + 1], pz = a.model.xyz[g * 3 + 2];
+    const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
+    const float pc0 = (Rt[0] * d0 + Rt[1] * d1) + Rt[2] * d2;
+    const float pc1 = (Rt[3] * d0 + Rt[4] * d1) + Rt[5] * d2;
+    const float z = (Rt[6] * d0 + Rt[7] * d1) + Rt[8] * d2;
+    if (!(z >= cf.near_plane && z <= cf.far_plane)) valid = false;
+    if (a.mask != nullptr && a.mask[i] != 0) valid = false;
+    if (!valid) {
+        a.ctx.tiles_touched[i] = 0;
+        a.ctx.radii[i] = 0;
+        return;
+    }
+    const float u = ((pc0 / z) * cam.fx + cam.cx) - 0.5f;
+    const float v = ((pc1 / z) * cam.fy + cam.cy) - 0.5f;
+    // fused activations
+    const float4 qr = *reinterpret_cast<const float4*>(a.model.quaternion_xyzw + g * 4);
+    const bool fused = cf.fused_activations != 0;
+    const float qn = fused ? sqrtf(((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w) : 1.0f;
+    const float qx = qr.x / qn, qy = qr.y / qn, qz = qr.z / qn, qw = qr.w / qn;
+    const float sg = cf.training ? 1.0f : cf.scale_global;
+    const float r0 = a.model.scale[g * 3], r1 = a.model.scale[g * 3 + 1], r2 = a.model.scale[g * 3 + 2];
+    const float s0 = (fused ? act_exp(r0) : r0) * sg, s1 = (fused ? act_exp(r1) : r1) * sg,
+                s2 = (fused ? act_exp(r2) : r2) * sg;
+    const float oraw = a.model.opacity[g];
+    const float opac = fused ? 1.0f / (1.0f + act_exp(-oraw)) : oraw;
+    // rotation, M = R diag(s), Sigma = M M^T
+    float R[3][3];
+    {
+        float xx = qx * qx, yy = qy * qy, zz = qz * qz, xy = qx * qy, xz = qx * qz, yz = qy * qz;
+        float wx = qw * qx, wy = qw * qy, wz = qw * qz;
+        R[0][0] = 1.0f - 2.0f * (yy + zz); R[0][1] = 2.0f * (xy - wz); R[0][2] = 2.0f * (xz + wy);
+        R[1][0] = 2.0f * (xy + wz); R[1][1] = 1.0f - 2.0f * (xx + zz); R[1][2] = 2.0f * (yz - wx);
+        R[2][0] = 2.0f * (xz - wy); R[2][1] = 2.0f * (yz + wx); R[2][2] = 1.0f - 2.0f * (xx + yy);
+    }
+    float M[3][3];
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+        M[r][0] = R[r][0] * s0;
+        M[r][1] = R[r][1] * s1;
+        M[r][2] = R[r][2] * s2;
+    }
+    float Sg[3][3];
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int c = r; c < 3; ++c) Sg[r][c] = Sg[c][r] = (M[r][0] * M[c][0] + M[r][1] * M[c][1]) + M[r][2] * M[c][2];
+    // projection
+    const float tanx = 0.5f * (float)cf.width / cam.fx, tany = 0.5f * (float)cf.height / cam.fy;
+    const float limx = fabsf((tanx * cf.projected_clamp_factor) * z), limy = fabsf((tany * cf.projected_clamp_factor) * z);
+    const float tx = fminf(limx, fmaxf(-limx, pc0)), ty = fminf(limy, fmaxf(-limy, pc1));
+    const float z2 = z * z;
+    const float J00 = cam.fx / z, J02 = -(tx * cam.fx) / z2, J11 = cam.fy / z, J12 = -(ty * cam.fy) / z2;
+    float T0[3], T1[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        T0[j] = J00 * Rt[j] + J02 * Rt[6 + j];
+        T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
+    }
+    float U0[3], U1[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        U0[j] = (T0[0] * Sg[0][j] + T0[1] * Sg[1][j]) + T0[2] * Sg[2][j];
+        U1[j] = (T1[0] * Sg[0][j] + T1[1] * Sg[1][j]) + T1[2] * Sg[2][j];
+    }
+    float ca = (U0[0] * T0[0] + U0[1] * T0[1]) + U0[2] * T0[2];
+    float cb = (U0[0] * T1[0] + U0[1] * T1[1]) + U0[2] * T1[2];
+    float cc = (U1[0] * T1[0] + U1[1] * T1[1]) + U1[2] * T1[2];
+    ca += cf.gaussian_lowpass_filter;
+    cc += cf.gaussian_lowpass_filter;
+    const float det = ca * cc - cb * cb;
+    const float det_inv = 1.0f / (det + cf.eps);
+    const float k0 = cc * det_inv, k1 = -cb * det_inv, k2 = ca * det_inv;
+    const float mid = 0.5f * (ca + cc);
+    const float sq = sqrtf(fmaxf(cf.cov2d_radii_eigen_eps, mid * mid - det));
+    const float radius = ceilf(cf.gaussian_std_sigma * sqrtf(fmaxf(mid + sq, mid - sq)));
+    int rmin[2], rmax[2];
+    tile_rect(tg, u, v, radius, rmin, rmax);
+    const int area = (rmax[0] - rmin[0]) * (rmax[1] - rmin[1]);
+    if (det <= 0.0f || area == 0 || opac <= cf.alpha_eps) {
+        a.ctx.tiles_touched[i] = 0;
+        a.ctx.radii[i] = 0;
+        return;
+    }
+    int cnt = 0;
+    for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opac, rmin, rmax,
+                  [&](int, int) { ++cnt; });
+    a.ctx.tiles_touched[i] = cnt;
+    a.ctx.radii[i] = (int)radius;
+    a.ctx.depths[i] = z;
+    *reinterpret_cast<float2*>(a.ctx.uvs + i * 2) = make_float2(u, v);
+    *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opac);
+    if (a.ctx.cov2d_vecs != nullptr) {
+        a.ctx.cov2d_vecs[i * 3] = ca;
+        a.ctx.cov2d_vecs[i * 3 + 1] = cb;
+        a.ctx.cov2d_vecs[i * 3 + 2] = cc;
+    }
+    // colour: SH of the normalised world-space view direction (render.py:587, 605-611)
+    const float dn = sqrtf((d0 * d0 + d1 * d1) + d2 * d2);
+    float bs[16];
+    sh_basis(DEG, d0 / dn, d1 / dn, d2 / dn, bs);
+    const float* base = a.model.sh_base + g * a.model.sh_base_stride;
+    const float* rest = a.model.sh_rest + g * a.model.sh_rest_stride;
+    float c3[3];
+#pragma unroll
+    for (int ch = 0; ch < 3; ++ch) c3[ch] = bs[0] * base[ch];
+    constexpr int NB = (DEG + 1) * (DEG + 1);
+#pragma unroll
+    for (int k = 1; k < NB; ++k) {
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + bs[k] * __ldg(rest + (k - 1) * 3 + ch);
+    }
+#pragma unroll
+    for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + 0.5f;
+    if (a.ctx.sh_to_rgb_ne_0 != nullptr)
+        a.ctx.sh_to_rgb_ne_0[i] = (uint8_t)(((c3[0] < 0.0f) << 2) | ((c3[1] < 0.0f) << 1) | (c3[2] < 0.0f));
+    a.ctx.rgb_gaussian[i * 3] = fmaxf(c3[0], 0.0f);
+    a.ctx.rgb_gaussian[i * 3 + 1] = fmaxf(c3[1], 0.0f);
+    a.ctx.rgb_gaussian[i * 3 + 2] = fmaxf(c3[2], 0.0f);
+}
+
+struct DupArgs {
+    D3gsOpConfig cfg;
+    D3gsSplatContext ctx;
+    const int32_t* scan;
+    uint64_t* keys;
+    int32_t* values;
+    int64_t num;
+};
+
+__global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_constant__ DupArgs a) {
+    const int64_t total = a.num * a.cfg.num_views;
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int r = a.ctx.radii[i];
+    if (r <= 0) return;
+    const D3gsOpConfig& cf = a.cfg;
+    const int b = (int)(i / a.num);
+    TileGeom tg;
+    tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
+    tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
+    tg.ts = (float)cf.tile_x;
+    int64_t off = i == 0 ? 0 : (int64_t)a.scan[i - 1];
+    const float2 uv = *reinterpret_cast<const float2*>(a.ctx.uvs + i * 2);
+    const float4 co = *reinterpret_cast<const float4*>(a.ctx.conic_opacity + i * 4);
+    int rmin[2], rmax[2];
+    tile_rect(tg, uv.x, uv.y, (float)r, rmin, rmax);
+    const uint32_t dbits = __float_as_uint(a.ctx.depths[i]);
+    const uint64_t tile_base = (uint64_t)b * (uint64_t)(tg.tiles_x * tg.tiles_y);
+    for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, uv.x, uv.y, co.x, co.y, co.z, co.w, rmin, rmax,
+                  [&](int x, int y) {
+                      uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
+                      a.keys[off] = (key << 32) | dbits;
+                      a.values[off] = (int32_t)i;
+                      ++off;
+                  });
+}
+
+int32_t check_cfg(const D3gsOpConfig* cfg) {
+    D3GS_REQUIRE(cfg != nullptr, "cfg is NULL");
+    D3GS_REQUIRE(cfg->tile_x == 16 && cfg->tile_y == 16, "only 16x16 tiles are supported (got %dx%d)", cfg->tile_x,
+                 cfg->tile_y);
+    D3GS_REQUIRE(cfg->width > 0 && cfg->height > 0, "bad image size %dx%d", cfg->width, cfg->height);
+    D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= D3GS_MAX_VIEWS, "num_views %d outside [1,%d]",
+                 cfg->num_views, D3GS_MAX_VIEWS);
+    D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
+    D3GS_REQUIRE(cfg->early_filter_algo == 0 || cfg->early_filter_algo == 1 || cfg->early_filter_algo == 3 ||
+                     cfg->early_filter_algo == 4,
+                 "early_filter_algo %d unsupported (NONE=0, AABB=1, OBB=3, OBB_DFVT=4)", cfg->early_filter_algo);
+    return D3GS_OK;
+}
+
+}  // namespace
+}  // namespace d3gs
+
+using namespace d3gs;
+
+extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsModel* model, const uint8_t* mask,
+                                           const D3gsSplatContext* ctx, void* stream) {
+    int32_t rc = check_cfg(cfg);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(model != nullptr && ctx != nullptr, "model/ctx is NULL");
+    D3GS_REQUIRE(model->num >= 0, "negative Gaussian count");
+    D3GS_REQUIRE(model->xyz && model->quaternion_xyzw && model->scale && model->opacity && model->sh_base,
+                 "model tensor pointer is NULL");
+    D3GS_REQUIRE(cfg->sh_degree == 0 || model->sh_rest != nullptr, "sh_rest is NULL with sh_degree > 0");
+    D3GS_REQUIRE(((uintptr_t)model->quaternion_xyzw & 15) == 0, "quaternion_xyzw must be 16-byte aligned");
+    D3GS_REQUIRE(ctx->tiles_touched && ctx->radii && ctx->depths && ctx->uvs && ctx->conic_opacity && ctx->rgb_gaussian,
+                 "context tensor pointer is NULL");
+    D3GS_REQUIRE(((uintptr_t)ctx->uvs & 7) == 0 && ((uintptr_t)ctx->conic_opacity & 15) == 0,
+                 "uvs / conic_opacity must be 8 / 16-byte aligned");
+    D3GS_REQUIRE(!cfg->training || (ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0),
+                 "training needs cov2d_vecs and sh_to_rgb_ne_0");
+    const int64_t total = model->num * cfg->num_views;
+    if (total == 0) return D3GS_OK;
+    D3GS_REQUIRE(total < (int64_t)1 << 31, "B*N = %lld does not fit int32 indexing", (long long)total);
+    PrepArgs a;
+    a.cfg = *cfg;
+    if (a.cfg.early_filter_algo == 4) a.cfg.early_filter_algo = 3;
+    a.model = *model;
+    a.ctx = *ctx;
+    a.mask = mask;
+    dim3 grid((unsigned)div_up64(total, 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (cfg->sh_degree) {
+        case 0: preprocess_fwd_kernel<0><<<grid, 256, 0, s>>>(a); break;
+        case 1: preprocess_fwd_kernel<1><<<grid, 256, 0, s>>>(a); break;
+        case 2: preprocess_fwd_kernel<2><<<grid, 256, 0, s>>>(a); break;
+        default: preprocess_fwd_kernel<3><<<grid, 256, 0, s>>>(a); break;
+    }
+    D3GS_LAUNCH_CHECK("preprocess_fwd_kernel");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, const int32_t* scan,
+                                       const D3gsSplatContext* ctx, uint64_t* keys, int32_t* values, void* stream) {
+    int32_t rc = check_cfg(cfg);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(ctx != nullptr && scan != nullptr, "ctx/scan is NULL");
+    const int64_t total = num * cfg->num_views;
+    if (total == 0) return D3GS_OK;
+    D3GS_REQUIRE(keys != nullptr && values != nullptr, "keys/values is NULL");
+    DupArgs a;
+    a.cfg = *cfg;
+    if (a.cfg.early_filter_algo == 4) a.cfg.early_filter_algo = 3;
+    a.ctx = *ctx;
+    a.scan = scan;
+    a.keys = keys;
+    a.values = values;
+    a.num = num;
+    duplicate_keys_kernel<<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    D3GS_LAUNCH_CHECK("duplicate_keys_kernel");
+    return D3GS_OK;
+}

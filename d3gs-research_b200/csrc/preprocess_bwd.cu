@@ -1,0 +1,303 @@
+// K8 preprocess backward: chain rule from the rasteriser's per-splat gradients (duv, dconic,
+// dopacity, dcolor) back to the 59 parameter floats of every Gaussian.
+//
+// Reference semantics: d3sim/algos/d3gs/render.py:3176-3360 with
+//   gaussian_2d_inverse_and_det_grad   d3sim/csrc/gs3d.py:559-588
+//   project_gaussian_to_2d_grad        gs3d.py:472-532
+//   scale_quat_to_cov3d_grad           gs3d.py:387-418
+//   pos_cam_to_uv_no_distort_grad      d3sim/csrc/camera.py:335-371
+//   sh_dir_to_rgb_grad                 gs3d.py:236-366
+//   fused activation gradients         d3sim/algos/d3gs/origin/model.py:327-431
+// One thread per Gaussian; the view batch is looped inside and summed in registers
+// (render.py:3182, origin/model.py:422-431).  Unlike the reference (zeros_like + skip,
+// render.py:2918, 3218-3220) every output element is written here, zeros included, so the caller
+// needs no memset of the 236-byte-per-Gaussian gradient.
+#include "common.cuh"
+
+namespace d3gs {
+namespace {
+
+struct BwdArgs {
+    D3gsOpConfig cfg;
+    D3gsModel model;
+    D3gsSplatContext ctx;
+    D3gsModelGrad grad;
+    const float* duv;
+    const float* dconic;
+    const float* dopacity;
+    const float* dcolor;
+};
+
+__constant__ float kC2[5] = {1.0925484305920792f, -1.0925484305920792f, 0.31539156525252005f, -1.0925484305920792f,
+                             0.5462742152960396f};
+__constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.4570457994644658f, 0.3731763325901154f,
+                             -0.4570457994644658f, 1.445305721320277f,  -0.5900435899266435f};
+
+template <int DEG>
+__global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
+    const int64_t N = a.model.num;
+    const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (g >= N) return;
+    const D3gsOpConfig& cf = a.cfg;
+    constexpr int NB = (DEG + 1) * (DEG + 1);
+    constexpr int NR = NB - 1;
+
+    float axyz[3] = {0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f}, as[3] = {0.f, 0.f, 0.f}, ao = 0.f;
+    float abase[3] = {0.f, 0.f, 0.f};
+    float arest[NR > 0 ? NR * 3 : 1];
+#pragma unroll
+    for (int k = 0; k < NR * 3; ++k) arest[k] = 0.f;
+
+    bool any_view = false;
+    for (int b = 0; b < cf.num_views; ++b) any_view |= a.ctx.radii[(int64_t)b * N + g] != 0;
+
+    if (any_view) {
+        // view-independent part: activations, rotation, M = R diag(s), Sigma
+        const float px = a.model.xyz[g * 3], py = a.model.xyz[g * 3 + 1], pz = a.model.xyz[g * 3 + 2];
+        const float4 qr = *reinterpret_cast<const float4*>(a.model.quaternion_xyzw + g * 4);
+        const bool fused = cf.fused_activations != 0;
+        const float qn = fused ? sqrtf(qr.x * qr.x + qr.y * qr.y + qr.z * qr.z + qr.w * qr.w) : 1.0f;
+        const float qx = qr.x / qn, qy = qr.y / qn, qz = qr.z / qn, qw = qr.w / qn;
+        const float r0 = a.model.scale[g * 3], r1 = a.model.scale[g * 3 + 1], r2 = a.model.scale[g * 3 + 2];
+        const float s[3] = {fused ? act_exp(r0) : r0, fused ? act_exp(r1) : r1, fused ? act_exp(r2) : r2};
+        const float oraw = a.model.opacity[g];
+        const float opac = fused ? 1.0f / (1.0f + act_exp(-oraw)) : oraw;
+        float R[3][3];
+        {
+            float xx = qx * qx, yy = qy * qy, zz = qz * qz, xy = qx * qy, xz = qx * qz, yz = qy * qz;
+            float wx = qw * qx, wy = qw * qy, wz = qw * qz;
+            R[0][0] = 1.0f - 2.0f * (yy + zz); R[0][1] = 2.0f * (xy - wz); R[0][2] = 2.0f * (xz + wy);
+            R[1][0] = 2.0f * (xy + wz); R[1][1] = 1.0f - 2.0f * (xx + zz); R[1][2] = 2.0f * (yz - wx);
+            R[2][0] = 2.0f * (xz - wy); R[2][1] = 2.0f * (yz + wx); R[2][2] = 1.0f - 2.0f * (xx + yy);
+        }
+        float M[3][3], Sg[3][3];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) M[r][c] = R[r][c] * s[c];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int c = r; c < 3; ++c) Sg[r][c] = Sg[c][r] = M[r][0] * M[c][0] + M[r][1] * M[c][1] + M[r][2] * M[c][2];
+        const float* rest = a.model.sh_rest + g * a.model.sh_rest_stride;
+        float dSacc[3][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};   // sum over views of dL/dSigma
+
+        for (int b = 0; b < cf.num_views; ++b) {
+            const int64_t i = (int64_t)b * N + g;
+            if (a.ctx.radii[i] == 0) continue;
+            const D3gsCamera& cam = cf.cameras[b];
+            const float* Rt = cam.cam2world_T;
+            const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
+            const float pc0 = Rt[0] * d0 + Rt[1] * d1 + Rt[2] * d2;
+            const float pc1 = Rt[3] * d0 + Rt[4] * d1 + Rt[5] * d2;
+            const float z = Rt[6] * d0 + Rt[7] * d1 + Rt[8] * d2;
+            const float tanx = 0.5f * (float)cf.width / cam.fx, tany = 0.5f * (float)cf.height / cam.fy;
+            const float limx = fabsf(tanx * cf.projected_clamp_factor * z), limy = fabsf(tany * cf.projected_clamp_factor * z);
+            const float tx = fminf(limx, fmaxf(-limx, pc0)), ty = fminf(limy, fmaxf(-limy, pc1));
+            const float xg = (pc0 < -limx || pc0 > limx) ? 0.0f : 1.0f;
+            const float yg = (pc1 < -limy || pc1 > limy) ? 0.0f : 1.0f;
+            const float zi = 1.0f / z, z2i = zi * zi;
+            const float J00 = cam.fx * zi, J02 = -(tx * cam.fx) * z2i, J11 = cam.fy * zi, J12 = -(ty * cam.fy) * z2i;
+            float T0[3], T1[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                T0[j] = J00 * Rt[j] + J02 * Rt[6 + j];
+                T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
+            }
+            // conic -> cov2d (gs3d.py:559-588)
+            const float ca = a.ctx.cov2d_vecs[i * 3], cb = a.ctx.cov2d_vecs[i * 3 + 1], cc = a.ctx.cov2d_vecs[i * 3 + 2];
+            const float g0 = a.dconic[i * 3], g1 = a.dconic[i * 3 + 1], g2 = a.dconic[i * 3 + 2];
+            const float det = ca * cc - cb * cb;
+            const float d2i = 1.0f / (det * det + 1e-8f);
+            const float da = d2i * (-cc * cc * g0 + cb * cc * g1 + (det - ca * cc) * g2);
+            const float db = d2i * 2.0f * (cb * cc * g0 - (0.5f * det + cb * cb) * g1 + ca * cb * g2);
+            const float dc = d2i * (-ca * ca * g2 + ca * cb * g1 + (det - ca * cc) * g0);
+            // cov2d = T Sigma T^T (gs3d.py:472-532): dSigma = T^T G T, dT = 2 G T Sigma
+            const float hb = 0.5f * db;
+            float GT0[3], GT1[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                GT0[j] = da * T0[j] + hb * T1[j];
+                GT1[j] = hb * T0[j] + dc * T1[j];
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k)
+#pragma unroll
+                for (int j = 0; j < 3; ++j) dSacc[k][j] += T0[k] * GT0[j] + T1[k] * GT1[j];
+            float dT0[3], dT1[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                dT0[j] = 2.0f * (GT0[0] * Sg[0][j] + GT0[1] * Sg[1][j] + GT0[2] * Sg[2][j]);
+                dT1[j] = 2.0f * (GT1[0] * Sg[0][j] + GT1[1] * Sg[1][j] + GT1[2] * Sg[2][j]);
+            }
+            // dJ = dT W^T; only the four non-zero entries of J matter
+            const float dJ00 = dT0[0] * Rt[0] + dT0[1] * Rt[1] + dT0[2] * Rt[2];
+            const float dJ02 = dT0[0] * Rt[6] + dT0[1] * Rt[7] + dT0[2] * Rt[8];
+            const float dJ11 = dT1[0] * Rt[3] + dT1[1] * Rt[4] + dT1[2] * Rt[5];
+            const float dJ12 = dT1[0] * Rt[6] + dT1[1] * Rt[7] + dT1[2] * Rt[8];
+            const float txf = tx * cam.fx, tyf = ty * cam.fy;
+            const float dm0 = xg * -dJ02 * cam.fx * z2i;
+            const float dm1 = yg * -dJ12 * cam.fy * z2i;
+            const float dm2 = -(cam.fx * dJ00 + cam.fy * dJ11) * z2i + 2.0f * (dJ02 * txf + dJ12 * tyf) * z2i * zi;
+            // pinhole (camera.py:335-371)
+            const float du = a.duv[i * 2] * cam.fx, dv = a.duv[i * 2 + 1] * cam.fy;
+            const float dp0 = du * zi + dm0, dp1 = dv * zi + dm1;
+            const float dp2 = -(du * pc0 + dv * pc1) * z2i + dm2;
+            float dxyz[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) dxyz[j] = Rt[j] * dp0 + Rt[3 + j] * dp1 + Rt[6 + j] * dp2;
+            ao += a.dopacity[i];
+            // colour (render.py:3341-3355)
+            const float dn = sqrtf(d0 * d0 + d1 * d1 + d2 * d2);
+            const float dni = 1.0f / dn;
+            const float x = d0 * dni, y = d1 * dni, zz_ = d2 * dni;
+            float cg[3] = {a.dcolor[i * 3], a.dcolor[i * 3 + 1], a.dcolor[i * 3 + 2]};
+            const uint8_t m = a.ctx.sh_to_rgb_ne_0[i];
+            if (cf.clamp_mask_reference_order) {   // bit k gates channel k (render.py:3344-3350)
+                if (m & 1) cg[0] = 0.f;
+                if (m & 2) cg[1] = 0.f;
+                if (m & 4) cg[2] = 0.f;
+            } else {                               // pack order r<<2 | g<<1 | b (render.py:608)
+                if (m & 4) cg[0] = 0.f;
+                if (m & 2) cg[1] = 0.f;
+                if (m & 1) cg[2] = 0.f;
+            }
+            const float C0 = 0.28209479177387814f, C1 = 0.4886025119029199f;
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) abase[ch] += C0 * cg[ch];
+            float ddx = 0.f, ddy = 0.f, ddz = 0.f;
+            if (DEG > 0) {
+                float bs[16], gx[16], gy[16], gz[16];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) { bs[k] = gx[k] = gy[k] = gz[k] = 0.f; }
+                bs[1] = -C1 * y; bs[2] = C1 * zz_; bs[3] = -C1 * x;
+                gy[1] = -C1; gz[2] = C1; gx[3] = -C1;
+                if (DEG > 1) {
+                    const float xx = x * x, yy = y * y, zz = zz_ * zz_, xy = x * y, yz = y * zz_, xz = x * zz_;
+                    bs[4] = kC2[0] * xy; bs[5] = kC2[1] * yz; bs[6] = kC2[2] * (2.0f * zz - xx - yy);
+                    bs[7] = kC2[3] * xz; bs[8] = kC2[4] * (xx - yy);
+                    gx[4] = kC2[0] * y; gy[4] = kC2[0] * x;
+                    gy[5] = kC2[1] * zz_; gz[5] = kC2[1] * y;
+                    gx[6] = kC2[2] * -2.0f * x; gy[6] = kC2[2] * -2.0f * y; gz[6] = kC2[2] * 4.0f * zz_;
+                    gx[7] = kC2[3] * zz_; gz[7] = kC2[3] * x;
+                    gx[8] = kC2[4] * 2.0f * x; gy[8] = kC2[4] * -2.0f * y;
+                    if (DEG > 2) {
+                        bs[9] = kC3[0] * y * (3.0f * xx - yy);
+                        bs[10] = kC3[1] * xy * zz_;
+                        bs[11] = kC3[2] * y * (4.0f * zz - xx - yy);
+                        bs[12] = kC3[3] * zz_ * (2.0f * zz - 3.0f * xx - 3.0f * yy);
+                        bs[13] = kC3[4] * x * (4.0f * zz - xx - yy);
+                        bs[14] = kC3[5] * zz_ * (xx - yy);
+                        bs[15] = kC3[6] * x * (xx - 3.0f * yy);
+                        gx[9] = kC3[0] * 6.0f * xy; gy[9] = kC3[0] * 3.0f * (xx - yy);
+                        gx[10] = kC3[1] * yz; gy[10] = kC3[1] * xz; gz[10] = kC3[1] * xy;
+                        gx[11] = kC3[2] * -2.0f * xy; gy[11] = kC3[2] * (-3.0f * yy + 4.0f * zz - xx); gz[11] = kC3[2] * 8.0f * yz;
+                        gx[12] = kC3[3] * -6.0f * xz; gy[12] = kC3[3] * -6.0f * yz; gz[12] = kC3[3] * 3.0f * (2.0f * zz - xx - yy);
+                        gx[13] = kC3[4] * (-3.0f * xx + 4.0f * zz - yy); gy[13] = kC3[4] * -2.0f * xy; gz[13] = kC3[4] * 8.0f * xz;
+                        gx[14] = kC3[5] * 2.0f * xz; gy[14] = kC3[5] * -2.0f * yz; gz[14] = kC3[5] * (xx - yy);
+                        gx[15] = kC3[6] * 3.0f * (xx - yy); gy[15] = kC3[6] * -6.0f * xy;
+                    }
+                }
+#pragma unroll
+                for (int k = 1; k < NB; ++k) {
+#pragma unroll
+                    for (int ch = 0; ch < 3; ++ch) {
+                        arest[(k - 1) * 3 + ch] += bs[k] * cg[ch];
+                        const float coef = __ldg(rest + (k - 1) * 3 + ch) * cg[ch];
+                        ddx += gx[k] * coef; ddy += gy[k] * coef; ddz += gz[k] * coef;
+                    }
+                }
+            }
+            // normalize_grad (render.py:3354)
+            const float dd = x * ddx + y * ddy + zz_ * ddz;
+            axyz[0] += dxyz[0] + (ddx - x * dd) * dni;
+            axyz[1] += dxyz[1] + (ddy - y * dd) * dni;
+            axyz[2] += dxyz[2] + (ddz - zz_ * dd) * dni;
+        }
+        // Sigma = M M^T (gs3d.py:387-418): dM = 2 dSigma M (dSigma symmetric), ds_j = <dM[:,j], R[:,j]>
+        float dM[3][3];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int c = 0; c < 3; ++c)
+                dM[r][c] = 2.0f * (dSacc[r][0] * M[0][c] + dSacc[r][1] * M[1][c] + dSacc[r][2] * M[2][c]);
+        float dR[3][3];
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            const float ds = dM[0][c] * R[0][c] + dM[1][c] * R[1][c] + dM[2][c] * R[2][c];
+            as[c] = fused ? ds * s[c] : ds;          // exponential_grad_out: g * out
+#pragma unroll
+            for (int r = 0; r < 3; ++r) dR[r][c] = dM[r][c] * s[c];
+        }
+        float dq[4];
+        dq[0] = 2.0f * (qy * (dR[0][1] + dR[1][0]) + qz * (dR[0][2] + dR[2][0]) + qw * (dR[2][1] - dR[1][2]) - 2.0f * qx * (dR[1][1] + dR[2][2]));
+        dq[1] = 2.0f * (qx * (dR[0][1] + dR[1][0]) + qz * (dR[1][2] + dR[2][1]) + qw * (dR[0][2] - dR[2][0]) - 2.0f * qy * (dR[0][0] + dR[2][2]));
+        dq[2] = 2.0f * (qx * (dR[0][2] + dR[2][0]) + qy * (dR[1][2] + dR[2][1]) + qw * (dR[1][0] - dR[0][1]) - 2.0f * qz * (dR[0][0] + dR[1][1]));
+        dq[3] = 2.0f * (qx * (dR[2][1] - dR[1][2]) + qy * (dR[0][2] - dR[2][0]) + qz * (dR[1][0] - dR[0][1]));
+        const float dot = fused ? qx * dq[0] + qy * dq[1] + qz * dq[2] + qw * dq[3] : 0.0f;
+        const float qni = 1.0f / qn;                 // normalize_grad_out: (g - n <n,g>) / |raw|
+        aq[0] = (dq[0] - qx * dot) * qni; aq[1] = (dq[1] - qy * dot) * qni;
+        aq[2] = (dq[2] - qz * dot) * qni; aq[3] = (dq[3] - qw * dot) * qni;
+        if (fused) ao = ao * opac * (1.0f - opac);   // sigmoid_grad_out: g * out * (1 - out)
+    }
+    a.grad.xyz[g * 3] = axyz[0]; a.grad.xyz[g * 3 + 1] = axyz[1]; a.grad.xyz[g * 3 + 2] = axyz[2];
+    *reinterpret_cast<float4*>(a.grad.quaternion_xyzw + g * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
+    a.grad.scale[g * 3] = as[0]; a.grad.scale[g * 3 + 1] = as[1]; a.grad.scale[g * 3 + 2] = as[2];
+    a.grad.opacity[g] = ao;
+    float* gb = a.grad.sh_base + g * a.grad.sh_base_stride;
+    gb[0] = abase[0]; gb[1] = abase[1]; gb[2] = abase[2];
+    if (a.grad.sh_rest != nullptr) {
+        float* gr = a.grad.sh_rest + g * a.grad.sh_rest_stride;
+        const int total_rest = a.grad.sh_rest_floats;
+#pragma unroll
+        for (int k = 0; k < NR * 3; ++k) gr[k] = arest[k];
+        for (int k = NR * 3; k < total_rest; ++k) gr[k] = 0.f;   // inactive higher degrees
+    }
+}
+
+}  // namespace
+}  // namespace d3gs
+
+using namespace d3gs;
+
+extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model,
+                                            const D3gsSplatContext* ctx, const float* duv, const float* dconic,
+                                            const float* dopacity, const float* dcolor, const D3gsModelGrad* grad,
+                                            void* stream) {
+    D3GS_REQUIRE(cfg && model && ctx && grad, "NULL argument");
+    D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= D3GS_MAX_VIEWS, "num_views %d outside [1,%d]", cfg->num_views,
+                 D3GS_MAX_VIEWS);
+    D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
+    D3GS_REQUIRE(duv && dconic && dopacity && dcolor, "NULL raster gradient");
+    D3GS_REQUIRE(ctx->radii && ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0, "context lacks radii/cov2d_vecs/sh_to_rgb_ne_0");
+    D3GS_REQUIRE(grad->xyz && grad->quaternion_xyzw && grad->scale && grad->opacity && grad->sh_base,
+                 "NULL gradient output");
+    D3GS_REQUIRE(cfg->sh_degree == 0 || (grad->sh_rest && model->sh_rest), "sh_rest needed with sh_degree > 0");
+    D3GS_REQUIRE(((uintptr_t)model->quaternion_xyzw & 15) == 0 && ((uintptr_t)grad->quaternion_xyzw & 15) == 0,
+                 "quaternion tensors must be 16-byte aligned");
+    D3GS_REQUIRE(grad->sh_rest == nullptr ||
+                     (grad->sh_rest_floats >= ((cfg->sh_degree + 1) * (cfg->sh_degree + 1) - 1) * 3 &&
+                      grad->sh_rest_floats <= grad->sh_rest_stride && grad->sh_rest_floats <= 45),
+                 "sh_rest gradient: floats per Gaussian (%d) must cover the active degree and fit the stride (%d)",
+                 grad->sh_rest_floats, grad->sh_rest_stride);
+    if (model->num == 0) return D3GS_OK;
+    BwdArgs a;
+    a.cfg = *cfg;
+    a.model = *model;
+    a.ctx = *ctx;
+    a.grad = *grad;
+    a.duv = duv;
+    a.dconic = dconic;
+    a.dopacity = dopacity;
+    a.dcolor = dcolor;
+    dim3 grid((unsigned)div_up64(model->num, 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (cfg->sh_degree) {
+        case 0: preprocess_bwd_kernel<0><<<grid, 256, 0, s>>>(a); break;
+        case 1: preprocess_bwd_kernel<1><<<grid, 256, 0, s>>>(a); break;
+        case 2: preprocess_bwd_kernel<2><<<grid, 256, 0, s>>>(a); break;
+        default: preprocess_bwd_kernel<3><<<grid, 256, 0, s>>>(a); break;
+    }
+    D3GS_LAUNCH_CHECK("preprocess_bwd_kernel");
+    return D3GS_OK;
+}

@@ -1,0 +1,284 @@
+// K4: stable LSD radix sort of (uint64 key, int32 value) pairs on a bit range -- a hand-written
+// "onesweep" (one read + one write of the pairs per 8-bit digit, chained-scan look-back between
+// tiles), replacing the reference's cub::DeviceRadixSort::SortPairs call
+// (d3sim/csrc/devsort.py:74-127, call site d3sim/algos/d3gs/render.py:845-887).
+//
+// Phases per call:
+//   1. one histogram kernel builds the 256-bin digit histograms of ALL passes (one read of keys);
+//   2. one tiny kernel turns each histogram into exclusive digit offsets;
+//   3. per pass, one onesweep kernel: a tile of 4096 pairs is ranked stably inside the CTA
+//      (warp match-any multi-split), the per-digit tile counts are published, each digit's
+//      global offset is obtained by looking back over the predecessor tiles, and the tile is
+//      written out through shared memory in digit-sorted runs.
+// Every wait on another CTA's flag is bounded; when it gives up it raises
+// D3GS_STATUS_SORT_TIMEOUT in the caller's status word and the kernel finishes without hanging.
+#include "common.cuh"
+
+namespace d3gs {
+namespace {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortItems = 16;
+constexpr int kSortTile = kSortThreads * kSortItems;   // 4096 pairs per CTA
+constexpr int kMaxPasses = 8;
+
+constexpr uint32_t kLbAggregate = 1u << 30;
+constexpr uint32_t kLbPrefix = 2u << 30;
+constexpr uint32_t kLbFlagMask = 3u << 30;
+constexpr uint32_t kLbValueMask = ~kLbFlagMask;
+
+struct PassTable {
+    int32_t shift[kMaxPasses];
+    uint32_t mask[kMaxPasses];
+    int32_t num_passes;
+};
+
+__global__ void __launch_bounds__(256)
+histogram_kernel(const uint64_t* __restrict__ keys, int64_t n, const __grid_constant__ PassTable pt,
+                 uint32_t* __restrict__ hist /* [passes][256] */) {
+    __shared__ uint32_t s_hist[kMaxPasses * kRadix];
+    for (int k = threadIdx.x; k < pt.num_passes * kRadix; k += 256) s_hist[k] = 0;
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
+        const uint64_t key = keys[i];
+#pragma unroll
+        for (int p = 0; p < kMaxPasses; ++p) {
+            if (p < pt.num_passes) atomicAdd(&s_hist[p * kRadix + (uint32_t)((key >> pt.shift[p]) & pt.mask[p])], 1u);
+        }
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < pt.num_passes * kRadix; k += 256) {
+        const uint32_t c = s_hist[k];
+        if (c) atomicAdd(&hist[k], c);
+    }
+}
+
+// exclusive scan of each pass's 256 bins, in place; one CTA of 256 threads per pass
+__global__ void __launch_bounds__(256) digit_offsets_kernel(uint32_t* __restrict__ hist) {
+    __shared__ uint32_t s_w[8];
+    uint32_t* h = hist + (size_t)blockIdx.x * kRadix;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint32_t c = h[t];
+    uint32_t inc = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += y;
+    }
+    if (lane == 31) s_w[warp] = inc;
+    __syncthreads();
+    uint32_t off = 0;
+    for (int w = 0; w < warp; ++w) off += s_w[w];
+    h[t] = off + inc - c;
+}
+
+struct SweepSmem {
+    uint64_t keys[kSortTile];
+    int32_t vals[kSortTile];
+    uint32_t warp_hist[kSortWarps][kRadix + 1];
+    uint32_t digit_off[kRadix + 1];
+    int64_t global_base[kRadix];
+    uint32_t scan_tmp[kSortWarps];
+    uint32_t tile;
+};
+
+__global__ void __launch_bounds__(kSortThreads)
+onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
+                const int32_t* __restrict__ vals_in, int32_t* __restrict__ vals_out, int64_t n, int shift,
+                uint32_t mask, const uint32_t* __restrict__ digit_base, uint32_t* __restrict__ ticket,
+                uint32_t* __restrict__ lookback /* [tiles][256] */, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    SweepSmem& sm = *reinterpret_cast<SweepSmem*>(smem_raw);
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    if (t == 0) sm.tile = atomicAdd(ticket, 1u);
+    for (int k = t; k < kSortWarps * (kRadix + 1); k += kSortThreads) (&sm.warp_hist[0][0])[k] = 0;
+    __syncthreads();
+    const uint32_t tile = sm.tile;
+    const int64_t tile_base = (int64_t)tile * kSortTile;
+    const int count = (int)min((int64_t)kSortTile, n - tile_base);
+
+    // ---- load (warp-striped: index = warp*512 + item*32 + lane) and rank ------------------------
+    uint64_t key[kSortItems];
+    int32_t val[kSortItems];
+    uint16_t rank[kSortItems];
+    const uint32_t lanemask_lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < kSortItems; ++i) {
+        const int local = warp * (32 * kSortItems) + i * 32 + lane;
+        const bool valid = local < count;
+        key[i] = valid ? keys_in[tile_base + local] : ~0ull;
+        val[i] = valid ? vals_in[tile_base + local] : 0;
+    }
+#pragma unroll
+    for (int i = 0; i < kSortItems; ++i) {
+        const int local = warp * (32 * kSortItems) + i * 32 + lane;
+        const uint32_t bin = (local < count) ? (uint32_t)((key[i] >> shift) & mask) : (uint32_t)kRadix;
+        const uint32_t peers = __match_any_sync(0xffffffffu, bin);
+        const uint32_t pre = sm.warp_hist[warp][bin];
+        __syncwarp();
+        if (lane == __ffs(peers) - 1) sm.warp_hist[warp][bin] = pre + __popc(peers);
+        __syncwarp();
+        rank[i] = (uint16_t)(pre + __popc(peers & lanemask_lt));
+    }
+    __syncthreads();
+
+    // ---- per-digit tile counts, publish, look back ---------------------------------------------
+    {
+        const int d = t;   // one thread per digit
+        uint32_t tot = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w) {
+            const uint32_t c = sm.warp_hist[w][d];
+            sm.warp_hist[w][d] = tot;   // exclusive offset of this warp inside the digit's run
+            tot += c;
+        }
+        uint32_t* my = lookback + (size_t)tile * kRadix + d;
+        if (tile == 0) atomicExch(my, kLbPrefix | tot);
+        else atomicExch(my, kLbAggregate | tot);
+        // block-wide exclusive scan over digits -> position of the digit's run in the sorted tile
+        uint32_t inc = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            uint32_t y = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += y;
+        }
+        if (lane == 31) sm.scan_tmp[warp] = inc;
+        __syncthreads();
+        uint32_t off = 0;
+        for (int w = 0; w < warp; ++w) off += sm.scan_tmp[w];
+        const uint32_t dig_off = off + inc - tot;
+        sm.digit_off[d] = dig_off;
+        // look-back: sum the counts of all predecessor tiles for this digit
+        uint32_t excl = 0;
+        if (tile > 0) {
+            int64_t look = (int64_t)tile - 1;
+            bool gave_up = false;
+            while (look >= 0) {
+                const volatile uint32_t* p = lookback + (size_t)look * kRadix + d;
+                uint32_t st = *p;
+                int spins = 0;
+                while ((st & kLbFlagMask) == 0) {
+                    if (++spins > (1 << 20)) { gave_up = true; break; }
+                    __nanosleep(20);
+                    st = *p;
+                }
+                if (gave_up) break;
+                excl += st & kLbValueMask;
+                if ((st & kLbFlagMask) == kLbPrefix) break;
+                --look;
+            }
+            if (gave_up) atomicOr(status, D3GS_STATUS_SORT_TIMEOUT);
+            atomicExch(my, kLbPrefix | ((excl + tot) & kLbValueMask));
+        }
+        sm.global_base[d] = (int64_t)digit_base[d] + (int64_t)excl - (int64_t)dig_off;
+    }
+    __syncthreads();
+
+    // ---- scatter into shared memory in digit-sorted order, then coalesced write-out --------------
+#pragma unroll
+    for (int i = 0; i < kSortItems; ++i) {
+        const int local = warp * (32 * kSortItems) + i * 32 + lane;
+        if (local < count) {
+            const uint32_t bin = (uint32_t)((key[i] >> shift) & mask);
+            const uint32_t pos = sm.digit_off[bin] + sm.warp_hist[warp][bin] + rank[i];
+            sm.keys[pos] = key[i];
+            sm.vals[pos] = val[i];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kSortItems; ++i) {
+        const int pos = i * kSortThreads + t;
+        if (pos < count) {
+            const uint64_t k = sm.keys[pos];
+            const uint32_t bin = (uint32_t)((k >> shift) & mask);
+            const int64_t g = sm.global_base[bin] + pos;
+            keys_out[g] = k;
+            vals_out[g] = sm.vals[pos];
+        }
+    }
+}
+
+struct SortLayout {
+    size_t hist_off, ticket_off, lookback_off, total;
+    int64_t tiles;
+};
+
+SortLayout sort_layout(int64_t n) {
+    SortLayout L;
+    L.tiles = div_up64(n > 0 ? n : 1, kSortTile);
+    L.hist_off = 0;
+    L.ticket_off = L.hist_off + sizeof(uint32_t) * kMaxPasses * kRadix;
+    L.lookback_off = L.ticket_off + 256;
+    L.total = L.lookback_off + (size_t)L.tiles * kRadix * sizeof(uint32_t);
+    return L;
+}
+
+}  // namespace
+}  // namespace d3gs
+
+using namespace d3gs;
+
+extern "C" size_t d3gs_sort_workspace_bytes(int64_t n, int32_t begin_bit, int32_t end_bit) {
+    (void)begin_bit;
+    (void)end_bit;
+    return sort_layout(n).total;
+}
+
+extern "C" int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int32_t* values_alt, int64_t n,
+                                   int32_t begin_bit, int32_t end_bit, void* workspace, size_t workspace_bytes,
+                                   int32_t* result_in_alt, uint32_t* status, void* stream) {
+    D3GS_REQUIRE(n >= 0, "negative pair count");
+    D3GS_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit <= end_bit, "bad bit range [%d,%d)", begin_bit, end_bit);
+    D3GS_REQUIRE(result_in_alt != nullptr && status != nullptr, "result_in_alt/status is NULL");
+    const int passes = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
+    *result_in_alt = passes & 1;
+    if (n == 0 || passes == 0) {
+        *result_in_alt = 0;
+        return D3GS_OK;
+    }
+    D3GS_REQUIRE(keys && keys_alt && values && values_alt && workspace, "NULL buffer");
+    D3GS_REQUIRE(n < ((int64_t)1 << 30), "pair count %lld exceeds the 2^30 limit of the look-back counters", (long long)n);
+    const SortLayout L = sort_layout(n);
+    D3GS_REQUIRE(workspace_bytes >= L.total, "sort workspace too small: %zu < %zu", workspace_bytes, L.total);
+    D3GS_REQUIRE(((uintptr_t)workspace & 15) == 0, "sort workspace must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    char* ws = reinterpret_cast<char*>(workspace);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(ws + L.hist_off);
+    uint32_t* tickets = reinterpret_cast<uint32_t*>(ws + L.ticket_off);
+    uint32_t* lookback = reinterpret_cast<uint32_t*>(ws + L.lookback_off);
+
+    PassTable pt;
+    pt.num_passes = passes;
+    for (int p = 0; p < kMaxPasses; ++p) {
+        const int sh = begin_bit + p * kRadixBits;
+        const int bits = p < passes ? (end_bit - sh < kRadixBits ? end_bit - sh : kRadixBits) : 0;
+        pt.shift[p] = p < passes ? sh : 0;
+        pt.mask[p] = bits > 0 ? ((1u << bits) - 1u) : 0u;
+    }
+    D3GS_CUDA(cudaFuncSetAttribute(onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(SweepSmem)));
+    D3GS_CUDA(cudaMemsetAsync(ws, 0, L.lookback_off, s));   // histograms + tickets
+    int hist_blocks = (int)(L.tiles < 148 * 8 ? L.tiles : 148 * 8);
+    histogram_kernel<<<hist_blocks, 256, 0, s>>>(keys, n, pt, hist);
+    D3GS_LAUNCH_CHECK("histogram_kernel");
+    digit_offsets_kernel<<<passes, 256, 0, s>>>(hist);
+    D3GS_LAUNCH_CHECK("digit_offsets_kernel");
+    uint64_t* kin = keys;
+    uint64_t* kout = keys_alt;
+    int32_t* vin = values;
+    int32_t* vout = values_alt;
+    for (int p = 0; p < passes; ++p) {
+        D3GS_CUDA(cudaMemsetAsync(lookback, 0, (size_t)L.tiles * kRadix * sizeof(uint32_t), s));
+        onesweep_kernel<<<(unsigned)L.tiles, kSortThreads, sizeof(SweepSmem), s>>>(
+            kin, kout, vin, vout, n, pt.shift[p], pt.mask[p], hist + (size_t)p * kRadix, tickets + p, lookback, status);
+        D3GS_LAUNCH_CHECK("onesweep_kernel");
+        uint64_t* tk = kin; kin = kout; kout = tk;
+        int32_t* tv = vin; vin = vout; vout = tv;
+    }
+    return D3GS_OK;
+}

@@ -1,0 +1,355 @@
+// K6 raster forward and K7 raster backward: per-tile front-to-back alpha blending.
+//
+// Reference semantics: d3sim/algos/d3gs/render.py:1329-2316 (forward is_bwd=False; backward
+// 1589-1676 + 1774-2210).  One CTA of 256 threads per 16x16 tile, one pixel per thread, pixels laid
+// out 8x4 per warp (render.py:1503-1512).  The tile's sorted list of 48-byte splat records is
+// streamed through shared memory with bulk async copies (cp.async.bulk + mbarrier, double
+// buffered) instead of the reference's per-thread gathers (render.py:1699-1716).
+//
+// The arithmetic that decides n_contrib -- power, exp, alpha, the transmittance product and the
+// three threshold compares -- is written with explicit round-to-nearest intrinsics so that its
+// bits are defined (see common.cuh); colour accumulation uses explicit fma as well.
+#include "common.cuh"
+
+namespace d3gs {
+namespace {
+
+constexpr int kBatch = 256;                        // records per staged batch
+constexpr int kRecFloat4 = 3;                      // 48 bytes
+constexpr uint32_t kRecBytes = kRecFloat4 * 16;
+
+struct RasterArgs {
+    int width, height, tiles_x, tiles_y;
+    float alpha_eps, t_eps;
+    float bg[3];
+    int training;
+    const int32_t* ranges;
+    const float4* records;
+    uint32_t* status;
+    // forward outputs / backward inputs
+    float* color;
+    float* final_T;
+    int32_t* n_contrib;
+    // backward
+    const float* drgb;
+    const float* dT;
+    float* duv;
+    float* dconic;
+    float* dopacity;
+    float* dcolor;
+};
+
+struct PixelCoord {
+    int px, py;
+    bool inside;
+};
+
+__device__ __forceinline__ PixelCoord pixel_of_thread(const RasterArgs& a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    PixelCoord p;
+    p.px = blockIdx.x * 16 + (warp & 1) * 8 + (lane & 7);
+    p.py = blockIdx.y * 16 + (warp >> 1) * 4 + (lane >> 3);
+    p.inside = p.px < a.width && p.py < a.height;
+    return p;
+}
+
+// Producer side of the staging pipeline (thread 0 only).
+__device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, uint64_t* bar, int r0, int n, int batch) {
+    const int cnt = min(kBatch, n - batch * kBatch);
+    const uint32_t bytes = (uint32_t)cnt * kRecBytes;
+    mbar_arrive_expect_tx(bar, bytes);
+    bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
+}
+
+__global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
+    __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    const int t = threadIdx.x;
+    const PixelCoord pc = pixel_of_thread(a);
+    const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
+    const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
+    const int n = r1 - r0;
+    const int nb = (n + kBatch - 1) / kBatch;
+    if (t == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, n, 0);
+
+    const float fpx = (float)pc.px, fpy = (float)pc.py;
+    bool done = !pc.inside;
+    float T = 1.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f;
+    int contributor = 0;
+    bool copy_failed = false;
+
+    for (int b = 0; b < nb; ++b) {
+        const int cur = b & 1;
+        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, n, b + 1);
+        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        // whole-tile early exit (render.py:1691-1694); an in-flight prefetch is drained first
+        const int num_done = __syncthreads_count(done || copy_failed);
+        if (num_done == 256) {
+            if (b + 1 < nb) mbar_wait_bounded(&s_bar[cur ^ 1], (uint32_t)(((b + 1) >> 1) & 1));
+            break;
+        }
+        const int cnt = min(kBatch, n - b * kBatch);
+        const float4* rec = s_rec[cur];
+        if (!__all_sync(0xffffffffu, done)) {
+            for (int j = 0; j < cnt; ++j) {
+                const float4 q0 = rec[j * 3];       // u, v, thr, id
+                const float4 q1 = rec[j * 3 + 1];   // ha, nb, hc, opacity
+                const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
+                const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
+                // power < thr  =>  alpha < alpha_eps: the pixel skips this splat (render.py:1796-1798)
+                const bool cand = !done && power >= q0.z;
+                if (!__any_sync(0xffffffffu, cand)) continue;
+                if (cand) {
+                    const float G = blend_exp(power);
+                    const float alpha = fminf(0.99f, f_mul(q1.w, G));
+                    if (alpha >= a.alpha_eps) {
+                        const float nT = f_mul(T, f_sub(1.0f, alpha));
+                        const bool should_done = nT < a.t_eps;
+                        if (power > 0.0f || should_done) {
+                            done = should_done;          // render.py:1803-1807
+                        } else {
+                            const float w = f_mul(alpha, T);
+                            T = nT;
+                            contributor = b * kBatch + j;   // render.py:1836
+                            const float4 q2 = rec[j * 3 + 2];
+                            C0 = f_fma(w, q2.x, C0);
+                            C1 = f_fma(w, q2.y, C1);
+                            C2 = f_fma(w, q2.z, C2);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();   // everyone is done reading s_rec[cur] before it is refilled
+    }
+    if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
+    if (pc.inside) {
+        const int64_t pix = ((int64_t)blockIdx.z * a.height + pc.py) * a.width + pc.px;
+        a.final_T[pix] = T;
+        a.n_contrib[pix] = contributor;
+        if (!a.training) {   // render.py:2259-2263: composite the background and clamp at inference
+            C0 = fminf(fmaxf(f_add(C0, f_mul(T, a.bg[0])), 0.0f), 1.0f);
+            C1 = fminf(fmaxf(f_add(C1, f_mul(T, a.bg[1])), 0.0f), 1.0f);
+            C2 = fminf(fmaxf(f_add(C2, f_mul(T, a.bg[2])), 0.0f), 1.0f);
+        }
+        a.color[pix * 3] = C0;
+        a.color[pix * 3 + 1] = C1;
+        a.color[pix * 3 + 2] = C2;
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Backward.  Per pixel the blend is replayed front to back (T from 1, colour suffix = final -
+// prefix, render.py:1868-1895); the nine per-splat partial derivatives are summed over the warp by
+// shuffles, over the CTA in shared memory, and leave the CTA as ONE atomic add per (tile, splat,
+// component) instead of the reference's one per warp (render.py:2061-2148).
+__global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
+    __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ float s_acc[kBatch][9];
+    __shared__ int s_max[8];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const PixelCoord pc = pixel_of_thread(a);
+    const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
+    const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
+    const int n = r1 - r0;
+    const int64_t pix = ((int64_t)blockIdx.z * a.height + pc.py) * a.width + pc.px;
+    // render.py:1594: list positions [0, n_contrib] took part in the forward blend
+    int contributor = 0;
+    float rr0 = 0.0f, rr1 = 0.0f, rr2 = 0.0f, dr0 = 0.0f, dr1 = 0.0f, dr2 = 0.0f, dTT = 0.0f;
+    if (pc.inside && n > 0) {
+        contributor = min(a.n_contrib[pix] + 1, n);
+        rr0 = a.color[pix * 3]; rr1 = a.color[pix * 3 + 1]; rr2 = a.color[pix * 3 + 2];
+        dr0 = a.drgb[pix * 3]; dr1 = a.drgb[pix * 3 + 1]; dr2 = a.drgb[pix * 3 + 2];
+        dTT = a.dT != nullptr ? a.dT[pix] * a.final_T[pix] : 0.0f;   // render.py:1935
+    }
+    int wmax = contributor;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
+    if (lane == 0) s_max[warp] = wmax;
+    if (t == 0) {
+        mbar_init(&s_bar[0], 1);
+        mbar_init(&s_bar[1], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    int bmax = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) bmax = max(bmax, s_max[w]);
+    const int nb = (bmax + kBatch - 1) / kBatch;     // batches anybody in the tile still needs
+    if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, bmax, 0);
+
+    const float fpx = (float)pc.px, fpy = (float)pc.py;
+    float T = 1.0f;
+    bool copy_failed = false;
+    for (int b = 0; b < nb; ++b) {
+        const int cur = b & 1;
+        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
+#pragma unroll
+        for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;
+        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        if (__syncthreads_or(copy_failed)) {
+            if (b + 1 < nb) mbar_wait_bounded(&s_bar[cur ^ 1], (uint32_t)(((b + 1) >> 1) & 1));
+            break;
+        }
+        const int cnt = min(kBatch, bmax - b * kBatch);
+        const float4* rec = s_rec[cur];
+        const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform
+        for (int j = 0; j < wlim; ++j) {
+            const float4 q0 = rec[j * 3];
+            const float4 q1 = rec[j * 3 + 1];
+            const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
+            const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
+            // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
+            const bool cand = (b * kBatch + j < contributor) && power >= q0.z && power <= 0.0f;
+            if (!__any_sync(0xffffffffu, cand)) continue;
+            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f, v8 = 0.f;
+            bool valid = false;
+            if (cand) {
+                const float G = blend_exp(power);
+                const float alpha = fminf(0.99f, f_mul(q1.w, G));
+                if (alpha >= a.alpha_eps) {
+                    valid = true;
+                    const float nT = f_mul(T, f_sub(1.0f, alpha));
+                    const float w = f_mul(alpha, T);
+                    T = nT;
+                    const float4 q2 = rec[j * 3 + 2];
+                    rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
+                    float dl = dr0 * fmaf(T, q2.x, -rr0);
+                    dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
+                    dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
+                    dl -= dTT;
+                    const float dL_dalpha = dl / (1.0f - alpha);          // render.py:1957
+                    const float dL_dG = q1.w * dL_dalpha;                 // render.py:1995
+                    const float gdx = G * dx, gdy = G * dy;
+                    const float ca = -2.0f * q1.x, cb = -q1.y, cc = -2.0f * q1.z;
+                    v0 = dL_dG * (-gdx * ca - gdy * cb);                  // render.py:2001-2006
+                    v1 = dL_dG * (-gdy * cc - gdx * cb);
+                    v2 = -0.5f * gdx * dx * dL_dG;                        // render.py:2013-2017
+                    v3 = -gdx * dy * dL_dG;
+                    v4 = -0.5f * gdy * dy * dL_dG;
+                    v5 = dL_dalpha * G;                                   // render.py:2018
+                    v6 = w * dr0; v7 = w * dr1; v8 = w * dr2;             // render.py:1962
+                }
+            }
+            if (!__any_sync(0xffffffffu, valid)) continue;
+            v0 = warp_sum(v0); v1 = warp_sum(v1); v2 = warp_sum(v2); v3 = warp_sum(v3); v4 = warp_sum(v4);
+            v5 = warp_sum(v5); v6 = warp_sum(v6); v7 = warp_sum(v7); v8 = warp_sum(v8);
+            if (lane == 0) {
+                float* acc = s_acc[j];
+                atomicAdd(acc + 0, v0); atomicAdd(acc + 1, v1); atomicAdd(acc + 2, v2);
+                atomicAdd(acc + 3, v3); atomicAdd(acc + 4, v4); atomicAdd(acc + 5, v5);
+                atomicAdd(acc + 6, v6); atomicAdd(acc + 7, v7); atomicAdd(acc + 8, v8);
+            }
+        }
+        __syncthreads();
+        if (t < cnt) {
+            const float* acc = s_acc[t];
+            bool any = false;
+#pragma unroll
+            for (int k = 0; k < 9; ++k) any |= acc[k] != 0.0f;
+            if (any) {
+                const int64_t id = __float_as_int(rec[t * 3].w);
+                atomicAdd(a.duv + id * 2, acc[0]);
+                atomicAdd(a.duv + id * 2 + 1, acc[1]);
+                atomicAdd(a.dconic + id * 3, acc[2]);
+                atomicAdd(a.dconic + id * 3 + 1, acc[3]);
+                atomicAdd(a.dconic + id * 3 + 2, acc[4]);
+                atomicAdd(a.dopacity + id, acc[5]);
+                atomicAdd(a.dcolor + id * 3, acc[6]);
+                atomicAdd(a.dcolor + id * 3 + 1, acc[7]);
+                atomicAdd(a.dcolor + id * 3 + 2, acc[8]);
+            }
+        }
+        __syncthreads();
+    }
+    if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
+}
+
+int32_t fill_args(const D3gsOpConfig* cfg, RasterArgs& a) {
+    D3GS_REQUIRE(cfg != nullptr, "cfg is NULL");
+    D3GS_REQUIRE(cfg->tile_x == 16 && cfg->tile_y == 16, "only 16x16 tiles are supported");
+    D3GS_REQUIRE(cfg->width > 0 && cfg->height > 0, "bad image size");
+    D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= 65535, "num_views out of range");
+    a.width = cfg->width;
+    a.height = cfg->height;
+    a.tiles_x = (cfg->width + 15) / 16;
+    a.tiles_y = (cfg->height + 15) / 16;
+    a.alpha_eps = cfg->alpha_eps;
+    a.t_eps = cfg->transmittance_eps;
+    a.bg[0] = cfg->bg_color[0]; a.bg[1] = cfg->bg_color[1]; a.bg[2] = cfg->bg_color[2];
+    a.training = cfg->training;
+    return D3GS_OK;
+}
+
+}  // namespace
+}  // namespace d3gs
+
+using namespace d3gs;
+
+extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const float* records,
+                                       float* color, float* final_T, int32_t* n_contrib, uint32_t* status,
+                                       void* stream) {
+    RasterArgs a = {};
+    int32_t rc = fill_args(cfg, a);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(ranges && color && final_T && n_contrib && status, "NULL argument");
+    D3GS_REQUIRE(((uintptr_t)records & 15) == 0, "records must be 16-byte aligned");
+    a.ranges = ranges;
+    a.records = reinterpret_cast<const float4*>(records);
+    a.status = status;
+    a.color = color;
+    a.final_T = final_T;
+    a.n_contrib = n_contrib;
+    dim3 grid(a.tiles_x, a.tiles_y, cfg->num_views);
+    raster_forward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    D3GS_LAUNCH_CHECK("raster_forward_kernel");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges,
+                                        const float* records, const float* color, const float* final_T,
+                                        const int32_t* n_contrib, const float* drgb, const float* dT, float* duv,
+                                        float* dconic, float* dopacity, float* dcolor, uint32_t* status,
+                                        void* stream) {
+    RasterArgs a = {};
+    int32_t rc = fill_args(cfg, a);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(ranges && color && final_T && n_contrib && drgb && status, "NULL argument");
+    D3GS_REQUIRE(duv && dconic && dopacity && dcolor, "NULL gradient output");
+    D3GS_REQUIRE(((uintptr_t)records & 15) == 0, "records must be 16-byte aligned");
+    D3GS_REQUIRE(num >= 0, "negative Gaussian count");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t bn = (size_t)num * cfg->num_views;
+    D3GS_CUDA(cudaMemsetAsync(duv, 0, bn * 2 * sizeof(float), s));
+    D3GS_CUDA(cudaMemsetAsync(dconic, 0, bn * 3 * sizeof(float), s));
+    D3GS_CUDA(cudaMemsetAsync(dopacity, 0, bn * sizeof(float), s));
+    D3GS_CUDA(cudaMemsetAsync(dcolor, 0, bn * 3 * sizeof(float), s));
+    a.ranges = ranges;
+    a.records = reinterpret_cast<const float4*>(records);
+    a.status = status;
+    a.color = const_cast<float*>(color);
+    a.final_T = const_cast<float*>(final_T);
+    a.n_contrib = const_cast<int32_t*>(n_contrib);
+    a.drgb = drgb;
+    a.dT = dT;
+    a.duv = duv;
+    a.dconic = dconic;
+    a.dopacity = dopacity;
+    a.dcolor = dcolor;
+    dim3 grid(a.tiles_x, a.tiles_y, cfg->num_views);
+    raster_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    D3GS_LAUNCH_CHECK("raster_backward_kernel");
+    return D3GS_OK;
+}

@@ -1,0 +1,496 @@
+"""The splat operator: drop-in for ``d3sim.algos.d3gs.render``.
+
+Same public names, argument order, tensor shapes and dtypes as the reference
+(d3sim/algos/d3gs/render.py): ``GaussianSplatOp(cfg).forward / .backward``,
+``rasterize_gaussians``, ``rasterize_gaussians_dynamic``, ``CameraBundle``, ``GaussianSplatOutput``,
+``GaussianSplatOpContext``, ``GaussianSplatGradients``.  Where the reference launches NVRTC-compiled
+kernel strings through cumm (render.py:676-681, 839-840, 937-939, 2308-2309, 3361-3369) and calls a
+pybind wrapper of cub's radix sort (render.py:845-887), this module calls the ahead-of-time
+sm_100a library through its C ABI on torch's current stream.  All buffers are torch allocations;
+the library allocates nothing.
+"""
+from __future__ import annotations
+
+import copy
+import ctypes as C
+import dataclasses
+from typing import Any
+
+import numpy as np
+import torch
+
+from . import _lib
+from .camera import BasicPinholeCamera
+from .config_def import EarlyFilterAlgo, GaussianSplatConfig, RasterizeBackwardAlgo
+from .model import GaussianModelOriginBase, carve_flat
+
+
+def div_up(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+@dataclasses.dataclass
+class GaussianSplatOpContext:
+    """Per-(view, Gaussian) tensors kept for the backward pass (render.py:57-72)."""
+    conic_opacity: torch.Tensor
+    radii: torch.Tensor
+    uvs: torch.Tensor
+    rgb_gaussian: torch.Tensor | None
+    gaussian_idx_sorted: torch.Tensor
+    workload_ranges: torch.Tensor
+    image_shape_wh: tuple[int, int]
+    depths: torch.Tensor
+    cov2d_vecs: torch.Tensor | None = None
+    sh_to_rgb_ne_0: torch.Tensor | None = None
+    per_gaussian_snap: Any = None
+    # not in the reference: the sorted, contiguous 48-byte splat records the raster kernels stream
+    splat_records: torch.Tensor | None = None
+
+
+@dataclasses.dataclass
+class GaussianSplatOutput:
+    """render.py:74-100.  ``color`` is NHWC [B,H,W,3]; in training it is not composited with a background."""
+    custom_features: torch.Tensor | None
+    T: torch.Tensor
+    color: torch.Tensor
+    depth: torch.Tensor | None = None
+    n_contrib: torch.Tensor | None = None
+    radii: torch.Tensor | None = None
+    sparse_gaussian_ids: torch.Tensor | None = None
+    sparse_batch_ids: torch.Tensor | None = None
+
+    @property
+    def image_shape_wh(self) -> tuple[int, int]:
+        return (self.T.shape[2], self.T.shape[1])
+
+    def select_batch(self, batch_idx: int):
+        sl = slice(batch_idx, batch_idx + 1)
+        return GaussianSplatOutput(
+            custom_features=None if self.custom_features is None else self.custom_features[sl],
+            T=self.T[sl], color=self.color[sl], depth=None if self.depth is None else self.depth[sl],
+            n_contrib=None if self.n_contrib is None else self.n_contrib[sl],
+            radii=None if self.radii is None else self.radii[sl])
+
+
+@dataclasses.dataclass
+class RasterizeGradientOutput:
+    """render.py:103-111."""
+    duv: torch.Tensor
+    dconic: torch.Tensor
+    dopacity: torch.Tensor
+    dcolor: torch.Tensor | None
+    dcustom_features: torch.Tensor | None = None
+    dz: torch.Tensor | None = None
+
+
+@dataclasses.dataclass
+class GaussianSplatGradients:
+    """render.py:113-120."""
+    drgb: torch.Tensor
+    dT: torch.Tensor | None
+    ddepth: torch.Tensor | None = None
+    dcustom_features: torch.Tensor | None = None
+
+
+@dataclasses.dataclass
+class CameraParamBundle:
+    focal_xy_ppoint: torch.Tensor
+    image_shape_wh: tuple[int, int]
+    frame_ids: torch.Tensor | None
+
+
+@dataclasses.dataclass
+class CameraBundle(CameraParamBundle):
+    """A batch of pinhole cameras (render.py:122-150): ``cam2world_T`` [B,4,3], ``focal_xy_ppoint`` [B,4]."""
+    cam2world_T: torch.Tensor = None
+    _host: np.ndarray | None = dataclasses.field(default=None, repr=False, compare=False)
+
+    @classmethod
+    def from_pinhole_cams(cls, cams: list[BasicPinholeCamera], device: torch.device | str = "cuda"):
+        c2w_t = np.stack([np.ascontiguousarray(cam.pose.to_world[:3].T) for cam in cams], axis=0).reshape(-1, 4, 3)
+        fpp = np.concatenate([np.stack([cam.focal_length for cam in cams]).reshape(-1, 2),
+                              np.stack([cam.principal_point for cam in cams]).reshape(-1, 2)], axis=1)
+        frame_ids = None
+        if cams[0].frame_local_id is not None:
+            frame_ids = torch.tensor([cam.frame_local_id for cam in cams], dtype=torch.int32, device=device)
+        host = np.concatenate([c2w_t.reshape(-1, 12), fpp], axis=1).astype(np.float32)
+        return cls(torch.from_numpy(np.ascontiguousarray(fpp.astype(np.float32))).to(device), cams[0].image_shape_wh,
+                   frame_ids, torch.from_numpy(np.ascontiguousarray(c2w_t.astype(np.float32))).to(device), host)
+
+    def host_params(self) -> np.ndarray:
+        """[B,16] float32 on the host (one device read, cached)."""
+        if self._host is None:
+            c2w = self.cam2world_T.detach().float().cpu().numpy().reshape(-1, 12)
+            fpp = self.focal_xy_ppoint.detach().float().cpu().numpy().reshape(-1, 4)
+            self._host = np.concatenate([c2w, fpp], axis=1).astype(np.float32)
+        return self._host
+
+
+def _camera_rows(cameras: BasicPinholeCamera | CameraBundle) -> np.ndarray:
+    if isinstance(cameras, BasicPinholeCamera):
+        k = cameras.intrinsic
+        c2w_t = np.ascontiguousarray(cameras.pose.to_world[:3].T).reshape(12)     # render.py:205
+        return np.concatenate([c2w_t, [k[0, 0], k[1, 1], k[0, 2], k[1, 2]]]).astype(np.float32)[None]
+    return cameras.host_params()
+
+
+class _Workspace:
+    """Grow-only scratch tensors so that the steady state performs no allocation for them."""
+
+    def __init__(self):
+        self.bufs: dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, nbytes: int, device) -> torch.Tensor:
+        t = self.bufs.get(name)
+        if t is None or t.numel() < nbytes or t.device != device:
+            t = torch.empty(max(int(nbytes * 1.25), 256), dtype=torch.uint8, device=device)
+            self.bufs[name] = t
+        return t
+
+
+class GaussianSplatOp:
+    """render.py:152-167.  ``cfg`` is deep-copied: create a new op to change options."""
+
+    def __init__(self, cfg: GaussianSplatConfig) -> None:
+        self._cfg = copy.deepcopy(cfg)
+        bad = self._cfg.unsupported_options()
+        if bad:
+            raise NotImplementedError("GaussianSplatConfig options not built in this library: " + ", ".join(bad))
+        self._lib = _lib.load()
+        self._ws = _Workspace()
+        self._sync: dict[Any, torch.Tensor] = {}
+        self.last_num_rendered = 0
+        # when True, forward() keeps copies of the intermediate binning arrays in ``self.debug`` (tests)
+        self.debug_capture = False
+        self.debug: dict[str, torch.Tensor] = {}
+
+    @property
+    def is_nchw(self):
+        return self._cfg.use_nchw
+
+    @property
+    def is_rgba(self):
+        return self._cfg.render_rgba
+
+    # ---- plumbing ---------------------------------------------------------------------------
+    def _sync_words(self, device) -> torch.Tensor:
+        """int64[2] on the device: [num_rendered, status bits]; read back with one copy."""
+        t = self._sync.get(device)
+        if t is None:
+            t = torch.zeros(2, dtype=torch.int64, device=device)
+            self._sync[device] = t
+        return t
+
+    def _op_config(self, model: GaussianModelOriginBase, cameras, training: bool) -> _lib.OpConfig:
+        cfg = self._cfg
+        rows = _camera_rows(cameras)
+        if rows.shape[0] > _lib.MAX_VIEWS:
+            raise NotImplementedError(f"at most {_lib.MAX_VIEWS} views per launch (got {rows.shape[0]})")
+        w, h = cameras.image_shape_wh
+        c = _lib.OpConfig()
+        c.width, c.height = int(w), int(h)
+        c.tile_x, c.tile_y = int(cfg.tile_size[0]), int(cfg.tile_size[1])
+        c.near_plane, c.far_plane, c.eps = cfg.near, cfg.far, cfg.eps
+        c.cov2d_radii_eigen_eps = cfg.cov2d_radii_eigen_eps
+        c.projected_clamp_factor = cfg.projected_clamp_factor
+        c.gaussian_std_sigma = cfg.gaussian_std_sigma
+        c.gaussian_lowpass_filter = cfg.gaussian_lowpass_filter
+        c.alpha_eps = cfg.alpha_eps
+        c.transmittance_eps = cfg.transmittance_eps
+        c.scale_global = cfg.scale_global
+        c.early_filter_algo = int(cfg.early_filter_algo)
+        c.sh_degree = int(model.cur_sh_degree)
+        c.training = int(bool(training))
+        c.clamp_mask_reference_order = int(bool(cfg.clamp_mask_reference_order))
+        c.fused_activations = int(model.has_fused_activations)
+        bg = np.asarray(cfg.bg_color, np.float32).reshape(-1)
+        for k in range(3):
+            c.bg_color[k] = float(bg[k])
+        c.num_views = rows.shape[0]
+        for b in range(rows.shape[0]):
+            cam = c.cameras[b]
+            for k in range(12):
+                cam.cam2world_T[k] = float(rows[b, k])
+            cam.fx, cam.fy, cam.cx, cam.cy = (float(v) for v in rows[b, 12:16])
+        return c
+
+    @staticmethod
+    def _model_struct(model: GaussianModelOriginBase) -> _lib.Model:
+        m = _lib.Model()
+        m.num = len(model)
+        for name in ("xyz", "quaternion_xyzw", "scale", "opacity", "color_sh"):
+            t = getattr(model, name)
+            assert t.is_contiguous() and t.dtype == torch.float32 and t.is_cuda, f"model.{name} must be contiguous fp32 CUDA"
+        m.xyz, m.quaternion_xyzw = model.xyz.data_ptr(), model.quaternion_xyzw.data_ptr()
+        m.scale, m.opacity = model.scale.data_ptr(), model.opacity.data_ptr()
+        k = model.color_sh.shape[1]
+        if model.color_sh_base is not None:
+            assert model.color_sh_base.is_contiguous()
+            m.sh_base, m.sh_base_stride = model.color_sh_base.data_ptr(), 3
+            m.sh_rest, m.sh_rest_stride = model.color_sh.data_ptr(), k * 3
+        else:   # un-split [N,(D+1)^2,3]: first coefficient is the base
+            m.sh_base, m.sh_base_stride = model.color_sh.data_ptr(), k * 3
+            m.sh_rest, m.sh_rest_stride = model.color_sh.data_ptr() + 12, k * 3
+        return m
+
+    @staticmethod
+    def _ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb, cov2d, ne0) -> _lib.SplatContext:
+        s = _lib.SplatContext()
+        s.tiles_touched, s.radii, s.depths = _lib.ptr(tiles_touched), _lib.ptr(radii), _lib.ptr(depths)
+        s.uvs, s.conic_opacity, s.rgb_gaussian = _lib.ptr(uvs), _lib.ptr(conic_opacity), _lib.ptr(rgb)
+        s.cov2d_vecs, s.sh_to_rgb_ne_0 = _lib.ptr(cov2d), _lib.ptr(ne0)
+        return s
+
+    # ---- forward (render.py:169-1015) ---------------------------------------------------------
+    def forward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
+                training: bool = False, instance2world_T: torch.Tensor | None = None,
+                custom_features: torch.Tensor | None = None, mask: torch.Tensor | None = None,
+                prep_user_inputs: dict[str, Any] | None = None):
+        assert model.act_applied, "model must be activated before render"
+        if instance2world_T is not None or custom_features is not None or prep_user_inputs is not None:
+            raise NotImplementedError("instance transforms, custom features and proxy inputs are not built")
+        lib = self._lib
+        dev = model.xyz.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        num = len(model)
+        ocfg = self._op_config(model, cameras, training)
+        B, W, H = ocfg.num_views, ocfg.width, ocfg.height
+        BN = B * num
+        tiles_x, tiles_y = div_up(W, 16), div_up(H, 16)
+        num_tiles = B * tiles_x * tiles_y
+        i32, f32 = torch.int32, torch.float32
+        depths = torch.empty(BN, dtype=f32, device=dev)
+        radii = torch.empty(BN, dtype=i32, device=dev)
+        uvs = torch.empty([BN, 2], dtype=f32, device=dev)
+        conic_opacity = torch.empty([BN, 4], dtype=f32, device=dev)
+        rgb_gaussian = torch.empty([BN, 3], dtype=f32, device=dev)
+        cov2d_vecs = torch.empty([BN, 3], dtype=f32, device=dev) if training else None
+        sh_ne0 = torch.empty([BN], dtype=torch.uint8, device=dev) if training else None
+        tiles_touched = torch.empty(BN, dtype=i32, device=dev)
+        mstruct = self._model_struct(model)
+        cstruct = self._ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb_gaussian, cov2d_vecs, sh_ne0)
+        mask_u8 = None
+        if mask is not None:
+            mask_u8 = mask.to(torch.uint8).contiguous()
+            assert mask_u8.numel() == BN
+        _lib.check(lib.d3gs_preprocess_forward(C.byref(ocfg), C.byref(mstruct), _lib.ptr(mask_u8), C.byref(cstruct),
+                                               stream), "d3gs_preprocess_forward")
+        if self.debug_capture:
+            self.debug = {"tiles_touched": tiles_touched.clone()}
+        # cumsum + total (render.py:694-695): one device->host read per forward, as in the reference
+        sync = self._sync_words(dev)
+        ws_scan = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(BN), dev)
+        _lib.check(lib.d3gs_scan_tiles(tiles_touched.data_ptr(), tiles_touched.data_ptr(), BN, sync.data_ptr(),
+                                       ws_scan.data_ptr(), ws_scan.numel(), sync.data_ptr() + 8, stream),
+                   "d3gs_scan_tiles")
+        num_rendered, status = (int(v) for v in sync.tolist())
+        if status != 0:
+            sync[1] = 0
+            raise RuntimeError(f"d3gs_b200 device status {status:#x}: a bounded wait gave up "
+                               "(1 scan, 2 sort, 4 bulk copy); results of the previous call are invalid")
+        if num_rendered >= 2 ** 31:
+            raise RuntimeError(f"num_rendered {num_rendered} does not fit the int32 offsets")
+        self.last_num_rendered = num_rendered
+        final_T = torch.empty([B, H, W], dtype=f32, device=dev)
+        n_contrib = torch.empty([B, H, W], dtype=i32, device=dev)
+        out_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
+        if num_rendered == 0:   # render.py:706-729: outputs are left uninitialised, no context
+            return GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
+                                       n_contrib=n_contrib), None
+        keys = torch.empty(num_rendered, dtype=torch.int64, device=dev)
+        keys_alt = torch.empty_like(keys)
+        gaussian_idx = torch.empty(num_rendered, dtype=i32, device=dev)
+        gaussian_idx_alt = torch.empty_like(gaussian_idx)
+        _lib.check(lib.d3gs_duplicate_keys(C.byref(ocfg), num, tiles_touched.data_ptr(), C.byref(cstruct),
+                                           keys.data_ptr(), gaussian_idx.data_ptr(), stream), "d3gs_duplicate_keys")
+        if self.debug_capture:
+            self.debug.update(scan=tiles_touched.clone(), keys=keys.clone(), values=gaussian_idx.clone())
+        end_bit = 32 + lib.d3gs_bit_length(num_tiles)                       # render.py:851-852
+        ws_sort = self._ws.get("sort", lib.d3gs_sort_workspace_bytes(num_rendered, 0, end_bit), dev)
+        in_alt = C.c_int32(0)
+        _lib.check(lib.d3gs_sort_pairs(keys.data_ptr(), keys_alt.data_ptr(), gaussian_idx.data_ptr(),
+                                       gaussian_idx_alt.data_ptr(), num_rendered, 0, end_bit, ws_sort.data_ptr(),
+                                       ws_sort.numel(), C.byref(in_alt), sync.data_ptr() + 8, stream),
+                   "d3gs_sort_pairs")
+        if in_alt.value:                                                    # render.py:884-887
+            keys, keys_alt = keys_alt, keys
+            gaussian_idx, gaussian_idx_alt = gaussian_idx_alt, gaussian_idx
+        gaussian_idx_sorted = gaussian_idx
+        if self.debug_capture:
+            self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted)
+        workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
+        _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles, stream),
+                   "d3gs_tile_ranges")
+        records = torch.empty([num_rendered, 12], dtype=f32, device=dev)
+        _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
+                                        float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")
+        _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), records.data_ptr(),
+                                           out_color.data_ptr(), final_T.data_ptr(), n_contrib.data_ptr(),
+                                           sync.data_ptr() + 8, stream), "d3gs_raster_forward")
+        output = GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
+                                     n_contrib=n_contrib, radii=radii)
+        if not training:
+            return output, None
+        ctx = GaussianSplatOpContext(conic_opacity=conic_opacity, radii=radii, uvs=uvs, rgb_gaussian=rgb_gaussian,
+                                     gaussian_idx_sorted=gaussian_idx_sorted, workload_ranges=workload_ranges,
+                                     image_shape_wh=(W, H), depths=depths, cov2d_vecs=cov2d_vecs,
+                                     sh_to_rgb_ne_0=sh_ne0, splat_records=records)
+        return output, ctx
+
+    # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
+    def rasterize_forward_backward(self, model, ctx: GaussianSplatOpContext, out: GaussianSplatOutput,
+                                   grad: GaussianSplatGradients | None = None, training: bool = False,
+                                   render_depth: bool = False, custom_features: torch.Tensor | None = None,
+                                   cameras=None):
+        if grad is None:
+            raise NotImplementedError("forward rasterisation is part of GaussianSplatOp.forward")
+        lib = self._lib
+        dev = out.T.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        B, H, W = out.T.shape
+        BN = ctx.depths.shape[0]
+        num = BN // B
+        drgb = grad.drgb
+        assert drgb.is_contiguous(), "drgb must be contiguous"
+        f32 = torch.float32
+        duv = torch.empty([BN, 2], dtype=f32, device=dev)
+        dconic = torch.empty([BN, 3], dtype=f32, device=dev)
+        dopacity = torch.empty([BN], dtype=f32, device=dev)
+        dcolor = torch.empty([BN, 3], dtype=f32, device=dev)
+        ocfg = _lib.OpConfig()
+        ocfg.width, ocfg.height, ocfg.tile_x, ocfg.tile_y = W, H, 16, 16
+        ocfg.alpha_eps, ocfg.transmittance_eps = self._cfg.alpha_eps, self._cfg.transmittance_eps
+        ocfg.num_views, ocfg.training = B, 1
+        sync = self._sync_words(dev)
+        dT = grad.dT
+        if dT is not None:
+            dT = dT.contiguous()
+        _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
+                                            ctx.splat_records.data_ptr(), out.color.data_ptr(), out.T.data_ptr(),
+                                            out.n_contrib.data_ptr(), drgb.data_ptr(), _lib.ptr(dT), duv.data_ptr(),
+                                            dconic.data_ptr(), dopacity.data_ptr(), dcolor.data_ptr(),
+                                            sync.data_ptr() + 8, stream), "d3gs_raster_backward")
+        return RasterizeGradientOutput(duv=duv, dconic=dconic, dopacity=dopacity, dcolor=dcolor)
+
+    # ---- backward (render.py:2779-3374) --------------------------------------------------------
+    def backward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
+                 ctx: GaussianSplatOpContext, out: GaussianSplatOutput, grad: GaussianSplatGradients,
+                 return_uv_grad: bool = False, instance2world_T: torch.Tensor | None = None,
+                 custom_features: torch.Tensor | None = None, prep_user_inputs: dict[str, Any] | None = None,
+                 grad_out: "GaussianModelOriginBase | None" = None):
+        """Returns ``(grad_model, duv | None, dcustom_features)`` like the reference.
+
+        ``grad_out`` (not in the reference) lets the caller supply the gradient container, e.g. views of
+        a persistent flat buffer that is all-reduced across ranks.
+        """
+        lib = self._lib
+        rg = self.rasterize_forward_backward(model, ctx, out, grad, training=True)
+        dev = model.xyz.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ocfg = self._op_config(model, cameras, True)
+        B = ocfg.num_views
+        num = len(model)
+        if grad_out is None:
+            if model.flat is not None or (model.color_sh_base is not None and model.color_sh.shape[1] == 15):
+                flat = torch.empty(59 * num, dtype=torch.float32, device=dev)
+                grad_out = type(model)(**carve_flat(flat, num), cur_sh_degree=model.cur_sh_degree, act_applied=True,
+                                       flat=flat)
+            else:
+                t = {k: torch.empty_like(v) for k, v in model.get_all_tensor_fields().items() if v.is_floating_point()}
+                if model.color_sh_base is None:
+                    t["color_sh_base"] = None
+                grad_out = type(model)(**t, cur_sh_degree=model.cur_sh_degree, act_applied=True)
+        g = _lib.ModelGrad()
+        g.xyz, g.quaternion_xyzw = grad_out.xyz.data_ptr(), grad_out.quaternion_xyzw.data_ptr()
+        g.scale, g.opacity = grad_out.scale.data_ptr(), grad_out.opacity.data_ptr()
+        k = grad_out.color_sh.shape[1]
+        if grad_out.color_sh_base is not None:
+            g.sh_base, g.sh_base_stride = grad_out.color_sh_base.data_ptr(), 3
+            g.sh_rest, g.sh_rest_stride, g.sh_rest_floats = grad_out.color_sh.data_ptr(), k * 3, k * 3
+        else:
+            g.sh_base, g.sh_base_stride = grad_out.color_sh.data_ptr(), k * 3
+            g.sh_rest, g.sh_rest_stride, g.sh_rest_floats = grad_out.color_sh.data_ptr() + 12, k * 3, k * 3 - 3
+        mstruct = self._model_struct(model)
+        cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
+                                   ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
+        _lib.check(lib.d3gs_preprocess_backward(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct), rg.duv.data_ptr(),
+                                                rg.dconic.data_ptr(), rg.dopacity.data_ptr(), rg.dcolor.data_ptr(),
+                                                C.byref(g), stream), "d3gs_preprocess_backward")
+        if return_uv_grad:
+            return grad_out, rg.duv.view(B, -1, 2), None
+        return grad_out, None, None
+
+
+class _RasterizeGaussians(torch.autograd.Function):
+    """Autograd glue with the reference's 18 forward arguments and 6 outputs (render.py:3376-3587).
+
+    Saved state is keyed by name on ``ctx`` for non-tensors and by a fixed tuple for tensors; the
+    reference's positional read-back of its saved tensors is not reproduced.
+    """
+
+    @staticmethod
+    def forward(ctx, xyz, color_sh, color_sh_base, scale, quaternion_xyzw, opacity, cur_sh_degree, instance_id,
+                custom_features, mask, model_cls, camera_params, cam2world_T, frame_ids, instance2world_T, training,
+                op: GaussianSplatOp, uv_grad_holder=None):
+        if isinstance(camera_params, CameraParamBundle) and not isinstance(camera_params, CameraBundle):
+            cams = CameraBundle(camera_params.focal_xy_ppoint, camera_params.image_shape_wh, frame_ids, cam2world_T)
+        else:
+            cams = camera_params
+        model = model_cls(xyz=xyz.detach(), color_sh=color_sh.detach(),
+                          color_sh_base=None if color_sh_base is None else color_sh_base.detach(),
+                          scale=scale.detach(), quaternion_xyzw=quaternion_xyzw.detach(), opacity=opacity.detach(),
+                          cur_sh_degree=cur_sh_degree, instance_id=instance_id, act_applied=True)
+        out, fwd_ctx = op.forward(model, cams, training, instance2world_T, custom_features, mask)
+        ctx.has_ctx = fwd_ctx is not None
+        if fwd_ctx is not None:
+            ctx.fwd_ctx = fwd_ctx
+            ctx.out = out
+            ctx.model = model
+            ctx.cams = cams
+        ctx.op = op
+        ctx.return_uv_grad = uv_grad_holder is not None
+        radii = out.radii if out.radii is not None else torch.zeros(0, dtype=torch.int32, device=xyz.device)
+        ctx.mark_non_differentiable(out.n_contrib, radii)
+        return out.color, out.depth, out.custom_features, out.T, out.n_contrib, radii
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, drgb, ddepth, dcustom_features, dT, dn_contrib, dradii):
+        if not ctx.has_ctx:
+            return (None,) * 18
+        op: GaussianSplatOp = ctx.op
+        if drgb is None:
+            drgb = torch.zeros_like(ctx.out.color)
+        if not drgb.is_contiguous():
+            drgb = drgb.contiguous()
+        gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=None, dcustom_features=None)
+        gm, duv, _ = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad)
+        return (gm.xyz, gm.color_sh, gm.color_sh_base, gm.scale, gm.quaternion_xyzw, gm.opacity, None, None, None,
+                None, None, None, None, None, None, None, None, duv)
+
+
+def rasterize_gaussians(model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
+                        op: GaussianSplatOp, training=False, uv_grad_holder: torch.Tensor | None = None,
+                        instance2world_T: torch.Tensor | None = None, custom_features: torch.Tensor | None = None,
+                        mask: torch.Tensor | None = None) -> GaussianSplatOutput:
+    """render.py:3783-3838."""
+    model = model.create_model_with_act()
+    c2w_t = frame_ids = None
+    if isinstance(cameras, CameraBundle):
+        c2w_t, frame_ids = cameras.cam2world_T, cameras.frame_ids
+    res = _RasterizeGaussians.apply(model.xyz, model.color_sh, model.color_sh_base, model.scale,
+                                    model.quaternion_xyzw, model.opacity, model.cur_sh_degree, model.instance_id,
+                                    custom_features, mask, type(model), cameras, c2w_t, frame_ids, instance2world_T,
+                                    training, op, uv_grad_holder)
+    return GaussianSplatOutput(color=res[0], depth=res[1], custom_features=res[2], T=res[3], n_contrib=res[4],
+                               radii=res[5])
+
+
+def rasterize_gaussians_dynamic(model, cameras, op: GaussianSplatOp, training=False, uv_grad_holder=None,
+                                instance2world_T=None, custom_features=None, prep_input_tensors=None,
+                                prep_inputs=None, mask=None) -> GaussianSplatOutput:
+    """render.py:3840-3891.  The proxy extension inputs are not built; without them this is
+    ``rasterize_gaussians``."""
+    if prep_input_tensors is not None or prep_inputs is not None:
+        raise NotImplementedError("user-defined proxy inputs are not built")
+    return rasterize_gaussians(model, cameras, op, training, uv_grad_holder, instance2world_T, custom_features, mask)

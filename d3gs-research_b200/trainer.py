@@ -1,0 +1,163 @@
+"""One training iteration of 3D Gaussian splatting as a fused sequence of library calls.
+
+``SplatTrainer.step`` performs what the reference's ``Trainer.train`` loop body does per iteration
+(d3sim/algos/d3gs/train.py:162-217): rasterize (training) -> 0.8*L1 + 0.2*(1-SSIM) -> backward ->
+Adam on the six parameter tensors -> densification statistics.  It drives the operator directly
+(no autograd graph), keeps the 59-float-per-Gaussian gradient in one flat buffer, and issues Adam
+plus statistics as one launch.
+
+Data-parallel over views (one process per GPU, ``torch.distributed`` NCCL): every rank holds the full
+Gaussian set and renders its own camera.  The reference's batch semantics are kept exactly: its loss
+is a mean over B*C*H*W (train.py:170-172), so every per-view gradient carries 1/B and the per-Gaussian
+gradient of the batch is the plain sum over views (render.py:3182-3199, origin/model.py:422-431).
+Here each rank scales its loss gradient by 1/world_size and the flat gradient buffer is all-reduced
+(sum) between the preprocess backward and the Adam launch.  Optimizer hyper-parameters are scaled with
+the global batch like tools.py:146-163.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib, config_def
+from .adam import _launch as _launch_adam
+from .adam import make_stats_struct
+from .fused_ssim import l1_dssim_forward_backward
+from .model import FLAT_ORDER, GaussianModelOriginBase, carve_flat, flat_field_sizes
+from .render import GaussianSplatGradients, GaussianSplatOp
+from .strategy import GaussianTrainState
+from .tools import get_expon_lr_func
+
+
+class SplatTrainer:
+    def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
+                 lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
+                 spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False):
+        """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs)."""
+        assert model.has_fused_activations, "the trainer drives the fused-activation model"
+        assert model.color_sh_base is not None and model.color_sh.shape[1] == 15, "degree-3 split SH layout"
+        self.model = model
+        if model.flat is None:
+            # move the parameters into one flat buffer; the model's tensors become views of it
+            n = len(model)
+            flat = torch.empty(59 * n, dtype=torch.float32, device=model.xyz.device)
+            views = carve_flat(flat, n)
+            for k in FLAT_ORDER:
+                views[k].copy_(getattr(model, k).detach())
+                setattr(model, k, views[k])
+            model.flat = flat
+        self.op = GaussianSplatOp(op_cfg)
+        self.lambda_dssim = float(lambda_dssim)
+        self.batch_size = int(batch_size)
+        self.pg = process_group
+        self.world = 1
+        if process_group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            self.world = torch.distributed.get_world_size(process_group)
+        self.need_max_radii = need_max_radii
+        n, dev = len(model), model.xyz.device
+        self.grad_flat = torch.zeros(59 * n, dtype=torch.float32, device=dev)
+        self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
+                                      act_applied=True, flat=self.grad_flat)
+        self.exp_avg = torch.zeros(59 * n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(59 * n, dtype=torch.float32, device=dev)
+        self.state = GaussianTrainState.create(n, device=dev)
+        oc = optim_cfg or config_def.Optimizer()
+        bs = math.sqrt(self.batch_size)                              # tools.py:147-163
+        self.lrs = {"xyz": oc.position_lr_init * spatial_lr_scale * bs, "color_sh_base": oc.feature_lr * bs,
+                    "color_sh": oc.feature_lr * bs / 20.0, "opacity": oc.opacity_lr * bs, "scale": oc.scaling_lr * bs,
+                    "quaternion_xyzw": oc.rotation_lr * bs}
+        self.eps = 1e-15 / bs
+        self.betas = (1 - self.batch_size * (1 - 0.9), 1 - self.batch_size * (1 - 0.999))
+        self.xyz_schedule = get_expon_lr_func(lr_init=oc.position_lr_init * spatial_lr_scale * bs,
+                                              lr_final=oc.position_lr_final * spatial_lr_scale * bs,
+                                              lr_delay_mult=oc.position_lr_delay_mult,
+                                              max_steps=oc.position_lr_max_steps)
+        self.use_xyz_schedule = False
+        self.step_count = 0
+        self._loss_scratch = None
+        self._loss_sums = torch.zeros(2, dtype=torch.float64, device=dev)
+        self._dcolor = None
+        self._offsets = {}
+        off = 0
+        for name in FLAT_ORDER:
+            cnt, _ = flat_field_sizes(n)[name]
+            self._offsets[name] = (off, cnt)
+            off += cnt
+
+    # ------------------------------------------------------------------------------------------
+    def _adam_segments(self):
+        self.step_count += 1
+        t = float(self.step_count)
+        b1, b2 = self.betas
+        bc1 = 1.0 - math.pow(b1, t)
+        bc2s = math.sqrt(1.0 - math.pow(b2, t))
+        if self.use_xyz_schedule:
+            self.lrs["xyz"] = float(self.xyz_schedule(self.step_count))   # train.py:286-292
+        segs = []
+        esz = 4
+        for name in FLAT_ORDER:
+            off, cnt = self._offsets[name]
+            s = _lib.AdamSegment()
+            s.param = self.model.flat.data_ptr() + off * esz
+            s.grad = self.grad_flat.data_ptr() + off * esz
+            s.exp_avg = self.exp_avg.data_ptr() + off * esz
+            s.exp_avg_sq = self.exp_avg_sq.data_ptr() + off * esz
+            s.count = cnt
+            s.lr, s.beta1, s.beta2, s.eps = float(self.lrs[name]), b1, b2, self.eps
+            s.bias_correction1, s.bias_correction2_sqrt = bc1, bc2s
+            s.grad_scale, s.weight_decay = 1.0, 0.0
+            segs.append(s)
+        return segs
+
+    @torch.no_grad()
+    def step(self, cameras, target_nchw: torch.Tensor, update: bool = True) -> dict:
+        """One iteration on this rank's view(s).  Returns ``{"out", "loss" (lazy), "num_rendered"}``."""
+        model = self.model
+        model.act_applied = True
+        out, ctx = self.op.forward(model, cameras, training=True)
+        if ctx is None:   # nothing visible: zero gradient, still take part in the collective
+            self.grad_flat.zero_()
+            loss = None
+            duv = None
+        else:
+            b, h, w, _ = out.color.shape
+            nbytes = 3 * b * 3 * h * w * 4
+            if self._loss_scratch is None or self._loss_scratch.numel() < nbytes:
+                self._loss_scratch = torch.empty(nbytes, dtype=torch.uint8, device=out.color.device)
+            if self._dcolor is None or self._dcolor.shape != out.color.shape:
+                self._dcolor = torch.empty_like(out.color)
+            # the loss of a data-parallel batch is the mean over all ranks' views: 1/world per rank
+            loss, dcolor = l1_dssim_forward_backward(out.color, target_nchw, self.lambda_dssim,
+                                                     grad_scale=1.0 / self.world, scratch=self._loss_scratch,
+                                                     sums=self._loss_sums, dcolor=self._dcolor)
+            _, duv, _ = self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
+                                         return_uv_grad=True, grad_out=self.grad_model)
+        if self.world > 1:
+            torch.distributed.all_reduce(self.grad_flat, group=self.pg)
+        if update:
+            stats = None
+            if duv is not None:
+                w, h = out.image_shape_wh
+                stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
+                                          loss_batch=duv.shape[0] * self.world)
+            _launch_adam(self._adam_segments(), stats, model.xyz.device)
+        return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
+
+    @torch.no_grad()
+    def render(self, cameras) -> "torch.Tensor":
+        """Forward-only rendering (inference mode: background composited, clamped)."""
+        self.model.act_applied = True
+        out, _ = self.op.forward(self.model, cameras, training=False)
+        return out
+
+    def reduce_stats(self):
+        """All-reduce the densification statistics (each rank accumulates its own views' share)."""
+        if self.world > 1:
+            torch.distributed.all_reduce(self.state.duv_ndc_length, group=self.pg)
+            torch.distributed.all_reduce(self.state.count, group=self.pg)
+            torch.distributed.all_reduce(self.state.max_radii, op=torch.distributed.ReduceOp.MAX, group=self.pg)
+
+    def parameter_checksum(self) -> torch.Tensor:
+        """Sum of the raw parameter bits; replicas must agree after every update."""
+        return self.model.flat.view(torch.int32).sum(dtype=torch.int64)

@@ -1,0 +1,232 @@
+/*
+ * d3gs_b200 -- C ABI of the B200 (sm_100a) 3D-Gaussian-splatting training-step library.
+ *
+ * Every entry point replaces one device launch site of the reference operator
+ * (d3sim/algos/d3gs/render.py, d3sim/ops/image/fused_ssim.py, d3sim/ops/optim/adam.py,
+ * d3sim/algos/d3gs/origin/strategy.py) or the reference's one native module
+ * (d3sim/csrc/devsort.py).  The reference launches its kernels through cumm's
+ * `inliner.kernel_raw/kernel_1d` on torch's current stream with torch-allocated tensors
+ * (render.py:676-681, 839-840, 883); the same contract holds here:
+ *
+ *   - all buffers are caller-owned device memory (plain pointers + element counts);
+ *     the library never allocates or frees, workspaces are sized by *_workspace_bytes();
+ *   - every call is asynchronous on the CUDA stream passed as `stream` (a cudaStream_t);
+ *   - return value 0 = success, negative = error; d3gs_last_error() returns the message of the
+ *     calling thread's last failure.  Device-side problems (a bounded wait that gave up) are
+ *     reported through the `status` word the caller passes, never by trapping.
+ *
+ * Flat indexing over a view batch follows render.py:317-318, 757: i = view * num + gaussian.
+ */
+#ifndef D3GS_B200_H_
+#define D3GS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define D3GS_MAX_VIEWS 8          /* views per launch (CameraBundle batch, render.py:129-150) */
+#define D3GS_SPLAT_RECORD_FLOATS 12
+
+/* error codes */
+#define D3GS_OK 0
+#define D3GS_ERR_INVALID_ARGUMENT (-1)
+#define D3GS_ERR_CUDA (-2)
+#define D3GS_ERR_UNSUPPORTED (-3)
+
+/* device status word bits (written by kernels whose bounded waits ran out) */
+#define D3GS_STATUS_SCAN_TIMEOUT 1u
+#define D3GS_STATUS_SORT_TIMEOUT 2u
+#define D3GS_STATUS_COPY_TIMEOUT 4u
+
+/* One pinhole camera: cam2world[:3].T flattened ([4,3]: rows 0..2 are the columns of the
+ * camera-to-world rotation, row 3 the camera centre; render.py:136, 205-206) and intrinsics. */
+typedef struct D3gsCamera {
+    float cam2world_T[12];
+    float fx, fy, cx, cy;
+} D3gsCamera;
+
+/* Scalar options of the operator; names and defaults follow GaussianSplatConfig
+ * (d3sim/algos/d3gs/config_def.py:77-161). */
+typedef struct D3gsOpConfig {
+    int32_t width, height;
+    int32_t tile_x, tile_y;                 /* 16 x 16 only */
+    float near_plane, far_plane;            /* near / far */
+    float eps;                              /* 1e-6, conic determinant guard */
+    float cov2d_radii_eigen_eps;            /* 0.1 */
+    float projected_clamp_factor;           /* 1.3 */
+    float gaussian_std_sigma;               /* 3.0 */
+    float gaussian_lowpass_filter;          /* 0.3 */
+    float alpha_eps;                        /* 1/255 */
+    float transmittance_eps;                /* 1e-4 */
+    float scale_global;                     /* inference only */
+    int32_t early_filter_algo;              /* EarlyFilterAlgo: 0 NONE, 1 AABB, 3 OBB, 4 OBB_DFVT */
+    int32_t sh_degree;                      /* active degree 0..3 (model.cur_sh_degree) */
+    int32_t training;
+    int32_t clamp_mask_reference_order;     /* 1: gate dcolor like render.py:3344-3350 */
+    int32_t fused_activations;              /* 1: normalize/exp/sigmoid applied in-kernel (GaussianModelOriginFused,
+                                               origin/model.py:453-462); 0: tensors are already activated */
+    float bg_color[3];
+    int32_t num_views;                      /* B */
+    D3gsCamera cameras[D3GS_MAX_VIEWS];
+} D3gsOpConfig;
+
+/* Gaussian parameters in the reference model layout (origin/model.py:36-44).  `sh_base` /
+ * `sh_rest` with strides (in floats per Gaussian) cover both the split layout
+ * (color_sh_base[N,3] + color_sh[N,15,3]) and the un-split one (color_sh[N,16,3]). */
+typedef struct D3gsModel {
+    int64_t num;
+    const float* xyz;               /* [N,3] */
+    const float* quaternion_xyzw;   /* [N,4] raw; normalised in-kernel */
+    const float* scale;             /* [N,3] log-scale */
+    const float* opacity;           /* [N]   logit */
+    const float* sh_base;           /* l=0 coefficients */
+    const float* sh_rest;           /* l>=1 coefficients, coefficient-major [.,3] */
+    int32_t sh_base_stride;
+    int32_t sh_rest_stride;
+} D3gsModel;
+
+typedef struct D3gsModelGrad {
+    float* xyz;
+    float* quaternion_xyzw;
+    float* scale;
+    float* opacity;
+    float* sh_base;
+    float* sh_rest;
+    int32_t sh_base_stride;
+    int32_t sh_rest_stride;
+    int32_t sh_rest_floats;         /* floats of l>=1 coefficients stored per Gaussian (45 for degree 3);
+                                       those above the active degree are written as zero */
+    int32_t reserved;
+} D3gsModelGrad;
+
+/* Per-(view,Gaussian) context written by the preprocess and consumed downstream
+ * (GaussianSplatOpContext, render.py:57-72; allocation render.py:641-665). */
+typedef struct D3gsSplatContext {
+    int32_t* tiles_touched;   /* [B*N] */
+    int32_t* radii;           /* [B*N] */
+    float* depths;            /* [B*N] */
+    float* uvs;               /* [B*N,2] */
+    float* conic_opacity;     /* [B*N,4] */
+    float* rgb_gaussian;      /* [B*N,3] */
+    float* cov2d_vecs;        /* [B*N,3] training only, may be NULL */
+    uint8_t* sh_to_rgb_ne_0;  /* [B*N]   training only, may be NULL */
+} D3gsSplatContext;
+
+/* ---- helpers -------------------------------------------------------------------------- */
+const char* d3gs_version(void);
+/* copies the calling thread's last error message; returns its length */
+size_t d3gs_last_error(char* buf, size_t cap);
+/* DeviceSort.get_higher_msb (csrc/devsort.py:129-149): number of bits needed for n */
+int32_t d3gs_bit_length(uint32_t n);
+/* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
+ * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment */
+size_t d3gs_struct_size(int32_t which);
+
+/* ---- K1 preprocess forward (render.py:250-681) ------------------------------------------- */
+/* mask: optional [B*N] bytes, non-zero = skip (render.py:306-309) */
+int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsModel* model, const uint8_t* mask,
+                                const D3gsSplatContext* ctx, void* stream);
+
+/* ---- K2 inclusive scan of tile counts (tiles_touched.cumsum_(0), render.py:694-695) ------ */
+size_t d3gs_scan_workspace_bytes(int64_t n);
+/* out may alias in.  total[0] (device int64) receives the last element = num_rendered. */
+int32_t d3gs_scan_tiles(const int32_t* in, int32_t* out, int64_t n, int64_t* total, void* workspace,
+                        size_t workspace_bytes, uint32_t* status, void* stream);
+
+/* ---- K3 key duplication (render.py:739-840) ---------------------------------------------- */
+/* key = (view*tiles + y*tiles_x + x) << 32 | float_bits(depth); value = flat index i */
+int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, const int32_t* scan, const D3gsSplatContext* ctx,
+                            uint64_t* keys, int32_t* values, void* stream);
+
+/* ---- K4 radix sort (DeviceSort, csrc/devsort.py:26-127) ---------------------------------- */
+size_t d3gs_sort_workspace_bytes(int64_t n, int32_t begin_bit, int32_t end_bit);
+/* Stable LSD radix sort of (uint64 key, int32 value) pairs on bits [begin_bit,end_bit), ping-ponging
+ * between the two buffer pairs like cub::DoubleBuffer.  *result_in_alt = 1 when the sorted data
+ * ended in keys_alt/values_alt (the reference's key_swap/value_swap, render.py:884-887). */
+int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int32_t* values_alt, int64_t n,
+                        int32_t begin_bit, int32_t end_bit, void* workspace, size_t workspace_bytes,
+                        int32_t* result_in_alt, uint32_t* status, void* stream);
+
+/* ---- K5 tile ranges (render.py:896-939) --------------------------------------------------- */
+/* ranges [num_tiles,2] int32 is zero-filled by this call, then [start,end) written per tile */
+int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges, int64_t num_tiles, void* stream);
+
+/* ---- staging for the rasteriser: gather splats into sorted, contiguous 48-byte records ------
+ * (replaces the per-batch gathers of render.py:1702-1716; lets the raster kernels stream their
+ * tile's list with bulk async copies).  records: [n, 12] floats, 16-byte aligned. */
+int32_t d3gs_pack_splats(const int32_t* sorted_values, int64_t n, const D3gsSplatContext* ctx, float alpha_eps,
+                         float* records, void* stream);
+
+/* ---- K6 raster forward (render.py:1329-2316, is_bwd=False) ------------------------------- */
+/* color [B,H,W,3] (NHWC), final_T [B,H,W], n_contrib [B,H,W] */
+int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const float* records, float* color,
+                            float* final_T, int32_t* n_contrib, uint32_t* status, void* stream);
+
+/* ---- K7 raster backward (render.py:1589-1676, 1774-2210) -------------------------------- */
+/* drgb [B,H,W,3], dT [B,H,W] or NULL; outputs [B*N,*] are zero-filled by this call */
+int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const float* records,
+                             const float* color, const float* final_T, const int32_t* n_contrib,
+                             const float* drgb, const float* dT, float* duv, float* dconic, float* dopacity,
+                             float* dcolor, uint32_t* status, void* stream);
+
+/* ---- K8 preprocess backward (render.py:2779-3374) ---------------------------------------- */
+/* every gradient element is written (zeros for culled Gaussians); sums over the view batch */
+int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
+                                 const float* duv, const float* dconic, const float* dopacity,
+                                 const float* dcolor, const D3gsModelGrad* grad, void* stream);
+
+/* ---- K9/K10 SSIM map and fused L1 + D-SSIM (fused_ssim.py:93-416, losses.py:19-20) ---------- */
+/* ssim map forward: x NHWC or NCHW [B,3,H,W]/[B,H,W,3], y NCHW; outputs NCHW; dmu* may be NULL */
+int32_t d3gs_ssim_forward(const float* x, const float* y, int32_t batch, int32_t height, int32_t width,
+                          int32_t x_is_nhwc, float* ssim_map, float* dmu1, float* dmu11, float* dmu12,
+                          void* stream);
+int32_t d3gs_ssim_backward(const float* dssim_map, const float* dmu1, const float* dmu11, const float* dmu12,
+                           const float* x, const float* y, int32_t batch, int32_t height, int32_t width,
+                           int32_t x_is_nhwc, float* dx, void* stream);
+/* loss = (1-lambda)*mean|x-y| + lambda*(1-mean(SSIM)) for x NHWC (the op's colour) and y NCHW;
+ * sums[0..1] (device doubles: sum|x-y|, sum SSIM) are zeroed and accumulated; dx NHWC receives
+ * grad_scale * dloss/dx.  scratch: 3*B*3*H*W floats. */
+size_t d3gs_l1_dssim_scratch_bytes(int32_t batch, int32_t height, int32_t width);
+int32_t d3gs_l1_dssim_forward_backward(const float* x, const float* y, int32_t batch, int32_t height,
+                                       int32_t width, float lambda_dssim, float grad_scale, double* sums,
+                                       float* dx, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- K11 + K12 fused Adam and densification statistics ------------------------------------
+ * (adam.py:32-148, 382-418; csrc/optim.py:22-49; origin/strategy.py:93-122) */
+typedef struct D3gsAdamSegment {
+    float* param;
+    const float* grad;
+    float* exp_avg;
+    float* exp_avg_sq;
+    int64_t count;
+    float lr, beta1, beta2, eps;
+    float bias_correction1, bias_correction2_sqrt;   /* host doubles rounded to float, adam.py:55-57 */
+    float grad_scale, weight_decay;
+} D3gsAdamSegment;
+
+typedef struct D3gsDensifyStats {
+    const float* duv;          /* [B,N,2] */
+    const int32_t* radii;      /* [B*N] */
+    float* duv_ndc_length;     /* [N] */
+    float* count;              /* [N] */
+    float* max_radii;          /* [N] */
+    int64_t num;
+    int32_t batch, width, height, need_max_radii;
+    int32_t loss_batch;        /* views the loss was averaged over (duv is scaled back by it,
+                                  origin/strategy.py:105-106); 0 = same as batch.  Larger than batch when the
+                                  view batch is spread over several GPUs. */
+    int32_t reserved;
+} D3gsDensifyStats;
+
+/* one launch over up to 8 parameter tensors; stats may be NULL */
+int32_t d3gs_adam_stats_step(const D3gsAdamSegment* segments, int32_t num_segments, const D3gsDensifyStats* stats,
+                             void* stream);
+int32_t d3gs_densify_stats(const D3gsDensifyStats* stats, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* D3GS_B200_H_ */

@@ -88,12 +88,13 @@ class OpConfig:
     training: bool = True
     scale_global: float = 1.0
     clamp_mask_reference_order: bool = True
+    fused_activations: bool = True
 
     def vec(self) -> np.ndarray:
         return np.array([self.width, self.height, self.tile, self.near, self.far, self.eps, self.eigen_eps,
                          self.clamp_factor, self.sigma, self.lowpass, self.alpha_eps, self.t_eps,
                          self.early_filter, self.sh_degree, int(self.training), self.scale_global,
-                         int(self.clamp_mask_reference_order), 0, 0, 0], dtype=np.float32)
+                         int(self.clamp_mask_reference_order), int(self.fused_activations), 0, 0], dtype=np.float32)
 
     @property
     def tiles_xy(self):

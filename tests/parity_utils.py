@@ -1,0 +1,74 @@
+"""Shared helpers of the parity tests: build the same seeded scene for the CPU oracle and the GPU library."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import d3gs_research_b200 as d3
+from d3gs_research_b200 import scenes
+from oracle import oracle as O
+
+
+def small_scene(n=2000, width=160, height=112, sh_degree=3, seed=0, views=1, log_scale=("normal", -2.6, 0.6),
+                pos=("uniform", 3.0), cam_radius=9.0, base="cfg1", sh_gain=4.0):
+    b = scenes.CONFIGS[base]
+    cfg = scenes.SceneConfig(**{**b.__dict__, "n": n, "width": width, "height": height, "sh_degree": sh_degree,
+                                "log_scale": log_scale, "pos": pos, "cam_radius": cam_radius, "num_views": views,
+                                "cam_layout": "sphere" if views > 1 else b.cam_layout})
+    sc = scenes.make_scene(cfg, seed=seed)
+    if sh_degree > 0:
+        sc["sh_rest"] = (sc["sh_rest"] * sh_gain).contiguous()
+    return sc
+
+
+def oracle_scene(sc) -> O.Scene:
+    return O.Scene(*(sc[k].numpy().copy() for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")),
+                   cams=np.ascontiguousarray(sc["cams"]).copy())
+
+
+def oracle_cfg(sc, op_cfg: "d3.GaussianSplatConfig", training=True) -> O.OpConfig:
+    c = sc["cfg"]
+    return O.OpConfig(width=c.width, height=c.height, sh_degree=c.sh_degree, early_filter=int(op_cfg.early_filter_algo),
+                      training=training, clamp_mask_reference_order=op_cfg.clamp_mask_reference_order,
+                      near=op_cfg.near, far=op_cfg.far, scale_global=op_cfg.scale_global)
+
+
+def gpu_model(sc, device, flat=True, requires_grad=False):
+    m = d3.GaussianModelOriginFused.from_tensors(sc["xyz"], sc["quat"], sc["scale"], sc["opacity"], sc["sh_base"],
+                                                 sc["sh_rest"], device=device, cur_sh_degree=sc["cfg"].sh_degree,
+                                                 flat=flat)
+    if requires_grad:
+        m.set_requires_grad(True)
+    return m
+
+
+def gpu_cameras(sc, device):
+    c = sc["cfg"]
+    fx, fy, cx, cy = sc["intrinsics"]
+    cams = [d3.BasicPinholeCamera.from_params(m, fx, fy, cx, cy, c.width, c.height) for m in sc["cam2worlds"]]
+    if len(cams) == 1:
+        return cams[0]
+    from d3gs_research_b200.render import CameraBundle
+    return CameraBundle.from_pinhole_cams(cams, device=device)
+
+
+def rel_inf(a, b, floor=1e-12):
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / (np.abs(b).max() + floor))
+
+
+def assert_close(a, b, tol, name, floor_frac=1e-3):
+    """|a-b| <= tol * max(|b|, floor) elementwise with floor = floor_frac * max|b|, plus the inf-norm ratio."""
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    assert a.shape == b.shape, f"{name}: shape {a.shape} vs {b.shape}"
+    scale = np.abs(b).max()
+    if scale == 0:
+        assert np.abs(a).max() == 0, f"{name}: expected all zeros"
+        return
+    err = np.abs(a - b)
+    bound = tol * np.maximum(np.abs(b), floor_frac * scale)
+    bad = err > bound
+    assert not bad.any(), (f"{name}: {int(bad.sum())}/{bad.size} elements off, max err {err.max():.3e} "
+                           f"(scale {scale:.3e}, rel-inf {err.max() / scale:.3e}, tol {tol})")
