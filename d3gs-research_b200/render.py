@@ -148,6 +148,36 @@ class _Workspace:
         return t
 
 
+class StageTimer:
+    """CUDA-event marks on the launching stream, the counterpart of the reference's
+    ``measure_and_print_torch(name, enable=cfg.verbose)`` blocks (render.py:250, 689, 739, 845, 896, 1004).
+    ``mark(name)`` closes the stage ``name``; durations are read after a synchronize."""
+
+    def __init__(self):
+        self.steps: list[list[tuple[str, torch.cuda.Event]]] = []
+
+    def begin_step(self):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.steps.append([("begin", ev)])
+
+    def mark(self, name: str):
+        if not self.steps:
+            self.begin_step()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.steps[-1].append((name, ev))
+
+    def summary(self) -> dict[str, float]:
+        """Mean milliseconds per stage over the recorded steps (call after torch.cuda.synchronize())."""
+        acc: dict[str, float] = {}
+        for marks in self.steps:
+            for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
+                acc[name] = acc.get(name, 0.0) + e0.elapsed_time(e1)
+        n = max(len(self.steps), 1)
+        return {k: v / n for k, v in acc.items()}
+
+
 class GaussianSplatOp:
     """render.py:152-167.  ``cfg`` is deep-copied: create a new op to change options."""
 
@@ -163,6 +193,12 @@ class GaussianSplatOp:
         # when True, forward() keeps copies of the intermediate binning arrays in ``self.debug`` (tests)
         self.debug_capture = False
         self.debug: dict[str, torch.Tensor] = {}
+        # optional StageTimer; None = no events recorded
+        self.timer: StageTimer | None = None
+
+    def _mark(self, name: str):
+        if self.timer is not None:
+            self.timer.mark(name)
 
     @property
     def is_nchw(self):
@@ -275,6 +311,7 @@ class GaussianSplatOp:
             assert mask_u8.numel() == BN
         _lib.check(lib.d3gs_preprocess_forward(C.byref(ocfg), C.byref(mstruct), _lib.ptr(mask_u8), C.byref(cstruct),
                                                stream), "d3gs_preprocess_forward")
+        self._mark("preprocess_fwd")
         if self.debug_capture:
             self.debug = {"tiles_touched": tiles_touched.clone()}
         # cumsum + total (render.py:694-695): one device->host read per forward, as in the reference
@@ -283,7 +320,9 @@ class GaussianSplatOp:
         _lib.check(lib.d3gs_scan_tiles(tiles_touched.data_ptr(), tiles_touched.data_ptr(), BN, sync.data_ptr(),
                                        ws_scan.data_ptr(), ws_scan.numel(), sync.data_ptr() + 8, stream),
                    "d3gs_scan_tiles")
+        self._mark("scan")
         num_rendered, status = (int(v) for v in sync.tolist())
+        self._mark("host_readback_idle")
         if status != 0:
             sync[1] = 0
             raise RuntimeError(f"d3gs_b200 device status {status:#x}: a bounded wait gave up "
@@ -303,6 +342,7 @@ class GaussianSplatOp:
         gaussian_idx_alt = torch.empty_like(gaussian_idx)
         _lib.check(lib.d3gs_duplicate_keys(C.byref(ocfg), num, tiles_touched.data_ptr(), C.byref(cstruct),
                                            keys.data_ptr(), gaussian_idx.data_ptr(), stream), "d3gs_duplicate_keys")
+        self._mark("duplicate_keys")
         if self.debug_capture:
             self.debug.update(scan=tiles_touched.clone(), keys=keys.clone(), values=gaussian_idx.clone())
         end_bit = 32 + lib.d3gs_bit_length(num_tiles)                       # render.py:851-852
@@ -312,7 +352,8 @@ class GaussianSplatOp:
                                        gaussian_idx_alt.data_ptr(), num_rendered, 0, end_bit, ws_sort.data_ptr(),
                                        ws_sort.numel(), C.byref(in_alt), sync.data_ptr() + 8, stream),
                    "d3gs_sort_pairs")
-        if in_alt.value:                                                    # render.py:884-887
+        self._mark("sort")
+        if in_alt.value:                                                   # render.py:884-887
             keys, keys_alt = keys_alt, keys
             gaussian_idx, gaussian_idx_alt = gaussian_idx_alt, gaussian_idx
         gaussian_idx_sorted = gaussian_idx
@@ -321,12 +362,15 @@ class GaussianSplatOp:
         workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
         _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles, stream),
                    "d3gs_tile_ranges")
+        self._mark("tile_ranges")
         records = torch.empty([num_rendered, 12], dtype=f32, device=dev)
         _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
                                         float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")
+        self._mark("pack_splats")
         _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), records.data_ptr(),
                                            out_color.data_ptr(), final_T.data_ptr(), n_contrib.data_ptr(),
                                            sync.data_ptr() + 8, stream), "d3gs_raster_forward")
+        self._mark("raster_fwd")
         output = GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
                                      n_contrib=n_contrib, radii=radii)
         if not training:
@@ -370,6 +414,7 @@ class GaussianSplatOp:
                                             out.n_contrib.data_ptr(), drgb.data_ptr(), _lib.ptr(dT), duv.data_ptr(),
                                             dconic.data_ptr(), dopacity.data_ptr(), dcolor.data_ptr(),
                                             sync.data_ptr() + 8, stream), "d3gs_raster_backward")
+        self._mark("raster_bwd")
         return RasterizeGradientOutput(duv=duv, dconic=dconic, dopacity=dopacity, dcolor=dcolor)
 
     # ---- backward (render.py:2779-3374) --------------------------------------------------------
@@ -416,6 +461,7 @@ class GaussianSplatOp:
         _lib.check(lib.d3gs_preprocess_backward(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct), rg.duv.data_ptr(),
                                                 rg.dconic.data_ptr(), rg.dopacity.data_ptr(), rg.dcolor.data_ptr(),
                                                 C.byref(g), stream), "d3gs_preprocess_backward")
+        self._mark("preprocess_bwd")
         if return_uv_grad:
             return grad_out, rg.duv.view(B, -1, 2), None
         return grad_out, None, None

@@ -115,8 +115,10 @@ class SplatTrainer:
         """One iteration on this rank's view(s).  Returns ``{"out", "loss" (lazy), "num_rendered"}``."""
         model = self.model
         model.act_applied = True
+        if self.op.timer is not None:
+            self.op.timer.begin_step()
         out, ctx = self.op.forward(model, cameras, training=True)
-        if ctx is None:   # nothing visible: zero gradient, still take part in the collective
+        if ctx is None:  # nothing visible: zero gradient, still take part in the collective
             self.grad_flat.zero_()
             loss = None
             duv = None
@@ -131,10 +133,12 @@ class SplatTrainer:
             loss, dcolor = l1_dssim_forward_backward(out.color, target_nchw, self.lambda_dssim,
                                                      grad_scale=1.0 / self.world, scratch=self._loss_scratch,
                                                      sums=self._loss_sums, dcolor=self._dcolor)
-            _, duv, _ = self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
+            self.op._mark("l1_dssim")
+            _, duv, _ =self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
                                          return_uv_grad=True, grad_out=self.grad_model)
         if self.world > 1:
             torch.distributed.all_reduce(self.grad_flat, group=self.pg)
+            self.op._mark("allreduce")
         if update:
             stats = None
             if duv is not None:
@@ -142,6 +146,7 @@ class SplatTrainer:
                 stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
                                           loss_batch=duv.shape[0] * self.world)
             _launch_adam(self._adam_segments(), stats, model.xyz.device)
+            self.op._mark("adam_stats")
         return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
 
     @torch.no_grad()
