@@ -62,7 +62,7 @@ class DensifyStats(C.Structure):
     _fields_ = [("duv", C.c_void_p), ("radii", C.c_void_p), ("duv_ndc_length", C.c_void_p), ("count", C.c_void_p),
                 ("max_radii", C.c_void_p), ("num", C.c_int64), ("batch", C.c_int32), ("width", C.c_int32),
                 ("height", C.c_int32), ("need_max_radii", C.c_int32), ("loss_batch", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("duv_stride", C.c_int32)]
 
 
 _STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats]
@@ -84,9 +84,9 @@ SIGNATURES = {
     "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
     "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P]),
-    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P, _P, _P,
-                                        _P, C.POINTER(ModelGrad), _P]),
+    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
+                                        C.POINTER(ModelGrad), _P]),
     "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "d3gs_ssim_backward": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P]),
     "d3gs_l1_dssim_scratch_bytes": (_SZ, [_I32, _I32, _I32]),

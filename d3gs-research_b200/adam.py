@@ -78,11 +78,17 @@ class GaussianAdam(torch.optim.Adam):
 
 def make_stats_struct(state, radii: torch.Tensor, duv: torch.Tensor, width: int, height: int,
                       need_max_radii: bool, loss_batch: int = 0) -> _lib.DensifyStats:
-    assert duv.ndim == 3 and duv.is_contiguous() and radii.is_contiguous()
+    """``duv`` is [B,N,2]: dense, or a strided view (last two dims' strides (s, 1)) of the packed per-splat
+    gradient array, which is then read in place."""
+    assert duv.ndim == 3 and duv.shape[2] == 2 and radii.is_contiguous()
     b, n, _ = duv.shape
+    if not (duv.stride(2) == 1 and duv.stride(0) == n * duv.stride(1) and duv.stride(1) % 2 == 0
+            and duv.data_ptr() % 8 == 0):
+        duv = duv.contiguous()
     assert radii.numel() == b * n and state.duv_ndc_length.shape[0] == n
     st = _lib.DensifyStats()
     st.duv, st.radii = duv.data_ptr(), radii.data_ptr()
+    st.duv_stride = int(duv.stride(1))
     st.duv_ndc_length, st.count, st.max_radii = (state.duv_ndc_length.data_ptr(), state.count.data_ptr(),
                                                  state.max_radii.data_ptr())
     st.num, st.batch, st.width, st.height, st.need_max_radii = n, b, int(width), int(height), int(need_max_radii)

@@ -14,26 +14,34 @@ namespace {
 constexpr int kMaxSegments = 8;
 constexpr int kAdamThreads = 256;
 constexpr int kAdamVec = 4;
-constexpr int kAdamUnroll = 4;
-constexpr int kAdamChunk = kAdamThreads * kAdamVec * kAdamUnroll;   // 4096 floats per CTA
+constexpr int kAdamUnroll = 2;
+constexpr int kAdamChunk = kAdamThreads * kAdamVec * kAdamUnroll;   // 2048 floats per CTA
+
+// per-segment scalars with the uniform divisions hoisted out of the element loop
+struct SegConst {
+    float inv_grad_scale, weight_decay, beta1, omb1, beta2, omb2, step_size, inv_bc2_sqrt, eps;
+};
 
 struct AdamArgs {
     D3gsAdamSegment seg[kMaxSegments];
+    SegConst sc[kMaxSegments];
     int64_t block_start[kMaxSegments + 2];   // first CTA of each segment; [num_segments] = stats; last = end
     int32_t num_segments;
     int32_t has_stats;
     D3gsDensifyStats stats;
 };
 
-// csrc/optim.py:22-49 (weight decay 0 / plain Adam path kept as in the reference)
-__device__ __forceinline__ void adam_update(float g, float& p, float& m, float& v, const D3gsAdamSegment& s) {
-    g = g / s.grad_scale;
-    if (s.weight_decay != 0.0f) g += p * s.weight_decay;
-    m = g * (1.0f - s.beta1) + m * s.beta1;            // mix(grad, exp_avg, beta1)
-    v = (g * g) * (1.0f - s.beta2) + v * s.beta2;
-    const float step_size = s.lr / s.bias_correction1;
-    const float denom = sqrtf(v) / s.bias_correction2_sqrt + s.eps;
-    p = p - step_size * m / denom;
+// csrc/optim.py:22-49: g /= grad_scale; m = mix(g, m, b1); v = mix(g*g, v, b2);
+// p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps).  The three divisions by per-tensor constants are
+// multiplications by reciprocals computed once on the host in double; the one per-element division is a
+// single correctly rounded reciprocal.
+__device__ __forceinline__ void adam_update(float g, float& p, float& m, float& v, const SegConst& c) {
+    g = g * c.inv_grad_scale;
+    if (c.weight_decay != 0.0f) g += p * c.weight_decay;
+    m = g * c.omb1 + m * c.beta1;
+    v = (g * g) * c.omb2 + v * c.beta2;
+    const float denom = sqrtf(v) * c.inv_bc2_sqrt + c.eps;
+    p = p - (c.step_size * m) * __frcp_rn(denom);
 }
 
 __device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t i) {
@@ -41,9 +49,10 @@ __device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t
     const float lb = (float)(st.loss_batch > 0 ? st.loss_batch : st.batch);
     const float sx = 0.5f * (float)st.width * lb, sy = 0.5f * (float)st.height * lb;
     const float mwh = (float)max(st.width, st.height);
+    const int64_t stride = st.duv_stride > 0 ? st.duv_stride : 2;
     for (int j = 0; j < st.batch; ++j) {
         const int64_t k = (int64_t)j * st.num + i;
-        const float2 d = *reinterpret_cast<const float2*>(st.duv + k * 2);
+        const float2 d = *reinterpret_cast<const float2*>(st.duv + k * stride);
         const float a = d.x * sx, b = d.y * sy;
         const float len = sqrtf(a * a + b * b);
         const int r = st.radii[k];
@@ -70,6 +79,7 @@ __global__ void __launch_bounds__(kAdamThreads) adam_stats_kernel(const __grid_c
         return;
     }
     const D3gsAdamSegment& s = a.seg[si];
+    const SegConst c = a.sc[si];
     const int64_t base = (blk - a.block_start[si]) * kAdamChunk;
     const bool vec_ok = (((uintptr_t)s.param | (uintptr_t)s.grad | (uintptr_t)s.exp_avg | (uintptr_t)s.exp_avg_sq) & 15) == 0;
     if (vec_ok && base + kAdamChunk <= s.count) {
@@ -84,10 +94,10 @@ __global__ void __launch_bounds__(kAdamThreads) adam_stats_kernel(const __grid_c
         }
 #pragma unroll
         for (int u = 0; u < kAdamUnroll; ++u) {
-            adam_update(g[u].x, p[u].x, m[u].x, v[u].x, s);
-            adam_update(g[u].y, p[u].y, m[u].y, v[u].y, s);
-            adam_update(g[u].z, p[u].z, m[u].z, v[u].z, s);
-            adam_update(g[u].w, p[u].w, m[u].w, v[u].w, s);
+            adam_update(g[u].x, p[u].x, m[u].x, v[u].x, c);
+            adam_update(g[u].y, p[u].y, m[u].y, v[u].y, c);
+            adam_update(g[u].z, p[u].z, m[u].z, v[u].z, c);
+            adam_update(g[u].w, p[u].w, m[u].w, v[u].w, c);
         }
 #pragma unroll
         for (int u = 0; u < kAdamUnroll; ++u) {
@@ -99,7 +109,7 @@ __global__ void __launch_bounds__(kAdamThreads) adam_stats_kernel(const __grid_c
     } else {
         for (int64_t o = base + threadIdx.x; o < min(base + (int64_t)kAdamChunk, s.count); o += kAdamThreads) {
             float p = s.param[o], m = s.exp_avg[o], v = s.exp_avg_sq[o];
-            adam_update(s.grad[o], p, m, v, s);
+            adam_update(s.grad[o], p, m, v, c);
             s.param[o] = p;
             s.exp_avg[o] = m;
             s.exp_avg_sq[o] = v;
@@ -111,7 +121,7 @@ int32_t check_stats(const D3gsDensifyStats* st) {
     D3GS_REQUIRE(st->num >= 0 && st->batch >= 1, "bad stats shape");
     D3GS_REQUIRE(st->duv && st->radii && st->duv_ndc_length && st->count, "NULL stats tensor");
     D3GS_REQUIRE(!st->need_max_radii || st->max_radii, "max_radii is NULL");
-    D3GS_REQUIRE(((uintptr_t)st->duv & 7) == 0, "duv must be 8-byte aligned");
+    D3GS_REQUIRE(((uintptr_t)st->duv & 7) == 0 && (st->duv_stride & 1) == 0, "duv must be 8-byte aligned, stride even");
     return D3GS_OK;
 }
 
@@ -135,6 +145,16 @@ extern "C" int32_t d3gs_adam_stats_step(const D3gsAdamSegment* segments, int32_t
         D3GS_REQUIRE(s.grad_scale != 0.0f && s.bias_correction1 != 0.0f && s.bias_correction2_sqrt != 0.0f,
                      "segment %d: zero grad_scale / bias correction", k);
         a.seg[k] = s;
+        SegConst& c = a.sc[k];
+        c.inv_grad_scale = (float)(1.0 / (double)s.grad_scale);
+        c.weight_decay = s.weight_decay;
+        c.beta1 = s.beta1;
+        c.omb1 = 1.0f - s.beta1;
+        c.beta2 = s.beta2;
+        c.omb2 = 1.0f - s.beta2;
+        c.step_size = s.lr / s.bias_correction1;
+        c.inv_bc2_sqrt = (float)(1.0 / (double)s.bias_correction2_sqrt);
+        c.eps = s.eps;
         a.block_start[k] = blocks;
         blocks += div_up64(s.count, kAdamChunk);
     }

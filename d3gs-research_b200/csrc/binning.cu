@@ -140,10 +140,13 @@ tile_ranges_kernel(const uint64_t* __restrict__ keys, int64_t n, int32_t* __rest
 }
 
 // One 48-byte record per sorted (tile, Gaussian) pair:
-//   [u, v, thr, id] [ha, nb, hc, opacity] [r, g, b, 0]
-// ha=-0.5*conic_a, nb=-conic_b, hc=-0.5*conic_c (exact scalings).  thr = -ln(opacity/alpha_eps) - 0.01 is
-// a conservative bound: power < thr implies opacity*exp(power) < 0.99*alpha_eps, so the blend loop may
-// skip the exponential for such a pixel without changing any result.
+//   [u, v, hx, hy] [ha, nb, hc, opacity] [r, g, b, thr]
+// ha=-0.5*conic_a, nb=-conic_b, hc=-0.5*conic_c (exact scalings).
+// thr = -ln(opacity/alpha_eps) - 0.01 is a conservative bound: power < thr implies
+// opacity*exp(power) < 0.99*alpha_eps, so the blend loop may skip such a pixel without changing any result.
+// (hx, hy) are the half extents of the axis-aligned box around {power >= thr}, slightly inflated and
+// widened by the half size of a warp's 8x4 pixel block (3.5, 1.5): a warp whose block centre is further
+// than (hx, hy) from (u, v) contains no pixel that the splat can touch.
 __global__ void __launch_bounds__(256)
 pack_splats_kernel(const int32_t* __restrict__ ids, int64_t n, const float* __restrict__ uvs,
                    const float* __restrict__ conic_opacity, const float* __restrict__ rgb, float alpha_eps,
@@ -154,11 +157,23 @@ pack_splats_kernel(const int32_t* __restrict__ ids, int64_t n, const float* __re
     const float2 uv = __ldg(reinterpret_cast<const float2*>(uvs) + id);
     const float4 co = __ldg(reinterpret_cast<const float4*>(conic_opacity) + id);
     const float r = __ldg(rgb + (int64_t)id * 3), g = __ldg(rgb + (int64_t)id * 3 + 1), b = __ldg(rgb + (int64_t)id * 3 + 2);
-    float thr = -1.0e30f;
-    if (co.w > alpha_eps && co.w < 1.0e30f) thr = act_log(alpha_eps / co.w) - 0.01f;
-    rec[i * 3] = make_float4(uv.x, uv.y, thr, __int_as_float(id));
+    float thr = -1.0e30f, hx = 1.0e30f, hy = 1.0e30f;
+    if (co.w > alpha_eps && co.w < 1.0e30f) {
+        thr = act_log(alpha_eps / co.w) - 0.01f;
+        // {a dx^2 + 2 b dx dy + c dy^2 <= R}, R = -2 thr: |dx| <= sqrt(R c / det), |dy| <= sqrt(R a / det)
+        const float det = co.x * co.z - co.y * co.y;
+        // Very elongated splats (a*c >> det) are left unculled: there the float evaluation of `power`
+        // cancels heavily and can exceed thr slightly outside the exact box.  Up to a*c/det = 1e3 the
+        // rounding error of power stays below 1e-3, a tenth of the 0.01 margin built into thr.
+        if (det > 0.0f && co.x * co.z < 1.0e3f * det) {
+            const float R = -2.0f * thr;
+            hx = sqrtf(R * co.z / det) * 1.0005f + 0.02f + 3.5f;
+            hy = sqrtf(R * co.x / det) * 1.0005f + 0.02f + 1.5f;
+        }
+    }
+    rec[i * 3] = make_float4(uv.x, uv.y, hx, hy);
     rec[i * 3 + 1] = make_float4(-0.5f * co.x, -co.y, -0.5f * co.z, co.w);
-    rec[i * 3 + 2] = make_float4(r, g, b, 0.0f);
+    rec[i * 3 + 2] = make_float4(r, g, b, thr);
 }
 
 }  // namespace

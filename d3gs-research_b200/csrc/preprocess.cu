@@ -160,133 +160,195 @@ struct PrepArgs {
     const uint8_t* mask;
 };
 
+constexpr int kRow = 45;   // shared-memory row length in floats (odd: conflict-free per-thread rows)
+
+// One CTA handles 256 consecutive (view, Gaussian) items.  Geometry first; the l>=1 SH coefficients of
+// the SURVIVING Gaussians only (180 bytes each) are then brought into shared memory with coalesced
+// loads and evaluated per thread from there: per-thread global loads with a 180-byte stride cost ~22
+// sectors per request.
 template <int DEG>
 __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+    constexpr int NB = (DEG + 1) * (DEG + 1);
+    constexpr int NR3 = (NB - 1) * 3;
+    __shared__ __align__(128) float s_rest[NR3 > 0 ? 256 * kRow : 4];
+    __shared__ int32_t s_src[256];   // Gaussian index whose coefficients row t needs, -1 = none
+    __shared__ __align__(8) uint64_t s_bar;
     const int64_t N = a.model.num;
     const int64_t total = N * a.cfg.num_views;
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= total) return;
-    const int b = (int)(i / N);
-    const int64_t g = i - (int64_t)b * N;
+    const int t = threadIdx.x;
+    const int64_t i0 = (int64_t)blockIdx.x * 256;
+    const int64_t i = i0 + t;
     const D3gsOpConfig& cf = a.cfg;
-    const D3gsCamera& cam = cf.cameras[b];
-    const float* Rt = cam.cam2world_T;   // Rt[k*3 + j]: k-th column of R_c2w
-    TileGeom tg;
-    tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
-    tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
-    tg.ts = (float)cf.tile_x;
-
-    bool valid = true;
-    const float px = a.model.xyz[g * 3], py = a.model.xyz[g * 3 + 1], pz = a.model.xyz[g * 3 + 2];
-    const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
-    const float pc0 = (Rt[0] * d0 + Rt[1] * d1) + Rt[2] * d2;
-    const float pc1 = (Rt[3] * d0 + Rt[4] * d1) + Rt[5] * d2;
-    const float z = (Rt[6] * d0 + Rt[7] * d1) + Rt[8] * d2;
-    if (!(z >= cf.near_plane && z <= cf.far_plane)) valid = false;
-    if (a.mask != nullptr && a.mask[i] != 0) valid = false;
-    if (!valid) {
-        a.ctx.tiles_touched[i] = 0;
-        a.ctx.radii[i] = 0;
-        return;
+    // Fast staging: when the CTA's 256 rows are one contiguous, 16-byte aligned span of the coefficient
+    // array (degree-3 layout, rows inside one view), a single bulk async copy fetches them while the
+    // threads do the geometry.  Otherwise the rows of the surviving Gaussians are gathered afterwards.
+    bool bulk = false;
+    if (NR3 > 0) {
+        const int64_t g_first = i0 % N;
+        const int rows = (int)min((int64_t)256, total - i0);
+        bulk = a.model.sh_rest_stride == 45 && g_first + rows <= N && (rows & 3) == 0 &&
+               ((uintptr_t)(a.model.sh_rest + g_first * 45) & 15) == 0;
+        if (bulk) {
+            if (t == 0) {
+                mbar_init(&s_bar, 1);
+                fence_mbar_init();
+                mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
+                bulk_copy_g2s(s_rest, a.model.sh_rest + g_first * 45, (uint32_t)rows * 180u, &s_bar);
+            }
+            __syncthreads();   // the barrier is initialised before anybody polls it
+        }
     }
-    const float u = ((pc0 / z) * cam.fx + cam.cx) - 0.5f;
-    const float v = ((pc1 / z) * cam.fy + cam.cy) - 0.5f;
-    // fused activations
-    const float4 qr = *reinterpret_cast<const float4*>(a.model.quaternion_xyzw + g * 4);
-    const bool fused = cf.fused_activations != 0;
-    const float qn = fused ? sqrtf(((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w) : 1.0f;
-    const float qx = qr.x / qn, qy = qr.y / qn, qz = qr.z / qn, qw = qr.w / qn;
-    const float sg = cf.training ? 1.0f : cf.scale_global;
-    const float r0 = a.model.scale[g * 3], r1 = a.model.scale[g * 3 + 1], r2 = a.model.scale[g * 3 + 2];
-    const float s0 = (fused ? act_exp(r0) : r0) * sg, s1 = (fused ? act_exp(r1) : r1) * sg,
-                s2 = (fused ? act_exp(r2) : r2) * sg;
-    const float oraw = a.model.opacity[g];
-    const float opac = fused ? 1.0f / (1.0f + act_exp(-oraw)) : oraw;
-    // rotation, M = R diag(s), Sigma = M M^T
-    float R[3][3];
-    {
-        float xx = qx * qx, yy = qy * qy, zz = qz * qz, xy = qx * qy, xz = qx * qz, yz = qy * qz;
-        float wx = qw * qx, wy = qw * qy, wz = qw * qz;
-        R[0][0] = 1.0f - 2.0f * (yy + zz); R[0][1] = 2.0f * (xy - wz); R[0][2] = 2.0f * (xz + wy);
-        R[1][0] = 2.0f * (xy + wz); R[1][1] = 1.0f - 2.0f * (xx + zz); R[1][2] = 2.0f * (yz - wx);
-        R[2][0] = 2.0f * (xz - wy); R[2][1] = 2.0f * (yz + wx); R[2][2] = 1.0f - 2.0f * (xx + yy);
-    }
-    float M[3][3];
+    bool valid = i < total;
+    int64_t g = 0;
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f;
+    if (valid) {
+        const int b = (int)(i / N);
+        g = i - (int64_t)b * N;
+        const D3gsCamera& cam = cf.cameras[b];
+        const float* Rt = cam.cam2world_T;   // Rt[k*3 + j]: k-th column of R_c2w
+        TileGeom tg;
+        tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
+        tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
+        tg.ts = (float)cf.tile_x;
+        const float px = a.model.xyz[g * 3], py = a.model.xyz[g * 3 + 1], pz = a.model.xyz[g * 3 + 2];
+        d0 = px - Rt[9]; d1 = py - Rt[10]; d2 = pz - Rt[11];
+        const float pc0 = (Rt[0] * d0 + Rt[1] * d1) + Rt[2] * d2;
+        const float pc1 = (Rt[3] * d0 + Rt[4] * d1) + Rt[5] * d2;
+        const float z = (Rt[6] * d0 + Rt[7] * d1) + Rt[8] * d2;
+        if (!(z >= cf.near_plane && z <= cf.far_plane)) valid = false;
+        if (a.mask != nullptr && a.mask[i] != 0) valid = false;
+        if (valid) {
+            const float u = ((pc0 / z) * cam.fx + cam.cx) - 0.5f;
+            const float v = ((pc1 / z) * cam.fy + cam.cy) - 0.5f;
+            // fused activations
+            const float4 qr = *reinterpret_cast<const float4*>(a.model.quaternion_xyzw + g * 4);
+            const bool fused = cf.fused_activations != 0;
+            const float qn = fused ? sqrtf(((qr.x * qr.x + qr.y * qr.y) + qr.z * qr.z) + qr.w * qr.w) : 1.0f;
+            const float qx = qr.x / qn, qy = qr.y / qn, qz = qr.z / qn, qw = qr.w / qn;
+            const float sg = cf.training ? 1.0f : cf.scale_global;
+            const float r0 = a.model.scale[g * 3], r1 = a.model.scale[g * 3 + 1], r2 = a.model.scale[g * 3 + 2];
+            const float s0 = (fused ? act_exp(r0) : r0) * sg, s1 = (fused ? act_exp(r1) : r1) * sg,
+                        s2 = (fused ? act_exp(r2) : r2) * sg;
+            const float oraw = a.model.opacity[g];
+            const float opac = fused ? 1.0f / (1.0f + act_exp(-oraw)) : oraw;
+            // rotation, M = R diag(s), Sigma = M M^T
+            float R[3][3];
+            {
+                float xx = qx * qx, yy = qy * qy, zz = qz * qz, xy = qx * qy, xz = qx * qz, yz = qy * qz;
+                float wx = qw * qx, wy = qw * qy, wz = qw * qz;
+                R[0][0] = 1.0f - 2.0f * (yy + zz); R[0][1] = 2.0f * (xy - wz); R[0][2] = 2.0f * (xz + wy);
+                R[1][0] = 2.0f * (xy + wz); R[1][1] = 1.0f - 2.0f * (xx + zz); R[1][2] = 2.0f * (yz - wx);
+                R[2][0] = 2.0f * (xz - wy); R[2][1] = 2.0f * (yz + wx); R[2][2] = 1.0f - 2.0f * (xx + yy);
+            }
+            float M[3][3];
 #pragma unroll
-    for (int r = 0; r < 3; ++r) {
-        M[r][0] = R[r][0] * s0;
-        M[r][1] = R[r][1] * s1;
-        M[r][2] = R[r][2] * s2;
-    }
-    float Sg[3][3];
+            for (int r = 0; r < 3; ++r) {
+                M[r][0] = R[r][0] * s0;
+                M[r][1] = R[r][1] * s1;
+                M[r][2] = R[r][2] * s2;
+            }
+            float Sg[3][3];
 #pragma unroll
-    for (int r = 0; r < 3; ++r)
+            for (int r = 0; r < 3; ++r)
 #pragma unroll
-        for (int c = r; c < 3; ++c) Sg[r][c] = Sg[c][r] = (M[r][0] * M[c][0] + M[r][1] * M[c][1]) + M[r][2] * M[c][2];
-    // projection
-    const float tanx = 0.5f * (float)cf.width / cam.fx, tany = 0.5f * (float)cf.height / cam.fy;
-    const float limx = fabsf((tanx * cf.projected_clamp_factor) * z), limy = fabsf((tany * cf.projected_clamp_factor) * z);
-    const float tx = fminf(limx, fmaxf(-limx, pc0)), ty = fminf(limy, fmaxf(-limy, pc1));
-    const float z2 = z * z;
-    const float J00 = cam.fx / z, J02 = -(tx * cam.fx) / z2, J11 = cam.fy / z, J12 = -(ty * cam.fy) / z2;
-    float T0[3], T1[3];
+                for (int c = r; c < 3; ++c)
+                    Sg[r][c] = Sg[c][r] = (M[r][0] * M[c][0] + M[r][1] * M[c][1]) + M[r][2] * M[c][2];
+            // projection
+            const float tanx = 0.5f * (float)cf.width / cam.fx, tany = 0.5f * (float)cf.height / cam.fy;
+            const float limx = fabsf((tanx * cf.projected_clamp_factor) * z), limy = fabsf((tany * cf.projected_clamp_factor) * z);
+            const float tx = fminf(limx, fmaxf(-limx, pc0)), ty = fminf(limy, fmaxf(-limy, pc1));
+            const float z2 = z * z;
+            const float J00 = cam.fx / z, J02 = -(tx * cam.fx) / z2, J11 = cam.fy / z, J12 = -(ty * cam.fy) / z2;
+            float T0[3], T1[3];
 #pragma unroll
-    for (int j = 0; j < 3; ++j) {
-        T0[j] = J00 * Rt[j] + J02 * Rt[6 + j];
-        T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
-    }
-    float U0[3], U1[3];
+            for (int j = 0; j < 3; ++j) {
+                T0[j] = J00 * Rt[j] + J02 * Rt[6 + j];
+                T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
+            }
+            float U0[3], U1[3];
 #pragma unroll
-    for (int j = 0; j < 3; ++j) {
-        U0[j] = (T0[0] * Sg[0][j] + T0[1] * Sg[1][j]) + T0[2] * Sg[2][j];
-        U1[j] = (T1[0] * Sg[0][j] + T1[1] * Sg[1][j]) + T1[2] * Sg[2][j];
+            for (int j = 0; j < 3; ++j) {
+                U0[j] = (T0[0] * Sg[0][j] + T0[1] * Sg[1][j]) + T0[2] * Sg[2][j];
+                U1[j] = (T1[0] * Sg[0][j] + T1[1] * Sg[1][j]) + T1[2] * Sg[2][j];
+            }
+            float ca = (U0[0] * T0[0] + U0[1] * T0[1]) + U0[2] * T0[2];
+            float cb = (U0[0] * T1[0] + U0[1] * T1[1]) + U0[2] * T1[2];
+            float cc = (U1[0] * T1[0] + U1[1] * T1[1]) + U1[2] * T1[2];
+            ca += cf.gaussian_lowpass_filter;
+            cc += cf.gaussian_lowpass_filter;
+            const float det = ca * cc - cb * cb;
+            const float det_inv = 1.0f / (det + cf.eps);
+            const float k0 = cc * det_inv, k1 = -cb * det_inv, k2 = ca * det_inv;
+            const float mid = 0.5f * (ca + cc);
+            const float sq = sqrtf(fmaxf(cf.cov2d_radii_eigen_eps, mid * mid - det));
+            const float radius = ceilf(cf.gaussian_std_sigma * sqrtf(fmaxf(mid + sq, mid - sq)));
+            int rmin[2], rmax[2];
+            tile_rect(tg, u, v, radius, rmin, rmax);
+            const int area = (rmax[0] - rmin[0]) * (rmax[1] - rmin[1]);
+            if (det <= 0.0f || area == 0 || opac <= cf.alpha_eps) {
+                valid = false;
+            } else {
+                int cnt = 0;
+                for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opac, rmin, rmax,
+                              [&](int, int) { ++cnt; });
+                a.ctx.tiles_touched[i] = cnt;
+                a.ctx.radii[i] = (int)radius;
+                a.ctx.depths[i] = z;
+                *reinterpret_cast<float2*>(a.ctx.uvs + i * 2) = make_float2(u, v);
+                *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opac);
+                if (a.ctx.cov2d_vecs != nullptr) {
+                    a.ctx.cov2d_vecs[i * 3] = ca;
+                    a.ctx.cov2d_vecs[i * 3 + 1] = cb;
+                    a.ctx.cov2d_vecs[i * 3 + 2] = cc;
+                }
+            }
+        }
+        if (!valid) {
+            a.ctx.tiles_touched[i] = 0;
+            a.ctx.radii[i] = 0;
+        }
     }
-    float ca = (U0[0] * T0[0] + U0[1] * T0[1]) + U0[2] * T0[2];
-    float cb = (U0[0] * T1[0] + U0[1] * T1[1]) + U0[2] * T1[2];
-    float cc = (U1[0] * T1[0] + U1[1] * T1[1]) + U1[2] * T1[2];
-    ca += cf.gaussian_lowpass_filter;
-    cc += cf.gaussian_lowpass_filter;
-    const float det = ca * cc - cb * cb;
-    const float det_inv = 1.0f / (det + cf.eps);
-    const float k0 = cc * det_inv, k1 = -cb * det_inv, k2 = ca * det_inv;
-    const float mid = 0.5f * (ca + cc);
-    const float sq = sqrtf(fmaxf(cf.cov2d_radii_eigen_eps, mid * mid - det));
-    const float radius = ceilf(cf.gaussian_std_sigma * sqrtf(fmaxf(mid + sq, mid - sq)));
-    int rmin[2], rmax[2];
-    tile_rect(tg, u, v, radius, rmin, rmax);
-    const int area = (rmax[0] - rmin[0]) * (rmax[1] - rmin[1]);
-    if (det <= 0.0f || area == 0 || opac <= cf.alpha_eps) {
-        a.ctx.tiles_touched[i] = 0;
-        a.ctx.radii[i] = 0;
-        return;
+    if constexpr (NR3 > 0) {
+        if (bulk) {
+            if (!mbar_wait_bounded(&s_bar, 0)) valid = false;   // the copy never landed: emit nothing from this CTA
+        } else {
+            s_src[t] = valid ? (int32_t)g : -1;
+            __syncthreads();
+            const float* src = a.model.sh_rest;
+            const int64_t stride = a.model.sh_rest_stride;
+            constexpr int kU = NR3 % 9 == 0 ? 9 : 3;   // loads of one round are issued back to back
+            for (int f0 = t; f0 < 256 * NR3; f0 += 256 * kU) {
+                float tmp[kU];
+                int dst[kU];
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    const int f = f0 + u * 256;
+                    const int row = f / NR3, k = f - row * NR3;
+                    const int32_t gs = f < 256 * NR3 ? s_src[row] : -1;
+                    dst[u] = gs >= 0 ? row * kRow + k : -1;
+                    tmp[u] = gs >= 0 ? src[(int64_t)gs * stride + k] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < kU; ++u)
+                    if (dst[u] >= 0) s_rest[dst[u]] = tmp[u];
+            }
+            __syncthreads();
+        }
     }
-    int cnt = 0;
-    for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opac, rmin, rmax,
-                  [&](int, int) { ++cnt; });
-    a.ctx.tiles_touched[i] = cnt;
-    a.ctx.radii[i] = (int)radius;
-    a.ctx.depths[i] = z;
-    *reinterpret_cast<float2*>(a.ctx.uvs + i * 2) = make_float2(u, v);
-    *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opac);
-    if (a.ctx.cov2d_vecs != nullptr) {
-        a.ctx.cov2d_vecs[i * 3] = ca;
-        a.ctx.cov2d_vecs[i * 3 + 1] = cb;
-        a.ctx.cov2d_vecs[i * 3 + 2] = cc;
-    }
+    if (!valid) return;
     // colour: SH of the normalised world-space view direction (render.py:587, 605-611)
     const float dn = sqrtf((d0 * d0 + d1 * d1) + d2 * d2);
     float bs[16];
     sh_basis(DEG, d0 / dn, d1 / dn, d2 / dn, bs);
     const float* base = a.model.sh_base + g * a.model.sh_base_stride;
-    const float* rest = a.model.sh_rest + g * a.model.sh_rest_stride;
+    const float* rest = s_rest + t * kRow;
     float c3[3];
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) c3[ch] = bs[0] * base[ch];
-    constexpr int NB = (DEG + 1) * (DEG + 1);
 #pragma unroll
     for (int k = 1; k < NB; ++k) {
 #pragma unroll
-        for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + bs[k] * __ldg(rest + (k - 1) * 3 + ch);
+        for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + bs[k] * rest[(k - 1) * 3 + ch];
     }
 #pragma unroll
     for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + 0.5f;

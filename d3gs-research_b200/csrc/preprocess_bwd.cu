@@ -8,10 +8,11 @@
 //   pos_cam_to_uv_no_distort_grad      d3sim/csrc/camera.py:335-371
 //   sh_dir_to_rgb_grad                 gs3d.py:236-366
 //   fused activation gradients         d3sim/algos/d3gs/origin/model.py:327-431
-// One thread per Gaussian; the view batch is looped inside and summed in registers
-// (render.py:3182, origin/model.py:422-431).  Unlike the reference (zeros_like + skip,
-// render.py:2918, 3218-3220) every output element is written here, zeros included, so the caller
-// needs no memset of the 236-byte-per-Gaussian gradient.
+// One thread per Gaussian; the view batch is looped inside and summed (render.py:3182,
+// origin/model.py:422-431).  Unlike the reference (zeros_like + skip, render.py:2918, 3218-3220) every
+// output element is written here, zeros included, so the caller needs no memset of the
+// 236-byte-per-Gaussian gradient.  The rasteriser's per-splat gradients arrive packed, 48 bytes per
+// (view, Gaussian).
 #include "common.cuh"
 
 namespace d3gs {
@@ -22,34 +23,85 @@ struct BwdArgs {
     D3gsModel model;
     D3gsSplatContext ctx;
     D3gsModelGrad grad;
-    const float* duv;
-    const float* dconic;
-    const float* dopacity;
-    const float* dcolor;
+    const float* splat_grads;   // [B*N, 12]: dconic a b c, dopacity | dcolor r g b, - | duv x y, - -
 };
+
+constexpr int kRow = 45;        // shared-memory row length in floats (odd: conflict-free per-thread rows)
 
 __constant__ float kC2[5] = {1.0925484305920792f, -1.0925484305920792f, 0.31539156525252005f, -1.0925484305920792f,
                              0.5462742152960396f};
 __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.4570457994644658f, 0.3731763325901154f,
                              -0.4570457994644658f, 1.445305721320277f,  -0.5900435899266435f};
 
-template <int DEG>
+// One CTA handles 256 consecutive Gaussians.  The l>=1 SH coefficients (180 bytes per Gaussian) are
+// brought into shared memory with coalesced loads, each thread works on its own row, writes the
+// coefficient gradients back into the row, and the rows leave with coalesced stores: per-thread
+// accesses with a 180-byte stride cost 20-30 sectors per request and throttled the load/store unit.
+// MULTI (more than one view): gradients accumulate over views in a second shared-memory buffer.
+template <int DEG, bool MULTI>
 __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ uint8_t s_vis[256];
+    __shared__ __align__(8) uint64_t s_bar;
+    float* s_in = smem;
+    float* s_out = MULTI ? smem + 256 * kRow : smem;
     const int64_t N = a.model.num;
-    const int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (g >= N) return;
+    const int t = threadIdx.x;
+    const int64_t g0 = (int64_t)blockIdx.x * 256;
+    const int64_t g = g0 + t;
     const D3gsOpConfig& cf = a.cfg;
     constexpr int NB = (DEG + 1) * (DEG + 1);
-    constexpr int NR = NB - 1;
+    constexpr int NR3 = (NB - 1) * 3;
+
+    bool any_view = false;
+    if (g < N)
+        for (int b = 0; b < cf.num_views; ++b) any_view |= a.ctx.radii[(int64_t)b * N + g] != 0;
+    s_vis[t] = any_view ? 1 : 0;
+    const int rows = (int)min((int64_t)256, N - g0);
+    // contiguous degree-3 layout: the CTA's rows are one 16-byte aligned span -> one bulk async copy
+    const bool bulk_in = NR3 > 0 && a.model.sh_rest_stride == 45 && (rows & 3) == 0 &&
+                         ((uintptr_t)(a.model.sh_rest + g0 * 45) & 15) == 0;
+    if (bulk_in && t == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
+        bulk_copy_g2s(s_in, a.model.sh_rest + g0 * 45, (uint32_t)rows * 180u, &s_bar);
+    }
+    __syncthreads();
+    if constexpr (NR3 > 0) {
+        if (bulk_in) {
+            mbar_wait_bounded(&s_bar, 0);
+        } else {
+            const float* src = a.model.sh_rest;
+            const int64_t stride = a.model.sh_rest_stride;
+            constexpr int kU = NR3 % 9 == 0 ? 9 : 3;
+            for (int f0 = t; f0 < 256 * NR3; f0 += 256 * kU) {
+                float tmp[kU];
+                int dst[kU];
+#pragma unroll
+                for (int u = 0; u < kU; ++u) {
+                    const int f = f0 + u * 256;
+                    const int row = f / NR3, k = f - row * NR3;
+                    const bool ok = f < 256 * NR3 && s_vis[row];
+                    dst[u] = ok ? row * kRow + k : -1;
+                    tmp[u] = ok ? src[(g0 + row) * stride + k] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < kU; ++u)
+                    if (dst[u] >= 0) s_in[dst[u]] = tmp[u];
+            }
+            __syncthreads();
+        }
+    }
+    float* my_in = s_in + t * kRow;
+    float* my_out = s_out + t * kRow;
 
     float axyz[3] = {0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f}, as[3] = {0.f, 0.f, 0.f}, ao = 0.f;
     float abase[3] = {0.f, 0.f, 0.f};
-    float arest[NR > 0 ? NR * 3 : 1];
+    if (MULTI || !any_view) {
 #pragma unroll
-    for (int k = 0; k < NR * 3; ++k) arest[k] = 0.f;
-
-    bool any_view = false;
-    for (int b = 0; b < cf.num_views; ++b) any_view |= a.ctx.radii[(int64_t)b * N + g] != 0;
+        for (int k = 0; k < NR3; ++k) my_out[k] = 0.f;
+    }
 
     if (any_view) {
         // view-independent part: activations, rotation, M = R diag(s), Sigma
@@ -79,7 +131,6 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
         for (int r = 0; r < 3; ++r)
 #pragma unroll
             for (int c = r; c < 3; ++c) Sg[r][c] = Sg[c][r] = M[r][0] * M[c][0] + M[r][1] * M[c][1] + M[r][2] * M[c][2];
-        const float* rest = a.model.sh_rest + g * a.model.sh_rest_stride;
         float dSacc[3][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};   // sum over views of dL/dSigma
 
         for (int b = 0; b < cf.num_views; ++b) {
@@ -87,6 +138,8 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
             if (a.ctx.radii[i] == 0) continue;
             const D3gsCamera& cam = cf.cameras[b];
             const float* Rt = cam.cam2world_T;
+            const float4* sg4 = reinterpret_cast<const float4*>(a.splat_grads + i * D3GS_SPLAT_GRAD_FLOATS);
+            const float4 gA = sg4[0], gB = sg4[1], gC = sg4[2];
             const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
             const float pc0 = Rt[0] * d0 + Rt[1] * d1 + Rt[2] * d2;
             const float pc1 = Rt[3] * d0 + Rt[4] * d1 + Rt[5] * d2;
@@ -106,12 +159,12 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
             }
             // conic -> cov2d (gs3d.py:559-588)
             const float ca = a.ctx.cov2d_vecs[i * 3], cb = a.ctx.cov2d_vecs[i * 3 + 1], cc = a.ctx.cov2d_vecs[i * 3 + 2];
-            const float g0 = a.dconic[i * 3], g1 = a.dconic[i * 3 + 1], g2 = a.dconic[i * 3 + 2];
+            const float g0c = gA.x, g1c = gA.y, g2c = gA.z;
             const float det = ca * cc - cb * cb;
             const float d2i = 1.0f / (det * det + 1e-8f);
-            const float da = d2i * (-cc * cc * g0 + cb * cc * g1 + (det - ca * cc) * g2);
-            const float db = d2i * 2.0f * (cb * cc * g0 - (0.5f * det + cb * cb) * g1 + ca * cb * g2);
-            const float dc = d2i * (-ca * ca * g2 + ca * cb * g1 + (det - ca * cc) * g0);
+            const float da = d2i * (-cc * cc * g0c + cb * cc * g1c + (det - ca * cc) * g2c);
+            const float db = d2i * 2.0f * (cb * cc * g0c - (0.5f * det + cb * cb) * g1c + ca * cb * g2c);
+            const float dc = d2i * (-ca * ca * g2c + ca * cb * g1c + (det - ca * cc) * g0c);
             // cov2d = T Sigma T^T (gs3d.py:472-532): dSigma = T^T G T, dT = 2 G T Sigma
             const float hb = 0.5f * db;
             float GT0[3], GT1[3];
@@ -140,18 +193,18 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
             const float dm1 = yg * -dJ12 * cam.fy * z2i;
             const float dm2 = -(cam.fx * dJ00 + cam.fy * dJ11) * z2i + 2.0f * (dJ02 * txf + dJ12 * tyf) * z2i * zi;
             // pinhole (camera.py:335-371)
-            const float du = a.duv[i * 2] * cam.fx, dv = a.duv[i * 2 + 1] * cam.fy;
+            const float du = gC.x * cam.fx, dv = gC.y * cam.fy;
             const float dp0 = du * zi + dm0, dp1 = dv * zi + dm1;
             const float dp2 = -(du * pc0 + dv * pc1) * z2i + dm2;
             float dxyz[3];
 #pragma unroll
             for (int j = 0; j < 3; ++j) dxyz[j] = Rt[j] * dp0 + Rt[3 + j] * dp1 + Rt[6 + j] * dp2;
-            ao += a.dopacity[i];
+            ao += gA.w;
             // colour (render.py:3341-3355)
             const float dn = sqrtf(d0 * d0 + d1 * d1 + d2 * d2);
             const float dni = 1.0f / dn;
             const float x = d0 * dni, y = d1 * dni, zz_ = d2 * dni;
-            float cg[3] = {a.dcolor[i * 3], a.dcolor[i * 3 + 1], a.dcolor[i * 3 + 2]};
+            float cg[3] = {gB.x, gB.y, gB.z};
             const uint8_t m = a.ctx.sh_to_rgb_ne_0[i];
             if (cf.clamp_mask_reference_order) {   // bit k gates channel k (render.py:3344-3350)
                 if (m & 1) cg[0] = 0.f;
@@ -202,9 +255,11 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
                 for (int k = 1; k < NB; ++k) {
 #pragma unroll
                     for (int ch = 0; ch < 3; ++ch) {
-                        arest[(k - 1) * 3 + ch] += bs[k] * cg[ch];
-                        const float coef = __ldg(rest + (k - 1) * 3 + ch) * cg[ch];
+                        const int e = (k - 1) * 3 + ch;
+                        const float coef = my_in[e] * cg[ch];
                         ddx += gx[k] * coef; ddy += gy[k] * coef; ddz += gz[k] * coef;
+                        if (MULTI) my_out[e] += bs[k] * cg[ch];
+                        else my_out[e] = bs[k] * cg[ch];   // in place: the coefficient was just consumed
                     }
                 }
             }
@@ -240,18 +295,38 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
         aq[2] = (dq[2] - qz * dot) * qni; aq[3] = (dq[3] - qw * dot) * qni;
         if (fused) ao = ao * opac * (1.0f - opac);   // sigmoid_grad_out: g * out * (1 - out)
     }
-    a.grad.xyz[g * 3] = axyz[0]; a.grad.xyz[g * 3 + 1] = axyz[1]; a.grad.xyz[g * 3 + 2] = axyz[2];
-    *reinterpret_cast<float4*>(a.grad.quaternion_xyzw + g * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
-    a.grad.scale[g * 3] = as[0]; a.grad.scale[g * 3 + 1] = as[1]; a.grad.scale[g * 3 + 2] = as[2];
-    a.grad.opacity[g] = ao;
-    float* gb = a.grad.sh_base + g * a.grad.sh_base_stride;
-    gb[0] = abase[0]; gb[1] = abase[1]; gb[2] = abase[2];
+    if (g < N) {
+        a.grad.xyz[g * 3] = axyz[0]; a.grad.xyz[g * 3 + 1] = axyz[1]; a.grad.xyz[g * 3 + 2] = axyz[2];
+        *reinterpret_cast<float4*>(a.grad.quaternion_xyzw + g * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
+        a.grad.scale[g * 3] = as[0]; a.grad.scale[g * 3 + 1] = as[1]; a.grad.scale[g * 3 + 2] = as[2];
+        a.grad.opacity[g] = ao;
+        float* gb = a.grad.sh_base + g * a.grad.sh_base_stride;
+        gb[0] = abase[0]; gb[1] = abase[1]; gb[2] = abase[2];
+    }
     if (a.grad.sh_rest != nullptr) {
-        float* gr = a.grad.sh_rest + g * a.grad.sh_rest_stride;
-        const int total_rest = a.grad.sh_rest_floats;
+        // rows leave shared memory as one bulk async store when the destination span is contiguous and
+        // aligned, else with coalesced per-element stores; coefficients above the active degree are zero
+        const int rf = a.grad.sh_rest_floats;
+        const int64_t stride = a.grad.sh_rest_stride;
+        const bool bulk_out = rf == 45 && stride == 45 && (rows & 3) == 0 &&
+                              ((uintptr_t)(a.grad.sh_rest + g0 * 45) & 15) == 0;
+        if (bulk_out) {
 #pragma unroll
-        for (int k = 0; k < NR * 3; ++k) gr[k] = arest[k];
-        for (int k = NR * 3; k < total_rest; ++k) gr[k] = 0.f;   // inactive higher degrees
+            for (int k = NR3; k < 45; ++k) my_out[k] = 0.0f;
+            fence_proxy_async_smem();   // generic-proxy writes to shared memory -> visible to the copy engine
+            __syncthreads();
+            if (t == 0) {
+                bulk_copy_s2g(a.grad.sh_rest + g0 * 45, s_out, (uint32_t)rows * 180u);
+                bulk_commit_group();
+                bulk_wait_group_read0();
+            }
+        } else {
+            __syncthreads();
+            for (int f = t; f < rows * rf; f += 256) {
+                const int row = f / rf, k = f - row * rf;
+                a.grad.sh_rest[(g0 + row) * stride + k] = k < NR3 ? s_out[row * kRow + k] : 0.0f;
+            }
+        }
     }
 }
 
@@ -261,14 +336,13 @@ __global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_consta
 using namespace d3gs;
 
 extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model,
-                                            const D3gsSplatContext* ctx, const float* duv, const float* dconic,
-                                            const float* dopacity, const float* dcolor, const D3gsModelGrad* grad,
-                                            void* stream) {
+                                            const D3gsSplatContext* ctx, const float* splat_grads,
+                                            const D3gsModelGrad* grad, void* stream) {
     D3GS_REQUIRE(cfg && model && ctx && grad, "NULL argument");
     D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= D3GS_MAX_VIEWS, "num_views %d outside [1,%d]", cfg->num_views,
                  D3GS_MAX_VIEWS);
     D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
-    D3GS_REQUIRE(duv && dconic && dopacity && dcolor, "NULL raster gradient");
+    D3GS_REQUIRE(splat_grads != nullptr && ((uintptr_t)splat_grads & 15) == 0, "splat_grads NULL or not 16-byte aligned");
     D3GS_REQUIRE(ctx->radii && ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0, "context lacks radii/cov2d_vecs/sh_to_rgb_ne_0");
     D3GS_REQUIRE(grad->xyz && grad->quaternion_xyzw && grad->scale && grad->opacity && grad->sh_base,
                  "NULL gradient output");
@@ -286,18 +360,28 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     a.model = *model;
     a.ctx = *ctx;
     a.grad = *grad;
-    a.duv = duv;
-    a.dconic = dconic;
-    a.dopacity = dopacity;
-    a.dcolor = dcolor;
+    a.splat_grads = splat_grads;
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
-    switch (cfg->sh_degree) {
-        case 0: preprocess_bwd_kernel<0><<<grid, 256, 0, s>>>(a); break;
-        case 1: preprocess_bwd_kernel<1><<<grid, 256, 0, s>>>(a); break;
-        case 2: preprocess_bwd_kernel<2><<<grid, 256, 0, s>>>(a); break;
-        default: preprocess_bwd_kernel<3><<<grid, 256, 0, s>>>(a); break;
+    const bool multi = cfg->num_views > 1;
+    const size_t smem = (size_t)256 * kRow * sizeof(float) * (multi ? 2 : 1);
+#define D3GS_LAUNCH_BWD(DEG, MULTI)                                                                              \
+    do {                                                                                                         \
+        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       (int)smem));                                                              \
+        preprocess_bwd_kernel<DEG, MULTI><<<grid, 256, smem, s>>>(a);                                            \
+    } while (0)
+    switch (cfg->sh_degree * 2 + (multi ? 1 : 0)) {
+        case 0: D3GS_LAUNCH_BWD(0, false); break;
+        case 1: D3GS_LAUNCH_BWD(0, true); break;
+        case 2: D3GS_LAUNCH_BWD(1, false); break;
+        case 3: D3GS_LAUNCH_BWD(1, true); break;
+        case 4: D3GS_LAUNCH_BWD(2, false); break;
+        case 5: D3GS_LAUNCH_BWD(2, true); break;
+        case 6: D3GS_LAUNCH_BWD(3, false); break;
+        default: D3GS_LAUNCH_BWD(3, true); break;
     }
+#undef D3GS_LAUNCH_BWD
     D3GS_LAUNCH_CHECK("preprocess_bwd_kernel");
     return D3GS_OK;
 }

@@ -2,21 +2,34 @@
 //
 // Reference semantics: d3sim/algos/d3gs/render.py:1329-2316 (forward is_bwd=False; backward
 // 1589-1676 + 1774-2210).  One CTA of 256 threads per 16x16 tile, one pixel per thread, pixels laid
-// out 8x4 per warp (render.py:1503-1512).  The tile's sorted list of 48-byte splat records is
-// streamed through shared memory with bulk async copies (cp.async.bulk + mbarrier, double
-// buffered) instead of the reference's per-thread gathers (render.py:1699-1716).
+// out 8x4 per warp (render.py:1503-1512).
+//
+// What is different from the reference's kernel, and why:
+//  * The tile's sorted list of 48-byte splat records is streamed through shared memory with bulk
+//    async copies (cp.async.bulk + mbarrier, double buffered) instead of per-thread gathers
+//    (render.py:1699-1716).
+//  * Both kernels were instruction-issue bound when every warp walked every record.  Now the 32
+//    lanes of a warp first test 32 records at once against the warp's 8x4 pixel block (each record
+//    carries a conservative bounding box of its alpha >= 1/255 region), ballot, and only the
+//    surviving records are visited, still in front-to-back order.
+//  * Backward: the nine per-splat partial derivatives are reduced over the warp with a
+//    transposing butterfly (14 shuffles instead of 45), accumulated per CTA in shared memory, and
+//    leave the CTA as three vector atomic adds per (tile, splat) instead of the reference's nine
+//    scalar atomics per warp (render.py:2061-2148).
 //
 // The arithmetic that decides n_contrib -- power, exp, alpha, the transmittance product and the
 // three threshold compares -- is written with explicit round-to-nearest intrinsics so that its
-// bits are defined (see common.cuh); colour accumulation uses explicit fma as well.
+// bits are defined (see common.cuh); skipping a record by its bounding box or by `power < thr`
+// never changes a result because both imply alpha < alpha_eps.
 #include "common.cuh"
 
 namespace d3gs {
 namespace {
 
 constexpr int kBatch = 256;                        // records per staged batch
-constexpr int kRecFloat4 = 3;                      // 48 bytes
+constexpr int kRecFloat4 = 3;                      // 48 bytes: [u v hx hy][ha nb hc o][r g b thr]
 constexpr uint32_t kRecBytes = kRecFloat4 * 16;
+constexpr int kGradFloats = D3GS_SPLAT_GRAD_FLOATS;   // 12: [dconic a b c, dopacity][dcolor r g b, 0][duv x y, 0 0]
 
 struct RasterArgs {
     int width, height, tiles_x, tiles_y;
@@ -25,6 +38,7 @@ struct RasterArgs {
     int training;
     const int32_t* ranges;
     const float4* records;
+    const int32_t* sorted_ids;
     uint32_t* status;
     // forward outputs / backward inputs
     float* color;
@@ -33,10 +47,7 @@ struct RasterArgs {
     // backward
     const float* drgb;
     const float* dT;
-    float* duv;
-    float* dconic;
-    float* dopacity;
-    float* dcolor;
+    float* splat_grads;
 };
 
 struct PixelCoord {
@@ -61,6 +72,18 @@ __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, ui
     bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
 }
 
+// Bit mask of the records [g*32, g*32+32) of the staged batch whose bounding box overlaps this
+// warp's 8x4 pixel block.  hx/hy in the record already include the block's half size.
+__device__ __forceinline__ uint32_t cull_group(const float4* rec, int g, int limit, float wcx, float wcy) {
+    const int j = g * 32 + (threadIdx.x & 31);
+    bool hit = false;
+    if (j < limit) {
+        const float4 q0 = rec[j * 3];
+        hit = fabsf(q0.x - wcx) <= q0.z && fabsf(q0.y - wcy) <= q0.w;
+    }
+    return __ballot_sync(0xffffffffu, hit);
+}
+
 __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
@@ -79,6 +102,8 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, n, 0);
 
     const float fpx = (float)pc.px, fpy = (float)pc.py;
+    const float wcx = (float)(blockIdx.x * 16 + ((t >> 5) & 1) * 8) + 3.5f;
+    const float wcy = (float)(blockIdx.y * 16 + (t >> 6) * 4) + 1.5f;
     bool done = !pc.inside;
     float T = 1.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f;
     int contributor = 0;
@@ -96,14 +121,19 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
         }
         const int cnt = min(kBatch, n - b * kBatch);
         const float4* rec = s_rec[cur];
-        if (!__all_sync(0xffffffffu, done)) {
-            for (int j = 0; j < cnt; ++j) {
-                const float4 q0 = rec[j * 3];       // u, v, thr, id
+        for (int g = 0; g * 32 < cnt; ++g) {
+            if (__all_sync(0xffffffffu, done)) break;
+            uint32_t m = cull_group(rec, g, cnt, wcx, wcy);
+            while (m) {
+                const int j = g * 32 + __ffs(m) - 1;
+                m &= m - 1;
+                const float4 q0 = rec[j * 3];       // u, v, hx, hy
                 const float4 q1 = rec[j * 3 + 1];   // ha, nb, hc, opacity
+                const float4 q2 = rec[j * 3 + 2];   // r, g, b, thr
                 const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
                 const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
                 // power < thr  =>  alpha < alpha_eps: the pixel skips this splat (render.py:1796-1798)
-                const bool cand = !done && power >= q0.z;
+                const bool cand = !done && power >= q2.w;
                 if (!__any_sync(0xffffffffu, cand)) continue;
                 if (cand) {
                     const float G = blend_exp(power);
@@ -117,7 +147,6 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
                             const float w = f_mul(alpha, T);
                             T = nT;
                             contributor = b * kBatch + j;   // render.py:1836
-                            const float4 q2 = rec[j * 3 + 2];
                             C0 = f_fma(w, q2.x, C0);
                             C1 = f_fma(w, q2.y, C1);
                             C2 = f_fma(w, q2.z, C2);
@@ -144,20 +173,21 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     }
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+__device__ __forceinline__ float shfl_x(float v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float x, float y, float z, float w) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float* addr, float x, float y) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(x), "f"(y) : "memory");
 }
 
 // Backward.  Per pixel the blend is replayed front to back (T from 1, colour suffix = final -
-// prefix, render.py:1868-1895); the nine per-splat partial derivatives are summed over the warp by
-// shuffles, over the CTA in shared memory, and leave the CTA as ONE atomic add per (tile, splat,
-// component) instead of the reference's one per warp (render.py:2061-2148).
+// prefix, render.py:1868-1895).
 __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
-    __shared__ float s_acc[kBatch][9];
+    __shared__ float s_acc[kBatch][9];   // per record: dconic a b c, dopacity, dcolor r g b, duv x y
     __shared__ int s_max[8];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const PixelCoord pc = pixel_of_thread(a);
@@ -191,11 +221,19 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, bmax, 0);
 
     const float fpx = (float)pc.px, fpy = (float)pc.py;
+    const float wcx = (float)(blockIdx.x * 16 + (warp & 1) * 8) + 3.5f;
+    const float wcy = (float)(blockIdx.y * 16 + (warp >> 1) * 4) + 1.5f;
+    const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
+    // after the butterfly, the four lanes of group (lane>>2) hold the total of component `slot`
+    const int slot = (h16 ? 4 : 0) + (h8 ? 2 : 0) + (h4 ? 1 : 0);
     float T = 1.0f;
     bool copy_failed = false;
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
         if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
+        const int cnt = min(kBatch, bmax - b * kBatch);
+        int32_t my_id = 0;
+        if (t < cnt) my_id = a.sorted_ids[r0 + b * kBatch + t];
 #pragma unroll
         for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;
         if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
@@ -203,73 +241,82 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
             if (b + 1 < nb) mbar_wait_bounded(&s_bar[cur ^ 1], (uint32_t)(((b + 1) >> 1) & 1));
             break;
         }
-        const int cnt = min(kBatch, bmax - b * kBatch);
         const float4* rec = s_rec[cur];
-        const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform
-        for (int j = 0; j < wlim; ++j) {
-            const float4 q0 = rec[j * 3];
-            const float4 q1 = rec[j * 3 + 1];
-            const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
-            const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
-            // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
-            const bool cand = (b * kBatch + j < contributor) && power >= q0.z && power <= 0.0f;
-            if (!__any_sync(0xffffffffu, cand)) continue;
-            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f, v8 = 0.f;
-            bool valid = false;
-            if (cand) {
-                const float G = blend_exp(power);
-                const float alpha = fminf(0.99f, f_mul(q1.w, G));
-                if (alpha >= a.alpha_eps) {
-                    valid = true;
-                    const float nT = f_mul(T, f_sub(1.0f, alpha));
-                    const float w = f_mul(alpha, T);
-                    T = nT;
-                    const float4 q2 = rec[j * 3 + 2];
-                    rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
-                    float dl = dr0 * fmaf(T, q2.x, -rr0);
-                    dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
-                    dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
-                    dl -= dTT;
-                    const float dL_dalpha = dl / (1.0f - alpha);          // render.py:1957
-                    const float dL_dG = q1.w * dL_dalpha;                 // render.py:1995
-                    const float gdx = G * dx, gdy = G * dy;
-                    const float ca = -2.0f * q1.x, cb = -q1.y, cc = -2.0f * q1.z;
-                    v0 = dL_dG * (-gdx * ca - gdy * cb);                  // render.py:2001-2006
-                    v1 = dL_dG * (-gdy * cc - gdx * cb);
-                    v2 = -0.5f * gdx * dx * dL_dG;                        // render.py:2013-2017
-                    v3 = -gdx * dy * dL_dG;
-                    v4 = -0.5f * gdy * dy * dL_dG;
-                    v5 = dL_dalpha * G;                                   // render.py:2018
-                    v6 = w * dr0; v7 = w * dr1; v8 = w * dr2;             // render.py:1962
+        const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
+        for (int g = 0; g * 32 < wlim; ++g) {
+            uint32_t m = cull_group(rec, g, wlim, wcx, wcy);
+            while (m) {
+                const int j = g * 32 + __ffs(m) - 1;
+                m &= m - 1;
+                const float4 q0 = rec[j * 3];
+                const float4 q1 = rec[j * 3 + 1];
+                const float4 q2 = rec[j * 3 + 2];
+                const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
+                const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
+                // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
+                const bool cand = (b * kBatch + j < contributor) && power >= q2.w && power <= 0.0f;
+                if (!__any_sync(0xffffffffu, cand)) continue;
+                float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f, v8 = 0.f;
+                bool valid = false;
+                if (cand) {
+                    const float G = blend_exp(power);
+                    const float alpha = fminf(0.99f, f_mul(q1.w, G));
+                    if (alpha >= a.alpha_eps) {
+                        valid = true;
+                        const float oma = f_sub(1.0f, alpha);
+                        const float w = f_mul(alpha, T);
+                        T = f_mul(T, oma);
+                        rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
+                        float dl = dr0 * fmaf(T, q2.x, -rr0);
+                        dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
+                        dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
+                        dl -= dTT;
+                        const float dL_dalpha = __fdividef(dl, oma);          // render.py:1957
+                        const float dL_dG = q1.w * dL_dalpha;                 // render.py:1995
+                        const float gdx = G * dx, gdy = G * dy;
+                        // conic = (-2 ha, -nb, -2 hc); render.py:2001-2017
+                        v0 = gdx * dx * dL_dG * -0.5f;                        // dconic a
+                        v1 = -gdx * dy * dL_dG;                               // dconic b
+                        v2 = gdy * dy * dL_dG * -0.5f;                        // dconic c
+                        v3 = dL_dalpha * G;                                   // dopacity, render.py:2018
+                        v4 = w * dr0; v5 = w * dr1; v6 = w * dr2;             // dcolor, render.py:1962
+                        v7 = dL_dG * fmaf(2.0f * gdx, q1.x, gdy * q1.y);      // duv x = dL_dG (-gdx a - gdy b)
+                        v8 = dL_dG * fmaf(2.0f * gdy, q1.z, gdx * q1.y);      // duv y = dL_dG (-gdy c - gdx b)
+                    }
                 }
-            }
-            if (!__any_sync(0xffffffffu, valid)) continue;
-            v0 = warp_sum(v0); v1 = warp_sum(v1); v2 = warp_sum(v2); v3 = warp_sum(v3); v4 = warp_sum(v4);
-            v5 = warp_sum(v5); v6 = warp_sum(v6); v7 = warp_sum(v7); v8 = warp_sum(v8);
-            if (lane == 0) {
-                float* acc = s_acc[j];
-                atomicAdd(acc + 0, v0); atomicAdd(acc + 1, v1); atomicAdd(acc + 2, v2);
-                atomicAdd(acc + 3, v3); atomicAdd(acc + 4, v4); atomicAdd(acc + 5, v5);
-                atomicAdd(acc + 6, v6); atomicAdd(acc + 7, v7); atomicAdd(acc + 8, v8);
+                if (!__any_sync(0xffffffffu, valid)) continue;
+                // transposing butterfly: 8 components in 9 shuffles, the ninth in 5
+                const float a0 = (h16 ? v4 : v0) + shfl_x(h16 ? v0 : v4, 16);
+                const float a1 = (h16 ? v5 : v1) + shfl_x(h16 ? v1 : v5, 16);
+                const float a2 = (h16 ? v6 : v2) + shfl_x(h16 ? v2 : v6, 16);
+                const float a3 = (h16 ? v7 : v3) + shfl_x(h16 ? v3 : v7, 16);
+                const float b0 = (h8 ? a2 : a0) + shfl_x(h8 ? a0 : a2, 8);
+                const float b1 = (h8 ? a3 : a1) + shfl_x(h8 ? a1 : a3, 8);
+                float c = (h4 ? b1 : b0) + shfl_x(h4 ? b0 : b1, 4);
+                c += shfl_x(c, 2);
+                c += shfl_x(c, 1);
+                v8 += shfl_x(v8, 16);
+                v8 += shfl_x(v8, 8);
+                v8 += shfl_x(v8, 4);
+                v8 += shfl_x(v8, 2);
+                v8 += shfl_x(v8, 1);
+                // nine lanes, nine different addresses: one shared-memory atomic instruction
+                const bool ninth = lane == 1;
+                if ((lane & 3) == 0 || ninth) atomicAdd(&s_acc[j][ninth ? 8 : slot], ninth ? v8 : c);
             }
         }
         __syncthreads();
         if (t < cnt) {
             const float* acc = s_acc[t];
-            bool any = false;
-#pragma unroll
-            for (int k = 0; k < 9; ++k) any |= acc[k] != 0.0f;
+            const float g0 = acc[0], g1 = acc[1], g2 = acc[2], g3 = acc[3], g4 = acc[4], g5 = acc[5], g6 = acc[6],
+                        g7 = acc[7], g8 = acc[8];
+            const bool any = (g0 != 0.f) | (g1 != 0.f) | (g2 != 0.f) | (g3 != 0.f) | (g4 != 0.f) | (g5 != 0.f) |
+                             (g6 != 0.f) | (g7 != 0.f) | (g8 != 0.f);
             if (any) {
-                const int64_t id = __float_as_int(rec[t * 3].w);
-                atomicAdd(a.duv + id * 2, acc[0]);
-                atomicAdd(a.duv + id * 2 + 1, acc[1]);
-                atomicAdd(a.dconic + id * 3, acc[2]);
-                atomicAdd(a.dconic + id * 3 + 1, acc[3]);
-                atomicAdd(a.dconic + id * 3 + 2, acc[4]);
-                atomicAdd(a.dopacity + id, acc[5]);
-                atomicAdd(a.dcolor + id * 3, acc[6]);
-                atomicAdd(a.dcolor + id * 3 + 1, acc[7]);
-                atomicAdd(a.dcolor + id * 3 + 2, acc[8]);
+                float* dst = a.splat_grads + (int64_t)my_id * kGradFloats;
+                red_add_v4(dst, g0, g1, g2, g3);
+                red_add_v4(dst + 4, g4, g5, g6, 0.0f);
+                red_add_v2(dst + 8, g7, g8);
             }
         }
         __syncthreads();
@@ -319,35 +366,30 @@ extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* r
 }
 
 extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges,
-                                        const float* records, const float* color, const float* final_T,
-                                        const int32_t* n_contrib, const float* drgb, const float* dT, float* duv,
-                                        float* dconic, float* dopacity, float* dcolor, uint32_t* status,
-                                        void* stream) {
+                                        const float* records, const int32_t* sorted_values, const float* color,
+                                        const float* final_T, const int32_t* n_contrib, const float* drgb,
+                                        const float* dT, float* splat_grads, uint32_t* status, void* stream) {
     RasterArgs a = {};
     int32_t rc = fill_args(cfg, a);
     if (rc != D3GS_OK) return rc;
-    D3GS_REQUIRE(ranges && color && final_T && n_contrib && drgb && status, "NULL argument");
-    D3GS_REQUIRE(duv && dconic && dopacity && dcolor, "NULL gradient output");
+    D3GS_REQUIRE(ranges && sorted_values && color && final_T && n_contrib && drgb && status, "NULL argument");
+    D3GS_REQUIRE(splat_grads != nullptr, "NULL gradient output");
     D3GS_REQUIRE(((uintptr_t)records & 15) == 0, "records must be 16-byte aligned");
+    D3GS_REQUIRE(((uintptr_t)splat_grads & 15) == 0, "splat_grads must be 16-byte aligned");
     D3GS_REQUIRE(num >= 0, "negative Gaussian count");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t bn = (size_t)num * cfg->num_views;
-    D3GS_CUDA(cudaMemsetAsync(duv, 0, bn * 2 * sizeof(float), s));
-    D3GS_CUDA(cudaMemsetAsync(dconic, 0, bn * 3 * sizeof(float), s));
-    D3GS_CUDA(cudaMemsetAsync(dopacity, 0, bn * sizeof(float), s));
-    D3GS_CUDA(cudaMemsetAsync(dcolor, 0, bn * 3 * sizeof(float), s));
+    D3GS_CUDA(cudaMemsetAsync(splat_grads, 0, bn * kGradFloats * sizeof(float), s));
     a.ranges = ranges;
     a.records = reinterpret_cast<const float4*>(records);
+    a.sorted_ids = sorted_values;
     a.status = status;
     a.color = const_cast<float*>(color);
     a.final_T = const_cast<float*>(final_T);
     a.n_contrib = const_cast<int32_t*>(n_contrib);
     a.drgb = drgb;
     a.dT = dT;
-    a.duv = duv;
-    a.dconic = dconic;
-    a.dopacity = dopacity;
-    a.dcolor = dcolor;
+    a.splat_grads = splat_grads;
     dim3 grid(a.tiles_x, a.tiles_y, cfg->num_views);
     raster_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("raster_backward_kernel");

@@ -81,6 +81,8 @@ class RasterizeGradientOutput:
     dcolor: torch.Tensor | None
     dcustom_features: torch.Tensor | None = None
     dz: torch.Tensor | None = None
+    # not in the reference: the [B*N,12] array the four tensors above are views of
+    packed: torch.Tensor | None = None
 
 
 @dataclasses.dataclass
@@ -396,11 +398,8 @@ class GaussianSplatOp:
         num = BN // B
         drgb = grad.drgb
         assert drgb.is_contiguous(), "drgb must be contiguous"
-        f32 = torch.float32
-        duv = torch.empty([BN, 2], dtype=f32, device=dev)
-        dconic = torch.empty([BN, 3], dtype=f32, device=dev)
-        dopacity = torch.empty([BN], dtype=f32, device=dev)
-        dcolor = torch.empty([BN, 3], dtype=f32, device=dev)
+        # packed per-splat gradients [BN,12]: dconic a b c, dopacity | dcolor r g b, 0 | duv x y, 0 0
+        packed = torch.empty([BN, 12], dtype=torch.float32, device=dev)
         ocfg = _lib.OpConfig()
         ocfg.width, ocfg.height, ocfg.tile_x, ocfg.tile_y = W, H, 16, 16
         ocfg.alpha_eps, ocfg.transmittance_eps = self._cfg.alpha_eps, self._cfg.transmittance_eps
@@ -410,12 +409,14 @@ class GaussianSplatOp:
         if dT is not None:
             dT = dT.contiguous()
         _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
-                                            ctx.splat_records.data_ptr(), out.color.data_ptr(), out.T.data_ptr(),
-                                            out.n_contrib.data_ptr(), drgb.data_ptr(), _lib.ptr(dT), duv.data_ptr(),
-                                            dconic.data_ptr(), dopacity.data_ptr(), dcolor.data_ptr(),
-                                            sync.data_ptr() + 8, stream), "d3gs_raster_backward")
+                                            ctx.splat_records.data_ptr(), ctx.gaussian_idx_sorted.data_ptr(),
+                                            out.color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
+                                            drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
+                                            stream), "d3gs_raster_backward")
         self._mark("raster_bwd")
-        return RasterizeGradientOutput(duv=duv, dconic=dconic, dopacity=dopacity, dcolor=dcolor)
+        # the reference's four tensors (render.py:1412-1418) are views of the packed array
+        return RasterizeGradientOutput(duv=packed[:, 8:10], dconic=packed[:, 0:3], dopacity=packed[:, 3],
+                                       dcolor=packed[:, 4:7], packed=packed)
 
     # ---- backward (render.py:2779-3374) --------------------------------------------------------
     def backward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
@@ -458,12 +459,12 @@ class GaussianSplatOp:
         mstruct = self._model_struct(model)
         cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
                                    ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
-        _lib.check(lib.d3gs_preprocess_backward(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct), rg.duv.data_ptr(),
-                                                rg.dconic.data_ptr(), rg.dopacity.data_ptr(), rg.dcolor.data_ptr(),
-                                                C.byref(g), stream), "d3gs_preprocess_backward")
+        _lib.check(lib.d3gs_preprocess_backward(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct),
+                                                rg.packed.data_ptr(), C.byref(g), stream), "d3gs_preprocess_backward")
         self._mark("preprocess_bwd")
         if return_uv_grad:
-            return grad_out, rg.duv.view(B, -1, 2), None
+            # [B,N,2] strided view of the packed array (the reference returns duv.view(B,-1,2), render.py:3373)
+            return grad_out, rg.packed.view(B, -1, 12)[:, :, 8:10], None
         return grad_out, None, None
 
 

@@ -63,7 +63,7 @@ class GaussianStrategyOrigin:
         assert out.radii is not None and out.sparse_gaussian_ids is None
         # the kernel indexes radii flat as view*N + gaussian (origin/strategy.py:102-104); the op returns
         # radii 1-D (render.py:642) and both 1-D and [B,N] are accepted here
-        return make_stats_struct(state, out.radii.reshape(-1), duv.contiguous(), width, height,
+        return make_stats_struct(state, out.radii.reshape(-1), duv, width, height,
                                  self.refine_scale2d_stop_iter > 0)
 
     @torch.no_grad()

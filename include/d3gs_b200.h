@@ -28,7 +28,8 @@ extern "C" {
 #endif
 
 #define D3GS_MAX_VIEWS 8          /* views per launch (CameraBundle batch, render.py:129-150) */
-#define D3GS_SPLAT_RECORD_FLOATS 12
+#define D3GS_SPLAT_RECORD_FLOATS 12   /* staged splat record: [u v hx hy][ha nb hc opacity][r g b thr] */
+#define D3GS_SPLAT_GRAD_FLOATS 12     /* packed per-splat raster gradient, see d3gs_raster_backward */
 
 /* error codes */
 #define D3GS_OK 0
@@ -166,17 +167,19 @@ int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, cons
                             float* final_T, int32_t* n_contrib, uint32_t* status, void* stream);
 
 /* ---- K7 raster backward (render.py:1589-1676, 1774-2210) -------------------------------- */
-/* drgb [B,H,W,3], dT [B,H,W] or NULL; outputs [B*N,*] are zero-filled by this call */
+/* drgb [B,H,W,3], dT [B,H,W] or NULL.  The reference's four per-splat gradient tensors (duv, dconic,
+ * dopacity, dcolor, render.py:1388-1401) are one packed array here so that the kernel can use 16-byte
+ * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, 0 | duv x,y, 0, 0},
+ * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort. */
 int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const float* records,
-                             const float* color, const float* final_T, const int32_t* n_contrib,
-                             const float* drgb, const float* dT, float* duv, float* dconic, float* dopacity,
-                             float* dcolor, uint32_t* status, void* stream);
+                             const int32_t* sorted_values, const float* color, const float* final_T,
+                             const int32_t* n_contrib, const float* drgb, const float* dT, float* splat_grads,
+                             uint32_t* status, void* stream);
 
 /* ---- K8 preprocess backward (render.py:2779-3374) ---------------------------------------- */
 /* every gradient element is written (zeros for culled Gaussians); sums over the view batch */
 int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
-                                 const float* duv, const float* dconic, const float* dopacity,
-                                 const float* dcolor, const D3gsModelGrad* grad, void* stream);
+                                 const float* splat_grads, const D3gsModelGrad* grad, void* stream);
 
 /* ---- K9/K10 SSIM map and fused L1 + D-SSIM (fused_ssim.py:93-416, losses.py:19-20) ---------- */
 /* ssim map forward: x NHWC or NCHW [B,3,H,W]/[B,H,W,3], y NCHW; outputs NCHW; dmu* may be NULL */
@@ -208,7 +211,7 @@ typedef struct D3gsAdamSegment {
 } D3gsAdamSegment;
 
 typedef struct D3gsDensifyStats {
-    const float* duv;          /* [B,N,2] */
+    const float* duv;          /* (view, Gaussian) pair k at duv + k*duv_stride: 2 floats */
     const int32_t* radii;      /* [B*N] */
     float* duv_ndc_length;     /* [N] */
     float* count;              /* [N] */
@@ -218,7 +221,8 @@ typedef struct D3gsDensifyStats {
     int32_t loss_batch;        /* views the loss was averaged over (duv is scaled back by it,
                                   origin/strategy.py:105-106); 0 = same as batch.  Larger than batch when the
                                   view batch is spread over several GPUs. */
-    int32_t reserved;
+    int32_t duv_stride;        /* floats between consecutive pairs: 2 for a dense [B,N,2] tensor, 12 when duv is
+                                  read in place from splat_grads + 8; 0 = 2 */
 } D3gsDensifyStats;
 
 /* one launch over up to 8 parameter tensors; stats may be NULL */
