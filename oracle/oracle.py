@@ -308,3 +308,19 @@ def run_iteration(cfg: OpConfig, sc: Scene, target_nchw, lambda_dssim: float, ad
         densify_stats(sc.b, sc.n, cfg.width, cfg.height, stats.get("need_max_radii", False), duv, res.prep["radii"],
                       stats["duv_ndc_length"], stats["count"], stats["max_radii"])
     return res
+
+
+def sh_eval(deg: int, dirs, base, rest):
+    """SH colour INCLUDING the +0.5 offset, no clamp (gs3d.py:151-201). rest: [n,15,3]."""
+    n = dirs.shape[0]
+    out = np.zeros((n, 3), np.float32)
+    lib().oracle_sh_eval(ctypes.c_int(deg), ctypes.c_int(n), _p(_f32(dirs)), _p(_f32(base)), _p(_f32(rest)), _p(out))
+    return out
+
+
+def cov3d(quat_xyzw, scale_act):
+    n = quat_xyzw.shape[0]
+    cov6 = np.zeros((n, 6), np.float32)
+    rot = np.zeros((n, 3, 3), np.float32)
+    lib().oracle_cov3d(ctypes.c_int(n), _p(_f32(quat_xyzw)), _p(_f32(scale_act)), _p(cov6), _p(rot))
+    return cov6, rot

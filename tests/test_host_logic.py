@@ -1,0 +1,138 @@
+"""Host-side logic that needs no GPU: configuration, containers, cameras, scenes, data-parallel semantics."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import d3gs_research_b200 as d3
+from d3gs_research_b200 import scenes
+from d3gs_research_b200.model import FLAT_ORDER, carve_flat
+
+
+def test_config_defaults_follow_reference():
+    c = d3.GaussianSplatConfig()
+    assert c.tile_size == (16, 16) and c.near == 0.2 and c.far == 10000.0 and c.alpha_eps == 1.0 / 255.0
+    assert c.gaussian_lowpass_filter == 0.3 and c.gaussian_std_sigma == 3.0 and c.projected_clamp_factor == 1.3
+    assert c.early_filter_algo == d3.EarlyFilterAlgo.OBB_DFVT and c.num_channels == 3 and c.block_size == 256
+    assert c.unsupported_options() == []
+    t = d3.Train(batch_size=4)
+    t.rescale_steps_by_batch_size(4)
+    assert t.iterations == 7500 and t.optim.position_lr_max_steps == 7500 and t.strategy.refine_every == 25
+
+
+@pytest.mark.parametrize("kw", [dict(enable_32bit_sort=True), dict(render_depth=True), dict(use_nchw=True),
+                                dict(sparse_mode=True), dict(tile_size=(8, 8)), dict(enable_anti_aliasing=True),
+                                dict(early_filter_algo=d3.EarlyFilterAlgo.ELLIPSE),
+                                dict(rasterize_backward_algo=d3.RasterizeBackwardAlgo.PER_GAUSSIAN)])
+def test_unsupported_options_raise_at_construction(kw):
+    from d3gs_research_b200.render import GaussianSplatOp
+    with pytest.raises(NotImplementedError):
+        GaussianSplatOp(d3.GaussianSplatConfig(**kw))
+
+
+def test_flat_model_views_and_containers():
+    n = 10
+    flat = torch.arange(59 * n, dtype=torch.float32)
+    v = carve_flat(flat, n)
+    assert [tuple(v[k].shape) for k in FLAT_ORDER] == [(n, 3), (n, 4), (n, 3), (n,), (n, 3), (n, 15, 3)]
+    assert v["xyz"].data_ptr() == flat.data_ptr() and v["color_sh"][-1, -1, -1] == 59 * n - 1
+    m = d3.GaussianModelOriginFused.create_flat(n, device="cpu")
+    assert len(m) == n and m.color_sh_degree == 3 and m.has_fused_activations and m.flat.numel() == 59 * n
+    assert m.get_unique_kernel_key() == "3_3_normalize_exponential_sigmoid_False"
+    z = d3.GaussianModelOriginFused.zeros_like(m, num=4, not_param=True)
+    assert len(z) == 4 and z.color_sh.shape == (4, 15, 3)
+    assert len(m.concat(z)) == 14 and len(m[2:5]) == 3
+    mp = m.to_parameter()
+    assert isinstance(mp.xyz, torch.nn.Parameter) and set(mp.get_all_parameter_fields()) >= {"xyz", "opacity"}
+    o = d3.GaussianModelOrigin.zeros(3, 3, split=True)
+    o.scale.fill_(0.5)
+    act = o.create_model_with_act()
+    assert act.act_applied and torch.allclose(act.scale, torch.exp(torch.tensor(0.5))) and not o.has_fused_activations
+    assert torch.allclose(act.opacity, torch.tensor(0.5))
+
+
+def test_camera_packing_matches_reference_layout():
+    from d3gs_research_b200.render import CameraBundle, _camera_rows
+    c2w = scenes.look_at_cam2world([1.0, 2.0, 8.0])
+    cam = d3.BasicPinholeCamera.from_params(c2w, 500.0, 510.0, 320.0, 240.0, 640, 480)
+    row = _camera_rows(cam)[0]
+    np.testing.assert_allclose(row[:12].reshape(4, 3), c2w[:3].T, rtol=1e-6)      # render.py:205
+    np.testing.assert_allclose(row[12:], [500, 510, 320, 240])
+    np.testing.assert_allclose(cam.focal_length, [500, 510])
+    b = CameraBundle.from_pinhole_cams([cam, cam], device="cpu")
+    assert tuple(b.cam2world_T.shape) == (2, 4, 3) and tuple(b.focal_xy_ppoint.shape) == (2, 4)
+    np.testing.assert_allclose(b.host_params()[1], row, rtol=1e-6)
+    # forward axis +z, looking at the origin: the origin projects to the principal point
+    R, c = c2w[:3, :3], c2w[:3, 3]
+    pc = R.T @ (np.zeros(3) - c)
+    assert pc[2] > 0 and abs(pc[0]) < 1e-9 and abs(pc[1]) < 1e-9
+
+
+def test_scene_generators_are_seeded_and_shaped():
+    a = scenes.make_scene("cfg0", seed=0)
+    b = scenes.make_scene("cfg0", seed=0)
+    assert a["xyz"].shape == (10_000, 3) and torch.equal(a["xyz"], b["xyz"]) and torch.equal(a["target"], b["target"])
+    assert a["target"].shape == (1, 3, 256, 256) and float(a["sh_rest"].abs().max()) == 0.0
+    c3 = scenes.make_scene("cfg3", seed=0, n=1000, views=8, width=64, height=36)
+    assert c3["cams"].shape == (8, 16) and c3["target"].shape == (8, 3, 36, 64)
+    assert abs(float(c3["quat"].norm(dim=1).mean()) - 1.0) < 1e-5
+    c4 = scenes.CONFIGS["cfg4"]
+    assert c4.n == 6_000_000 and (c4.width, c4.height) == (3840, 2160) and c4.num_views == 64
+
+
+def test_optimizer_factory_hyperparameters():
+    m = d3.GaussianModelOriginFused.create_flat(8, device="cpu").to_parameter()
+    opts, sched = d3.create_origin_3dgs_optimizers(m, d3.Optimizer(), batch_size=4, spatial_lr_scale=2.0)
+    assert set(opts) == {"xyz", "color_sh_base", "color_sh", "opacity", "scale", "quaternion_xyzw"}
+    g = opts["xyz"].param_groups[0]
+    assert abs(g["lr"] - 1.6e-4 * 2.0 * 2.0) < 1e-12 and abs(g["eps"] - 1e-15 / 2.0) < 1e-24
+    assert g["betas"] == (1 - 4 * (1 - 0.9), 1 - 4 * (1 - 0.999))
+    assert abs(opts["color_sh"].param_groups[0]["lr"] - 0.0025 * 2.0 / 20.0) < 1e-12
+    assert abs(sched(0) - 1.6e-4 * 4.0) < 1e-12        # no delay steps: the delay multiplier is inactive
+    assert abs(sched(30000) - 1.6e-6 * 4.0) < 1e-12
+
+
+def _dp_worker(rank, world, port, q):
+    """Each rank computes its own view's gradient with the loss scaled by 1/world; all-reduce (sum) must equal
+    the gradient of the reference's batched loss (mean over B*C*H*W, train.py:170-172)."""
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from oracle import oracle as O
+    from parity_utils import oracle_scene, small_scene
+    sc = small_scene(n=400, width=64, height=48, sh_degree=1, seed=4, views=world)
+    osc = oracle_scene(sc)
+    cfg = O.OpConfig(width=64, height=48, sh_degree=1)
+    tgt = sc["target"].numpy()
+    one = O.Scene(osc.xyz, osc.quat, osc.scale, osc.opacity, osc.sh_base, osc.sh_rest, cams=osc.cams[rank:rank + 1].copy())
+    res = O.forward(cfg, one)
+    _, dx = O.l1_dssim(res.color, np.ascontiguousarray(tgt[rank:rank + 1]), 0.2)
+    O.backward(cfg, one, res, dx / world)
+    flat = torch.from_numpy(np.concatenate([res.grads[k].reshape(-1) for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")]))
+    dist.all_reduce(flat)
+    if rank == 0:
+        full = O.forward(cfg, osc)
+        _, dxf = O.l1_dssim(full.color, np.ascontiguousarray(tgt), 0.2)       # mean over B*C*H*W
+        O.backward(cfg, osc, full, dxf)
+        ref = np.concatenate([full.grads[k].reshape(-1) for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")])
+        q.put(float(np.abs(flat.numpy() - ref).max() / np.abs(ref).max()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_data_parallel_allreduce_equals_batched_gradient_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_dp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err = q.get(timeout=180)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert err < 1e-5, err
