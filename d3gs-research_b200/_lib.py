@@ -78,6 +78,8 @@ SIGNATURES = {
     "d3gs_preprocess_forward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), _P, C.POINTER(SplatContext), _P]),
     "d3gs_scan_workspace_bytes": (_SZ, [_I64]),
     "d3gs_scan_tiles": (_I32, [_P, _P, _I64, _P, _P, _SZ, _P, _P]),
+    "d3gs_scan_tiles_static_max_items": (_I64, []),
+    "d3gs_scan_tiles_static": (_I32, [_P, _P, _I64, _P, _P, _P]),
     "d3gs_duplicate_keys": (_I32, [C.POINTER(OpConfig), _I64, _P, C.POINTER(SplatContext), _P, _P, _P]),
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),

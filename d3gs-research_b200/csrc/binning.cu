@@ -236,3 +236,64 @@ extern "C" int32_t d3gs_pack_splats(const int32_t* sorted_values, int64_t n, con
     D3GS_LAUNCH_CHECK("pack_splats_kernel");
     return D3GS_OK;
 }
+
+// ---- allocation-free scan ----------------------------------------------------------------------
+// Same single-pass scan as d3gs_scan_tiles, for callers that cannot hand the library a workspace because
+// they are not able to obtain device memory at the moment of the call: a host application that gave its
+// whole memory budget to another engine's pool, a plug-in running inside a frame loop where cudaMalloc's
+// implicit device-wide synchronisation would stall the frame, or a thin C caller with no allocator of its
+// own.  The tile-status words live in a fixed array inside the loaded module instead.
+namespace d3gs {
+namespace {
+
+constexpr int64_t kStaticScanMaxItems = (int64_t)1 << 24;                          // 16,777,216 counts
+constexpr size_t kStaticScanBytes = 16 + (size_t)(kStaticScanMaxItems / kScanTile) * sizeof(uint64_t);   // 32,784 B
+
+// Held by every GPU that loads the library, from load to exit.
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scan_ptr[kMaxDevices] = {};
+bool g_static_scan_ready[kMaxDevices] = {};
+
+}  // namespace
+}  // namespace d3gs
+
+extern "C" int64_t d3gs_scan_tiles_static_max_items(void) { return d3gs::kStaticScanMaxItems; }
+
+extern "C" int32_t d3gs_scan_tiles_static(const int32_t* in, int32_t* out, int64_t n, int64_t* total, uint32_t* status,
+                                          void* stream) {
+    using namespace d3gs;
+    D3GS_REQUIRE(n >= 0, "negative element count");
+    D3GS_REQUIRE(n <= kStaticScanMaxItems,
+                 "d3gs_scan_tiles_static handles at most %lld elements (built-in scratch of %zu bytes); got %lld -- "
+                 "use d3gs_scan_tiles with a caller-provided workspace",
+                 (long long)kStaticScanMaxItems, kStaticScanBytes, (long long)n);
+    D3GS_REQUIRE(total != nullptr && status != nullptr, "total/status is NULL");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        D3GS_CUDA(cudaMemsetAsync(total, 0, sizeof(int64_t), s));
+        return D3GS_OK;
+    }
+    D3GS_REQUIRE(in != nullptr && out != nullptr, "in/out is NULL");
+    int dev = -1;
+    D3GS_CUDA(cudaGetDevice(&dev));
+    D3GS_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside [0,%d)", dev, kMaxDevices);
+    if (!g_static_scan_ready[dev]) {
+        // Set-up, once per device, with that device current: in host code the array's name is only a
+        // stand-in symbol, so its device address has to be asked for before it can be given to a kernel.
+        void* p = nullptr;
+        D3GS_CUDA(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+        D3GS_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned NULL");
+        g_static_scan_ptr[dev] = p;
+        g_static_scan_ready[dev] = true;
+    }
+    unsigned char* base = reinterpret_cast<unsigned char*>(g_static_scan_ptr[dev]);
+    const int64_t tiles = div_up64(n, kScanTile);
+    // every call shares the array and finds the previous call's ticket and tile states in it: clear the part in use
+    D3GS_CUDA(cudaMemsetAsync(base, 0, 16 + (size_t)tiles * sizeof(uint64_t), s));
+    scan_lookback_kernel<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, total, reinterpret_cast<uint32_t*>(base),
+                                                                 reinterpret_cast<uint64_t*>(base + 16), status);
+    D3GS_LAUNCH_CHECK("scan_lookback_kernel (static scratch)");
+    return D3GS_OK;
+}

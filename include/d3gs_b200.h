@@ -137,6 +137,20 @@ size_t d3gs_scan_workspace_bytes(int64_t n);
 int32_t d3gs_scan_tiles(const int32_t* in, int32_t* out, int64_t n, int64_t* total, void* workspace,
                         size_t workspace_bytes, uint32_t* status, void* stream);
 
+/* ---- allocation-free scan (no counterpart in the reference) ------------------------------
+ * The same scan for callers that cannot obtain device memory when they call: a host whose whole memory
+ * budget belongs to another engine's pool, a frame loop that must not run into cudaMalloc's device-wide
+ * synchronisation, or a thin C caller without an allocator.  The tile-status scratch is a fixed
+ * 32,784-byte array inside the module (every GPU that loads the library holds it until exit), so the call
+ * takes no workspace and performs no cudaMalloc/cudaFree.  Limit: n <= d3gs_scan_tiles_static_max_items()
+ * = 16,777,216; larger n is rejected with an error (use d3gs_scan_tiles).  The first call on each device
+ * looks up the array's device address (cudaGetSymbolAddress, with that device current): make that first
+ * call before any stream capture.  All calls share the one array: calls that may overlap on the GPU
+ * (different streams) race on it and must be serialised by the caller. */
+int64_t d3gs_scan_tiles_static_max_items(void);
+int32_t d3gs_scan_tiles_static(const int32_t* in, int32_t* out, int64_t n, int64_t* total, uint32_t* status,
+                               void* stream);
+
 /* ---- K3 key duplication (render.py:739-840) ---------------------------------------------- */
 /* key = (view*tiles + y*tiles_x + x) << 32 | float_bits(depth); value = flat index i */
 int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, const int32_t* scan, const D3gsSplatContext* ctx,
