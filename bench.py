@@ -187,7 +187,7 @@ def main():
     from d3gs_research_b200 import scenes
     from d3gs_research_b200.config_def import EarlyFilterAlgo
     from d3gs_research_b200.render import StageTimer
-    from d3gs_research_b200.trainer import SplatTrainer
+    from d3gs_research_b200.trainer import HostFeed, SplatTrainer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -217,20 +217,25 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    feed = HostFeed(dev)
+
     def timed(steps: int, e2e: bool):
-        loss_host = torch.zeros(2, dtype=torch.float64).pin_memory()
+        # one pinned slot per step: every step's loss sums are read back inside the timed region
+        loss_host = torch.zeros(steps, 2, dtype=torch.float64).pin_memory()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for k in range(steps):
             if e2e:
-                tgt = target_host.to(dev, non_blocking=True)        # this step's target from pinned host memory
-                info = trainer.step(cam, tgt)
-                loss_host.copy_(trainer._loss_sums, non_blocking=False)   # loss sums back to the host
+                # this step's target image: pinned host memory -> device on a side stream, overlapped with the
+                # forward pass of the same step; the loss kernels wait for it
+                tgt, ready = feed.push(target_host)
+                info = trainer.step(cam, tgt, target_ready=ready)
+                loss_host[k].copy_(trainer._loss_sums, non_blocking=True)   # this step's loss sums -> host
             else:
                 info = trainer.step(cam, target_dev)
         e1.record()
-        barrier()
+        barrier()      # synchronises: all uploads consumed, all loss read-backs landed
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         if world > 1:

@@ -48,7 +48,7 @@ class ModelGrad(C.Structure):
 class SplatContext(C.Structure):
     _fields_ = [("tiles_touched", C.c_void_p), ("radii", C.c_void_p), ("depths", C.c_void_p), ("uvs", C.c_void_p),
                 ("conic_opacity", C.c_void_p), ("rgb_gaussian", C.c_void_p), ("cov2d_vecs", C.c_void_p),
-                ("sh_to_rgb_ne_0", C.c_void_p)]
+                ("sh_to_rgb_ne_0", C.c_void_p), ("tile_mask", C.c_void_p)]
 
 
 class AdamSegment(C.Structure):

@@ -289,8 +289,17 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                 valid = false;
             } else {
                 int cnt = 0;
+                // accepted tiles as a bit mask over the 3-sigma rect (row-major), so that the key
+                // duplication does not have to repeat the overlap tests; rects above 64 tiles are re-walked
+                uint64_t tmask = 0;
+                const int rw = rmax[0] - rmin[0];
+                const bool small_rect = area <= 64;
                 for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opac, rmin, rmax,
-                              [&](int, int) { ++cnt; });
+                              [&](int x, int y) {
+                                  ++cnt;
+                                  if (small_rect) tmask |= 1ull << ((y - rmin[1]) * rw + (x - rmin[0]));
+                              });
+                if (a.ctx.tile_mask != nullptr) a.ctx.tile_mask[i] = tmask;
                 a.ctx.tiles_touched[i] = cnt;
                 a.ctx.radii[i] = (int)radius;
                 a.ctx.depths[i] = z;
@@ -382,11 +391,26 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
     tg.ts = (float)cf.tile_x;
     int64_t off = i == 0 ? 0 : (int64_t)a.scan[i - 1];
     const float2 uv = *reinterpret_cast<const float2*>(a.ctx.uvs + i * 2);
-    const float4 co = *reinterpret_cast<const float4*>(a.ctx.conic_opacity + i * 4);
     int rmin[2], rmax[2];
     tile_rect(tg, uv.x, uv.y, (float)r, rmin, rmax);
     const uint32_t dbits = __float_as_uint(a.ctx.depths[i]);
     const uint64_t tile_base = (uint64_t)b * (uint64_t)(tg.tiles_x * tg.tiles_y);
+    const int rw = rmax[0] - rmin[0];
+    if (a.ctx.tile_mask != nullptr && rw * (rmax[1] - rmin[1]) <= 64) {
+        // the preprocess left the accepted tiles as a row-major bit mask over the 3-sigma rect
+        uint64_t m = a.ctx.tile_mask[i];
+        while (m) {
+            const int bit = __ffsll((long long)m) - 1;
+            m &= m - 1;
+            const int y = rmin[1] + bit / rw, x = rmin[0] + bit % rw;
+            const uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
+            a.keys[off] = (key << 32) | dbits;
+            a.values[off] = (int32_t)i;
+            ++off;
+        }
+        return;
+    }
+    const float4 co = *reinterpret_cast<const float4*>(a.ctx.conic_opacity + i * 4);
     for_each_tile(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, uv.x, uv.y, co.x, co.y, co.z, co.w, rmin, rmax,
                   [&](int x, int y) {
                       uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);

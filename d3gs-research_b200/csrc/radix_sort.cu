@@ -155,21 +155,41 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ key
         // look-back: sum the counts of all predecessor tiles for this digit
         uint32_t excl = 0;
         if (tile > 0) {
+            // Predecessors are read eight at a time (independent loads, one memory latency per batch) and
+            // consumed in order; the walk stops at the first inclusive prefix and waits, bounded, at the
+            // first tile that has not published yet.  (Batches of 32 measured slower than 8.)
+            constexpr int kLook = 8;
             int64_t look = (int64_t)tile - 1;
-            bool gave_up = false;
-            while (look >= 0) {
-                const volatile uint32_t* p = lookback + (size_t)look * kRadix + d;
-                uint32_t st = *p;
-                int spins = 0;
-                while ((st & kLbFlagMask) == 0) {
-                    if (++spins > (1 << 20)) { gave_up = true; break; }
-                    __nanosleep(20);
-                    st = *p;
+            bool gave_up = false, done = false;
+            int spins = 0;
+            while (look >= 0 && !done && !gave_up) {
+                uint32_t st[kLook];
+#pragma unroll
+                for (int k = 0; k < kLook; ++k) {
+                    const int64_t idx = look - k;
+                    st[k] = idx >= 0 ? *((const volatile uint32_t*)(lookback + (size_t)idx * kRadix + d)) : kLbPrefix;
                 }
-                if (gave_up) break;
-                excl += st & kLbValueMask;
-                if ((st & kLbFlagMask) == kLbPrefix) break;
-                --look;
+                int consumed = 0;
+                bool blocked = false;
+#pragma unroll
+                for (int k = 0; k < kLook; ++k) {
+                    if (!done && !blocked) {
+                        if ((st[k] & kLbFlagMask) == 0) {
+                            blocked = true;
+                        } else {
+                            excl += st[k] & kLbValueMask;
+                            ++consumed;
+                            if ((st[k] & kLbFlagMask) == kLbPrefix) done = true;
+                        }
+                    }
+                }
+                look -= consumed;
+                if (blocked) {
+                    if (++spins > (1 << 20)) gave_up = true;
+                    __nanosleep(20);
+                } else {
+                    spins = 0;
+                }
             }
             if (gave_up) atomicOr(status, D3GS_STATUS_SORT_TIMEOUT);
             atomicExch(my, kLbPrefix | ((excl + tot) & kLbValueMask));

@@ -272,11 +272,13 @@ class GaussianSplatOp:
         return m
 
     @staticmethod
-    def _ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb, cov2d, ne0) -> _lib.SplatContext:
+    def _ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb, cov2d, ne0,
+                    tile_mask=None) -> _lib.SplatContext:
         s = _lib.SplatContext()
         s.tiles_touched, s.radii, s.depths = _lib.ptr(tiles_touched), _lib.ptr(radii), _lib.ptr(depths)
         s.uvs, s.conic_opacity, s.rgb_gaussian = _lib.ptr(uvs), _lib.ptr(conic_opacity), _lib.ptr(rgb)
         s.cov2d_vecs, s.sh_to_rgb_ne_0 = _lib.ptr(cov2d), _lib.ptr(ne0)
+        s.tile_mask = _lib.ptr(tile_mask)
         return s
 
     # ---- forward (render.py:169-1015) ---------------------------------------------------------
@@ -305,8 +307,10 @@ class GaussianSplatOp:
         cov2d_vecs = torch.empty([BN, 3], dtype=f32, device=dev) if training else None
         sh_ne0 = torch.empty([BN], dtype=torch.uint8, device=dev) if training else None
         tiles_touched = torch.empty(BN, dtype=i32, device=dev)
+        tile_mask = torch.empty(BN, dtype=torch.int64, device=dev)   # binning scratch, dropped after the key emission
         mstruct = self._model_struct(model)
-        cstruct = self._ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb_gaussian, cov2d_vecs, sh_ne0)
+        cstruct = self._ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb_gaussian, cov2d_vecs, sh_ne0,
+                                   tile_mask)
         mask_u8 = None
         if mask is not None:
             mask_u8 = mask.to(torch.uint8).contiguous()

@@ -30,6 +30,34 @@ from .strategy import GaussianTrainState
 from .tools import get_expon_lr_func
 
 
+class HostFeed:
+    """Uploads per-step inputs that live in pinned host memory on a side stream, double buffered.
+
+    ``push(host_tensor)`` starts the copy and returns ``(device_tensor, event)``; pass both to
+    ``SplatTrainer.step`` so that the copy overlaps the preprocess/sort/raster kernels of the same step.
+    A buffer is reused two pushes later; the copy into it first waits for the compute stream's work that
+    was enqueued at the time of the push, which includes every reader of that buffer."""
+
+    def __init__(self, device, slots: int = 2):
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device)
+        self.bufs: list[torch.Tensor | None] = [None] * slots
+        self.k = 0
+
+    def push(self, host: torch.Tensor):
+        assert host.is_pinned(), "per-step inputs must be in pinned host memory for an asynchronous upload"
+        i = self.k % len(self.bufs)
+        self.k += 1
+        if self.bufs[i] is None or self.bufs[i].shape != host.shape:
+            self.bufs[i] = torch.empty(host.shape, dtype=host.dtype, device=self.device)
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            self.bufs[i].copy_(host, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        return self.bufs[i], ev
+
+
 class SplatTrainer:
     def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
@@ -111,8 +139,12 @@ class SplatTrainer:
         return segs
 
     @torch.no_grad()
-    def step(self, cameras, target_nchw: torch.Tensor, update: bool = True) -> dict:
-        """One iteration on this rank's view(s).  Returns ``{"out", "loss" (lazy), "num_rendered"}``."""
+    def step(self, cameras, target_nchw: torch.Tensor, update: bool = True,
+             target_ready: "torch.cuda.Event | None" = None) -> dict:
+        """One iteration on this rank's view(s).  Returns ``{"out", "loss" (lazy), "num_rendered"}``.
+
+        ``target_ready``: an event recorded after an asynchronous upload of ``target_nchw`` on another
+        stream; the loss kernels wait for it, so the upload overlaps the forward pass."""
         model = self.model
         model.act_applied = True
         if self.op.timer is not None:
@@ -129,6 +161,8 @@ class SplatTrainer:
                 self._loss_scratch = torch.empty(nbytes, dtype=torch.uint8, device=out.color.device)
             if self._dcolor is None or self._dcolor.shape != out.color.shape:
                 self._dcolor = torch.empty_like(out.color)
+            if target_ready is not None:
+                torch.cuda.current_stream(out.color.device).wait_event(target_ready)
             # the loss of a data-parallel batch is the mean over all ranks' views: 1/world per rank
             loss, dcolor = l1_dssim_forward_backward(out.color, target_nchw, self.lambda_dssim,
                                                      grad_scale=1.0 / self.world, scratch=self._loss_scratch,

@@ -114,6 +114,10 @@ typedef struct D3gsSplatContext {
     float* rgb_gaussian;      /* [B*N,3] */
     float* cov2d_vecs;        /* [B*N,3] training only, may be NULL */
     uint8_t* sh_to_rgb_ne_0;  /* [B*N]   training only, may be NULL */
+    uint64_t* tile_mask;      /* [B*N]   optional (may be NULL; not in the reference): the tiles the early filter
+                                 accepted, as a row-major bit mask over the 3-sigma tile rect when that rect has at
+                                 most 64 tiles.  Written by the preprocess, read by the key duplication, which then
+                                 does not repeat the overlap tests. */
 } D3gsSplatContext;
 
 /* ---- helpers -------------------------------------------------------------------------- */
