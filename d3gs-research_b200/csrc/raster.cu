@@ -9,13 +9,14 @@
 //    async copies (cp.async.bulk + mbarrier, double buffered) instead of per-thread gathers
 //    (render.py:1699-1716).
 //  * Both kernels were instruction-issue bound when every warp walked every record.  Now the 32
-//    lanes of a warp first test 32 records at once against the warp's 8x4 pixel block (each record
-//    carries a conservative bounding box of its alpha >= 1/255 region), ballot, and only the
-//    surviving records are visited, still in front-to-back order.
-//  * Backward: the nine per-splat partial derivatives are reduced over the warp with a
-//    transposing butterfly (14 shuffles instead of 45), accumulated per CTA in shared memory, and
-//    leave the CTA as three vector atomic adds per (tile, splat) instead of the reference's nine
-//    scalar atomics per warp (render.py:2061-2148).
+//    lanes of a warp first test 32 records at once (each record carries a conservative bounding
+//    box of its alpha >= 1/255 region) against the four 4x2 sub-blocks of the warp's 8x4 pixel
+//    block, ballot, and then every QUARTER of the warp walks only the survivors of its own
+//    sub-block, front to back: one pass of the instruction stream serves up to four records.
+//  * Backward: the nine per-splat partial derivatives are reduced inside each quarter with a
+//    transposing butterfly (10 shuffles for four records instead of 45 for one), accumulated per
+//    CTA in shared memory, and leave the CTA as three vector atomic adds per (tile, splat) instead
+//    of the reference's nine scalar atomics per warp (render.py:2061-2148).
 //
 // The arithmetic that decides n_contrib -- power, exp, alpha, the transmittance product and the
 // three threshold compares -- is written with explicit round-to-nearest intrinsics so that its
@@ -55,11 +56,15 @@ struct PixelCoord {
     bool inside;
 };
 
+// Pixel of a thread.  A warp covers an 8x4 pixel block of the tile (render.py:1503-1512 uses the same
+// block per warp); inside it every QUARTER of the warp (8 lanes) covers a 4x2 sub-block:
+//   quarter q = lane>>3: x half (q&1)*4, y half (q>>1)*2; inside the quarter lane&3 -> x, (lane>>2)&1 -> y.
+// Results do not depend on which thread owns which pixel.
 __device__ __forceinline__ PixelCoord pixel_of_thread(const RasterArgs& a) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane >> 3;
     PixelCoord p;
-    p.px = blockIdx.x * 16 + (warp & 1) * 8 + (lane & 7);
-    p.py = blockIdx.y * 16 + (warp >> 1) * 4 + (lane >> 3);
+    p.px = blockIdx.x * 16 + (warp & 1) * 8 + (q & 1) * 4 + (lane & 3);
+    p.py = blockIdx.y * 16 + (warp >> 1) * 4 + (q >> 1) * 2 + ((lane >> 2) & 1);
     p.inside = p.px < a.width && p.py < a.height;
     return p;
 }
@@ -72,21 +77,35 @@ __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, ui
     bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
 }
 
-// Bit mask of the records [g*32, g*32+32) of the staged batch whose bounding box overlaps this
-// warp's 8x4 pixel block.  hx/hy in the record already include the block's half size.
-__device__ __forceinline__ uint32_t cull_group(const float4* rec, int g, int limit, float wcx, float wcy) {
-    const int j = g * 32 + (threadIdx.x & 31);
-    bool hit = false;
+// The 32 lanes test the records [g*32, g*32+32) of the staged batch, one record per lane, against the
+// four 4x2 sub-blocks of this warp's pixel block and leave the four ballot masks in masks[0..3].
+// The record's (hx, hy) already include the half size of the 8x4 block (3.5, 1.5); a sub-block is
+// 2.0 / 1.0 smaller and its centre sits at (+-2, +-1) from the block centre (wcx, wcy).
+__device__ __forceinline__ void cull_group(const float4* rec, int g, int limit, float wcx, float wcy, uint32_t* masks) {
+    const int lane = threadIdx.x & 31;
+    const int j = g * 32 + lane;
+    bool left = false, right = false, top = false, bottom = false;
     if (j < limit) {
         const float4 q0 = rec[j * 3];
-        hit = fabsf(q0.x - wcx) <= q0.z && fabsf(q0.y - wcy) <= q0.w;
+        const float ddx = q0.x - wcx, ddy = q0.y - wcy, hxq = q0.z - 2.0f, hyq = q0.w - 1.0f;
+        left = fabsf(ddx + 2.0f) <= hxq;
+        right = fabsf(ddx - 2.0f) <= hxq;
+        top = fabsf(ddy + 1.0f) <= hyq;
+        bottom = fabsf(ddy - 1.0f) <= hyq;
     }
-    return __ballot_sync(0xffffffffu, hit);
+    const uint32_t m0 = __ballot_sync(0xffffffffu, left && top);
+    const uint32_t m1 = __ballot_sync(0xffffffffu, right && top);
+    const uint32_t m2 = __ballot_sync(0xffffffffu, left && bottom);
+    const uint32_t m3 = __ballot_sync(0xffffffffu, right && bottom);
+    if (lane < 4) masks[lane] = lane == 0 ? m0 : (lane == 1 ? m1 : (lane == 2 ? m2 : m3));
 }
+
+constexpr int kGroups = kBatch / 32;
 
 __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ uint32_t s_mask[8][kGroups][4];   // per warp, per group of 32 records, per quarter
     const int t = threadIdx.x;
     const PixelCoord pc = pixel_of_thread(a);
     const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
@@ -104,6 +123,7 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     const float fpx = (float)pc.px, fpy = (float)pc.py;
     const float wcx = (float)(blockIdx.x * 16 + ((t >> 5) & 1) * 8) + 3.5f;
     const float wcy = (float)(blockIdx.y * 16 + (t >> 6) * 4) + 1.5f;
+    const int quarter = (t & 31) >> 3, warp = t >> 5;
     bool done = !pc.inside;
     float T = 1.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f;
     int contributor = 0;
@@ -121,11 +141,20 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
         }
         const int cnt = min(kBatch, n - b * kBatch);
         const float4* rec = s_rec[cur];
-        for (int g = 0; g * 32 < cnt; ++g) {
-            if (__all_sync(0xffffffffu, done)) break;
-            uint32_t m = cull_group(rec, g, cnt, wcx, wcy);
-            while (m) {
-                const int j = g * 32 + __ffs(m) - 1;
+        // Cull the whole batch first, then every quarter (8 lanes, a 4x2 pixel sub-block) walks its own
+        // survivor list front to back, independently of the other quarters: one pass of the instruction
+        // stream serves up to four different records.
+        const int ng = (cnt + 31) >> 5;
+        if (!__all_sync(0xffffffffu, done)) {
+            for (int g = 0; g < ng; ++g) cull_group(rec, g, cnt, wcx, wcy, s_mask[warp][g]);
+            __syncwarp();
+            int gq = 0;
+            uint32_t m = s_mask[warp][0][quarter];
+            while (true) {
+                while (m == 0 && gq + 1 < ng) m = s_mask[warp][++gq][quarter];
+                const bool act = m != 0;
+                if (!__any_sync(0xffffffffu, act && !done)) break;
+                const int j = gq * 32 + (act ? __ffs(m) - 1 : 0);
                 m &= m - 1;
                 const float4 q0 = rec[j * 3];       // u, v, hx, hy
                 const float4 q1 = rec[j * 3 + 1];   // ha, nb, hc, opacity
@@ -133,7 +162,7 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
                 const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
                 const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
                 // power < thr  =>  alpha < alpha_eps: the pixel skips this splat (render.py:1796-1798)
-                const bool cand = !done && power >= q2.w;
+                const bool cand = act && !done && power >= q2.w;
                 if (!__any_sync(0xffffffffu, cand)) continue;
                 if (cand) {
                     const float G = blend_exp(power);
@@ -189,6 +218,7 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ float s_acc[kBatch][9];   // per record: dconic a b c, dopacity, dcolor r g b, duv x y
     __shared__ int s_max[8];
+    __shared__ uint32_t s_mask[8][kGroups][4];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const PixelCoord pc = pixel_of_thread(a);
     const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
@@ -223,9 +253,10 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     const float fpx = (float)pc.px, fpy = (float)pc.py;
     const float wcx = (float)(blockIdx.x * 16 + (warp & 1) * 8) + 3.5f;
     const float wcy = (float)(blockIdx.y * 16 + (warp >> 1) * 4) + 1.5f;
-    const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
-    // after the butterfly, the four lanes of group (lane>>2) hold the total of component `slot`
-    const int slot = (h16 ? 4 : 0) + (h8 ? 2 : 0) + (h4 ? 1 : 0);
+    const int quarter = lane >> 3;
+    const bool h4 = (lane & 4) != 0, h2 = (lane & 2) != 0, h1 = (lane & 1) != 0;
+    // after the butterfly, lane k of a quarter holds the quarter's total of component `slot`
+    const int slot = (h4 ? 4 : 0) + (h2 ? 2 : 0) + (h1 ? 1 : 0);
     float T = 1.0f;
     bool copy_failed = false;
     for (int b = 0; b < nb; ++b) {
@@ -243,10 +274,18 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
         }
         const float4* rec = s_rec[cur];
         const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
-        for (int g = 0; g * 32 < wlim; ++g) {
-            uint32_t m = cull_group(rec, g, wlim, wcx, wcy);
-            while (m) {
-                const int j = g * 32 + __ffs(m) - 1;
+        const int ng = (wlim + 31) >> 5;
+        if (ng > 0) {
+            for (int g = 0; g < ng; ++g) cull_group(rec, g, wlim, wcx, wcy, s_mask[warp][g]);
+            __syncwarp();
+            int gq = 0;
+            uint32_t m = s_mask[warp][0][quarter];
+            // every quarter (8 lanes, 4x2 pixels) walks its own survivors; one pass serves up to four records
+            while (true) {
+                while (m == 0 && gq + 1 < ng) m = s_mask[warp][++gq][quarter];
+                const bool act = m != 0;
+                if (!__any_sync(0xffffffffu, act)) break;
+                const int j = gq * 32 + (act ? __ffs(m) - 1 : 0);
                 m &= m - 1;
                 const float4 q0 = rec[j * 3];
                 const float4 q1 = rec[j * 3 + 1];
@@ -254,7 +293,7 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
                 const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
                 const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
                 // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
-                const bool cand = (b * kBatch + j < contributor) && power >= q2.w && power <= 0.0f;
+                const bool cand = act && (b * kBatch + j < contributor) && power >= q2.w && power <= 0.0f;
                 if (!__any_sync(0xffffffffu, cand)) continue;
                 float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f, v8 = 0.f;
                 bool valid = false;
@@ -284,25 +323,26 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
                         v8 = dL_dG * fmaf(2.0f * gdy, q1.z, gdx * q1.y);      // duv y = dL_dG (-gdy c - gdx b)
                     }
                 }
-                if (!__any_sync(0xffffffffu, valid)) continue;
-                // transposing butterfly: 8 components in 9 shuffles, the ninth in 5
-                const float a0 = (h16 ? v4 : v0) + shfl_x(h16 ? v0 : v4, 16);
-                const float a1 = (h16 ? v5 : v1) + shfl_x(h16 ? v1 : v5, 16);
-                const float a2 = (h16 ? v6 : v2) + shfl_x(h16 ? v2 : v6, 16);
-                const float a3 = (h16 ? v7 : v3) + shfl_x(h16 ? v3 : v7, 16);
-                const float b0 = (h8 ? a2 : a0) + shfl_x(h8 ? a0 : a2, 8);
-                const float b1 = (h8 ? a3 : a1) + shfl_x(h8 ? a1 : a3, 8);
-                float c = (h4 ? b1 : b0) + shfl_x(h4 ? b0 : b1, 4);
-                c += shfl_x(c, 2);
-                c += shfl_x(c, 1);
-                v8 += shfl_x(v8, 16);
-                v8 += shfl_x(v8, 8);
+                const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
+                if (vmask == 0) continue;
+                // transposing butterfly inside each quarter: 8 components in 7 shuffles, the ninth in 3
+                const float a0 = (h4 ? v4 : v0) + shfl_x(h4 ? v0 : v4, 4);
+                const float a1 = (h4 ? v5 : v1) + shfl_x(h4 ? v1 : v5, 4);
+                const float a2 = (h4 ? v6 : v2) + shfl_x(h4 ? v2 : v6, 4);
+                const float a3 = (h4 ? v7 : v3) + shfl_x(h4 ? v3 : v7, 4);
+                const float b0 = (h2 ? a2 : a0) + shfl_x(h2 ? a0 : a2, 2);
+                const float b1 = (h2 ? a3 : a1) + shfl_x(h2 ? a1 : a3, 2);
+                const float c = (h1 ? b1 : b0) + shfl_x(h1 ? b0 : b1, 1);
                 v8 += shfl_x(v8, 4);
                 v8 += shfl_x(v8, 2);
                 v8 += shfl_x(v8, 1);
-                // nine lanes, nine different addresses: one shared-memory atomic instruction
-                const bool ninth = lane == 1;
-                if ((lane & 3) == 0 || ninth) atomicAdd(&s_acc[j][ninth ? 8 : slot], ninth ? v8 : c);
+                // quarters with at least one valid lane add their nine sums: lane k adds component k,
+                // the first lane of the quarter also the ninth
+                const bool qvalid = ((vmask >> (quarter * 8)) & 0xffu) != 0;
+                if (qvalid) {
+                    atomicAdd(&s_acc[j][slot], c);
+                    if ((lane & 7) == 0) atomicAdd(&s_acc[j][8], v8);
+                }
             }
         }
         __syncthreads();
