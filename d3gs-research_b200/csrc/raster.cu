@@ -11,8 +11,11 @@
 //  * Both kernels were instruction-issue bound when every warp walked every record.  Now the 32
 //    lanes of a warp first test 32 records at once (each record carries a conservative bounding
 //    box of its alpha >= 1/255 region) against the four 4x2 sub-blocks of the warp's 8x4 pixel
-//    block, ballot, and then every QUARTER of the warp walks only the survivors of its own
-//    sub-block, front to back: one pass of the instruction stream serves up to four records.
+//    block, ballot, and append the survivors of every sub-block to a compact index list in shared
+//    memory.  Then every QUARTER of the warp walks only the list of its own sub-block, front to
+//    back: one pass of the instruction stream serves up to four records.  The forward pass body is
+//    branch free (selects and predicates), which is cheaper than votes and divergent branches
+//    when nearly every pass has a contributing pixel.
 //  * Backward: the nine per-splat partial derivatives are reduced inside each quarter with a
 //    transposing butterfly (10 shuffles for four records instead of 45 for one), accumulated per
 //    CTA in shared memory, and leave the CTA as three vector atomic adds per (tile, splat) instead
@@ -77,11 +80,15 @@ __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, ui
     bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
 }
 
+constexpr int kListStride = kBatch + 8;   // bytes per quarter list; +8 keeps the four lists on different banks
+
 // The 32 lanes test the records [g*32, g*32+32) of the staged batch, one record per lane, against the
-// four 4x2 sub-blocks of this warp's pixel block and leave the four ballot masks in masks[0..3].
+// four 4x2 sub-blocks of this warp's pixel block and append the index of every record that touches
+// sub-block q to lists[q] (in list order); c[q] is the running length, the same in all lanes.
 // The record's (hx, hy) already include the half size of the 8x4 block (3.5, 1.5); a sub-block is
 // 2.0 / 1.0 smaller and its centre sits at (+-2, +-1) from the block centre (wcx, wcy).
-__device__ __forceinline__ void cull_group(const float4* rec, int g, int limit, float wcx, float wcy, uint32_t* masks) {
+__device__ __forceinline__ void cull_to_lists(const float4* rec, int g, int limit, float wcx, float wcy,
+                                              uint8_t* lists, int& c0, int& c1, int& c2, int& c3) {
     const int lane = threadIdx.x & 31;
     const int j = g * 32 + lane;
     bool left = false, right = false, top = false, bottom = false;
@@ -93,19 +100,25 @@ __device__ __forceinline__ void cull_group(const float4* rec, int g, int limit, 
         top = fabsf(ddy + 1.0f) <= hyq;
         bottom = fabsf(ddy - 1.0f) <= hyq;
     }
+    const uint32_t lt = (1u << lane) - 1u;
     const uint32_t m0 = __ballot_sync(0xffffffffu, left && top);
     const uint32_t m1 = __ballot_sync(0xffffffffu, right && top);
     const uint32_t m2 = __ballot_sync(0xffffffffu, left && bottom);
     const uint32_t m3 = __ballot_sync(0xffffffffu, right && bottom);
-    if (lane < 4) masks[lane] = lane == 0 ? m0 : (lane == 1 ? m1 : (lane == 2 ? m2 : m3));
+    if (left && top) lists[c0 + __popc(m0 & lt)] = (uint8_t)j;
+    if (right && top) lists[kListStride + c1 + __popc(m1 & lt)] = (uint8_t)j;
+    if (left && bottom) lists[2 * kListStride + c2 + __popc(m2 & lt)] = (uint8_t)j;
+    if (right && bottom) lists[3 * kListStride + c3 + __popc(m3 & lt)] = (uint8_t)j;
+    c0 += __popc(m0);
+    c1 += __popc(m1);
+    c2 += __popc(m2);
+    c3 += __popc(m3);
 }
-
-constexpr int kGroups = kBatch / 32;
 
 __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
-    __shared__ uint32_t s_mask[8][kGroups][4];   // per warp, per group of 32 records, per quarter
+    __shared__ uint8_t s_list[8][4 * kListStride];   // per warp: the four quarters' survivor lists
     const int t = threadIdx.x;
     const PixelCoord pc = pixel_of_thread(a);
     const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
@@ -146,42 +159,37 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
         // stream serves up to four different records.
         const int ng = (cnt + 31) >> 5;
         if (!__all_sync(0xffffffffu, done)) {
-            for (int g = 0; g < ng; ++g) cull_group(rec, g, cnt, wcx, wcy, s_mask[warp][g]);
+            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+            for (int g = 0; g < ng; ++g) cull_to_lists(rec, g, cnt, wcx, wcy, s_list[warp], c0, c1, c2, c3);
             __syncwarp();
-            int gq = 0;
-            uint32_t m = s_mask[warp][0][quarter];
-            while (true) {
-                while (m == 0 && gq + 1 < ng) m = s_mask[warp][++gq][quarter];
-                const bool act = m != 0;
-                if (!__any_sync(0xffffffffu, act && !done)) break;
-                const int j = gq * 32 + (act ? __ffs(m) - 1 : 0);
-                m &= m - 1;
+            const int mine = quarter == 0 ? c0 : (quarter == 1 ? c1 : (quarter == 2 ? c2 : c3));
+            const uint8_t* lst = &s_list[warp][quarter * kListStride];
+            const int base = b * kBatch;
+            for (int i = 0;; ++i) {
+                const bool live = i < mine && !done;
+                if (!__any_sync(0xffffffffu, live)) break;
+                // past the end of its list a quarter reads a stale index (< kBatch); `live` masks the result
+                const int j = lst[i];
                 const float4 q0 = rec[j * 3];       // u, v, hx, hy
                 const float4 q1 = rec[j * 3 + 1];   // ha, nb, hc, opacity
                 const float4 q2 = rec[j * 3 + 2];   // r, g, b, thr
                 const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
                 const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
+                const float G = blend_exp(power);
+                const float alpha = fminf(0.99f, f_mul(q1.w, G));
+                const float nT = f_mul(T, f_sub(1.0f, alpha));
                 // power < thr  =>  alpha < alpha_eps: the pixel skips this splat (render.py:1796-1798)
-                const bool cand = act && !done && power >= q2.w;
-                if (!__any_sync(0xffffffffu, cand)) continue;
-                if (cand) {
-                    const float G = blend_exp(power);
-                    const float alpha = fminf(0.99f, f_mul(q1.w, G));
-                    if (alpha >= a.alpha_eps) {
-                        const float nT = f_mul(T, f_sub(1.0f, alpha));
-                        const bool should_done = nT < a.t_eps;
-                        if (power > 0.0f || should_done) {
-                            done = should_done;          // render.py:1803-1807
-                        } else {
-                            const float w = f_mul(alpha, T);
-                            T = nT;
-                            contributor = b * kBatch + j;   // render.py:1836
-                            C0 = f_fma(w, q2.x, C0);
-                            C1 = f_fma(w, q2.y, C1);
-                            C2 = f_fma(w, q2.z, C2);
-                        }
-                    }
-                }
+                const bool ok = live && power >= q2.w && alpha >= a.alpha_eps;
+                const bool should_done = nT < a.t_eps;
+                // render.py:1803-1807: a splat with power > 0 or one that would end the pixel is not blended
+                const bool upd = ok && !(power > 0.0f) && !should_done;
+                done = done || (ok && should_done);
+                const float w = f_mul(alpha, T);
+                T = upd ? nT : T;
+                contributor = upd ? base + j : contributor;   // render.py:1836
+                C0 = upd ? f_fma(w, q2.x, C0) : C0;
+                C1 = upd ? f_fma(w, q2.y, C1) : C1;
+                C2 = upd ? f_fma(w, q2.z, C2) : C2;
             }
         }
         __syncthreads();   // everyone is done reading s_rec[cur] before it is refilled
@@ -218,7 +226,7 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ float s_acc[kBatch][9];   // per record: dconic a b c, dopacity, dcolor r g b, duv x y
     __shared__ int s_max[8];
-    __shared__ uint32_t s_mask[8][kGroups][4];
+    __shared__ uint8_t s_list[8][4 * kListStride];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const PixelCoord pc = pixel_of_thread(a);
     const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
@@ -276,17 +284,16 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
         const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
         const int ng = (wlim + 31) >> 5;
         if (ng > 0) {
-            for (int g = 0; g < ng; ++g) cull_group(rec, g, wlim, wcx, wcy, s_mask[warp][g]);
+            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+            for (int g = 0; g < ng; ++g) cull_to_lists(rec, g, wlim, wcx, wcy, s_list[warp], c0, c1, c2, c3);
             __syncwarp();
-            int gq = 0;
-            uint32_t m = s_mask[warp][0][quarter];
+            const int mine = quarter == 0 ? c0 : (quarter == 1 ? c1 : (quarter == 2 ? c2 : c3));
+            const int maxc = max(max(c0, c1), max(c2, c3));
+            const uint8_t* lst = &s_list[warp][quarter * kListStride];
             // every quarter (8 lanes, 4x2 pixels) walks its own survivors; one pass serves up to four records
-            while (true) {
-                while (m == 0 && gq + 1 < ng) m = s_mask[warp][++gq][quarter];
-                const bool act = m != 0;
-                if (!__any_sync(0xffffffffu, act)) break;
-                const int j = gq * 32 + (act ? __ffs(m) - 1 : 0);
-                m &= m - 1;
+            for (int i = 0; i < maxc; ++i) {
+                const bool act = i < mine;
+                const int j = lst[i];   // stale (< kBatch) past the end of the quarter's list; `act` masks it
                 const float4 q0 = rec[j * 3];
                 const float4 q1 = rec[j * 3 + 1];
                 const float4 q2 = rec[j * 3 + 2];
