@@ -290,46 +290,39 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
             const int mine = quarter == 0 ? c0 : (quarter == 1 ? c1 : (quarter == 2 ? c2 : c3));
             const int maxc = max(max(c0, c1), max(c2, c3));
             const uint8_t* lst = &s_list[warp][quarter * kListStride];
+            const int base = b * kBatch;
             // every quarter (8 lanes, 4x2 pixels) walks its own survivors; one pass serves up to four records
             for (int i = 0; i < maxc; ++i) {
                 const bool act = i < mine;
-                const int j = lst[i];   // stale (< kBatch) past the end of the quarter's list; `act` masks it
+                // a quarter past the end of its list replays record 0 with zero weights: every value below
+                // stays finite, so the branch-free selects cannot leak a NaN into T or the colour suffix
+                const int j = act ? (int)lst[i] : 0;
                 const float4 q0 = rec[j * 3];
                 const float4 q1 = rec[j * 3 + 1];
                 const float4 q2 = rec[j * 3 + 2];
                 const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
                 const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
+                const float G = blend_exp(power);
+                const float alpha = fminf(0.99f, f_mul(q1.w, G));
                 // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
-                const bool cand = act && (b * kBatch + j < contributor) && power >= q2.w && power <= 0.0f;
-                if (!__any_sync(0xffffffffu, cand)) continue;
-                float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f, v4 = 0.f, v5 = 0.f, v6 = 0.f, v7 = 0.f, v8 = 0.f;
-                bool valid = false;
-                if (cand) {
-                    const float G = blend_exp(power);
-                    const float alpha = fminf(0.99f, f_mul(q1.w, G));
-                    if (alpha >= a.alpha_eps) {
-                        valid = true;
-                        const float oma = f_sub(1.0f, alpha);
-                        const float w = f_mul(alpha, T);
-                        T = f_mul(T, oma);
-                        rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
-                        float dl = dr0 * fmaf(T, q2.x, -rr0);
-                        dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
-                        dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
-                        dl -= dTT;
-                        const float dL_dalpha = __fdividef(dl, oma);          // render.py:1957
-                        const float dL_dG = q1.w * dL_dalpha;                 // render.py:1995
-                        const float gdx = G * dx, gdy = G * dy;
-                        // conic = (-2 ha, -nb, -2 hc); render.py:2001-2017
-                        v0 = gdx * dx * dL_dG * -0.5f;                        // dconic a
-                        v1 = -gdx * dy * dL_dG;                               // dconic b
-                        v2 = gdy * dy * dL_dG * -0.5f;                        // dconic c
-                        v3 = dL_dalpha * G;                                   // dopacity, render.py:2018
-                        v4 = w * dr0; v5 = w * dr1; v6 = w * dr2;             // dcolor, render.py:1962
-                        v7 = dL_dG * fmaf(2.0f * gdx, q1.x, gdy * q1.y);      // duv x = dL_dG (-gdx a - gdy b)
-                        v8 = dL_dG * fmaf(2.0f * gdy, q1.z, gdx * q1.y);      // duv y = dL_dG (-gdy c - gdx b)
-                    }
-                }
+                const bool valid = act && (base + j < contributor) && power >= q2.w && power <= 0.0f &&
+                                   alpha >= a.alpha_eps;
+                const float oma = f_sub(1.0f, alpha);
+                const float w = valid ? f_mul(alpha, T) : 0.0f;
+                T = valid ? f_mul(T, oma) : T;
+                rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
+                float dl = dr0 * fmaf(T, q2.x, -rr0);
+                dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
+                dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
+                dl -= dTT;
+                // m = dL/dalpha * G (render.py:1957, 2018).  The per-splat sums are kept as moments of m over
+                // the pixels; the record's constants (opacity, conic) are applied once when the batch is
+                // flushed: dL/dG * G = opacity * m (render.py:1995).
+                const float m = valid ? __fdividef(dl, oma) * G : 0.0f;
+                const float mx = m * dx, my = m * dy;
+                float v0 = mx * dx, v1 = mx * dy, v2 = my * dy, v3 = m;      // sum m dx^2, m dx dy, m dy^2, m
+                float v4 = w * dr0, v5 = w * dr1, v6 = w * dr2;              // dcolor, render.py:1962
+                float v7 = mx, v8 = my;                                      // sum m dx, m dy
                 const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
                 if (vmask == 0) continue;
                 // transposing butterfly inside each quarter: 8 components in 7 shuffles, the ninth in 3
@@ -355,10 +348,16 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
         __syncthreads();
         if (t < cnt) {
             const float* acc = s_acc[t];
-            const float g0 = acc[0], g1 = acc[1], g2 = acc[2], g3 = acc[3], g4 = acc[4], g5 = acc[5], g6 = acc[6],
-                        g7 = acc[7], g8 = acc[8];
-            const bool any = (g0 != 0.f) | (g1 != 0.f) | (g2 != 0.f) | (g3 != 0.f) | (g4 != 0.f) | (g5 != 0.f) |
-                             (g6 != 0.f) | (g7 != 0.f) | (g8 != 0.f);
+            const float sxx = acc[0], sxy = acc[1], syy = acc[2], s0 = acc[3], g4 = acc[4], g5 = acc[5], g6 = acc[6],
+                        sx = acc[7], sy = acc[8];
+            const bool any = (sxx != 0.f) | (sxy != 0.f) | (syy != 0.f) | (s0 != 0.f) | (g4 != 0.f) | (g5 != 0.f) |
+                             (g6 != 0.f) | (sx != 0.f) | (sy != 0.f);
+            // conic = (-2 ha, -nb, -2 hc), render.py:2001-2017: d/dconic = -0.5 o sxx, -o sxy, -0.5 o syy;
+            // d/duv = o (2 ha sx + nb sy, 2 hc sy + nb sx); d/dopacity = s0
+            const float4 k1 = rec[t * 3 + 1];   // ha, nb, hc, opacity
+            const float g0 = -0.5f * k1.w * sxx, g1 = -k1.w * sxy, g2 = -0.5f * k1.w * syy, g3 = s0;
+            const float g7 = k1.w * fmaf(2.0f * k1.x, sx, k1.y * sy);
+            const float g8 = k1.w * fmaf(2.0f * k1.z, sy, k1.y * sx);
             if (any) {
                 float* dst = a.splat_grads + (int64_t)my_id * kGradFloats;
                 red_add_v4(dst, g0, g1, g2, g3);
