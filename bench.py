@@ -29,7 +29,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "training iters/sec (fwd+bwd+SSIM+Adam) at 3M Gaussians 1080p; views/sec at 1/2/4/8 B200"
 UNIT = "views/s"
-WORKLOAD = "cfg3: 3M Gaussians, SH3 fp32, 1920x1080, 1 view/GPU, L1+D-SSIM, grad allreduce, fused Adam"
+WORKLOAD = "cfg3: 3M Gaussians, SH3 fp32, 1920x1080, 1 view/GPU, L1+D-SSIM, gradient sum over ranks, fused Adam"
 
 
 def parse():
@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--n", type=int, default=0, help="override the Gaussian count (profiling on small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--replicated-adam", action="store_true",
+                    help="N>1: all-reduce + full Adam on every rank instead of the sharded optimizer")
     ap.add_argument("--cpu-sample", type=int, default=4, help="CPU baseline runs on 1/S of the Gaussians")
     return ap.parse_args()
 
@@ -206,7 +208,8 @@ def main():
     model = d3.GaussianModelOriginFused.from_tensors(sc["xyz"], sc["quat"], sc["scale"], sc["opacity"], sc["sh_base"],
                                                      sc["sh_rest"], device=dev, cur_sh_degree=scfg.sh_degree)
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
-    trainer = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world)
+    trainer = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world,
+                           shard_optimizer=False if args.replicated_adam else None)
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
     target_host = sc["target"][rank % sc["target"].shape[0]][None].contiguous().pin_memory()
@@ -257,6 +260,13 @@ def main():
         trainer.step(cam, tgt, target_ready=ready)
     ms_e2e, _ = timed(args.steps, e2e=True)
 
+    replicas_agree = None
+    if world > 1:   # every replica must hold bit-identical parameters after the same updates
+        c = trainer.parameter_checksum().reshape(1)
+        c_lo, c_hi = c.clone(), c.clone()
+        dist.all_reduce(c_lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(c_hi, op=dist.ReduceOp.MAX)
+        replicas_agree = bool((c_lo == c_hi).item())
     K = int(info["num_rendered"])
     V = int((info["out"].radii > 0).sum().item())
     P, Tn = W * H, ((W + 15) // 16) * ((H + 15) // 16)
@@ -274,7 +284,7 @@ def main():
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-    kernel_stages = {k: v for k, v in stage_ms.items() if k not in ("host_readback_idle", "allreduce")}
+    kernel_stages = {k: v for k, v in stage_ms.items() if k not in ("host_readback_idle", "allreduce", "reduce_scatter", "all_gather")}
     dom = max(kernel_stages, key=kernel_stages.get)
     dom_bytes = algorithmic_bytes(dom, N, V, K, P, Tn)
     achieved = dom_bytes / (kernel_stages[dom] * 1e-3) / 1e9
@@ -285,7 +295,10 @@ def main():
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD if args.config == "cfg3" and not n_override else f"{args.config} n={N}",
                    "gaussians": N, "visible": V, "sort_pairs": K, "resolution": [W, H], "views_per_gpu": 1,
-                   "parallelism": f"dp{world} over views, replicated Gaussians", "early_filter": "OBB_DFVT",
+                   "parallelism": f"dp{world} over views, replicated Gaussians",
+                   "optimizer": ("sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded
+                                 else ("replicated after all-reduce" if world > 1 else "single rank")),
+                   "replicas_agree": replicas_agree, "early_filter": "OBB_DFVT",
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(target_host.numel() * 4),
                 "d2h_bytes_per_step": 16 + 16, "ms_per_step": ms_e2e / args.steps},

@@ -33,7 +33,8 @@ def flat_field_sizes(n: int, sh_rest: int = 15) -> dict[str, tuple[int, tuple]]:
 
 
 def carve_flat(flat: torch.Tensor, n: int, sh_rest: int = 15) -> dict[str, torch.Tensor]:
-    """Views of the six model tensors inside one flat float32 buffer of 59*n elements.
+    """Views of the six model tensors inside one flat float32 buffer of at least 59*n elements (a longer
+    buffer carries padding at its end, e.g. to a whole number of optimizer slices).
 
     Every view starts on a 16-byte boundary when n is a multiple of 4 (the kernels' float4 paths
     check alignment themselves and fall back to scalar accesses otherwise).
@@ -43,7 +44,7 @@ def carve_flat(flat: torch.Tensor, n: int, sh_rest: int = 15) -> dict[str, torch
         cnt, shape = flat_field_sizes(n, sh_rest)[name]
         out[name] = flat[off:off + cnt].view(*shape)
         off += cnt
-    assert off == flat.numel()
+    assert off <= flat.numel()
     return out
 
 

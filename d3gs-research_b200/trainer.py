@@ -10,9 +10,13 @@ Data-parallel over views (one process per GPU, ``torch.distributed`` NCCL): ever
 Gaussian set and renders its own camera.  The reference's batch semantics are kept exactly: its loss
 is a mean over B*C*H*W (train.py:170-172), so every per-view gradient carries 1/B and the per-Gaussian
 gradient of the batch is the plain sum over views (render.py:3182-3199, origin/model.py:422-431).
-Here each rank scales its loss gradient by 1/world_size and the flat gradient buffer is all-reduced
-(sum) between the preprocess backward and the Adam launch.  Optimizer hyper-parameters are scaled with
-the global batch like tools.py:146-163.
+Here each rank scales its loss gradient by 1/world_size and the flat gradient buffer is summed over the
+ranks between the preprocess backward and the Adam launch.  With ``shard_optimizer`` (the default for
+more than one rank) the sum is a reduce-scatter: every rank owns one contiguous slice of the flat
+parameter buffer together with its Adam moments, updates only that slice, and an in-place all-gather
+brings the updated slices back to every replica.  The bytes on the wire equal those of an all-reduce,
+while the Adam launch, which is bound by HBM bandwidth, shrinks by the number of ranks.
+Optimizer hyper-parameters are scaled with the global batch like tools.py:146-163.
 """
 from __future__ import annotations
 
@@ -28,6 +32,36 @@ from .model import FLAT_ORDER, GaussianModelOriginBase, carve_flat, flat_field_s
 from .render import GaussianSplatGradients, GaussianSplatOp
 from .strategy import GaussianTrainState
 from .tools import get_expon_lr_func
+
+
+def shard_layout(total: int, world: int, align: int = 4) -> tuple[int, int]:
+    """``(shard_len, padded_total)``: equal slices of a flat buffer, each a multiple of ``align`` elements
+    (16 bytes for float32) so that every slice starts on a vector boundary; the tail slice is padding."""
+    s = -(-total // world)
+    s = -(-s // align) * align
+    return s, s * world
+
+
+def clip_fields(offsets: dict, lo: int, hi: int) -> list[tuple[str, int, int]]:
+    """Intersect the fields ``name -> (offset, count)`` of a flat buffer with the slice [lo, hi):
+    ``[(name, start, count)]`` with ``start`` an absolute element index, empty intersections dropped."""
+    out = []
+    for name, (off, cnt) in offsets.items():
+        a, b = max(off, lo), min(off + cnt, hi)
+        if b > a:
+            out.append((name, a, b - a))
+    return out
+
+
+def sharded_update(grad_flat: torch.Tensor, param_flat: torch.Tensor, grad_shard: torch.Tensor, rank: int,
+                   group, apply_fn) -> None:
+    """Reduce-scatter ``grad_flat`` (sum), let ``apply_fn(lo, hi, grad_shard)`` update ``param_flat[lo:hi]`` in
+    place, then all-gather the slices in place.  Both flat buffers hold ``world * len(grad_shard)`` elements."""
+    s = grad_shard.numel()
+    lo, hi = rank * s, (rank + 1) * s
+    torch.distributed.reduce_scatter_tensor(grad_shard, grad_flat, group=group)
+    apply_fn(lo, hi, grad_shard)
+    torch.distributed.all_gather_into_tensor(param_flat, param_flat[lo:hi], group=group)
 
 
 class HostFeed:
@@ -61,15 +95,27 @@ class HostFeed:
 class SplatTrainer:
     def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
-                 spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False):
-        """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs)."""
+                 spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False,
+                 shard_optimizer: bool | None = None):
+        """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs).
+        ``shard_optimizer``: reduce-scatter + sliced Adam + all-gather instead of all-reduce + replicated
+        Adam; default on when there is more than one rank."""
         assert model.has_fused_activations, "the trainer drives the fused-activation model"
         assert model.color_sh_base is not None and model.color_sh.shape[1] == 15, "degree-3 split SH layout"
         self.model = model
-        if model.flat is None:
-            # move the parameters into one flat buffer; the model's tensors become views of it
-            n = len(model)
-            flat = torch.empty(59 * n, dtype=torch.float32, device=model.xyz.device)
+        self.pg = process_group
+        self.world, self.rank = 1, 0
+        if process_group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            self.world = torch.distributed.get_world_size(process_group)
+            self.rank = torch.distributed.get_rank(process_group)
+        self.sharded = (self.world > 1) if shard_optimizer is None else (bool(shard_optimizer) and self.world > 1)
+        n, dev = len(model), model.xyz.device
+        total = 59 * n
+        self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)
+        if model.flat is None or model.flat.numel() < padded:
+            # move the parameters into one flat buffer (padded to a whole number of slices when the
+            # optimizer is sharded); the model's tensors become views of it
+            flat = torch.zeros(padded, dtype=torch.float32, device=dev)
             views = carve_flat(flat, n)
             for k in FLAT_ORDER:
                 views[k].copy_(getattr(model, k).detach())
@@ -78,17 +124,15 @@ class SplatTrainer:
         self.op = GaussianSplatOp(op_cfg)
         self.lambda_dssim = float(lambda_dssim)
         self.batch_size = int(batch_size)
-        self.pg = process_group
-        self.world = 1
-        if process_group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
-            self.world = torch.distributed.get_world_size(process_group)
         self.need_max_radii = need_max_radii
-        n, dev = len(model), model.xyz.device
-        self.grad_flat = torch.zeros(59 * n, dtype=torch.float32, device=dev)
+        self.grad_flat = torch.zeros(padded, dtype=torch.float32, device=dev)
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
-        self.exp_avg = torch.zeros(59 * n, dtype=torch.float32, device=dev)
-        self.exp_avg_sq = torch.zeros(59 * n, dtype=torch.float32, device=dev)
+        # Adam moments: the whole buffer on one rank, only this rank's slice when sharded
+        self.state_lo = self.rank * self.shard_len if self.sharded else 0
+        self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) if self.sharded else None
+        self.exp_avg = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self.state = GaussianTrainState.create(n, device=dev)
         oc = optim_cfg or config_def.Optimizer()
         bs = math.sqrt(self.batch_size)                              # tools.py:147-163
@@ -124,13 +168,14 @@ class SplatTrainer:
             self.lrs["xyz"] = float(self.xyz_schedule(self.step_count))   # train.py:286-292
         segs = []
         esz = 4
-        for name in FLAT_ORDER:
-            off, cnt = self._offsets[name]
+        lo = self.state_lo
+        grad = self.grad_shard if self.sharded else self.grad_flat   # both start at flat index `lo`
+        for name, a, cnt in clip_fields(self._offsets, lo, lo + self.shard_len):
             s = _lib.AdamSegment()
-            s.param = self.model.flat.data_ptr() + off * esz
-            s.grad = self.grad_flat.data_ptr() + off * esz
-            s.exp_avg = self.exp_avg.data_ptr() + off * esz
-            s.exp_avg_sq = self.exp_avg_sq.data_ptr() + off * esz
+            s.param = self.model.flat.data_ptr() + a * esz
+            s.grad = grad.data_ptr() + (a - lo) * esz
+            s.exp_avg = self.exp_avg.data_ptr() + (a - lo) * esz
+            s.exp_avg_sq = self.exp_avg_sq.data_ptr() + (a - lo) * esz
             s.count = cnt
             s.lr, s.beta1, s.beta2, s.eps = float(self.lrs[name]), b1, b2, self.eps
             s.bias_correction1, s.bias_correction2_sqrt = bc1, bc2s
@@ -170,17 +215,26 @@ class SplatTrainer:
             self.op._mark("l1_dssim")
             _, duv, _ =self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
                                          return_uv_grad=True, grad_out=self.grad_model)
-        if self.world > 1:
-            torch.distributed.all_reduce(self.grad_flat, group=self.pg)
-            self.op._mark("allreduce")
-        if update:
-            stats = None
-            if duv is not None:
-                w, h = out.image_shape_wh
-                stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
-                                          loss_batch=duv.shape[0] * self.world)
-            _launch_adam(self._adam_segments(), stats, model.xyz.device)
-            self.op._mark("adam_stats")
+        stats = None
+        if update and duv is not None:
+            w, h = out.image_shape_wh
+            stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
+                                      loss_batch=duv.shape[0] * self.world)
+        if self.sharded and update:
+            def apply(lo, hi, grad_shard):
+                self.op._mark("reduce_scatter")
+                _launch_adam(self._adam_segments(), stats, model.xyz.device)
+                self.op._mark("adam_stats")
+            sharded_update(self.grad_flat, model.flat, self.grad_shard, self.rank, self.pg, apply)
+            self.op._mark("all_gather")
+        else:
+            if self.world > 1:
+                torch.distributed.all_reduce(self.grad_flat, group=self.pg)
+                self.op._mark("allreduce")
+            if update:
+                assert not self.sharded, "a sharded optimizer cannot apply a replicated update"
+                _launch_adam(self._adam_segments(), stats, model.xyz.device)
+                self.op._mark("adam_stats")
         return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
 
     @torch.no_grad()
@@ -199,4 +253,4 @@ class SplatTrainer:
 
     def parameter_checksum(self) -> torch.Tensor:
         """Sum of the raw parameter bits; replicas must agree after every update."""
-        return self.model.flat.view(torch.int32).sum(dtype=torch.int64)
+        return self.model.flat[:59 * len(self.model)].view(torch.int32).sum(dtype=torch.int64)

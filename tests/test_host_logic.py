@@ -136,3 +136,85 @@ def test_data_parallel_allreduce_equals_batched_gradient_gloo():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert err < 1e-5, err
+
+
+def test_shard_layout_and_field_clipping():
+    from d3gs_research_b200.trainer import clip_fields, shard_layout
+    n = 1001
+    total = 59 * n
+    for world in (1, 2, 3, 8):
+        s, padded = shard_layout(total, world)
+        assert s % 4 == 0 and padded == s * world and padded >= total and padded - total < 4 * world + world
+    offsets, off = {}, 0
+    for name, per in zip(FLAT_ORDER, (3, 4, 3, 1, 3, 45)):
+        offsets[name] = (off, per * n)
+        off += per * n
+    s, padded = shard_layout(total, 3)
+    covered = np.zeros(padded, dtype=np.int32)
+    for r in range(3):
+        for name, a, cnt in clip_fields(offsets, r * s, (r + 1) * s):
+            o, c = offsets[name]
+            assert o <= a and a + cnt <= o + c and r * s <= a and a + cnt <= (r + 1) * s
+            covered[a:a + cnt] += 1
+    assert (covered[:total] == 1).all() and (covered[total:] == 0).all()   # every parameter in exactly one slice
+
+
+def _shard_worker(rank, world, port, q):
+    """Reduce-scatter + sliced update + in-place all-gather must leave every replica with exactly the
+    parameters of all-reduce + replicated update."""
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from d3gs_research_b200.trainer import clip_fields, shard_layout, sharded_update
+    n = 37
+    total = 59 * n
+    s, padded = shard_layout(total, world)
+    offsets, off = {}, 0
+    for name, per in zip(FLAT_ORDER, (3, 4, 3, 1, 3, 45)):
+        offsets[name] = (off, per * n)
+        off += per * n
+    lrs = {name: 0.01 * (k + 1) for k, name in enumerate(FLAT_ORDER)}
+    g0 = torch.Generator().manual_seed(7)
+    param0 = torch.zeros(padded)
+    param0[:total] = torch.randn(total, generator=g0)
+
+    def adam(p, g, m, v, lr, t):
+        m.mul_(0.9).add_(g, alpha=0.1)
+        v.mul_(0.999).addcmul_(g, g, value=0.001)
+        p.addcdiv_(m / (1 - 0.9 ** t), (v / (1 - 0.999 ** t)).sqrt_().add_(1e-15), value=-lr)
+
+    # replicated: all-reduce, every rank updates everything
+    pr, mr, vr = param0.clone(), torch.zeros(padded), torch.zeros(padded)
+    # sharded: moments exist for this rank's slice only
+    ps, ms, vs, gs = param0.clone(), torch.zeros(s), torch.zeros(s), torch.zeros(s)
+    for t in (1, 2, 3):
+        grad = torch.zeros(padded)
+        grad[:total] = torch.randn(total, generator=torch.Generator().manual_seed(100 * t + rank))
+        full = grad.clone()
+        dist.all_reduce(full)
+        for name, (o, c) in offsets.items():
+            adam(pr[o:o + c], full[o:o + c], mr[o:o + c], vr[o:o + c], lrs[name], t)
+
+        def apply(lo, hi, grad_shard):
+            for name, a, cnt in clip_fields(offsets, lo, hi):
+                adam(ps[a:a + cnt], grad_shard[a - lo:a - lo + cnt], ms[a - lo:a - lo + cnt], vs[a - lo:a - lo + cnt],
+                     lrs[name], t)
+        sharded_update(grad, ps, gs, rank, None, apply)
+    q.put((rank, bool(torch.equal(ps, pr)), float(ps[total:].abs().max()) if padded > total else 0.0))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_optimizer_equals_replicated_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_shard_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=180) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True, 0.0), (1, True, 0.0)], got
