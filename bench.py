@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--n", type=int, default=0, help="override the Gaussian count (profiling on small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-update", action="store_true",
+                    help="N>1: sharded optimizer through NCCL reduce-scatter / all-gather instead of the peer-memory kernel")
     ap.add_argument("--replicated-adam", action="store_true",
                     help="N>1: all-reduce + full Adam on every rank instead of the sharded optimizer")
     ap.add_argument("--cpu-sample", type=int, default=4, help="CPU baseline runs on 1/S of the Gaussians")
@@ -209,7 +211,8 @@ def main():
                                                      sc["sh_rest"], device=dev, cur_sh_degree=scfg.sh_degree)
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
     trainer = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world,
-                           shard_optimizer=False if args.replicated_adam else None)
+                           shard_optimizer=False if args.replicated_adam else None,
+                           peer_update=False if (args.nccl_update or args.replicated_adam) else None)
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
     target_host = sc["target"][rank % sc["target"].shape[0]][None].contiguous().pin_memory()
@@ -273,6 +276,12 @@ def main():
     views = world
     value = views * args.steps / (ms_total / 1e3)
     e2e_value = views * args.steps / (ms_e2e / 1e3)
+    optimizer_kind = ("single rank" if world == 1 else
+                      "sharded, one kernel over NVLink peer memory: sum of all ranks' gradient slices, Adam, store to "
+                      "all ranks' parameters" if trainer._peerset is not None else
+                      "sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded else
+                      "replicated after all-reduce")
+    trainer.close()    # unmap the peer buffers (collective) before the process group goes away
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -284,7 +293,8 @@ def main():
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-    kernel_stages = {k: v for k, v in stage_ms.items() if k not in ("host_readback_idle", "allreduce", "reduce_scatter", "all_gather")}
+    kernel_stages = {k: v for k, v in stage_ms.items() if k not in ("host_readback_idle", "allreduce", "reduce_scatter", "all_gather", "barrier_grads",
+                                                                  "barrier_params")}
     dom = max(kernel_stages, key=kernel_stages.get)
     dom_bytes = algorithmic_bytes(dom, N, V, K, P, Tn)
     achieved = dom_bytes / (kernel_stages[dom] * 1e-3) / 1e9
@@ -296,8 +306,7 @@ def main():
         "config": {"workload": WORKLOAD if args.config == "cfg3" and not n_override else f"{args.config} n={N}",
                    "gaussians": N, "visible": V, "sort_pairs": K, "resolution": [W, H], "views_per_gpu": 1,
                    "parallelism": f"dp{world} over views, replicated Gaussians",
-                   "optimizer": ("sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded
-                                 else ("replicated after all-reduce" if world > 1 else "single rank")),
+                   "optimizer": optimizer_kind,
                    "replicas_agree": replicas_agree, "early_filter": "OBB_DFVT",
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(target_host.numel() * 4),

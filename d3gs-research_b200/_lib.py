@@ -65,7 +65,16 @@ class DensifyStats(C.Structure):
                 ("duv_stride", C.c_int32)]
 
 
-_STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats]
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class PeerSet(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("grad", C.c_void_p * MAX_PEERS),
+                ("param", C.c_void_p * MAX_PEERS), ("status", C.c_void_p)]
+
+
+_STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats, PeerSet]
 
 _P, _I32, _I64, _F, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
 
@@ -95,6 +104,11 @@ SIGNATURES = {
     "d3gs_l1_dssim_forward_backward": (_I32, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P, _SZ, _P]),
     "d3gs_adam_stats_step": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), _P]),
     "d3gs_densify_stats": (_I32, [C.POINTER(DensifyStats), _P]),
+    "d3gs_adam_stats_step_peers": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), C.POINTER(PeerSet), _P]),
+    "d3gs_peer_buffer_create": (_I32, [_I64, C.POINTER(_P), _P]),
+    "d3gs_peer_buffer_open": (_I32, [_P, C.POINTER(_P)]),
+    "d3gs_peer_buffer_close": (_I32, [_P]),
+    "d3gs_peer_buffer_destroy": (_I32, [_P]),
 }
 
 

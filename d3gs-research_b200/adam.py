@@ -51,7 +51,10 @@ def _segments_of(optim: "GaussianAdam") -> list[_lib.AdamSegment]:
     return segs
 
 
-def _launch(segs: list[_lib.AdamSegment], stats: _lib.DensifyStats | None, device):
+def _launch(segs: list[_lib.AdamSegment], stats: _lib.DensifyStats | None, device,
+            peers: "_lib.PeerSet | None" = None):
+    """``peers``: gradients are summed over every rank's buffer and parameters stored into every rank's
+    buffer through peer mappings (``d3gs_adam_stats_step_peers``)."""
     lib = _lib.load()
     stream = torch.cuda.current_stream(device).cuda_stream
     first = True
@@ -59,7 +62,11 @@ def _launch(segs: list[_lib.AdamSegment], stats: _lib.DensifyStats | None, devic
         chunk = segs[k:k + MAX_SEGMENTS]
         arr = (_lib.AdamSegment * max(len(chunk), 1))(*chunk)
         st = C.byref(stats) if (stats is not None and first) else None
-        _lib.check(lib.d3gs_adam_stats_step(arr, len(chunk), st, stream), "d3gs_adam_stats_step")
+        if peers is None:
+            _lib.check(lib.d3gs_adam_stats_step(arr, len(chunk), st, stream), "d3gs_adam_stats_step")
+        else:
+            _lib.check(lib.d3gs_adam_stats_step_peers(arr, len(chunk), st, C.byref(peers), stream),
+                       "d3gs_adam_stats_step_peers")
         first = False
 
 

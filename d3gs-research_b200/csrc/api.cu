@@ -52,6 +52,7 @@ extern "C" size_t d3gs_struct_size(int32_t which) {
         case 4: return sizeof(D3gsSplatContext);
         case 5: return sizeof(D3gsAdamSegment);
         case 6: return sizeof(D3gsDensifyStats);
+        case 7: return sizeof(D3gsPeerSet);
         default: return 0;
     }
 }

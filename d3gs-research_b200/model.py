@@ -32,20 +32,26 @@ def flat_field_sizes(n: int, sh_rest: int = 15) -> dict[str, tuple[int, tuple]]:
             "opacity": (n, (n,)), "color_sh_base": (3 * n, (n, 3)), "color_sh": (sh_rest * 3 * n, (n, sh_rest, 3))}
 
 
-def carve_flat(flat: torch.Tensor, n: int, sh_rest: int = 15) -> dict[str, torch.Tensor]:
-    """Views of the six model tensors inside one flat float32 buffer of at least 59*n elements (a longer
-    buffer carries padding at its end, e.g. to a whole number of optimizer slices).
+def flat_layout(n: int, sh_rest: int = 15, align: int = 4) -> tuple[dict[str, tuple[int, int, tuple]], int]:
+    """``({name: (offset, count, shape)}, total)`` of the six tensors inside one flat float32 buffer.
 
-    Every view starts on a 16-byte boundary when n is a multiple of 4 (the kernels' float4 paths
-    check alignment themselves and fall back to scalar accesses otherwise).
-    """
+    Every field starts on a multiple of ``align`` elements (16 bytes: the kernels read quaternions and
+    SH rows with vector loads), so ``total`` is 59*n plus at most 3 elements of padding per field; it is
+    exactly 59*n when n is a multiple of 4."""
     out, off = {}, 0
     for name in FLAT_ORDER:
         cnt, shape = flat_field_sizes(n, sh_rest)[name]
-        out[name] = flat[off:off + cnt].view(*shape)
-        off += cnt
-    assert off <= flat.numel()
-    return out
+        out[name] = (off, cnt, shape)
+        off = -(-(off + cnt) // align) * align
+    return out, off
+
+
+def carve_flat(flat: torch.Tensor, n: int, sh_rest: int = 15) -> dict[str, torch.Tensor]:
+    """Views of the six model tensors inside one flat float32 buffer laid out by ``flat_layout`` (a longer
+    buffer carries padding at its end, e.g. to a whole number of optimizer slices)."""
+    layout, total = flat_layout(n, sh_rest)
+    assert total <= flat.numel()
+    return {name: flat[off:off + cnt].view(*shape) for name, (off, cnt, shape) in layout.items()}
 
 
 @dataclasses.dataclass(kw_only=True)
@@ -224,8 +230,8 @@ class GaussianModelOriginBase:
 
     @classmethod
     def create_flat(cls, N: int, device: torch.device | str = "cuda", cur_sh_degree: int = 3):
-        """Degree-3 split model whose six tensors are views of one flat [59*N] buffer."""
-        flat = torch.zeros(59 * N, dtype=torch.float32, device=device)
+        """Degree-3 split model whose six tensors are views of one flat buffer (``flat_layout``)."""
+        flat = torch.zeros(flat_layout(N)[1], dtype=torch.float32, device=device)
         views = carve_flat(flat, N)
         return cls(**views, cur_sh_degree=cur_sh_degree, flat=flat)
 

@@ -22,7 +22,7 @@ import torch
 from . import _lib
 from .camera import BasicPinholeCamera
 from .config_def import EarlyFilterAlgo, GaussianSplatConfig, RasterizeBackwardAlgo
-from .model import GaussianModelOriginBase, carve_flat
+from .model import GaussianModelOriginBase, carve_flat, flat_layout
 
 
 def div_up(a: int, b: int) -> int:
@@ -442,7 +442,7 @@ class GaussianSplatOp:
         num = len(model)
         if grad_out is None:
             if model.flat is not None or (model.color_sh_base is not None and model.color_sh.shape[1] == 15):
-                flat = torch.empty(59 * num, dtype=torch.float32, device=dev)
+                flat = torch.zeros(flat_layout(num)[1], dtype=torch.float32, device=dev)
                 grad_out = type(model)(**carve_flat(flat, num), cur_sh_degree=model.cur_sh_degree, act_applied=True,
                                        flat=flat)
             else:

@@ -16,10 +16,16 @@ more than one rank) the sum is a reduce-scatter: every rank owns one contiguous 
 parameter buffer together with its Adam moments, updates only that slice, and an in-place all-gather
 brings the updated slices back to every replica.  The bytes on the wire equal those of an all-reduce,
 while the Adam launch, which is bound by HBM bandwidth, shrinks by the number of ranks.
+With ``peer_update`` (the default on NCCL when the buffers can be mapped) the three steps are one kernel
+over NVLink peer memory: ``PeerBuffer`` gives every process a mapping of every rank's gradient and
+parameter buffer, the Adam launch sums its slice of all gradient buffers with peer loads and stores the
+new parameters into all parameter buffers, and two one-element all-reduces order it against the other
+ranks (all gradients written / all parameters written).
 Optimizer hyper-parameters are scaled with the global batch like tools.py:146-163.
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 
 import torch
@@ -28,7 +34,7 @@ from . import _lib, config_def
 from .adam import _launch as _launch_adam
 from .adam import make_stats_struct
 from .fused_ssim import l1_dssim_forward_backward
-from .model import FLAT_ORDER, GaussianModelOriginBase, carve_flat, flat_field_sizes
+from .model import FLAT_ORDER, GaussianModelOriginBase, carve_flat, flat_layout
 from .render import GaussianSplatGradients, GaussianSplatOp
 from .strategy import GaussianTrainState
 from .tools import get_expon_lr_func
@@ -64,6 +70,78 @@ def sharded_update(grad_flat: torch.Tensor, param_flat: torch.Tensor, grad_shard
     torch.distributed.all_gather_into_tensor(param_flat, param_flat[lo:hi], group=group)
 
 
+class _DeviceSpan:
+    """Lets torch alias raw device memory (``torch.as_tensor`` reads ``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, numel: int):
+        self.__cuda_array_interface__ = {"shape": (numel,), "typestr": "<f4", "data": (ptr, False), "version": 2,
+                                         "strides": None}
+
+
+class PeerBuffer:
+    """One float32 buffer per rank of a node, each mapped into every rank's process.
+
+    ``tensor`` aliases this rank's buffer; ``ptrs[q]`` is rank q's buffer as mapped here.  Construction is
+    collective over ``group``; it raises on every rank when any rank could not allocate or map."""
+
+    def __init__(self, numel: int, device, group=None):
+        dist = torch.distributed
+        lib = _lib.load()
+        self.numel, self.device, self.group = numel, device, group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.world, self.rank = world, rank
+        self.ptrs: list[int] = [0] * world
+        self._own = 0
+        ok = torch.ones(1, dtype=torch.int32, device=device)
+        handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
+        err = ""
+        with torch.cuda.device(device):
+            ptr = C.c_void_p()
+            if lib.d3gs_peer_buffer_create(numel * 4, C.byref(ptr), handle) != 0:
+                ok.zero_()
+                err = _lib.last_error()
+            else:
+                self._own = ptr.value
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                self.close(collective=False)
+                raise RuntimeError(f"peer buffer allocation failed on some rank ({err or 'not this one'})")
+            handles = [None] * world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            for q in range(world):
+                if q == rank:
+                    self.ptrs[q] = self._own
+                    continue
+                mapped = C.c_void_p()
+                if lib.d3gs_peer_buffer_open(handles[q], C.byref(mapped)) != 0:
+                    ok.zero_()
+                    err = _lib.last_error()
+                    break
+                self.ptrs[q] = mapped.value
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                self.close(collective=False)
+                raise RuntimeError(f"peer buffer mapping failed on some rank ({err or 'not this one'})")
+        self.tensor = torch.as_tensor(_DeviceSpan(self._own, numel), device=device)
+        assert self.tensor.data_ptr() == self._own, "torch copied the buffer instead of aliasing it"
+
+    def close(self, collective: bool = True):
+        """Unmap the peers' buffers, then (after every rank has unmapped) free this rank's."""
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for q, p in enumerate(self.ptrs):
+                if p and q != self.rank:
+                    lib.d3gs_peer_buffer_close(p)
+            self.ptrs = [0] * self.world
+            if collective:
+                torch.distributed.barrier(group=self.group)
+            if self._own:
+                lib.d3gs_peer_buffer_destroy(self._own)
+                self._own = 0
+        self.tensor = None
+
+
 class HostFeed:
     """Uploads per-step inputs that live in pinned host memory on a side stream, double buffered.
 
@@ -96,10 +174,11 @@ class SplatTrainer:
     def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
                  spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False,
-                 shard_optimizer: bool | None = None):
+                 shard_optimizer: bool | None = None, peer_update: bool | None = None):
         """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs).
         ``shard_optimizer``: reduce-scatter + sliced Adam + all-gather instead of all-reduce + replicated
-        Adam; default on when there is more than one rank."""
+        Adam; default on when there is more than one rank.  ``peer_update``: do the sharded update as one
+        kernel over mapped peer buffers; default: tried on NCCL, NCCL collectives when mapping fails."""
         assert model.has_fused_activations, "the trainer drives the fused-activation model"
         assert model.color_sh_base is not None and model.color_sh.shape[1] == 15, "degree-3 split SH layout"
         self.model = model
@@ -110,12 +189,31 @@ class SplatTrainer:
             self.rank = torch.distributed.get_rank(process_group)
         self.sharded = (self.world > 1) if shard_optimizer is None else (bool(shard_optimizer) and self.world > 1)
         n, dev = len(model), model.xyz.device
-        total = 59 * n
+        layout, total = flat_layout(n)
+        self.flat_total = total
         self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)
-        if model.flat is None or model.flat.numel() < padded:
+        self.peer_param = self.peer_grad = None
+        want_peer = self.sharded and dev.type == "cuda" and self.world <= _lib.MAX_PEERS and \
+            torch.distributed.get_backend(process_group) == "nccl"
+        if peer_update is not None:
+            assert not peer_update or want_peer, "peer_update needs a sharded optimizer on NCCL with at most 8 ranks"
+            want_peer = bool(peer_update)
+        if want_peer:
+            try:
+                self.peer_param = PeerBuffer(padded, dev, process_group)
+                self.peer_grad = PeerBuffer(padded, dev, process_group)
+            except RuntimeError:
+                if peer_update:
+                    raise
+                if self.peer_param is not None:
+                    self.peer_param.close()
+                self.peer_param = self.peer_grad = None
+        if self.peer_param is not None or model.flat is None or model.flat.numel() < padded:
             # move the parameters into one flat buffer (padded to a whole number of slices when the
-            # optimizer is sharded); the model's tensors become views of it
-            flat = torch.zeros(padded, dtype=torch.float32, device=dev)
+            # optimizer is sharded, inside the mapped buffer for the peer update); the model's tensors
+            # become views of it
+            flat = self.peer_param.tensor if self.peer_param is not None else \
+                torch.zeros(padded, dtype=torch.float32, device=dev)
             views = carve_flat(flat, n)
             for k in FLAT_ORDER:
                 views[k].copy_(getattr(model, k).detach())
@@ -125,12 +223,23 @@ class SplatTrainer:
         self.lambda_dssim = float(lambda_dssim)
         self.batch_size = int(batch_size)
         self.need_max_radii = need_max_radii
-        self.grad_flat = torch.zeros(padded, dtype=torch.float32, device=dev)
+        self.grad_flat = self.peer_grad.tensor if self.peer_grad is not None else \
+            torch.zeros(padded, dtype=torch.float32, device=dev)
+        self._peerset = None
+        if self.peer_param is not None:
+            ps = _lib.PeerSet()
+            ps.world, ps.rank = self.world, self.rank
+            for q in range(self.world):
+                ps.grad[q], ps.param[q] = self.peer_grad.ptrs[q], self.peer_param.ptrs[q]
+            ps.status = self.op._sync_words(dev).data_ptr() + 8   # the word every forward pass checks
+            self._peerset = ps
+            self._bar = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
         # Adam moments: the whole buffer on one rank, only this rank's slice when sharded
         self.state_lo = self.rank * self.shard_len if self.sharded else 0
-        self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) if self.sharded else None
+        self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) \
+            if (self.sharded and self._peerset is None) else None
         self.exp_avg = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self.state = GaussianTrainState.create(n, device=dev)
@@ -150,12 +259,7 @@ class SplatTrainer:
         self._loss_scratch = None
         self._loss_sums = torch.zeros(2, dtype=torch.float64, device=dev)
         self._dcolor = None
-        self._offsets = {}
-        off = 0
-        for name in FLAT_ORDER:
-            cnt, _ = flat_field_sizes(n)[name]
-            self._offsets[name] = (off, cnt)
-            off += cnt
+        self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
 
     # ------------------------------------------------------------------------------------------
     def _adam_segments(self):
@@ -169,11 +273,14 @@ class SplatTrainer:
         segs = []
         esz = 4
         lo = self.state_lo
-        grad = self.grad_shard if self.sharded else self.grad_flat   # both start at flat index `lo`
+        if self.grad_shard is not None:
+            grad_ptr = self.grad_shard.data_ptr()              # reduce-scatter output: starts at flat index `lo`
+        else:
+            grad_ptr = self.grad_flat.data_ptr() + lo * esz    # this rank's flat gradient buffer
         for name, a, cnt in clip_fields(self._offsets, lo, lo + self.shard_len):
             s = _lib.AdamSegment()
             s.param = self.model.flat.data_ptr() + a * esz
-            s.grad = grad.data_ptr() + (a - lo) * esz
+            s.grad = grad_ptr + (a - lo) * esz
             s.exp_avg = self.exp_avg.data_ptr() + (a - lo) * esz
             s.exp_avg_sq = self.exp_avg_sq.data_ptr() + (a - lo) * esz
             s.count = cnt
@@ -220,7 +327,21 @@ class SplatTrainer:
             w, h = out.image_shape_wh
             stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
                                       loss_batch=duv.shape[0] * self.world)
-        if self.sharded and update:
+        self.apply_gradients(stats, update)
+        return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
+
+    @torch.no_grad()
+    def apply_gradients(self, stats=None, update: bool = True) -> None:
+        """Sum ``grad_flat`` over the ranks and take the Adam step (second half of ``step``)."""
+        model = self.model
+        if self._peerset is not None and update:
+            torch.distributed.all_reduce(self._bar, group=self.pg)    # every rank's gradient is complete
+            self.op._mark("barrier_grads")
+            _launch_adam(self._adam_segments(), stats, model.xyz.device, peers=self._peerset)
+            self.op._mark("adam_stats")
+            torch.distributed.all_reduce(self._bar, group=self.pg)    # every rank's parameters are complete
+            self.op._mark("barrier_params")
+        elif self.sharded and update:
             def apply(lo, hi, grad_shard):
                 self.op._mark("reduce_scatter")
                 _launch_adam(self._adam_segments(), stats, model.xyz.device)
@@ -235,7 +356,6 @@ class SplatTrainer:
                 assert not self.sharded, "a sharded optimizer cannot apply a replicated update"
                 _launch_adam(self._adam_segments(), stats, model.xyz.device)
                 self.op._mark("adam_stats")
-        return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
 
     @torch.no_grad()
     def render(self, cameras) -> "torch.Tensor":
@@ -243,6 +363,22 @@ class SplatTrainer:
         self.model.act_applied = True
         out, _ = self.op.forward(self.model, cameras, training=False)
         return out
+
+    def close(self):
+        """Release the mapped peer buffers (collective).  The model's tensors are moved to ordinary memory."""
+        if self.peer_param is None:
+            return
+        n = len(self.model)
+        flat = self.model.flat.clone()
+        views = carve_flat(flat, n)
+        for k in FLAT_ORDER:
+            setattr(self.model, k, views[k])
+        self.model.flat = flat
+        self.grad_flat = self.grad_model = None
+        self._peerset = None
+        self.peer_grad.close()
+        self.peer_param.close()
+        self.peer_param = self.peer_grad = None
 
     def reduce_stats(self):
         """All-reduce the densification statistics (each rank accumulates its own views' share)."""
@@ -253,4 +389,4 @@ class SplatTrainer:
 
     def parameter_checksum(self) -> torch.Tensor:
         """Sum of the raw parameter bits; replicas must agree after every update."""
-        return self.model.flat[:59 * len(self.model)].view(torch.int32).sum(dtype=torch.int64)
+        return self.model.flat[:self.flat_total].view(torch.int32).sum(dtype=torch.int64)

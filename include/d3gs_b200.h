@@ -127,7 +127,7 @@ size_t d3gs_last_error(char* buf, size_t cap);
 /* DeviceSort.get_higher_msb (csrc/devsort.py:129-149): number of bits needed for n */
 int32_t d3gs_bit_length(uint32_t n);
 /* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
- * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment */
+ * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet */
 size_t d3gs_struct_size(int32_t which);
 
 /* ---- K1 preprocess forward (render.py:250-681) ------------------------------------------- */
@@ -247,6 +247,41 @@ typedef struct D3gsDensifyStats {
 int32_t d3gs_adam_stats_step(const D3gsAdamSegment* segments, int32_t num_segments, const D3gsDensifyStats* stats,
                              void* stream);
 int32_t d3gs_densify_stats(const D3gsDensifyStats* stats, void* stream);
+
+/* ---- data-parallel update over peer memory (no counterpart in the reference, which trains on one GPU;
+ * the batch semantics it implements are those of train.py:170-172 and tools.py:146-163) ------------
+ * Every rank (one process per GPU) renders its own view and holds the full model.  The flat gradient
+ * and parameter buffers of all ranks live in buffers that each process has mapped (CUDA IPC, NVLink
+ * peer access).  A rank owns one slice of the parameters with its Adam moments; one launch
+ *   - reads that slice of EVERY rank's gradient buffer (bulk async copies into shared memory, so that
+ *     enough bytes are in flight to cover the latency of the links) and adds them in rank order,
+ *   - applies Adam to the slice,
+ *   - writes the new parameters into EVERY rank's parameter buffer (peer stores),
+ * so gradients and parameters cross NVLink in opposite directions at the same time and never make a
+ * second trip through HBM.  The kernel does not wait for other ranks: the caller orders the launches with
+ * a collective barrier before (all gradients written) and after (all parameters written).
+ * Segments: param points into param[rank], grad into grad[rank]; their element offsets are applied to
+ * every peer's buffer. */
+#define D3GS_MAX_PEERS 8
+typedef struct D3gsPeerSet {
+    int32_t world, rank;
+    const float* grad[D3GS_MAX_PEERS];   /* each rank's flat gradient buffer as mapped in this process */
+    float* param[D3GS_MAX_PEERS];        /* each rank's flat parameter buffer as mapped in this process */
+    uint32_t* status;                    /* optional device word: D3GS_STATUS_COPY_TIMEOUT is OR-ed in when a
+                                            staged copy did not arrive in time (that chunk is left unchanged) */
+} D3gsPeerSet;
+int32_t d3gs_adam_stats_step_peers(const D3gsAdamSegment* segments, int32_t num_segments,
+                                   const D3gsDensifyStats* stats, const D3gsPeerSet* peers, void* stream);
+
+/* Buffers another process on the same node can map.  create: cudaMalloc on the current device, zero-filled,
+ * plus a 64-byte handle to send to the peers; open: map a peer's buffer into this process (enables peer
+ * access to its device); close / destroy release a mapping / the allocation.  Not for the per-step path:
+ * all four synchronise the device. */
+#define D3GS_PEER_HANDLE_BYTES 64
+int32_t d3gs_peer_buffer_create(int64_t bytes, void** ptr, void* handle);
+int32_t d3gs_peer_buffer_open(const void* handle, void** ptr);
+int32_t d3gs_peer_buffer_close(void* ptr);
+int32_t d3gs_peer_buffer_destroy(void* ptr);
 
 #ifdef __cplusplus
 }

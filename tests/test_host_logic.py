@@ -33,13 +33,18 @@ def test_unsupported_options_raise_at_construction(kw):
 
 
 def test_flat_model_views_and_containers():
+    from d3gs_research_b200.model import flat_layout
+    assert flat_layout(12)[1] == 59 * 12                       # no padding when n is a multiple of 4
     n = 10
-    flat = torch.arange(59 * n, dtype=torch.float32)
+    layout, total = flat_layout(n)
+    assert total == 600 and all(off % 4 == 0 for off, _, _ in layout.values())   # every field on a 16-byte boundary
+    flat = torch.arange(total, dtype=torch.float32)
     v = carve_flat(flat, n)
     assert [tuple(v[k].shape) for k in FLAT_ORDER] == [(n, 3), (n, 4), (n, 3), (n,), (n, 3), (n, 15, 3)]
-    assert v["xyz"].data_ptr() == flat.data_ptr() and v["color_sh"][-1, -1, -1] == 59 * n - 1
+    assert v["xyz"].data_ptr() == flat.data_ptr() and v["quaternion_xyzw"][0, 0] == 32
+    assert v["color_sh"][-1, -1, -1] == layout["color_sh"][0] + 450 - 1
     m = d3.GaussianModelOriginFused.create_flat(n, device="cpu")
-    assert len(m) == n and m.color_sh_degree == 3 and m.has_fused_activations and m.flat.numel() == 59 * n
+    assert len(m) == n and m.color_sh_degree == 3 and m.has_fused_activations and m.flat.numel() == total
     assert m.get_unique_kernel_key() == "3_3_normalize_exponential_sigmoid_False"
     z = d3.GaussianModelOriginFused.zeros_like(m, num=4, not_param=True)
     assert len(z) == 4 and z.color_sh.shape == (4, 15, 3)
