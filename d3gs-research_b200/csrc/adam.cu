@@ -49,13 +49,15 @@ struct AdamArgs {
 // p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps).  The three divisions by per-tensor constants are
 // multiplications by reciprocals computed once on the host in double; the one per-element division is a
 // single correctly rounded reciprocal.
+// Every operation is an explicit round-to-nearest intrinsic, so the vector path, the scalar path and the
+// peer variant produce the same bits for the same inputs whatever the compiler would have contracted.
 __device__ __forceinline__ void adam_update(float g, float& p, float& m, float& v, const SegConst& c) {
-    g = g * c.inv_grad_scale;
-    if (c.weight_decay != 0.0f) g += p * c.weight_decay;
-    m = g * c.omb1 + m * c.beta1;
-    v = (g * g) * c.omb2 + v * c.beta2;
-    const float denom = sqrtf(v) * c.inv_bc2_sqrt + c.eps;
-    p = p - (c.step_size * m) * __frcp_rn(denom);
+    g = __fmul_rn(g, c.inv_grad_scale);
+    if (c.weight_decay != 0.0f) g = __fmaf_rn(p, c.weight_decay, g);
+    m = __fmaf_rn(g, c.omb1, __fmul_rn(m, c.beta1));
+    v = __fmaf_rn(__fmul_rn(g, g), c.omb2, __fmul_rn(v, c.beta2));
+    const float denom = __fmaf_rn(__fsqrt_rn(v), c.inv_bc2_sqrt, c.eps);
+    p = __fmaf_rn(-__fmul_rn(c.step_size, m), __frcp_rn(denom), p);
 }
 
 __device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t i) {
