@@ -231,11 +231,15 @@ def main():
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        nxt = feed.push(target_host) if e2e else None
         for k in range(steps):
             if e2e:
-                # this step's target image: pinned host memory -> device on a side stream, overlapped with the
-                # forward pass of the same step; the loss kernels wait for it
-                tgt, ready = feed.push(target_host)
+                # this step's target image travels pinned host memory -> device on a side stream.  The upload
+                # of step k+1 is started before step k is enqueued (two device slots), like a loader that
+                # prefetches one batch: it overlaps a whole step; the loss kernels wait for its event.
+                tgt, ready = nxt
+                if k + 1 < steps:
+                    nxt = feed.push(target_host)
                 info = trainer.step(cam, tgt, target_ready=ready)
                 loss_host[k].copy_(trainer._loss_sums, non_blocking=True)   # this step's loss sums -> host
             else:
