@@ -125,6 +125,22 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
     return float(table.get(stage, 0.0))
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from `ncu --set full` captures of
+# the small case `--n 750000` (N, V, K, P, Tn below); summaries with the commands are in profiles/ncu_*.md.
+# A full-size launch is too large to capture under a 40-pass replay, so the figure is scaled to the bench's
+# workload by the ratio of algorithmic bytes (traffic of these kernels grows with the units processed).
+NCU_SMALL_CASE = dict(N=750000, V=574917, K=1068256, P=2073600, Tn=8160)
+NCU_SMALL_TRAFFIC = {"raster_bwd": 157.59e6, "raster_fwd": 57.10e6, "adam_stats": 1244.93e6, "preprocess_bwd": 351.21e6,
+                     "preprocess_fwd": 227.38e6, "l1_dssim": 224.19e6, "pack_splats": 35.39e6, "duplicate_keys": 21.03e6}
+
+
+def ncu_traffic(stage: str, N: int, V: int, K: int, P: int, Tn: int):
+    if stage not in NCU_SMALL_TRAFFIC:
+        return None
+    small = algorithmic_bytes(stage, **NCU_SMALL_CASE)
+    return NCU_SMALL_TRAFFIC[stage] * algorithmic_bytes(stage, N, V, K, P, Tn) / small
+
+
 def cpu_baseline(cfg_name: str, sample: int, views: int = 1):
     """Times the CPU oracle on a bounded sample (1/sample of the Gaussians, full resolution, one view)
     and scales the per-Gaussian stages back to the full count."""
@@ -319,7 +335,9 @@ def main():
         "clocks": clocks,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / peak, "traffic": ncu_traffic(dom, N, V, K, P, Tn),
+                     "traffic_source": "ncu dram bytes of the 750k-Gaussian case scaled by algorithmic bytes (profiles/)",
+                     "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes,
                      "iteration": {"algorithmic_bytes": iter_bytes,
                                    "achieved": iter_bytes / (ms_total / args.steps * 1e-3) / 1e9,
