@@ -155,6 +155,15 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // waits until the committed bulk stores have finished READING shared memory (it may then be reused/freed)
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// 4-byte asynchronous global -> shared copy (no register staging, any number in flight per thread);
+// valid == false writes zero and reads nothing.
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src_gmem, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem),
+                 "r"(valid ? 4 : 0)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

@@ -6,7 +6,7 @@
 // d3sim/algos/d3gs/train.py:169-172 / losses.py:19-20 for the loss combination.
 //
 // The reference applies the window as 121 taps per output; here it is applied separably (11
-// horizontal + 11 vertical taps) from shared memory.  In the fused entry point the rasteriser's
+// horizontal + 11 vertical taps) from shared memory, four outputs per thread along the filter direction.  In the fused entry point the rasteriser's
 // NHWC colour is read directly and dL/dcolor is written NHWC, so the reference's
 // permute(0,3,1,2).contiguous() round trip (train.py:169) and its autograd mirror disappear.
 #include <cmath>
@@ -16,7 +16,13 @@
 namespace d3gs {
 namespace {
 
-constexpr int kWin = 11, kPad = 5, kTile = 16, kHalo = kTile + 2 * kPad;   // 26
+constexpr int kWin = 11, kPad = 5;
+constexpr int kTX = 32, kTY = 16;                       // output pixels per CTA
+constexpr int kHX = kTX + 2 * kPad, kHY = kTY + 2 * kPad;   // 42 x 26 input halo
+constexpr int kSX = 48;                                 // halo row stride: rows start on 16-byte boundaries
+constexpr int kStrip = 4;                               // outputs per thread along the filter direction
+constexpr int kTaps = kStrip + kWin - 1;                // 14 inputs feed 4 outputs
+constexpr int kThreads = 128;                           // = columns x strips of the vertical pass: no idle warps there
 
 struct Window {
     float g[kWin];
@@ -52,68 +58,135 @@ struct SsimArgs {
     float gs, gl;         // fused: dloss/dssim per element, dloss/d|x-y| per element (both incl. grad_scale)
 };
 
-__device__ __forceinline__ float load_x(const SsimArgs& a, int b, int c, int yy, int xx) {
-    if (a.x_is_nhwc) return a.x[(((int64_t)b * a.height + yy) * a.width + xx) * 3 + c];
-    return a.x[(((int64_t)b * 3 + c) * a.height + yy) * a.width + xx];
+// Both kernels filter separably out of shared memory with register blocking: a thread produces kStrip
+// consecutive outputs along the filter direction from kTaps inputs it loads once (as float4 in the
+// horizontal pass), so a tap costs one FMA and 1/4 of a shared-memory load instead of one load per FMA.
+
+// Starts the asynchronous load of the 42x26 halo of all three channels of an image into s[3][kHY][kSX]
+// (zero outside the image, fused_ssim.py:175-178); the caller waits with cp_async_wait_all + __syncthreads.
+// NHWC rows are read as runs of 126 consecutive floats.  cp.async keeps every element's load in flight at
+// once; a register-staged loop had one load per thread in flight and was bound by DRAM latency.
+__device__ __forceinline__ void load_halo(float (*s)[kHY][kSX], const float* img, bool nhwc, int b, int by, int bx,
+                                          int height, int width, int t) {
+    const int64_t plane = (int64_t)height * width;
+    if (nhwc) {
+        for (int k = t; k < kHY * kHX * 3; k += kThreads) {
+            const int ly = k / (kHX * 3), r = k - ly * (kHX * 3), lx = r / 3, c = r - lx * 3;
+            const int gy = by + ly - kPad, gx = bx + lx - kPad;
+            const bool ok = gy >= 0 && gy < height && gx >= 0 && gx < width;
+            cp_async4(&s[c][ly][lx], ok ? img + (((int64_t)b * height + gy) * width + gx) * 3 + c : img, ok);
+        }
+    } else {
+        for (int k = t; k < 3 * kHY * kHX; k += kThreads) {
+            const int c = k / (kHY * kHX), r = k - c * (kHY * kHX), ly = r / kHX, lx = r - ly * kHX;
+            const int gy = by + ly - kPad, gx = bx + lx - kPad;
+            const bool ok = gy >= 0 && gy < height && gx >= 0 && gx < width;
+            cp_async4(&s[c][ly][lx], ok ? img + ((int64_t)b * 3 + c) * plane + (int64_t)gy * width + gx : img, ok);
+        }
+    }
+    for (int k = t; k < 3 * kHY * (kSX - kHX); k += kThreads) {   // the float4 loads touch the row padding
+        const int c = k / (kHY * (kSX - kHX)), r = k - c * (kHY * (kSX - kHX)), ly = r / (kSX - kHX);
+        s[c][ly][kHX + r - ly * (kSX - kHX)] = 0.0f;
+    }
+}
+
+__device__ __forceinline__ void unpack16(const float* row, float (&v)[16]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 q = reinterpret_cast<const float4*>(row)[k];
+        v[4 * k] = q.x; v[4 * k + 1] = q.y; v[4 * k + 2] = q.z; v[4 * k + 3] = q.w;
+    }
 }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(256) ssim_forward_kernel(const __grid_constant__ SsimArgs a) {
-    __shared__ float s_x[kHalo][kHalo + 1];
-    __shared__ float s_y[kHalo][kHalo + 1];
-    __shared__ float s_h[5][kHalo][kTile];
-    __shared__ float s_red[2][8];
-    const int tx = threadIdx.x, ty = threadIdx.y, t = ty * kTile + tx;
-    const int bx = blockIdx.x * kTile, by = blockIdx.y * kTile, b = blockIdx.z;
-    const int px = bx + tx, py = by + ty;
-    const bool inside = px < a.width && py < a.height;
+__global__ void __launch_bounds__(kThreads) ssim_forward_kernel(const __grid_constant__ SsimArgs a) {
+    __shared__ __align__(16) float s_x[3][kHY][kSX];
+    __shared__ __align__(16) float s_y[3][kHY][kSX];
+    __shared__ __align__(16) float s_h[5][kHY][kTX];
+    __shared__ float s_red[2][kThreads / 32];
+    const int t = threadIdx.x;
+    const int bx = blockIdx.x * kTX, by = blockIdx.y * kTY, b = blockIdx.z;
     const int64_t plane = (int64_t)a.height * a.width;
+    load_halo(s_x, a.x, a.x_is_nhwc != 0, b, by, bx, a.height, a.width, t);
+    load_halo(s_y, a.y, false, b, by, bx, a.height, a.width, t);
+    cp_async_wait_all();
     float acc_l1 = 0.0f, acc_ssim = 0.0f;
     for (int c = 0; c < 3; ++c) {
-        __syncthreads();
-        for (int k = t; k < kHalo * kHalo; k += 256) {
-            const int ly = k / kHalo, lx = k - ly * kHalo;
-            const int gy = by + ly - kPad, gx = bx + lx - kPad;
-            const bool ok = gy >= 0 && gy < a.height && gx >= 0 && gx < a.width;
-            s_x[ly][lx] = ok ? load_x(a, b, c, gy, gx) : 0.0f;
-            s_y[ly][lx] = ok ? a.y[((int64_t)b * 3 + c) * plane + (int64_t)gy * a.width + gx] : 0.0f;
-        }
-        __syncthreads();
-        for (int k = t; k < kHalo * kTile; k += 256) {
-            const int ly = k / kTile, lx = k - ly * kTile;
-            float hx = 0.f, hy = 0.f, hxx = 0.f, hyy = 0.f, hxy = 0.f;
+        __syncthreads();   // halo loaded (c == 0) / previous channel's vertical pass is done with s_h
+        for (int item = t; item < kHY * (kTX / kStrip); item += kThreads) {   // horizontal: 26 rows x 8 strips of 4
+            const int row = item >> 3, st = item & 7;
+            float xv[16], yv[16];
+            unpack16(&s_x[c][row][st * kStrip], xv);
+            unpack16(&s_y[c][row][st * kStrip], yv);
+            float acc[kStrip][5];
 #pragma unroll
-            for (int j = 0; j < kWin; ++j) {
-                const float xv = s_x[ly][lx + j], yv = s_y[ly][lx + j], w = a.win.g[j];
-                hx += xv * w; hy += yv * w; hxx += xv * xv * w; hyy += yv * yv * w; hxy += xv * yv * w;
+            for (int o = 0; o < kStrip; ++o)
+#pragma unroll
+                for (int m = 0; m < 5; ++m) acc[o][m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kTaps; ++i) {
+                const float x = xv[i], y = yv[i], xx = x * x, yy = y * y, xy = x * y;
+#pragma unroll
+                for (int o = 0; o < kStrip; ++o) {
+                    const int j = i - o;
+                    if (j >= 0 && j < kWin) {
+                        const float w = a.win.g[j];
+                        acc[o][0] += x * w; acc[o][1] += y * w; acc[o][2] += xx * w; acc[o][3] += yy * w; acc[o][4] += xy * w;
+                    }
+                }
             }
-            s_h[0][ly][lx] = hx; s_h[1][ly][lx] = hy; s_h[2][ly][lx] = hxx; s_h[3][ly][lx] = hyy; s_h[4][ly][lx] = hxy;
+#pragma unroll
+            for (int m = 0; m < 5; ++m)
+                *reinterpret_cast<float4*>(&s_h[m][row][st * kStrip]) = make_float4(acc[0][m], acc[1][m], acc[2][m], acc[3][m]);
         }
         __syncthreads();
-        float m1 = 0.f, m2 = 0.f, m11 = 0.f, m22 = 0.f, m12 = 0.f;
+        {   // vertical: 32 columns x 4 strips of 4 rows = one item per thread
+            const int col = t & 31, st = t >> 5;
+            float acc[kStrip][5];
 #pragma unroll
-        for (int i = 0; i < kWin; ++i) {
-            const float w = a.win.g[i];
-            m1 += s_h[0][ty + i][tx] * w; m2 += s_h[1][ty + i][tx] * w; m11 += s_h[2][ty + i][tx] * w;
-            m22 += s_h[3][ty + i][tx] * w; m12 += s_h[4][ty + i][tx] * w;
-        }
-        if (inside) {
-            const float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
-            const float A1 = 2.0f * m1 * m2 + C1, A2 = 2.0f * (m12 - m1 * m2) + C2;
-            const float B1 = m1 * m1 + m2 * m2 + C1, B2 = (m11 - m1 * m1) + (m22 - m2 * m2) + C2;
-            const float inv = 1.0f / (B1 * B2);
-            const float ssim = A1 * A2 * inv;
-            const int64_t o = ((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px;
-            if (a.ssim_map) a.ssim_map[o] = ssim;
-            if (a.dmu1) {
-                // d ssim / d mu1, d E[x^2], d E[xy] with the other moments held fixed (fused_ssim.py:226-228)
-                a.dmu1[o] = 2.0f * m2 * (A2 - A1) * inv - 2.0f * m1 * ssim * (B2 - B1) * inv;
-                a.dmu11[o] = -ssim / B2;
-                a.dmu12[o] = 2.0f * A1 * inv;
+            for (int o = 0; o < kStrip; ++o)
+#pragma unroll
+                for (int m = 0; m < 5; ++m) acc[o][m] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kTaps; ++i) {
+                float v[5];
+#pragma unroll
+                for (int m = 0; m < 5; ++m) v[m] = s_h[m][st * kStrip + i][col];
+#pragma unroll
+                for (int o = 0; o < kStrip; ++o) {
+                    const int j = i - o;
+                    if (j >= 0 && j < kWin) {
+                        const float w = a.win.g[j];
+#pragma unroll
+                        for (int m = 0; m < 5; ++m) acc[o][m] += v[m] * w;
+                    }
+                }
             }
-            if (FUSED) {
-                acc_ssim += ssim;
-                acc_l1 += fabsf(s_x[ty + kPad][tx + kPad] - s_y[ty + kPad][tx + kPad]);
+            const int px = bx + col;
+#pragma unroll
+            for (int o = 0; o < kStrip; ++o) {
+                const int py = by + st * kStrip + o;
+                if (px < a.width && py < a.height) {
+                    const float m1 = acc[o][0], m2 = acc[o][1], m11 = acc[o][2], m22 = acc[o][3], m12 = acc[o][4];
+                    const float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
+                    const float A1 = 2.0f * m1 * m2 + C1, A2 = 2.0f * (m12 - m1 * m2) + C2;
+                    const float B1 = m1 * m1 + m2 * m2 + C1, B2 = (m11 - m1 * m1) + (m22 - m2 * m2) + C2;
+                    const float inv = 1.0f / (B1 * B2);
+                    const float ssim = A1 * A2 * inv;
+                    const int64_t off = ((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px;
+                    if (a.ssim_map) a.ssim_map[off] = ssim;
+                    if (a.dmu1) {
+                        // d ssim / d mu1, d E[x^2], d E[xy] with the other moments held fixed (fused_ssim.py:226-228)
+                        a.dmu1[off] = 2.0f * m2 * (A2 - A1) * inv - 2.0f * m1 * ssim * (B2 - B1) * inv;
+                        a.dmu11[off] = -ssim / B2;
+                        a.dmu12[off] = 2.0f * A1 * inv;
+                    }
+                    if (FUSED) {
+                        acc_ssim += ssim;
+                        const int ly = st * kStrip + o + kPad, lx = col + kPad;
+                        acc_l1 += fabsf(s_x[c][ly][lx] - s_y[c][ly][lx]);
+                    }
+                }
             }
         }
     }
@@ -128,7 +201,7 @@ __global__ void __launch_bounds__(256) ssim_forward_kernel(const __grid_constant
         __syncthreads();
         if (t == 0) {
             double l1 = 0.0, ss = 0.0;
-            for (int w = 0; w < 8; ++w) { l1 += s_red[0][w]; ss += s_red[1][w]; }
+            for (int w = 0; w < kThreads / 32; ++w) { l1 += s_red[0][w]; ss += s_red[1][w]; }
             atomicAdd(&a.sums[0], l1);
             atomicAdd(&a.sums[1], ss);
         }
@@ -136,59 +209,109 @@ __global__ void __launch_bounds__(256) ssim_forward_kernel(const __grid_constant
 }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(256) ssim_backward_kernel(const __grid_constant__ SsimArgs a) {
-    __shared__ float s_a[kHalo][kHalo + 1];
-    __shared__ float s_b[kHalo][kHalo + 1];
-    __shared__ float s_c[kHalo][kHalo + 1];
-    __shared__ float s_h[3][kHalo][kTile];
-    const int tx = threadIdx.x, ty = threadIdx.y, t = ty * kTile + tx;
-    const int bx = blockIdx.x * kTile, by = blockIdx.y * kTile, b = blockIdx.z;
-    const int px = bx + tx, py = by + ty;
-    const bool inside = px < a.width && py < a.height;
+__global__ void __launch_bounds__(kThreads) ssim_backward_kernel(const __grid_constant__ SsimArgs a) {
+    __shared__ __align__(16) float s_m[3][kHY][kSX];   // ds*dmu1, ds*dmu11, ds*dmu12 of one channel
+    __shared__ __align__(16) float s_h[3][kHY][kTX];
+    const int t = threadIdx.x;
+    const int bx = blockIdx.x * kTX, by = blockIdx.y * kTY, b = blockIdx.z;
     const int64_t plane = (int64_t)a.height * a.width;
-    for (int c = 0; c < 3; ++c) {
-        __syncthreads();
-        for (int k = t; k < kHalo * kHalo; k += 256) {
-            const int ly = k / kHalo, lx = k - ly * kHalo;
+    const int col = t & 31, vst = t >> 5;               // this thread's column / strip in the vertical pass
+    const int px = bx + col;
+    float d[kStrip][3];                                 // results of the vertical-pass threads, all channels
+    // stage the three derivative maps of channel c (asynchronously in the fused variant)
+    auto stage = [&](int c) {
+        float(*dst)[kHY][kSX] = s_m;
+        for (int k = t; k < kHY * kSX; k += kThreads) {
+            const int ly = k / kSX, lx = k - ly * kSX;
             const int gy = by + ly - kPad, gx = bx + lx - kPad;
-            const bool ok = gy >= 0 && gy < a.height && gx >= 0 && gx < a.width;
-            float va = 0.f, vb = 0.f, vc = 0.f;
-            if (ok) {
-                const int64_t o = ((int64_t)b * 3 + c) * plane + (int64_t)gy * a.width + gx;
-                const float ds = FUSED ? 1.0f : a.dssim[o];   // fused: the constant factor is applied at the end
-                va = ds * a.dmu1[o]; vb = ds * a.dmu11[o]; vc = ds * a.dmu12[o];
+            const bool ok = lx < kHX && gy >= 0 && gy < a.height && gx >= 0 && gx < a.width;
+            const int64_t o = ok ? ((int64_t)b * 3 + c) * plane + (int64_t)gy * a.width + gx : 0;
+            if (FUSED) {   // the constant dloss/dssim is applied at the end: plain asynchronous copies
+                cp_async4(&dst[0][ly][lx], a.dmu1 + o, ok);
+                cp_async4(&dst[1][ly][lx], a.dmu11 + o, ok);
+                cp_async4(&dst[2][ly][lx], a.dmu12 + o, ok);
+            } else {
+                const float ds = ok ? a.dssim[o] : 0.0f;
+                dst[0][ly][lx] = ok ? ds * a.dmu1[o] : 0.0f;
+                dst[1][ly][lx] = ok ? ds * a.dmu11[o] : 0.0f;
+                dst[2][ly][lx] = ok ? ds * a.dmu12[o] : 0.0f;
             }
-            s_a[ly][lx] = va; s_b[ly][lx] = vb; s_c[ly][lx] = vc;
+        }
+    };
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        __syncthreads();   // everyone is done with the previous channel's s_m and s_h
+        stage(c);
+        if (FUSED) cp_async_wait_all();
+        __syncthreads();
+        float(*s_cur)[kHY][kSX] = s_m;
+        for (int item = t; item < kHY * (kTX / kStrip); item += kThreads) {
+            const int row = item >> 3, st = item & 7;
+#pragma unroll
+            for (int m = 0; m < 3; ++m) {
+                float v[16];
+                unpack16(&s_cur[m][row][st * kStrip], v);
+                float acc[kStrip] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < kTaps; ++i)
+#pragma unroll
+                    for (int o = 0; o < kStrip; ++o) {
+                        const int j = i - o;
+                        if (j >= 0 && j < kWin) acc[o] += v[i] * a.win.g[j];
+                    }
+                *reinterpret_cast<float4*>(&s_h[m][row][st * kStrip]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            }
         }
         __syncthreads();
-        for (int k = t; k < kHalo * kTile; k += 256) {
-            const int ly = k / kTile, lx = k - ly * kTile;
-            float ha = 0.f, hb = 0.f, hc = 0.f;
+        {
+            float acc[kStrip][3];
 #pragma unroll
-            for (int j = 0; j < kWin; ++j) {
-                const float w = a.win.g[j];
-                ha += s_a[ly][lx + j] * w; hb += s_b[ly][lx + j] * w; hc += s_c[ly][lx + j] * w;
-            }
-            s_h[0][ly][lx] = ha; s_h[1][ly][lx] = hb; s_h[2][ly][lx] = hc;
-        }
-        __syncthreads();
-        float c1 = 0.f, c2 = 0.f, c3 = 0.f;
+            for (int o = 0; o < kStrip; ++o) acc[o][0] = acc[o][1] = acc[o][2] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kWin; ++i) {
-            const float w = a.win.g[i];
-            c1 += s_h[0][ty + i][tx] * w; c2 += s_h[1][ty + i][tx] * w; c3 += s_h[2][ty + i][tx] * w;
-        }
-        if (inside) {
-            const float xv = load_x(a, b, c, py, px);
-            const float yv = a.y[((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px];
-            float d = c1 + 2.0f * xv * c2 + c3 * yv;                 // fused_ssim.py:361
-            if (FUSED) {
-                const float df = xv - yv;
-                const float sg = df > 0.0f ? 1.0f : (df < 0.0f ? -1.0f : 0.0f);
-                d = a.gs * d + a.gl * sg;
+            for (int i = 0; i < kTaps; ++i) {
+                const float v0 = s_h[0][vst * kStrip + i][col], v1 = s_h[1][vst * kStrip + i][col],
+                            v2 = s_h[2][vst * kStrip + i][col];
+#pragma unroll
+                for (int o = 0; o < kStrip; ++o) {
+                    const int j = i - o;
+                    if (j >= 0 && j < kWin) {
+                        const float w = a.win.g[j];
+                        acc[o][0] += v0 * w; acc[o][1] += v1 * w; acc[o][2] += v2 * w;
+                    }
+                }
             }
-            if (a.x_is_nhwc) a.dx[(((int64_t)b * a.height + py) * a.width + px) * 3 + c] = d;
-            else a.dx[((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px] = d;
+#pragma unroll
+            for (int o = 0; o < kStrip; ++o) {
+                const int py = by + vst * kStrip + o;
+                d[o][c] = 0.0f;
+                if (px < a.width && py < a.height) {
+                    const float xv = a.x_is_nhwc ? a.x[(((int64_t)b * a.height + py) * a.width + px) * 3 + c]
+                                                 : a.x[((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px];
+                    const float yv = a.y[((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px];
+                    float g = acc[o][0] + 2.0f * xv * acc[o][1] + acc[o][2] * yv;                 // fused_ssim.py:361
+                    if (FUSED) {
+                        const float df = xv - yv;
+                        const float sg = df > 0.0f ? 1.0f : (df < 0.0f ? -1.0f : 0.0f);
+                        g = a.gs * g + a.gl * sg;
+                    }
+                    d[o][c] = g;
+                }
+            }
+        }
+    }
+    {
+#pragma unroll
+        for (int o = 0; o < kStrip; ++o) {
+            const int py = by + vst * kStrip + o;
+            if (px < a.width && py < a.height) {
+                if (a.x_is_nhwc) {
+                    float* dst = a.dx + (((int64_t)b * a.height + py) * a.width + px) * 3;
+                    dst[0] = d[o][0]; dst[1] = d[o][1]; dst[2] = d[o][2];
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) a.dx[((int64_t)b * 3 + c) * plane + (int64_t)py * a.width + px] = d[o][c];
+                }
+            }
         }
     }
 }
@@ -196,7 +319,7 @@ __global__ void __launch_bounds__(256) ssim_backward_kernel(const __grid_constan
 int32_t check_shape(int32_t batch, int32_t height, int32_t width) {
     D3GS_REQUIRE(batch >= 1 && batch <= 65535, "batch %d outside [1,65535]", batch);
     D3GS_REQUIRE(height >= 1 && width >= 1, "bad image size %dx%d", width, height);
-    D3GS_REQUIRE((height + kTile - 1) / kTile <= 65535, "image too tall");
+    D3GS_REQUIRE((height + kTY - 1) / kTY <= 65535, "image too tall");
     return D3GS_OK;
 }
 
@@ -217,7 +340,7 @@ extern "C" int32_t d3gs_ssim_forward(const float* x, const float* y, int32_t bat
     a.x = x; a.y = y; a.batch = batch; a.height = height; a.width = width; a.x_is_nhwc = x_is_nhwc;
     a.win = make_window();
     a.ssim_map = ssim_map; a.dmu1 = dmu1; a.dmu11 = dmu11; a.dmu12 = dmu12;
-    dim3 grid((width + kTile - 1) / kTile, (height + kTile - 1) / kTile, batch), block(kTile, kTile);
+    dim3 grid((width + kTX - 1) / kTX, (height + kTY - 1) / kTY, batch), block(kThreads);
     ssim_forward_kernel<false><<<grid, block, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("ssim_forward_kernel");
     return D3GS_OK;
@@ -234,7 +357,7 @@ extern "C" int32_t d3gs_ssim_backward(const float* dssim_map, const float* dmu1,
     a.win = make_window();
     a.dmu1 = const_cast<float*>(dmu1); a.dmu11 = const_cast<float*>(dmu11); a.dmu12 = const_cast<float*>(dmu12);
     a.dssim = dssim_map; a.dx = dx;
-    dim3 grid((width + kTile - 1) / kTile, (height + kTile - 1) / kTile, batch), block(kTile, kTile);
+    dim3 grid((width + kTX - 1) / kTX, (height + kTY - 1) / kTY, batch), block(kThreads);
     ssim_backward_kernel<false><<<grid, block, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("ssim_backward_kernel");
     return D3GS_OK;
@@ -266,7 +389,7 @@ extern "C" int32_t d3gs_l1_dssim_forward_backward(const float* x, const float* y
         a.dmu11 = a.dmu1 + plane3;
         a.dmu12 = a.dmu11 + plane3;
     }
-    dim3 grid((width + kTile - 1) / kTile, (height + kTile - 1) / kTile, batch), block(kTile, kTile);
+    dim3 grid((width + kTX - 1) / kTX, (height + kTY - 1) / kTY, batch), block(kThreads);
     ssim_forward_kernel<true><<<grid, block, 0, s>>>(a);
     D3GS_LAUNCH_CHECK("ssim_forward_kernel<fused>");
     if (dx == nullptr) return D3GS_OK;

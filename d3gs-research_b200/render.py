@@ -369,6 +369,8 @@ class GaussianSplatOp:
         _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles, stream),
                    "d3gs_tile_ranges")
         self._mark("tile_ranges")
+        if self.debug_capture:
+            self.debug.update(ranges=workload_ranges)
         records = torch.empty([num_rendered, 12], dtype=f32, device=dev)
         _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
                                         float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")

@@ -277,15 +277,14 @@ def test_adam_and_densify_stats(cuda_device):
         assert_close(getattr(state, k).cpu().numpy(), hstate[k], GRAD_TOL, f"stats {k}")
 
 
-def test_full_size_properties_cfg3(cuda_device):
-    """BASELINE size (3 M Gaussians, 1080p): size-independent invariants of the binning stages."""
+def _full_size_invariants(cuda_device, cfg_name, training):
     from d3gs_research_b200 import scenes
-    sc = scenes.make_scene("cfg3", seed=0, views=1)
+    sc = scenes.make_scene(cfg_name, seed=0, views=1)
     op = d3.GaussianSplatOp(d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT))
     op.debug_capture = True
     model = gpu_model(sc, cuda_device)
     model.act_applied = True
-    out, ctx = op.forward(model, gpu_cameras(sc, cuda_device), training=True)
+    out, ctx = op.forward(model, gpu_cameras(sc, cuda_device), training=training)
     torch.cuda.synchronize()
     d = op.debug
     K = op.last_num_rendered
@@ -300,7 +299,7 @@ def test_full_size_properties_cfg3(cuda_device):
     assert torch.equal(d["values"][ref_i], d["sorted_values"])
     # every tile's range holds exactly that tile's keys
     tiles = (sk >> 32).int()
-    r = ctx.workload_ranges
+    r = d["ranges"] if ctx is None else ctx.workload_ranges
     counts = torch.bincount(tiles.long(), minlength=r.shape[0]).int()
     assert torch.equal(r[:, 1] - r[:, 0], counts)
     nz = counts > 0
@@ -310,3 +309,25 @@ def test_full_size_properties_cfg3(cuda_device):
     assert bool(((T >= 0) & (T <= 1)).all())
     assert bool((out.n_contrib >= 0).all())
     assert bool(torch.isfinite(out.color).all())
+    # no pixel can have contributed beyond the end of its tile's list
+    h, w = T.shape[-2], T.shape[-1]
+    tiles_x = (w + 15) // 16
+    ty, tx = torch.meshgrid(torch.arange(h, device=T.device) // 16, torch.arange(w, device=T.device) // 16,
+                            indexing="ij")
+    per_pixel = (r[:, 1] - r[:, 0])[(ty * tiles_x + tx).flatten().long()].view(h, w)
+    assert bool((out.n_contrib[0] < torch.clamp(per_pixel, min=1)).all())
+    return K, out
+
+
+def test_full_size_properties_cfg3(cuda_device):
+    """BASELINE size (3 M Gaussians, 1080p): size-independent invariants of the binning and raster stages."""
+    K, _ = _full_size_invariants(cuda_device, "cfg3", training=True)
+    assert K > 1_000_000
+
+
+def test_full_size_properties_cfg4_render(cuda_device):
+    """Largest configuration (6 M Gaussians, 3840x2160, forward only): the same invariants in inference mode,
+    where the background is composited and the colour clamped to [0, 1]."""
+    K, out = _full_size_invariants(cuda_device, "cfg4", training=False)
+    assert K > 5_000_000
+    assert bool(((out.color >= 0) & (out.color <= 1)).all())
