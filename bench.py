@@ -16,6 +16,7 @@ loss read back every step).
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import math
 import os
@@ -52,56 +53,132 @@ def parse():
 # ---------------------------------------------------------------------------------------------
 # clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs.
+
+    The values are the ones `nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.*` prints, read
+    through NVML in this process (read-only queries).  A query holds a driver lock for 3.5 ms or more (up to
+    30 ms was seen), during which kernel launches of the step stall: polling every 20 ms, or running nvidia-smi
+    beside an 80 ms timed region, added 0.1-0.5 ms per step in one run out of three.  So the samples are taken
+    where they cannot delay a launch: `sample()` is called by the timed loop after its last launch is enqueued
+    and before it synchronises (the GPU is still executing the last step), and a background thread adds one
+    sample every 500 ms for long runs.  nvidia-smi is the fallback when the NVML binding is missing; it is
+    started before the warm-up so that its start-up cost is over when the timing begins.  Only samples taken
+    between begin() and stop() are reported."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event (throttle) reason bits
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
+        self.samples: list[tuple[float, float, float, int]] = []   # (time, sm MHz, max MHz, reason bits)
+        self.nvml = None
+        self.running = False
+        self.t_begin = None
+        self.max_poll_ms = 0.0
 
     def start(self):
+        """Start sampling (call before the warm-up)."""
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+                uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.running = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
 
+    def begin(self):
+        """The timed region starts now."""
+        self.t_begin = time.monotonic()
+
+    def sample(self):
+        """One NVML sample now (no-op for the nvidia-smi fallback, which samples by itself)."""
+        nv = self.nvml
+        if nv is None:
+            return
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        try:
+            t0 = time.monotonic()
+            sm = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+            bits = int(get_reasons(self.handle))
+            self.samples.append((t0, sm, self.max_sm, bits))
+            self.max_poll_ms = max(self.max_poll_ms, (time.monotonic() - t0) * 1e3)
+        except Exception:
+            pass
+
+    def _poll(self):
+        while self.running:
+            time.sleep(0.5)
+            if self.running and self.t_begin is not None:
+                self.sample()
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
+        t_end = time.monotonic()
+        t0 = self.t_begin if self.t_begin is not None else 0.0
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 9:
-                continue
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=1)
+            for ts, clk, mxc, bits in self.samples:
+                if t0 <= ts <= t_end:
+                    sm.append(clk)
+                    mx.append(mxc)
+                    reasons.update(nm for nm, bit in self.REASON_BITS.items() if bits & bit)
+            source = "NVML"
+        elif self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for nm, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for ts, ln in self.lines:
+                parts = [p.strip() for p in ln.split(",")]
+                if len(parts) < 9 or not (t0 <= ts <= t_end + 0.15):
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+            source = "nvidia-smi"
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": source,
+                "max_poll_ms": round(self.max_poll_ms, 3)}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -241,9 +318,11 @@ def main():
 
     feed = HostFeed(dev)
 
-    def timed(steps: int, e2e: bool):
+    def timed(steps: int, e2e: bool, sample_clocks: bool = False):
         # one pinned slot per step: every step's loss sums are read back inside the timed region
         loss_host = torch.zeros(steps, 2, dtype=torch.float64).pin_memory()
+        gc.collect()
+        gc.disable()   # a generational collection in the launch loop stalls the queue for milliseconds
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -261,13 +340,19 @@ def main():
             else:
                 info = trainer.step(cam, target_dev)
         e1.record()
+        if sample_clocks:   # everything is enqueued and the GPU is still executing: the query delays no launch
+            sampler.sample()
         barrier()      # synchronises: all uploads consumed, all loss read-backs landed
+        gc.enable()
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), info
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         trainer.step(cam, target_dev)
     for _ in range(3):      # warm the host-buffer path (side stream, staging buffers) as well
@@ -287,16 +372,24 @@ def main():
             dst.copy_(src)
         trainer.step_count = snap["step"]
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    trainer.op.timer = StageTimer()
-    ms_total, info = timed(args.steps, e2e=False)
-    stage_ms = trainer.op.timer.summary()
-    trainer.op.timer = None
+    # The first loop after the snapshot's allocations was slower by 0.1-1.5 ms per step in one run out of five
+    # (whichever loop came first); a few untimed steps absorb that before anything is measured.
+    for _ in range(3):
+        trainer.step(cam, target_dev)
+    restore()
+    sampler.begin()
+    ms_total, info = timed(args.steps, e2e=False, sample_clocks=rank == 0)
     clocks = sampler.stop() if rank == 0 else None
     restore()
     ms_e2e, _ = timed(args.steps, e2e=True)
+    # Per-stage times come from a third pass over the same steps: the event records between the launches
+    # cost about 0.05 ms per step, which the two timed loops above do not pay.
+    restore()
+    trainer.op.timer = StageTimer(prealloc=20 * (args.steps + 1))
+    torch.cuda.synchronize()
+    timed(args.steps, e2e=False)
+    stage_ms = trainer.op.timer.summary()
+    trainer.op.timer = None
 
     replicas_agree = None
     if world > 1:   # every replica must hold bit-identical parameters after the same updates

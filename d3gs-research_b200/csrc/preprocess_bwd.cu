@@ -39,7 +39,7 @@ __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.457045
 // accesses with a 180-byte stride cost 20-30 sectors per request and throttled the load/store unit.
 // MULTI (more than one view): gradients accumulate over views in a second shared-memory buffer.
 template <int DEG, bool MULTI>
-__global__ void __launch_bounds__(256) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
+__global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint8_t s_vis[256];
     __shared__ __align__(8) uint64_t s_bar;

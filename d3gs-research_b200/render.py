@@ -136,6 +136,12 @@ def _camera_rows(cameras: BasicPinholeCamera | CameraBundle) -> np.ndarray:
     return cameras.host_params()
 
 
+def _pair_capacity(n: int) -> int:
+    """Allocation size for a buffer of n (tile, splat) pairs: n + n/8, rounded up to a multiple of 2^20."""
+    q = 1 << 20
+    return max(-(-(n + n // 8) // q) * q, q)
+
+
 class _Workspace:
     """Grow-only scratch tensors so that the steady state performs no allocation for them."""
 
@@ -155,20 +161,28 @@ class StageTimer:
     ``measure_and_print_torch(name, enable=cfg.verbose)`` blocks (render.py:250, 689, 739, 845, 896, 1004).
     ``mark(name)`` closes the stage ``name``; durations are read after a synchronize."""
 
-    def __init__(self):
+    def __init__(self, prealloc: int = 0):
+        """``prealloc``: number of events to create up front (a CUDA event is created by its first record; inside
+        a timed loop that creation is host work between two launches)."""
         self.steps: list[list[tuple[str, torch.cuda.Event]]] = []
+        self.pool: list[torch.cuda.Event] = []
+        for _ in range(prealloc):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.pool.append(ev)
+
+    def _event(self) -> torch.cuda.Event:
+        ev = self.pool.pop() if self.pool else torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
 
     def begin_step(self):
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        self.steps.append([("begin", ev)])
+        self.steps.append([("begin", self._event())])
 
     def mark(self, name: str):
         if not self.steps:
             self.begin_step()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        self.steps[-1].append((name, ev))
+        self.steps[-1].append((name, self._event()))
 
     def summary(self) -> dict[str, float]:
         """Mean milliseconds per stage over the recorded steps (call after torch.cuda.synchronize())."""
@@ -342,10 +356,14 @@ class GaussianSplatOp:
         if num_rendered == 0:   # render.py:706-729: outputs are left uninitialised, no context
             return GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
                                        n_contrib=n_contrib), None
-        keys = torch.empty(num_rendered, dtype=torch.int64, device=dev)
-        keys_alt = torch.empty_like(keys)
-        gaussian_idx = torch.empty(num_rendered, dtype=i32, device=dev)
-        gaussian_idx_alt = torch.empty_like(gaussian_idx)
+        # Pair-sized buffers are allocated with a capacity quantised to 2^20 pairs above 1.125 x the count: the
+        # count changes a little every training step, and exact sizes would make the caching allocator miss
+        # and fall back to cudaMalloc (a device-wide stall of milliseconds) every few steps.
+        cap = _pair_capacity(num_rendered)
+        keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
+        keys_alt = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
+        gaussian_idx = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
+        gaussian_idx_alt = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
         _lib.check(lib.d3gs_duplicate_keys(C.byref(ocfg), num, tiles_touched.data_ptr(), C.byref(cstruct),
                                            keys.data_ptr(), gaussian_idx.data_ptr(), stream), "d3gs_duplicate_keys")
         self._mark("duplicate_keys")
@@ -371,7 +389,7 @@ class GaussianSplatOp:
         self._mark("tile_ranges")
         if self.debug_capture:
             self.debug.update(ranges=workload_ranges)
-        records = torch.empty([num_rendered, 12], dtype=f32, device=dev)
+        records = torch.empty(cap * 12, dtype=f32, device=dev)[:num_rendered * 12].view(num_rendered, 12)
         _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
                                         float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")
         self._mark("pack_splats")
