@@ -130,9 +130,16 @@ class ClockSampler:
             pass
 
     def _poll(self):
+        last = None
         while self.running:
-            time.sleep(0.5)
-            if self.running and self.t_begin is not None:
+            time.sleep(0.02)
+            if self.t_begin is None:
+                continue
+            now = time.monotonic()
+            if last is None:
+                last = self.t_begin       # the first background sample comes 0.5 s into the timed region
+            if self.running and now - last >= 0.5:
+                last = now
                 self.sample()
 
     def _read(self):

@@ -69,6 +69,24 @@ def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views):
     assert_close(out.T.cpu().numpy(), ref.T, IMG_TOL, "T")
 
 
+@pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB_DFVT])
+def test_binning_bit_exact_large_gaussians(cuda_device, early_filter):
+    """Gaussians that cover hundreds of tiles take the warp-cooperative paths of the tile count and of the key
+    emission; the unsorted key list must still come out in the reference's per-Gaussian row-major order."""
+    sc = small_scene(n=500, width=400, height=304, sh_degree=1, seed=11, log_scale=("normal", -0.9, 0.8))
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter)
+    dbg = {k: v.cpu().numpy() for k, v in op.debug.items()}
+    assert ref.prep["tiles_touched"].max() > 200, "the scene has no screen-filling Gaussian"
+    np.testing.assert_array_equal(dbg["tiles_touched"], ref.prep["tiles_touched"])
+    np.testing.assert_array_equal(dbg["scan"], ref.scan)
+    np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
+    np.testing.assert_array_equal(dbg["values"], ref.vals)
+    np.testing.assert_array_equal(dbg["sorted_keys"].view(np.uint64), ref.sorted_keys)
+    np.testing.assert_array_equal(dbg["sorted_values"], ref.sorted_ids)
+    np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+
+
 def test_forward_inference_background(cuda_device):
     sc = small_scene(n=3000, width=96, height=80, sh_degree=1, seed=11)
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.NONE, bg_color=np.array([0.2, 0.5, 0.9], np.float32),
