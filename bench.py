@@ -360,11 +360,15 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    # The warm-up keeps each step's result alive until the next one returns, exactly like the timed loops: the
+    # second generation of output buffers is then already in the allocator's cache (without this the first
+    # timed loop paid a cudaMalloc of up to 9 ms in its second step, one run out of four).
+    info = None
     for _ in range(max(args.warmup, 3)):
-        trainer.step(cam, target_dev)
+        info = trainer.step(cam, target_dev)
     for _ in range(3):      # warm the host-buffer path (side stream, staging buffers) as well
         tgt, ready = feed.push(target_host)
-        trainer.step(cam, tgt, target_ready=ready)
+        info = trainer.step(cam, tgt, target_ready=ready)
     # Both timed loops start from the same parameters and optimizer state: training moves the Gaussians, so
     # the work per step drifts with the step count and the two figures would not measure the same steps.
     snap = {"flat": trainer.model.flat.clone(), "m": trainer.exp_avg.clone(), "v": trainer.exp_avg_sq.clone(),
@@ -379,10 +383,8 @@ def main():
             dst.copy_(src)
         trainer.step_count = snap["step"]
 
-    # The first loop after the snapshot's allocations was slower by 0.1-1.5 ms per step in one run out of five
-    # (whichever loop came first); a few untimed steps absorb that before anything is measured.
-    for _ in range(3):
-        trainer.step(cam, target_dev)
+    for _ in range(3):      # the same pattern once more after the snapshot's allocations
+        info = trainer.step(cam, target_dev)
     restore()
     sampler.begin()
     ms_total, info = timed(args.steps, e2e=False, sample_clocks=rank == 0)
