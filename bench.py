@@ -205,6 +205,10 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
         "raster_bwd": 48 * K + 36 * P + 36 * K,
         "preprocess_bwd": (53 + 36) * V + 4 * N + 236 * V + 236 * N,
         "adam_stats": 1652 * N + 12 * N + 24 * N,
+        # single-rank fused path: the same per-unit figures, so that the iteration total stays comparable (the
+        # fused launch actually moves 472 B per Gaussian less: the gradient is neither written nor read)
+        "preprocess_bwd_adam": (53 + 36) * V + 4 * N + 236 * V + 236 * N + 1652 * N,
+        "densify_stats": 12 * N + 24 * N,
     }
     return float(table.get(stage, 0.0))
 
@@ -448,7 +452,7 @@ def main():
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(target_host.numel() * 4),
                 "d2h_bytes_per_step": 16 + 16, "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": 19 * args.steps,
+        "gpu_launches": 19 * args.steps,   # per step: see profiles/launch_list_cfg3_1gpu.md
         "clocks": clocks,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",

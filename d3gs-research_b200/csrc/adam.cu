@@ -26,11 +26,6 @@ constexpr int kAdamVec = 4;
 constexpr int kAdamUnroll = 2;
 constexpr int kAdamChunk = kAdamThreads * kAdamVec * kAdamUnroll;   // 2048 floats per CTA
 
-// per-segment scalars with the uniform divisions hoisted out of the element loop
-struct SegConst {
-    float inv_grad_scale, weight_decay, beta1, omb1, beta2, omb2, step_size, inv_bc2_sqrt, eps;
-};
-
 struct AdamArgs {
     D3gsAdamSegment seg[kMaxSegments];
     SegConst sc[kMaxSegments];
@@ -44,21 +39,6 @@ struct AdamArgs {
     int64_t param_off[kMaxSegments], grad_off[kMaxSegments];
     D3gsPeerSet peers;
 };
-
-// csrc/optim.py:22-49: g /= grad_scale; m = mix(g, m, b1); v = mix(g*g, v, b2);
-// p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps).  The three divisions by per-tensor constants are
-// multiplications by reciprocals computed once on the host in double; the one per-element division is a
-// single correctly rounded reciprocal.
-// Every operation is an explicit round-to-nearest intrinsic, so the vector path, the scalar path and the
-// peer variant produce the same bits for the same inputs whatever the compiler would have contracted.
-__device__ __forceinline__ void adam_update(float g, float& p, float& m, float& v, const SegConst& c) {
-    g = __fmul_rn(g, c.inv_grad_scale);
-    if (c.weight_decay != 0.0f) g = __fmaf_rn(p, c.weight_decay, g);
-    m = __fmaf_rn(g, c.omb1, __fmul_rn(m, c.beta1));
-    v = __fmaf_rn(__fmul_rn(g, g), c.omb2, __fmul_rn(v, c.beta2));
-    const float denom = __fmaf_rn(__fsqrt_rn(v), c.inv_bc2_sqrt, c.eps);
-    p = __fmaf_rn(-__fmul_rn(c.step_size, m), __frcp_rn(denom), p);
-}
 
 __device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t i) {
     float la = 0.0f, ca = 0.0f, mr = st.need_max_radii ? st.max_radii[i] : 0.0f;
@@ -268,16 +248,7 @@ static int32_t adam_launch(const D3gsAdamSegment* segments, int32_t num_segments
             D3GS_REQUIRE(a.param_off[k] >= 0 && a.grad_off[k] >= 0,
                          "segment %d does not lie inside this rank's flat buffers", k);
         }
-        SegConst& c = a.sc[k];
-        c.inv_grad_scale = (float)(1.0 / (double)s.grad_scale);
-        c.weight_decay = s.weight_decay;
-        c.beta1 = s.beta1;
-        c.omb1 = 1.0f - s.beta1;
-        c.beta2 = s.beta2;
-        c.omb2 = 1.0f - s.beta2;
-        c.step_size = s.lr / s.bias_correction1;
-        c.inv_bc2_sqrt = (float)(1.0 / (double)s.bias_correction2_sqrt);
-        c.eps = s.eps;
+        a.sc[k] = make_seg_const(s);
         a.block_start[k] = blocks;
         blocks += div_up64(s.count, a.chunk);
     }

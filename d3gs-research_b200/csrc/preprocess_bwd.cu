@@ -24,6 +24,10 @@ struct BwdArgs {
     D3gsSplatContext ctx;
     D3gsModelGrad grad;
     const float* splat_grads;   // [B*N, 12]: dconic a b c, dopacity | dcolor r g b, - | duv x y, - -
+    // fused optimizer step (ADAM variant): per field xyz, quaternion, scale, opacity, sh_base, sh_rest
+    SegConst sc[6];
+    float* exp_avg[6];
+    float* exp_avg_sq[6];
 };
 
 constexpr int kRow = 45;        // shared-memory row length in floats (odd: conflict-free per-thread rows)
@@ -38,7 +42,12 @@ __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.457045
 // coefficient gradients back into the row, and the rows leave with coalesced stores: per-thread
 // accesses with a 180-byte stride cost 20-30 sectors per request and throttled the load/store unit.
 // MULTI (more than one view): gradients accumulate over views in a second shared-memory buffer.
-template <int DEG, bool MULTI>
+// ADAM (single GPU, single view): the gradient is not written at all.  The thread applies Adam to the 14
+// floats of its Gaussian's small fields straight from registers, and the CTA applies it to its 256 x 45
+// higher-order SH coefficients with coalesced accesses, taking the gradient rows from shared memory.  Compared
+// with a gradient buffer followed by the optimizer kernel this removes one write and one read of the whole
+// 236-byte-per-Gaussian gradient.
+template <int DEG, bool MULTI, bool ADAM>
 __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint8_t s_vis[256];
@@ -295,6 +304,78 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
         aq[2] = (dq[2] - qz * dot) * qni; aq[3] = (dq[3] - qw * dot) * qni;
         if (fused) ao = ao * opac * (1.0f - opac);   // sigmoid_grad_out: g * out * (1 - out)
     }
+    if (ADAM) {
+        // The 14 small-field gradients of every thread join the SH rows in shared memory, then the CTA walks
+        // the six parameter spans of its 256 Gaussians with coalesced float4 accesses (several in flight per
+        // thread), exactly like the stand-alone optimizer kernel but with the gradient coming from shared
+        // memory.  The parameters are updated in place: a CTA reads and writes only its own Gaussians'.
+        float* s_small = smem + 256 * kRow;   // [xyz 768 | quaternion 1024 | scale 768 | opacity 256 | sh_base 768]
+        s_small[t * 3] = axyz[0]; s_small[t * 3 + 1] = axyz[1]; s_small[t * 3 + 2] = axyz[2];
+        *reinterpret_cast<float4*>(s_small + 768 + t * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
+        s_small[1792 + t * 3] = as[0]; s_small[1792 + t * 3 + 1] = as[1]; s_small[1792 + t * 3 + 2] = as[2];
+        s_small[2560 + t] = ao;
+        s_small[2816 + t * 3] = abase[0]; s_small[2816 + t * 3 + 1] = abase[1]; s_small[2816 + t * 3 + 2] = abase[2];
+        __syncthreads();
+        const float* params[6] = {a.model.xyz, a.model.quaternion_xyzw, a.model.scale, a.model.opacity,
+                                  a.model.sh_base, a.model.sh_rest};
+        const int per[6] = {3, 4, 3, 1, 3, 45};
+        const int soff[6] = {0, 768, 1792, 2560, 2816, -1};
+#pragma unroll
+        for (int fld = 0; fld < 6; ++fld) {
+            const int count = rows * per[fld];
+            float* pp = const_cast<float*>(params[fld]) + g0 * per[fld];
+            float* pm = a.exp_avg[fld] + g0 * per[fld];
+            float* pv = a.exp_avg_sq[fld] + g0 * per[fld];
+            const float* gs = fld == 5 ? s_out : s_small + soff[fld];
+            const SegConst c = a.sc[fld];
+            const bool vec = (count & 3) == 0 && (((uintptr_t)pp | (uintptr_t)pm | (uintptr_t)pv) & 15) == 0;
+            if (vec) {
+                constexpr int kU = 4;
+                for (int q0 = t; q0 < count / 4; q0 += 256 * kU) {
+                    float4 p[kU], m[kU], v[kU];
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const int q = q0 + u * 256;
+                        if (q < count / 4) {
+                            p[u] = reinterpret_cast<const float4*>(pp)[q];
+                            m[u] = reinterpret_cast<const float4*>(pm)[q];
+                            v[u] = reinterpret_cast<const float4*>(pv)[q];
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const int q = q0 + u * 256;
+                        if (q < count / 4) {
+                            float4 gr = reinterpret_cast<const float4*>(gs)[q];
+                            if (fld == 5 && NR3 < 45) {   // coefficients above the active degree have no gradient
+                                const int k0 = (q * 4) % 45;
+                                if (k0 >= NR3) gr.x = 0.0f;
+                                if ((k0 + 1) % 45 >= NR3) gr.y = 0.0f;
+                                if ((k0 + 2) % 45 >= NR3) gr.z = 0.0f;
+                                if ((k0 + 3) % 45 >= NR3) gr.w = 0.0f;
+                            }
+                            adam_update(gr.x, p[u].x, m[u].x, v[u].x, c);
+                            adam_update(gr.y, p[u].y, m[u].y, v[u].y, c);
+                            adam_update(gr.z, p[u].z, m[u].z, v[u].z, c);
+                            adam_update(gr.w, p[u].w, m[u].w, v[u].w, c);
+                            reinterpret_cast<float4*>(pp)[q] = p[u];
+                            reinterpret_cast<float4*>(pm)[q] = m[u];
+                            reinterpret_cast<float4*>(pv)[q] = v[u];
+                        }
+                    }
+                }
+            } else {
+                for (int f = t; f < count; f += 256) {
+                    float gr = gs[f];
+                    if (fld == 5 && NR3 < 45 && f % 45 >= NR3) gr = 0.0f;
+                    float p = pp[f], m = pm[f], v = pv[f];
+                    adam_update(gr, p, m, v, c);
+                    pp[f] = p; pm[f] = m; pv[f] = v;
+                }
+            }
+        }
+        return;
+    }
     if (g < N) {
         a.grad.xyz[g * 3] = axyz[0]; a.grad.xyz[g * 3 + 1] = axyz[1]; a.grad.xyz[g * 3 + 2] = axyz[2];
         *reinterpret_cast<float4*>(a.grad.quaternion_xyzw + g * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
@@ -335,27 +416,35 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
 
 using namespace d3gs;
 
-extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model,
-                                            const D3gsSplatContext* ctx, const float* splat_grads,
-                                            const D3gsModelGrad* grad, void* stream) {
-    D3GS_REQUIRE(cfg && model && ctx && grad, "NULL argument");
+static int32_t check_backward_inputs(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
+                                     const float* splat_grads) {
+    D3GS_REQUIRE(cfg && model && ctx, "NULL argument");
     D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= D3GS_MAX_VIEWS, "num_views %d outside [1,%d]", cfg->num_views,
                  D3GS_MAX_VIEWS);
     D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
     D3GS_REQUIRE(splat_grads != nullptr && ((uintptr_t)splat_grads & 15) == 0, "splat_grads NULL or not 16-byte aligned");
     D3GS_REQUIRE(ctx->radii && ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0, "context lacks radii/cov2d_vecs/sh_to_rgb_ne_0");
+    D3GS_REQUIRE(((uintptr_t)model->quaternion_xyzw & 15) == 0, "quaternion tensors must be 16-byte aligned");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model,
+                                            const D3gsSplatContext* ctx, const float* splat_grads,
+                                            const D3gsModelGrad* grad, void* stream) {
+    D3GS_REQUIRE(grad != nullptr, "NULL argument");
+    int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
+    if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(grad->xyz && grad->quaternion_xyzw && grad->scale && grad->opacity && grad->sh_base,
                  "NULL gradient output");
     D3GS_REQUIRE(cfg->sh_degree == 0 || (grad->sh_rest && model->sh_rest), "sh_rest needed with sh_degree > 0");
-    D3GS_REQUIRE(((uintptr_t)model->quaternion_xyzw & 15) == 0 && ((uintptr_t)grad->quaternion_xyzw & 15) == 0,
-                 "quaternion tensors must be 16-byte aligned");
+    D3GS_REQUIRE(((uintptr_t)grad->quaternion_xyzw & 15) == 0, "quaternion tensors must be 16-byte aligned");
     D3GS_REQUIRE(grad->sh_rest == nullptr ||
                      (grad->sh_rest_floats >= ((cfg->sh_degree + 1) * (cfg->sh_degree + 1) - 1) * 3 &&
                       grad->sh_rest_floats <= grad->sh_rest_stride && grad->sh_rest_floats <= 45),
                  "sh_rest gradient: floats per Gaussian (%d) must cover the active degree and fit the stride (%d)",
                  grad->sh_rest_floats, grad->sh_rest_stride);
     if (model->num == 0) return D3GS_OK;
-    BwdArgs a;
+    BwdArgs a = {};
     a.cfg = *cfg;
     a.model = *model;
     a.ctx = *ctx;
@@ -367,9 +456,9 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     const size_t smem = (size_t)256 * kRow * sizeof(float) * (multi ? 2 : 1);
 #define D3GS_LAUNCH_BWD(DEG, MULTI)                                                                              \
     do {                                                                                                         \
-        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                       (int)smem));                                                              \
-        preprocess_bwd_kernel<DEG, MULTI><<<grid, 256, smem, s>>>(a);                                            \
+        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI, false>,                                 \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
+        preprocess_bwd_kernel<DEG, MULTI, false><<<grid, 256, smem, s>>>(a);                                     \
     } while (0)
     switch (cfg->sh_degree * 2 + (multi ? 1 : 0)) {
         case 0: D3GS_LAUNCH_BWD(0, false); break;
@@ -383,5 +472,55 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     }
 #undef D3GS_LAUNCH_BWD
     D3GS_LAUNCH_CHECK("preprocess_bwd_kernel");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const D3gsModel* model,
+                                                 const D3gsSplatContext* ctx, const float* splat_grads,
+                                                 const D3gsAdamSegment* segments, void* stream) {
+    int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(segments != nullptr, "segments is NULL");
+    D3GS_REQUIRE(cfg->num_views == 1, "the fused backward + Adam handles one view per launch (got %d)", cfg->num_views);
+    D3GS_REQUIRE(model->sh_rest != nullptr && model->sh_rest_stride == 45 && model->sh_base_stride == 3,
+                 "the fused backward + Adam needs the split degree-3 SH layout (strides 3 and 45)");
+    const float* params[6] = {model->xyz, model->quaternion_xyzw, model->scale, model->opacity, model->sh_base,
+                              model->sh_rest};
+    const int64_t per[6] = {3, 4, 3, 1, 3, 45};
+    BwdArgs a = {};
+    for (int k = 0; k < 6; ++k) {
+        const D3gsAdamSegment& sg = segments[k];
+        D3GS_REQUIRE(sg.param == params[k], "segment %d does not point at the model's tensor", k);
+        D3GS_REQUIRE(sg.count == per[k] * model->num, "segment %d: %lld elements, expected %lld", k, (long long)sg.count,
+                     (long long)(per[k] * model->num));
+        D3GS_REQUIRE(sg.exp_avg && sg.exp_avg_sq, "segment %d: NULL moment tensor", k);
+        D3GS_REQUIRE(sg.grad_scale != 0.0f && sg.bias_correction1 != 0.0f && sg.bias_correction2_sqrt != 0.0f,
+                     "segment %d: zero grad_scale / bias correction", k);
+        a.sc[k] = make_seg_const(sg);
+        a.exp_avg[k] = sg.exp_avg;
+        a.exp_avg_sq[k] = sg.exp_avg_sq;
+    }
+    if (model->num == 0) return D3GS_OK;
+    a.cfg = *cfg;
+    a.model = *model;
+    a.ctx = *ctx;
+    a.splat_grads = splat_grads;
+    dim3 grid((unsigned)div_up64(model->num, 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)256 * (kRow + 14) * sizeof(float);   // SH rows + the 14 small-field gradients
+#define D3GS_LAUNCH_BWD_ADAM(DEG)                                                                               \
+    do {                                                                                                        \
+        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, false, true>,                                 \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
+        preprocess_bwd_kernel<DEG, false, true><<<grid, 256, smem, s>>>(a);                                     \
+    } while (0)
+    switch (cfg->sh_degree) {
+        case 0: D3GS_LAUNCH_BWD_ADAM(0); break;
+        case 1: D3GS_LAUNCH_BWD_ADAM(1); break;
+        case 2: D3GS_LAUNCH_BWD_ADAM(2); break;
+        default: D3GS_LAUNCH_BWD_ADAM(3); break;
+    }
+#undef D3GS_LAUNCH_BWD_ADAM
+    D3GS_LAUNCH_CHECK("preprocess_bwd_kernel<adam>");
     return D3GS_OK;
 }

@@ -447,11 +447,13 @@ class GaussianSplatOp:
                  ctx: GaussianSplatOpContext, out: GaussianSplatOutput, grad: GaussianSplatGradients,
                  return_uv_grad: bool = False, instance2world_T: torch.Tensor | None = None,
                  custom_features: torch.Tensor | None = None, prep_user_inputs: dict[str, Any] | None = None,
-                 grad_out: "GaussianModelOriginBase | None" = None):
+                 grad_out: "GaussianModelOriginBase | None" = None, adam_segments=None):
         """Returns ``(grad_model, duv | None, dcustom_features)`` like the reference.
 
         ``grad_out`` (not in the reference) lets the caller supply the gradient container, e.g. views of
-        a persistent flat buffer that is all-reduced across ranks.
+        a persistent flat buffer that is summed across ranks.  ``adam_segments`` (not in the reference): six
+        ``_lib.AdamSegment`` for xyz, quaternion, scale, opacity, sh_base, sh_rest; the backward then applies
+        Adam to the model in place instead of producing gradients (``grad_model`` is None).
         """
         lib = self._lib
         rg = self.rasterize_forward_backward(model, ctx, out, grad, training=True)
@@ -460,6 +462,17 @@ class GaussianSplatOp:
         ocfg = self._op_config(model, cameras, True)
         B = ocfg.num_views
         num = len(model)
+        if adam_segments is not None:
+            assert len(adam_segments) == 6 and B == 1
+            mstruct = self._model_struct(model)
+            cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
+                                       ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
+            arr = (_lib.AdamSegment * 6)(*adam_segments)
+            _lib.check(lib.d3gs_preprocess_backward_adam(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct),
+                                                         rg.packed.data_ptr(), arr, stream),
+                       "d3gs_preprocess_backward_adam")
+            self._mark("preprocess_bwd_adam")
+            return None, (rg.packed.view(B, -1, 12)[:, :, 8:10] if return_uv_grad else None), None
         if grad_out is None:
             if model.flat is not None or (model.color_sh_base is not None and model.color_sh.shape[1] == 15):
                 flat = torch.zeros(flat_layout(num)[1], dtype=torch.float32, device=dev)

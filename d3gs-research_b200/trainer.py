@@ -174,11 +174,14 @@ class SplatTrainer:
     def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
                  spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False,
-                 shard_optimizer: bool | None = None, peer_update: bool | None = None):
+                 shard_optimizer: bool | None = None, peer_update: bool | None = None,
+                 fuse_backward_adam: bool | None = None):
         """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs).
         ``shard_optimizer``: reduce-scatter + sliced Adam + all-gather instead of all-reduce + replicated
         Adam; default on when there is more than one rank.  ``peer_update``: do the sharded update as one
-        kernel over mapped peer buffers; default: tried on NCCL, NCCL collectives when mapping fails."""
+        kernel over mapped peer buffers; default: tried on NCCL, NCCL collectives when mapping fails.
+        ``fuse_backward_adam`` (single rank, one view per step; default on): the preprocess backward applies
+        Adam as it produces the gradients, which are then never stored; ``grad_flat`` is not written."""
         assert model.has_fused_activations, "the trainer drives the fused-activation model"
         assert model.color_sh_base is not None and model.color_sh.shape[1] == 15, "degree-3 split SH layout"
         self.model = model
@@ -220,6 +223,8 @@ class SplatTrainer:
                 setattr(model, k, views[k])
             model.flat = flat
         self.op = GaussianSplatOp(op_cfg)
+        self.fused_adam = (self.world == 1) if fuse_backward_adam is None else bool(fuse_backward_adam)
+        assert not (self.fused_adam and self.world > 1), "the fused backward + Adam is the single-rank path"
         self.lambda_dssim = float(lambda_dssim)
         self.batch_size = int(batch_size)
         self.need_max_radii = need_max_radii
@@ -320,8 +325,17 @@ class SplatTrainer:
                                                      grad_scale=1.0 / self.world, scratch=self._loss_scratch,
                                                      sums=self._loss_sums, dcolor=self._dcolor)
             self.op._mark("l1_dssim")
-            _, duv, _ =self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
-                                         return_uv_grad=True, grad_out=self.grad_model)
+            fuse = self.fused_adam and update and out.color.shape[0] == 1
+            _, duv, _ = self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
+                                         return_uv_grad=True, grad_out=None if fuse else self.grad_model,
+                                         adam_segments=self._adam_segments() if fuse else None)
+            if fuse:   # Adam is done; only the densification statistics are left
+                w, h = out.image_shape_wh
+                stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
+                                          loss_batch=duv.shape[0] * self.world)
+                _launch_adam([], stats, model.xyz.device)
+                self.op._mark("densify_stats")
+                return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
         stats = None
         if update and duv is not None:
             w, h = out.image_shape_wh

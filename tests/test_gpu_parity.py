@@ -295,6 +295,37 @@ def test_adam_and_densify_stats(cuda_device):
         assert_close(getattr(state, k).cpu().numpy(), hstate[k], GRAD_TOL, f"stats {k}")
 
 
+@pytest.mark.parametrize("n,sh_degree", [(3000, 3), (2501, 1)])
+def test_fused_backward_adam_matches_separate_kernels(cuda_device, n, sh_degree):
+    """The single-rank trainer applies Adam inside the preprocess backward; it must leave the parameters and
+    moments that the gradient buffer + optimizer kernel leave.  The per-splat gradients come out of
+    floating-point atomics, so the two runs differ in the last bits of some gradients: the moments (linear in
+    the gradient) are compared tightly, the parameters over the bulk (Adam's normalised step amplifies a
+    last-bit difference of a near-zero gradient)."""
+    from d3gs_research_b200.trainer import SplatTrainer
+    sc = small_scene(n=n, width=176, height=128, sh_degree=sh_degree, seed=5)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
+    target = torch.rand(1, 3, 128, 176, generator=torch.Generator().manual_seed(2)).to(cuda_device)
+    res = {}
+    for fused in (True, False):
+        model = gpu_model(sc, cuda_device)
+        model.cur_sh_degree = sh_degree
+        init = model.flat.clone()
+        tr = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=1, fuse_backward_adam=fused)
+        assert tr.fused_adam == fused
+        for _ in range(2):
+            tr.step(gpu_cameras(sc, cuda_device), target)
+        torch.cuda.synchronize()
+        res[fused] = (model.flat.clone(), tr.exp_avg.clone(), tr.exp_avg_sq.clone(), tr.state.count.clone())
+    assert float((res[True][0] - init).abs().max()) > 0
+    assert torch.equal(res[True][3], res[False][3])
+    for k, name in ((1, "exp_avg"), (2, "exp_avg_sq")):
+        assert_close(res[True][k].cpu().numpy(), res[False][k].cpu().numpy(), GRAD_TOL, name)
+    d = (res[True][0] - res[False][0]).abs()
+    scale = (res[True][0] - init).abs().max()
+    assert float((d > 1e-4 * scale).float().mean()) < 1e-3
+
+
 def _full_size_invariants(cuda_device, cfg_name, training):
     from d3gs_research_b200 import scenes
     sc = scenes.make_scene(cfg_name, seed=0, views=1)
