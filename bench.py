@@ -207,8 +207,8 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
         "adam_stats": 1652 * N + 12 * N + 24 * N,
         # single-rank fused path: the same per-unit figures, so that the iteration total stays comparable (the
         # fused launch actually moves 472 B per Gaussian less: the gradient is neither written nor read)
-        "preprocess_bwd_adam": (53 + 36) * V + 4 * N + 236 * V + 236 * N + 1652 * N,
-        "densify_stats": 12 * N + 24 * N,
+        "preprocess_bwd_adam": (53 + 36) * V + 4 * N + 236 * V + 236 * N + 1652 * N + 12 * N + 24 * N,
+        "densify_stats": 0,
     }
     return float(table.get(stage, 0.0))
 

@@ -105,7 +105,7 @@ SIGNATURES = {
     "d3gs_adam_stats_step": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), _P]),
     "d3gs_densify_stats": (_I32, [C.POINTER(DensifyStats), _P]),
     "d3gs_preprocess_backward_adam": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
-                                             C.POINTER(AdamSegment), _P]),
+                                             C.POINTER(AdamSegment), C.POINTER(DensifyStats), _P]),
     "d3gs_adam_stats_step_peers": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), C.POINTER(PeerSet), _P]),
     "d3gs_peer_buffer_create": (_I32, [_I64, C.POINTER(_P), _P]),
     "d3gs_peer_buffer_open": (_I32, [_P, C.POINTER(_P)]),

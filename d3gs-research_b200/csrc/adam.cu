@@ -40,29 +40,6 @@ struct AdamArgs {
     D3gsPeerSet peers;
 };
 
-__device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t i) {
-    float la = 0.0f, ca = 0.0f, mr = st.need_max_radii ? st.max_radii[i] : 0.0f;
-    const float lb = (float)(st.loss_batch > 0 ? st.loss_batch : st.batch);
-    const float sx = 0.5f * (float)st.width * lb, sy = 0.5f * (float)st.height * lb;
-    const float mwh = (float)max(st.width, st.height);
-    const int64_t stride = st.duv_stride > 0 ? st.duv_stride : 2;
-    for (int j = 0; j < st.batch; ++j) {
-        const int64_t k = (int64_t)j * st.num + i;
-        const float2 d = *reinterpret_cast<const float2*>(st.duv + k * stride);
-        const float a = d.x * sx, b = d.y * sy;
-        const float len = sqrtf(a * a + b * b);
-        const int r = st.radii[k];
-        if (r > 0) {
-            la += len;
-            ca += 1.0f;
-            if (st.need_max_radii) mr = fmaxf(mr, (float)r / mwh);
-        }
-    }
-    st.duv_ndc_length[i] += la;
-    st.count[i] += ca;
-    if (st.need_max_radii) st.max_radii[i] = mr;
-}
-
 __global__ void __launch_bounds__(kAdamThreads) adam_stats_kernel(const __grid_constant__ AdamArgs a) {
     const int64_t blk = blockIdx.x;
     int si = 0;

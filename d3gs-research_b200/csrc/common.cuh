@@ -151,6 +151,30 @@ __device__ __forceinline__ void adam_update(float g, float& p, float& m, float& 
     p = __fmaf_rn(-__fmul_rn(c.step_size, m), __frcp_rn(denom), p);
 }
 
+// densification statistics of one Gaussian (d3sim/algos/d3gs/origin/strategy.py:93-122)
+__device__ __forceinline__ void stats_update(const D3gsDensifyStats& st, int64_t i) {
+    float la = 0.0f, ca = 0.0f, mr = st.need_max_radii ? st.max_radii[i] : 0.0f;
+    const float lb = (float)(st.loss_batch > 0 ? st.loss_batch : st.batch);
+    const float sx = 0.5f * (float)st.width * lb, sy = 0.5f * (float)st.height * lb;
+    const float mwh = (float)max(st.width, st.height);
+    const int64_t stride = st.duv_stride > 0 ? st.duv_stride : 2;
+    for (int j = 0; j < st.batch; ++j) {
+        const int64_t k = (int64_t)j * st.num + i;
+        const float2 d = *reinterpret_cast<const float2*>(st.duv + k * stride);
+        const float a = d.x * sx, b = d.y * sy;
+        const float len = sqrtf(a * a + b * b);
+        const int r = st.radii[k];
+        if (r > 0) {
+            la += len;
+            ca += 1.0f;
+            if (st.need_max_radii) mr = fmaxf(mr, (float)r / mwh);
+        }
+    }
+    st.duv_ndc_length[i] += la;
+    st.count[i] += ca;
+    if (st.need_max_radii) st.max_radii[i] = mr;
+}
+
 __device__ __forceinline__ int f2i_sat(float v) {
     v = fminf(fmaxf(v, -2.0e9f), 2.0e9f);
     return (int)v;

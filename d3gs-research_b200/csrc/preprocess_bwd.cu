@@ -28,6 +28,8 @@ struct BwdArgs {
     SegConst sc[6];
     float* exp_avg[6];
     float* exp_avg_sq[6];
+    int32_t has_stats;
+    D3gsDensifyStats stats;
 };
 
 constexpr int kRow = 45;        // shared-memory row length in floats (odd: conflict-free per-thread rows)
@@ -309,6 +311,7 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
         // the six parameter spans of its 256 Gaussians with coalesced float4 accesses (several in flight per
         // thread), exactly like the stand-alone optimizer kernel but with the gradient coming from shared
         // memory.  The parameters are updated in place: a CTA reads and writes only its own Gaussians'.
+        if (a.has_stats && g < N) stats_update(a.stats, g);
         float* s_small = smem + 256 * kRow;   // [xyz 768 | quaternion 1024 | scale 768 | opacity 256 | sh_base 768]
         s_small[t * 3] = axyz[0]; s_small[t * 3 + 1] = axyz[1]; s_small[t * 3 + 2] = axyz[2];
         *reinterpret_cast<float4*>(s_small + 768 + t * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
@@ -477,7 +480,8 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
 
 extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const D3gsModel* model,
                                                  const D3gsSplatContext* ctx, const float* splat_grads,
-                                                 const D3gsAdamSegment* segments, void* stream) {
+                                                 const D3gsAdamSegment* segments, const D3gsDensifyStats* stats,
+                                                 void* stream) {
     int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(segments != nullptr, "segments is NULL");
@@ -499,6 +503,15 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
         a.sc[k] = make_seg_const(sg);
         a.exp_avg[k] = sg.exp_avg;
         a.exp_avg_sq[k] = sg.exp_avg_sq;
+    }
+    if (stats != nullptr) {
+        D3GS_REQUIRE(stats->num == model->num && stats->batch == 1, "statistics shape does not match the model / one view");
+        D3GS_REQUIRE(stats->duv && stats->radii && stats->duv_ndc_length && stats->count, "NULL stats tensor");
+        D3GS_REQUIRE(!stats->need_max_radii || stats->max_radii, "max_radii is NULL");
+        D3GS_REQUIRE(((uintptr_t)stats->duv & 7) == 0 && (stats->duv_stride & 1) == 0,
+                     "duv must be 8-byte aligned, stride even");
+        a.has_stats = 1;
+        a.stats = *stats;
     }
     if (model->num == 0) return D3GS_OK;
     a.cfg = *cfg;

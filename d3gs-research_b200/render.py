@@ -447,13 +447,14 @@ class GaussianSplatOp:
                  ctx: GaussianSplatOpContext, out: GaussianSplatOutput, grad: GaussianSplatGradients,
                  return_uv_grad: bool = False, instance2world_T: torch.Tensor | None = None,
                  custom_features: torch.Tensor | None = None, prep_user_inputs: dict[str, Any] | None = None,
-                 grad_out: "GaussianModelOriginBase | None" = None, adam_segments=None):
+                 grad_out: "GaussianModelOriginBase | None" = None, adam_segments=None, stats_fn=None):
         """Returns ``(grad_model, duv | None, dcustom_features)`` like the reference.
 
         ``grad_out`` (not in the reference) lets the caller supply the gradient container, e.g. views of
         a persistent flat buffer that is summed across ranks.  ``adam_segments`` (not in the reference): six
         ``_lib.AdamSegment`` for xyz, quaternion, scale, opacity, sh_base, sh_rest; the backward then applies
-        Adam to the model in place instead of producing gradients (``grad_model`` is None).
+        Adam to the model in place instead of producing gradients (``grad_model`` is None); ``stats_fn(duv)``
+        may then return a ``_lib.DensifyStats`` to accumulate in the same launch.
         """
         lib = self._lib
         rg = self.rasterize_forward_backward(model, ctx, out, grad, training=True)
@@ -468,11 +469,14 @@ class GaussianSplatOp:
             cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
                                        ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
             arr = (_lib.AdamSegment * 6)(*adam_segments)
+            duv = rg.packed.view(B, -1, 12)[:, :, 8:10]
+            stats = stats_fn(duv) if stats_fn is not None else None
             _lib.check(lib.d3gs_preprocess_backward_adam(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct),
-                                                         rg.packed.data_ptr(), arr, stream),
+                                                         rg.packed.data_ptr(), arr,
+                                                         C.byref(stats) if stats is not None else None, stream),
                        "d3gs_preprocess_backward_adam")
             self._mark("preprocess_bwd_adam")
-            return None, (rg.packed.view(B, -1, 12)[:, :, 8:10] if return_uv_grad else None), None
+            return None, (duv if return_uv_grad else None), None
         if grad_out is None:
             if model.flat is not None or (model.color_sh_base is not None and model.color_sh.shape[1] == 15):
                 flat = torch.zeros(flat_layout(num)[1], dtype=torch.float32, device=dev)

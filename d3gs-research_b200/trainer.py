@@ -326,15 +326,13 @@ class SplatTrainer:
                                                      sums=self._loss_sums, dcolor=self._dcolor)
             self.op._mark("l1_dssim")
             fuse = self.fused_adam and update and out.color.shape[0] == 1
+            w, h = out.image_shape_wh
+            stats_fn = (lambda d: make_stats_struct(self.state, out.radii, d, w, h, self.need_max_radii,
+                                                    loss_batch=d.shape[0] * self.world)) if fuse else None
             _, duv, _ = self.op.backward(model, cameras, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None),
                                          return_uv_grad=True, grad_out=None if fuse else self.grad_model,
-                                         adam_segments=self._adam_segments() if fuse else None)
-            if fuse:   # Adam is done; only the densification statistics are left
-                w, h = out.image_shape_wh
-                stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
-                                          loss_batch=duv.shape[0] * self.world)
-                _launch_adam([], stats, model.xyz.device)
-                self.op._mark("densify_stats")
+                                         adam_segments=self._adam_segments() if fuse else None, stats_fn=stats_fn)
+            if fuse:   # Adam and the densification statistics were part of the backward launch
                 return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
         stats = None
         if update and duv is not None:

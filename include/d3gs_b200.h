@@ -253,10 +253,11 @@ int32_t d3gs_densify_stats(const D3gsDensifyStats* stats, void* stream);
  * d3gs_preprocess_backward are never written or read (render.py:3176-3360 followed by adam.py:382-418).
  * segments[0..5] = xyz, quaternion_xyzw, scale, opacity, sh_base, sh_rest in this order; segment.param must be
  * the model's tensor (updated in place), segment.count its element count, segment.grad is ignored.  Needs the
- * split degree-3 layout (sh_base_stride 3, sh_rest_stride 45) and cfg->num_views == 1.  The densification
- * statistics are a separate d3gs_densify_stats call. */
+ * split degree-3 layout (sh_base_stride 3, sh_rest_stride 45) and cfg->num_views == 1.  stats (may be NULL):
+ * the densification statistics of the same iteration, accumulated by the same launch. */
 int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
-                                      const float* splat_grads, const D3gsAdamSegment* segments, void* stream);
+                                      const float* splat_grads, const D3gsAdamSegment* segments,
+                                      const D3gsDensifyStats* stats, void* stream);
 
 /* ---- data-parallel update over peer memory (no counterpart in the reference, which trains on one GPU;
  * the batch semantics it implements are those of train.py:170-172 and tools.py:146-163) ------------
