@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl-update", action="store_true",
                     help="N>1: sharded optimizer through NCCL reduce-scatter / all-gather instead of the peer-memory kernel")
+    ap.add_argument("--separate-adam", action="store_true",
+                    help="N=1: gradient buffer + optimizer kernel instead of Adam inside the preprocess backward")
     ap.add_argument("--replicated-adam", action="store_true",
                     help="N>1: all-reduce + full Adam on every rank instead of the sharded optimizer")
     ap.add_argument("--cpu-sample", type=int, default=4, help="CPU baseline runs on 1/S of the Gaussians")
@@ -316,7 +318,8 @@ def main():
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
     trainer = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world,
                            shard_optimizer=False if args.replicated_adam else None,
-                           peer_update=False if (args.nccl_update or args.replicated_adam) else None)
+                           peer_update=False if (args.nccl_update or args.replicated_adam) else None,
+                           fuse_backward_adam=False if (args.separate_adam or world > 1) else None)
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
     target_host = sc["target"][rank % sc["target"].shape[0]][None].contiguous().pin_memory()
@@ -417,11 +420,13 @@ def main():
     views = world
     value = views * args.steps / (ms_total / 1e3)
     e2e_value = views * args.steps / (ms_e2e / 1e3)
-    optimizer_kind = ("single rank" if world == 1 else
+    optimizer_kind = (("single rank, Adam inside the preprocess backward" if trainer.fused_adam else
+                       "single rank, gradient buffer + optimizer kernel") if world == 1 else
                       "sharded, one kernel over NVLink peer memory: sum of all ranks' gradient slices, Adam, store to "
                       "all ranks' parameters" if trainer._peerset is not None else
                       "sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded else
                       "replicated after all-reduce")
+    launches_per_step = 18 if trainer.fused_adam else 19
     trainer.close()    # unmap the peer buffers (collective) before the process group goes away
     if rank != 0:
         if world > 1:
@@ -452,7 +457,7 @@ def main():
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(target_host.numel() * 4),
                 "d2h_bytes_per_step": 16 + 16, "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": 19 * args.steps,   # per step: see profiles/launch_list_cfg3_1gpu.md
+        "gpu_launches": launches_per_step * args.steps,   # per step: see profiles/launch_list_cfg3_1gpu.md
         "clocks": clocks,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
