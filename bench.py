@@ -404,7 +404,7 @@ def main():
     trainer.op.timer = StageTimer(prealloc=20 * (args.steps + 1))
     torch.cuda.synchronize()
     timed(args.steps, e2e=False)
-    stage_ms = trainer.op.timer.summary()
+    stage_ms = trainer.op.timer.summary(median=True)   # per-stage median over the steps of the pass
     trainer.op.timer = None
 
     replicas_agree = None

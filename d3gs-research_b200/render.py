@@ -184,14 +184,20 @@ class StageTimer:
             self.begin_step()
         self.steps[-1].append((name, self._event()))
 
-    def summary(self) -> dict[str, float]:
-        """Mean milliseconds per stage over the recorded steps (call after torch.cuda.synchronize())."""
-        acc: dict[str, float] = {}
+    def summary(self, median: bool = False) -> dict[str, float]:
+        """Milliseconds per stage over the recorded steps (call after torch.cuda.synchronize()): the mean, or
+        the per-stage median, which ignores a one-off stall of a single step."""
+        acc: dict[str, list[float]] = {}
         for marks in self.steps:
+            per: dict[str, float] = {}
             for (_, e0), (name, e1) in zip(marks[:-1], marks[1:]):
-                acc[name] = acc.get(name, 0.0) + e0.elapsed_time(e1)
+                per[name] = per.get(name, 0.0) + e0.elapsed_time(e1)
+            for k, v in per.items():
+                acc.setdefault(k, []).append(v)
+        if median:
+            return {k: sorted(v)[len(v) // 2] for k, v in acc.items()}
         n = max(len(self.steps), 1)
-        return {k: v / n for k, v in acc.items()}
+        return {k: sum(v) / n for k, v in acc.items()}
 
 
 class GaussianSplatOp:
