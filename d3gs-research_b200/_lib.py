@@ -74,7 +74,20 @@ class PeerSet(C.Structure):
                 ("param", C.c_void_p * MAX_PEERS), ("status", C.c_void_p)]
 
 
-_STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats, PeerSet]
+class RefineConfig(C.Structure):
+    _fields_ = [("prune_opacity_thresh", C.c_float), ("grow_grad2d", C.c_float), ("grow_scale3d", C.c_float),
+                ("grow_scale2d", C.c_float), ("prune_scale3d", C.c_float), ("prune_scale2d", C.c_float),
+                ("scene_scale", C.c_float), ("prune_too_big", C.c_int32), ("refine_by_radii", C.c_int32),
+                ("fused_activations", C.c_int32)]
+
+
+class RefineMoments(C.Structure):
+    _fields_ = [("exp_avg_src", C.c_void_p * 6), ("exp_avg_sq_src", C.c_void_p * 6), ("exp_avg_dst", C.c_void_p * 6),
+                ("exp_avg_sq_dst", C.c_void_p * 6)]
+
+
+_STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats, PeerSet, RefineConfig,
+            RefineMoments]
 
 _P, _I32, _I64, _F, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
 
@@ -107,6 +120,10 @@ SIGNATURES = {
     "d3gs_preprocess_backward_adam": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
                                              C.POINTER(AdamSegment), C.POINTER(DensifyStats), _P]),
     "d3gs_adam_stats_step_peers": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), C.POINTER(PeerSet), _P]),
+    "d3gs_refine_classify": (_I32, [C.POINTER(Model), C.POINTER(RefineConfig), _P, _P, _P, _P, _P, _P]),
+    "d3gs_refine_apply": (_I32, [C.POINTER(Model), C.POINTER(Model), C.POINTER(RefineConfig), C.POINTER(RefineMoments),
+                                 _P, _P, _P, C.POINTER(C.c_int64), _P, _P]),
+    "d3gs_reset_opacity": (_I32, [_P, _I64, _F, _I32, _P, _P, _P]),
     "d3gs_peer_buffer_create": (_I32, [_I64, C.POINTER(_P), _P]),
     "d3gs_peer_buffer_open": (_I32, [_P, C.POINTER(_P)]),
     "d3gs_peer_buffer_close": (_I32, [_P]),

@@ -53,6 +53,8 @@ extern "C" size_t d3gs_struct_size(int32_t which) {
         case 5: return sizeof(D3gsAdamSegment);
         case 6: return sizeof(D3gsDensifyStats);
         case 7: return sizeof(D3gsPeerSet);
+        case 8: return sizeof(D3gsRefineConfig);
+        case 9: return sizeof(D3gsRefineMoments);
         default: return 0;
     }
 }

@@ -267,6 +267,54 @@ class SplatTrainer:
         self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
 
     # ------------------------------------------------------------------------------------------
+    def _field_views(self, flat: torch.Tensor) -> dict:
+        """Views of a flat buffer in this trainer's layout, shaped like the model's tensors."""
+        return {name: flat[off:off + cnt].view(getattr(self.model, name).shape) for name, (off, cnt) in self._offsets.items()}
+
+    @torch.no_grad()
+    def refine(self, strategy, step: int, generator: "torch.Generator | None" = None) -> tuple:
+        """Densify and prune between two training steps (``GaussianStrategyOrigin.refine_gs``,
+        d3sim/algos/d3gs/origin/strategy.py:159-363; the trainer calls it every ``refine_every`` iterations
+        between ``refine_start_iter`` and ``refine_stop_iter``, origin/trainer.py:377-386).  The model's tensors,
+        the Adam moments, the gradient buffer and the statistics are rebuilt for the new Gaussian count.
+        Single rank only: with several ranks the peer-mapped buffers would have to be re-created for the new
+        count on every rank, which is not built.  Returns ``(n_keep, n_dup_kept, n_split_kept, n_split)``."""
+        assert self.world == 1, "SplatTrainer.refine is built for one rank"
+        model, dev = self.model, self.model.xyz.device
+        m_views, v_views = self._field_views(self.exp_avg), self._field_views(self.exp_avg_sq)
+        moments = {name: (m_views[name], v_views[name]) for name in self._offsets}
+        new_model, new_moments, _, totals = strategy.refine_tensors(model, moments, self.state, step, generator)
+        n = len(new_model)
+        layout, total = flat_layout(n)
+        for k in FLAT_ORDER:
+            setattr(model, k, getattr(new_model, k))
+        model.flat = new_model.flat
+        self.flat_total, self.shard_len = total, total
+        self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
+        self.exp_avg = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(total, dtype=torch.float32, device=dev)
+        m_views, v_views = self._field_views(self.exp_avg), self._field_views(self.exp_avg_sq)
+        for name, (m, v) in new_moments.items():
+            m_views[name].copy_(m)
+            v_views[name].copy_(v)
+        self.grad_flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
+                                      act_applied=True, flat=self.grad_flat)
+        self.state = GaussianTrainState.create(n, self.state.scene_scale, device=dev)   # reset, origin/strategy.py:349
+        return totals
+
+    @torch.no_grad()
+    def reset_opacity(self, strategy) -> None:
+        """origin/trainer.py:388-417 on the trainer's buffers: clamp the opacities, zero their Adam moments."""
+        assert not self.sharded, "the opacity moments of a sharded optimizer live on several ranks"
+        off, cnt = self._offsets["opacity"]
+        lib = _lib.load()
+        dev = self.model.opacity.device
+        _lib.check(lib.d3gs_reset_opacity(self.model.opacity.data_ptr(), cnt, float(strategy.reset_opacity_thresh),
+                                          int(self.model.has_fused_activations),
+                                          self.exp_avg.data_ptr() + off * 4, self.exp_avg_sq.data_ptr() + off * 4,
+                                          torch.cuda.current_stream(dev).cuda_stream), "d3gs_reset_opacity")
+
     def _adam_segments(self):
         self.step_count += 1
         t = float(self.step_count)

@@ -127,7 +127,8 @@ size_t d3gs_last_error(char* buf, size_t cap);
 /* DeviceSort.get_higher_msb (csrc/devsort.py:129-149): number of bits needed for n */
 int32_t d3gs_bit_length(uint32_t n);
 /* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
- * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet */
+ * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet,
+ * 8 D3gsRefineConfig, 9 D3gsRefineMoments */
 size_t d3gs_struct_size(int32_t which);
 
 /* ---- K1 preprocess forward (render.py:250-681) ------------------------------------------- */
@@ -293,6 +294,44 @@ int32_t d3gs_peer_buffer_create(int64_t bytes, void** ptr, void* handle);
 int32_t d3gs_peer_buffer_open(const void* handle, void** ptr);
 int32_t d3gs_peer_buffer_close(void* ptr);
 int32_t d3gs_peer_buffer_destroy(void* ptr);
+
+/* ---- densification, pruning, opacity reset (origin/strategy.py:159-363, strategy.py:131-202,
+ * origin/trainer.py:388-417): the step that follows every refine_every-th training iteration ----------
+ * d3gs_refine_classify applies the reference's tests to every Gaussian and writes
+ *   columns [4][N] int32: keep (not pruned), duplicate that is kept, split whose two children are kept, split;
+ *   flags   [N] uint8: bit0 duplicate, bit1 split, bit2 pruned, bit3 split children pruned.
+ * The caller scans each column (d3gs_scan_tiles), reads the four totals {keep, dup, split_kept, split},
+ * allocates the new model of keep + dup + 2*split_kept Gaussians and 2*split unit normals (the reference draws
+ * them with torch.randn, strategy.py:286), and calls d3gs_refine_apply, which writes the output rows in the
+ * reference's order [survivors | duplicates | first split copies | second split copies]: parameters copied,
+ * split children moved to R(q)(normal*scale) + xyz with scale/1.6, Adam moments gathered for survivors and
+ * zero for new Gaussians, src_index (optional) = source Gaussian of every output row. */
+typedef struct D3gsRefineConfig {
+    float prune_opacity_thresh, grow_grad2d, grow_scale3d, grow_scale2d, prune_scale3d, prune_scale2d;
+    float scene_scale;
+    int32_t prune_too_big;      /* step > reset_opacity_every (strategy.py:178) */
+    int32_t refine_by_radii;    /* step < refine_scale2d_stop_iter (strategy.py:177) */
+    int32_t fused_activations;  /* the model stores raw scale / opacity / quaternion (GaussianModelOriginFused) */
+} D3gsRefineConfig;
+
+typedef struct D3gsRefineMoments {  /* per field xyz, quaternion, scale, opacity, sh_base, sh_rest; NULL = skip */
+    const float* exp_avg_src[6];
+    const float* exp_avg_sq_src[6];
+    float* exp_avg_dst[6];
+    float* exp_avg_sq_dst[6];
+} D3gsRefineMoments;
+
+int32_t d3gs_refine_classify(const D3gsModel* model, const D3gsRefineConfig* rc, const float* duv_ndc_length,
+                             const float* count, const float* max_radii, int32_t* columns, uint8_t* flags,
+                             void* stream);
+/* dst's tensors are written (the struct's const qualifiers describe the other entry points); scans = the
+ * inclusive scans of columns; totals = host array of the four totals; moments may be NULL */
+int32_t d3gs_refine_apply(const D3gsModel* src, const D3gsModel* dst, const D3gsRefineConfig* rc,
+                          const D3gsRefineMoments* moments, const int32_t* scans, const uint8_t* flags,
+                          const float* normals, const int64_t* totals, int32_t* src_index, void* stream);
+/* opacity = logit(min(activated opacity, thresh)) in place; the given Adam moments of opacity are zeroed */
+int32_t d3gs_reset_opacity(float* opacity, int64_t num, float thresh, int32_t fused_activations, float* exp_avg,
+                           float* exp_avg_sq, void* stream);
 
 #ifdef __cplusplus
 }

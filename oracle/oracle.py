@@ -324,3 +324,112 @@ def cov3d(quat_xyzw, scale_act):
     rot = np.zeros((n, 3, 3), np.float32)
     lib().oracle_cov3d(ctypes.c_int(n), _p(_f32(quat_xyzw)), _p(_f32(scale_act)), _p(cov6), _p(rot))
     return cov6, rot
+
+
+# ---- densification / pruning / opacity reset (test infrastructure like the rest of this file) ----------------
+def _act_exp(a):
+    f = lib().oracle_expf
+    return np.array([f(float(x)) for x in np.asarray(a, np.float32).ravel()], np.float32).reshape(np.shape(a))
+
+
+def _act_log(a):
+    f = lib().oracle_logf
+    return np.array([f(float(x)) for x in np.asarray(a, np.float32).ravel()], np.float32).reshape(np.shape(a))
+
+
+def _sigmoid(a):
+    one = np.float32(1.0)
+    return (one / (one + _act_exp(-np.asarray(a, np.float32)))).astype(np.float32)
+
+
+@dataclass
+class RefineConfig:
+    """Thresholds of GaussianStrategyOrigin (d3sim/algos/d3gs/origin/strategy.py:21-35)."""
+    reset_opacity_thresh: float = 0.01
+    prune_opacity_thresh: float = 0.005
+    grow_grad2d: float = 0.0002
+    grow_scale3d: float = 0.01
+    grow_scale2d: float = 0.05
+    prune_scale3d: float = 0.1
+    prune_scale2d: float = 0.15
+    refine_scale2d_stop_iter: int = 0
+    reset_opacity_every: int = 3000
+
+
+def refine_masks(rc: RefineConfig, model: dict, state: dict, scene_scale: float, step: int):
+    """The mask kernel of refine_gs (origin/strategy.py:195-241) on a fused-activation model (raw scale and
+    opacity).  Returns (should_dupli, should_split, origin_prune)."""
+    f32 = np.float32
+    scale = _act_exp(model["scale"])
+    opac = _sigmoid(model["opacity"])
+    cnt = state["count"].astype(f32)
+    grad_high = (state["duv_ndc_length"].astype(f32) / np.maximum(cnt, f32(1.0))) >= f32(rc.grow_grad2d)
+    smax = scale.max(axis=1)
+    small = smax <= f32(rc.grow_scale3d) * f32(scene_scale)
+    dup = grad_high & small
+    large = ~small
+    prune = opac < f32(rc.prune_opacity_thresh)
+    if step > rc.reset_opacity_every:
+        prune = prune | (smax > f32(rc.prune_scale3d) * f32(scene_scale))
+    if step < rc.refine_scale2d_stop_iter:
+        large = large | (state["max_radii"] > f32(rc.grow_scale2d))
+        prune = prune | (state["max_radii"] > f32(rc.prune_scale2d))
+    split = grad_high & large
+    return dup, split, prune | split
+
+
+def refine_gs(rc: RefineConfig, model: dict, moments: dict, state: dict, scene_scale: float, step: int, normals):
+    """refine_gs (origin/strategy.py:159-363) + select_gs_optimizer_by_mask / zero_optimizer_by_range
+    (strategy.py:131-178) with numpy.  ``model``: name -> array (raw parameters, first axis N); ``moments``: name ->
+    (exp_avg, exp_avg_sq); ``normals``: [2 * n_split, 3] standard normal draws (torch.randn in the reference).
+    Returns (new_model, new_moments, res_inds, n_dupli, n_split)."""
+    f32 = np.float32
+    dup, split, origin_prune = refine_masks(rc, model, state, scene_scale, step)
+    n = model["xyz"].shape[0]
+    dup_inds, split_inds = np.nonzero(dup)[0], np.nonzero(split)[0]
+    n_dup, n_split = len(dup_inds), len(split_inds)
+    assert normals.shape == (2 * n_split, 3)
+    new_inds = np.concatenate([dup_inds, split_inds, split_inds])
+    new = {k: v[new_inds].copy() for k, v in model.items()}
+    new_prune = np.zeros(n_dup + 2 * n_split, dtype=bool)
+    new_prune[:n_dup] = origin_prune[dup_inds]
+    # split children (origin/strategy.py:286-331)
+    sl = slice(n_dup, None)
+    q = new["quat"][sl].astype(f32)
+    qn = np.sqrt(((q[:, 0] * q[:, 0] + q[:, 1] * q[:, 1]) + q[:, 2] * q[:, 2]) + q[:, 3] * q[:, 3]).astype(f32)
+    q = (q / qn[:, None]).astype(f32)
+    x, y, z, w = q[:, 0], q[:, 1], q[:, 2], q[:, 3]
+    two, one = f32(2.0), f32(1.0)
+    R = np.empty((len(q), 3, 3), f32)
+    R[:, 0, 0] = one - two * (y * y + z * z); R[:, 0, 1] = two * (x * y - w * z); R[:, 0, 2] = two * (x * z + w * y)
+    R[:, 1, 0] = two * (x * y + w * z); R[:, 1, 1] = one - two * (x * x + z * z); R[:, 1, 2] = two * (y * z - w * x)
+    R[:, 2, 0] = two * (x * z - w * y); R[:, 2, 1] = two * (y * z + w * x); R[:, 2, 2] = one - two * (x * x + y * y)
+    s_act = _act_exp(new["scale"][sl])
+    v = (normals.astype(f32) * s_act).astype(f32)
+    new_xyz = (((R[:, :, 0] * v[:, 0:1] + R[:, :, 1] * v[:, 1:2]) + R[:, :, 2] * v[:, 2:3]) + new["xyz"][sl]).astype(f32)
+    new_scaling = (s_act / f32(1.6)).astype(f32)
+    child_prune = _sigmoid(new["opacity"][sl]) < f32(rc.prune_opacity_thresh)
+    if step > rc.reset_opacity_every:
+        child_prune = child_prune | (new_scaling.max(axis=1) > f32(rc.prune_scale3d) * f32(scene_scale))
+    if step < rc.refine_scale2d_stop_iter:
+        child_prune = child_prune | (state["max_radii"][new_inds[sl]] > f32(rc.prune_scale2d))
+    new["xyz"][sl] = new_xyz
+    new["scale"][sl] = _act_log(new_scaling)
+    new_prune[sl] = child_prune
+    keep_o, keep_n = ~origin_prune, ~new_prune
+    res_model = {k: np.concatenate([model[k][keep_o], new[k][keep_n]]) for k in model}
+    res_inds = np.concatenate([np.arange(n)[keep_o], new_inds[keep_n]])
+    n_keep = int(keep_o.sum())
+    res_moments = {}
+    for k, (m, vv) in moments.items():
+        mm, v2 = m[res_inds].copy(), vv[res_inds].copy()
+        mm[n_keep:] = 0
+        v2[n_keep:] = 0
+        res_moments[k] = (mm, v2)
+    return res_model, res_moments, res_inds, n_dup, n_split
+
+
+def reset_opacity(opacity_raw, thresh: float):
+    """origin/trainer.py:388-417: logit(min(sigmoid(opacity), thresh))."""
+    o = np.minimum(_sigmoid(opacity_raw), np.float32(thresh)).astype(np.float32)
+    return _act_log((o / (np.float32(1.0) - o)).astype(np.float32))
