@@ -223,3 +223,39 @@ def test_sharded_optimizer_equals_replicated_gloo():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == [(0, True, 0.0), (1, True, 0.0)], got
+
+
+def test_ply_roundtrip_and_point_cloud_init(tmp_path):
+    from d3gs_research_b200.tools import (init_original_3dgs_model, load_3dgs_origin_model, points_to_gaussian_init_scale,
+                                          save_3dgs_origin_model)
+    n = 37
+    g = torch.Generator().manual_seed(3)
+    m = d3.GaussianModelOriginFused.from_tensors(torch.randn(n, 3, generator=g), torch.randn(n, 4, generator=g),
+                                                 torch.randn(n, 3, generator=g), torch.randn(n, generator=g),
+                                                 torch.randn(n, 3, generator=g), torch.randn(n, 15, 3, generator=g), device="cpu")
+    path = str(tmp_path / "m.ply")
+    save_3dgs_origin_model(m, path)
+    head = open(path, "rb").read(400).decode("ascii", "replace")
+    assert head.startswith("ply\nformat binary_little_endian 1.0\nelement vertex 37\nproperty float x\n")
+    assert "property float f_rest_44" in open(path, "rb").read(4000).decode("ascii", "replace")
+    for split in (True, False):
+        r = load_3dgs_origin_model(path, fused=True, split=split, device="cpu")
+        assert torch.equal(r.xyz, m.xyz) and torch.equal(r.quaternion_xyzw, m.quaternion_xyzw)
+        assert torch.equal(r.scale, m.scale) and torch.equal(r.opacity, m.opacity) and r.cur_sh_degree == 3
+        if split:
+            assert torch.equal(r.color_sh_base, m.color_sh_base) and torch.equal(r.color_sh, m.color_sh)
+        else:
+            assert torch.equal(r.color_sh[:, 0], m.color_sh_base) and torch.equal(r.color_sh[:, 1:], m.color_sh)
+    # the file layout is the Inria one: rot_0 is w, f_rest is channel-major
+    from d3gs_research_b200.tools import _read_ply_vertices
+    v = _read_ply_vertices(path)
+    assert np.allclose(v["rot_0"], m.quaternion_xyzw[:, 3].numpy()) and np.allclose(v["f_rest_1"], m.color_sh[:, 1, 0].numpy())
+    assert np.allclose(v["f_rest_15"], m.color_sh[:, 0, 1].numpy())
+    # point-cloud initialisation: a regular grid has all three nearest neighbours at the grid spacing
+    pts = np.stack(np.meshgrid(np.arange(4.0), np.arange(4.0), np.arange(4.0), indexing="ij"), -1).reshape(-1, 3) * 0.5
+    s = points_to_gaussian_init_scale(torch.from_numpy(pts.astype(np.float32)))
+    assert torch.allclose(s, torch.full_like(s, float(np.log(0.5))), atol=1e-5)
+    m2 = d3.GaussianModelOriginFused.create_flat(64, device="cpu")
+    init_original_3dgs_model(m2, pts, np.full((64, 3), 0.5))
+    assert m2.cur_sh_degree == 0 and float(m2.color_sh_base.abs().max()) == 0.0 and float(m2.quaternion_xyzw[:, 3].min()) == 1.0
+    assert abs(float(torch.sigmoid(m2.opacity[0])) - 0.1) < 1e-6
