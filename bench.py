@@ -217,7 +217,7 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from `ncu --set full` captures of
-# the small case `--n 750000` (N, V, K, P, Tn below); summaries with the commands are in profiles/ncu_*.md.
+# the small case `--n 750000` (N, V, K, P, Tn below); the summaries under profiles/ give the commands.
 # A full-size launch is too large to capture under a 40-pass replay, so the figure is scaled to the bench's
 # workload by the ratio of algorithmic bytes (traffic of these kernels grows with the units processed).
 NCU_SMALL_CASE = dict(N=750000, V=574917, K=1068256, P=2073600, Tn=8160)
@@ -458,12 +458,12 @@ def main():
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(target_host.numel() * 4),
                 "d2h_bytes_per_step": 16 + 16, "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": launches_per_step * args.steps,   # per step: see profiles/launch_list_cfg3_1gpu.md
+        "gpu_launches": launches_per_step * args.steps,   # launches of this library per step (profiles/ lists them)
         "clocks": clocks,
         "stage_ms": {k: round(v, 4) for k, v in stage_ms.items()},
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": ncu_traffic(dom, N, V, K, P, Tn),
-                     "traffic_source": "ncu dram bytes of the 750k-Gaussian case scaled by algorithmic bytes (profiles/)",
+                     "traffic_source": "ncu dram bytes of the 750k-Gaussian case scaled by algorithmic bytes",
                      "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes,
                      "iteration": {"algorithmic_bytes": iter_bytes,

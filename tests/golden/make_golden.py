@@ -1,6 +1,6 @@
 """Generates tests/golden/ref_vectors.npz by importing the reference's own pure-torch helper modules.
 
-Run in a container where the reference tree is mounted:  python tests/golden/make_golden.py [/root/reference]
+Run where the reference tree is available:  python tests/golden/make_golden.py <path to the d3gs-research checkout>
 The modules are loaded by file path (the d3sim package itself cannot be imported: its JIT dependencies are
 absent) and called unmodified.  ``build_rotation`` hard-codes device="cuda" for its temporaries; torch.zeros is
 wrapped for the duration of the call so that the same code runs on the CPU.
@@ -87,4 +87,4 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("D3SIM_REFERENCE", "reference"))
