@@ -107,8 +107,9 @@ SIGNATURES = {
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
     "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
-    "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P]),
-    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_tile_order": (_I32, [_P, _I64, _P, _P]),
+    "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
                                         C.POINTER(ModelGrad), _P]),
     "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),

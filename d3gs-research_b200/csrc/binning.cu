@@ -139,6 +139,34 @@ tile_ranges_kernel(const uint64_t* __restrict__ keys, int64_t n, int32_t* __rest
     if (i == n - 1) ranges[(int64_t)t * 2 + 1] = (int32_t)n;
 }
 
+// Tiles by decreasing list length (in buckets of 32 entries): the raster grids take them in this order, so
+// that the CTAs that start last are the cheapest.  One CTA: a shared-memory histogram over 64 length
+// buckets, a scan from the longest bucket down, and a scatter; the order inside a bucket is arbitrary (the
+// raster results do not depend on the order in which tiles are processed).
+constexpr int kOrderBuckets = 64;
+__device__ __forceinline__ int order_bucket(int len) { return kOrderBuckets - 1 - min(len >> 5, kOrderBuckets - 1); }
+
+__global__ void __launch_bounds__(1024) tile_order_kernel(const int32_t* __restrict__ ranges, int num_tiles,
+                                                         int32_t* __restrict__ order) {
+    __shared__ int s_cnt[kOrderBuckets];
+    __shared__ int s_off[kOrderBuckets];
+    const int t = threadIdx.x;
+    if (t < kOrderBuckets) s_cnt[t] = 0;
+    __syncthreads();
+    for (int i = t; i < num_tiles; i += 1024) atomicAdd(&s_cnt[order_bucket(ranges[i * 2 + 1] - ranges[i * 2])], 1);
+    __syncthreads();
+    if (t == 0) {
+        int acc = 0;
+        for (int b = 0; b < kOrderBuckets; ++b) {
+            s_off[b] = acc;
+            acc += s_cnt[b];
+        }
+    }
+    __syncthreads();
+    for (int i = t; i < num_tiles; i += 1024)
+        order[atomicAdd(&s_off[order_bucket(ranges[i * 2 + 1] - ranges[i * 2])], 1)] = i;
+}
+
 // One 48-byte record per sorted (tile, Gaussian) pair:
 //   [u, v, hx, hy] [ha, nb, hc, opacity] [r, g, b, thr]
 // ha=-0.5*conic_a, nb=-conic_b, hc=-0.5*conic_c (exact scalings).
@@ -219,6 +247,15 @@ extern "C" int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int3
     D3GS_REQUIRE(n < (int64_t)1 << 31, "pair count %lld does not fit the int32 ranges", (long long)n);
     tile_ranges_kernel<<<(unsigned)div_up64(n, 256), 256, 0, s>>>(sorted_keys, n, ranges);
     D3GS_LAUNCH_CHECK("tile_ranges_kernel");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_tile_order(const int32_t* ranges, int64_t num_tiles, int32_t* order, void* stream) {
+    D3GS_REQUIRE(num_tiles >= 0 && num_tiles < ((int64_t)1 << 31), "tile count out of range");
+    if (num_tiles == 0) return D3GS_OK;
+    D3GS_REQUIRE(ranges != nullptr && order != nullptr, "NULL argument");
+    tile_order_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(ranges, (int)num_tiles, order);
+    D3GS_LAUNCH_CHECK("tile_order_kernel");
     return D3GS_OK;
 }
 

@@ -41,6 +41,7 @@ struct RasterArgs {
     float bg[3];
     int training;
     const int32_t* ranges;
+    const int32_t* tile_order;   // optional: CTA k handles tile tile_order[k] (longest lists first)
     const float4* records;
     const int32_t* sorted_ids;
     uint32_t* status;
@@ -59,15 +60,31 @@ struct PixelCoord {
     bool inside;
 };
 
+// The tile a CTA works on.  The grid is one-dimensional; with an order table the CTAs take the tiles by
+// decreasing list length, so that the last CTAs to start are the cheapest and the grid ends without a tail.
+struct TileId {
+    int x, y, view, tile;
+};
+__device__ __forceinline__ TileId tile_of_cta(const RasterArgs& a) {
+    TileId t;
+    t.tile = a.tile_order != nullptr ? a.tile_order[blockIdx.x] : (int)blockIdx.x;
+    const int per_view = a.tiles_x * a.tiles_y;
+    t.view = t.tile / per_view;
+    const int r = t.tile - t.view * per_view;
+    t.y = r / a.tiles_x;
+    t.x = r - t.y * a.tiles_x;
+    return t;
+}
+
 // Pixel of a thread.  A warp covers an 8x4 pixel block of the tile (render.py:1503-1512 uses the same
 // block per warp); inside it every QUARTER of the warp (8 lanes) covers a 4x2 sub-block:
 //   quarter q = lane>>3: x half (q&1)*4, y half (q>>1)*2; inside the quarter lane&3 -> x, (lane>>2)&1 -> y.
 // Results do not depend on which thread owns which pixel.
-__device__ __forceinline__ PixelCoord pixel_of_thread(const RasterArgs& a) {
+__device__ __forceinline__ PixelCoord pixel_of_thread(const RasterArgs& a, const TileId& tl) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane >> 3;
     PixelCoord p;
-    p.px = blockIdx.x * 16 + (warp & 1) * 8 + (q & 1) * 4 + (lane & 3);
-    p.py = blockIdx.y * 16 + (warp >> 1) * 4 + (q >> 1) * 2 + ((lane >> 2) & 1);
+    p.px = tl.x * 16 + (warp & 1) * 8 + (q & 1) * 4 + (lane & 3);
+    p.py = tl.y * 16 + (warp >> 1) * 4 + (q >> 1) * 2 + ((lane >> 2) & 1);
     p.inside = p.px < a.width && p.py < a.height;
     return p;
 }
@@ -120,8 +137,9 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ uint8_t s_list[8][4 * kListStride];   // per warp: the four quarters' survivor lists
     const int t = threadIdx.x;
-    const PixelCoord pc = pixel_of_thread(a);
-    const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
+    const TileId tl = tile_of_cta(a);
+    const PixelCoord pc = pixel_of_thread(a, tl);
+    const int tile = tl.tile;
     const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
     const int n = r1 - r0;
     const int nb = (n + kBatch - 1) / kBatch;
@@ -134,8 +152,8 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, n, 0);
 
     const float fpx = (float)pc.px, fpy = (float)pc.py;
-    const float wcx = (float)(blockIdx.x * 16 + ((t >> 5) & 1) * 8) + 3.5f;
-    const float wcy = (float)(blockIdx.y * 16 + (t >> 6) * 4) + 1.5f;
+    const float wcx = (float)(tl.x * 16 + ((t >> 5) & 1) * 8) + 3.5f;
+    const float wcy = (float)(tl.y * 16 + (t >> 6) * 4) + 1.5f;
     const int quarter = (t & 31) >> 3, warp = t >> 5;
     bool done = !pc.inside;
     float T = 1.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f;
@@ -196,7 +214,7 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
     }
     if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
     if (pc.inside) {
-        const int64_t pix = ((int64_t)blockIdx.z * a.height + pc.py) * a.width + pc.px;
+        const int64_t pix = ((int64_t)tl.view * a.height + pc.py) * a.width + pc.px;
         a.final_T[pix] = T;
         a.n_contrib[pix] = contributor;
         if (!a.training) {   // render.py:2259-2263: composite the background and clamp at inference
@@ -228,11 +246,12 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     __shared__ int s_max[8];
     __shared__ uint8_t s_list[8][4 * kListStride];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    const PixelCoord pc = pixel_of_thread(a);
-    const int tile = (blockIdx.z * a.tiles_y + blockIdx.y) * a.tiles_x + blockIdx.x;
+    const TileId tl = tile_of_cta(a);
+    const PixelCoord pc = pixel_of_thread(a, tl);
+    const int tile = tl.tile;
     const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
     const int n = r1 - r0;
-    const int64_t pix = ((int64_t)blockIdx.z * a.height + pc.py) * a.width + pc.px;
+    const int64_t pix = ((int64_t)tl.view * a.height + pc.py) * a.width + pc.px;
     // render.py:1594: list positions [0, n_contrib] took part in the forward blend
     int contributor = 0;
     float rr0 = 0.0f, rr1 = 0.0f, rr2 = 0.0f, dr0 = 0.0f, dr1 = 0.0f, dr2 = 0.0f, dTT = 0.0f;
@@ -259,8 +278,8 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, bmax, 0);
 
     const float fpx = (float)pc.px, fpy = (float)pc.py;
-    const float wcx = (float)(blockIdx.x * 16 + (warp & 1) * 8) + 3.5f;
-    const float wcy = (float)(blockIdx.y * 16 + (warp >> 1) * 4) + 1.5f;
+    const float wcx = (float)(tl.x * 16 + (warp & 1) * 8) + 3.5f;
+    const float wcy = (float)(tl.y * 16 + (warp >> 1) * 4) + 1.5f;
     const int quarter = lane >> 3;
     const bool h4 = (lane & 4) != 0, h2 = (lane & 2) != 0, h1 = (lane & 1) != 0;
     // after the butterfly, lane k of a quarter holds the quarter's total of component `slot`
@@ -391,28 +410,30 @@ int32_t fill_args(const D3gsOpConfig* cfg, RasterArgs& a) {
 
 using namespace d3gs;
 
-extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const float* records,
-                                       float* color, float* final_T, int32_t* n_contrib, uint32_t* status,
-                                       void* stream) {
+extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const int32_t* tile_order,
+                                       const float* records, float* color, float* final_T, int32_t* n_contrib,
+                                       uint32_t* status, void* stream) {
     RasterArgs a = {};
     int32_t rc = fill_args(cfg, a);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(ranges && color && final_T && n_contrib && status, "NULL argument");
     D3GS_REQUIRE(((uintptr_t)records & 15) == 0, "records must be 16-byte aligned");
     a.ranges = ranges;
+    a.tile_order = tile_order;
     a.records = reinterpret_cast<const float4*>(records);
     a.status = status;
     a.color = color;
     a.final_T = final_T;
     a.n_contrib = n_contrib;
-    dim3 grid(a.tiles_x, a.tiles_y, cfg->num_views);
+    const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
     raster_forward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("raster_forward_kernel");
     return D3GS_OK;
 }
 
 extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges,
-                                        const float* records, const int32_t* sorted_values, const float* color,
+                                        const int32_t* tile_order, const float* records,
+                                        const int32_t* sorted_values, const float* color,
                                         const float* final_T, const int32_t* n_contrib, const float* drgb,
                                         const float* dT, float* splat_grads, uint32_t* status, void* stream) {
     RasterArgs a = {};
@@ -427,6 +448,7 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
     const size_t bn = (size_t)num * cfg->num_views;
     D3GS_CUDA(cudaMemsetAsync(splat_grads, 0, bn * kGradFloats * sizeof(float), s));
     a.ranges = ranges;
+    a.tile_order = tile_order;
     a.records = reinterpret_cast<const float4*>(records);
     a.sorted_ids = sorted_values;
     a.status = status;
@@ -436,7 +458,7 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
     a.drgb = drgb;
     a.dT = dT;
     a.splat_grads = splat_grads;
-    dim3 grid(a.tiles_x, a.tiles_y, cfg->num_views);
+    const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
     raster_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("raster_backward_kernel");
     return D3GS_OK;

@@ -43,8 +43,10 @@ class GaussianSplatOpContext:
     cov2d_vecs: torch.Tensor | None = None
     sh_to_rgb_ne_0: torch.Tensor | None = None
     per_gaussian_snap: Any = None
-    # not in the reference: the sorted, contiguous 48-byte splat records the raster kernels stream
+    # not in the reference: the sorted, contiguous 48-byte splat records the raster kernels stream, and the
+    # order in which their CTAs take the tiles (longest lists first)
     splat_records: torch.Tensor | None = None
+    tile_order: torch.Tensor | None = None
 
 
 @dataclasses.dataclass
@@ -398,10 +400,13 @@ class GaussianSplatOp:
         records = torch.empty(cap * 12, dtype=f32, device=dev)[:num_rendered * 12].view(num_rendered, 12)
         _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
                                         float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")
+        tile_order = torch.empty(num_tiles, dtype=i32, device=dev)
+        _lib.check(lib.d3gs_tile_order(workload_ranges.data_ptr(), num_tiles, tile_order.data_ptr(), stream),
+                   "d3gs_tile_order")
         self._mark("pack_splats")
-        _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), records.data_ptr(),
-                                           out_color.data_ptr(), final_T.data_ptr(), n_contrib.data_ptr(),
-                                           sync.data_ptr() + 8, stream), "d3gs_raster_forward")
+        _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), tile_order.data_ptr(),
+                                           records.data_ptr(), out_color.data_ptr(), final_T.data_ptr(),
+                                           n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
         self._mark("raster_fwd")
         output = GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
                                      n_contrib=n_contrib, radii=radii)
@@ -410,7 +415,7 @@ class GaussianSplatOp:
         ctx = GaussianSplatOpContext(conic_opacity=conic_opacity, radii=radii, uvs=uvs, rgb_gaussian=rgb_gaussian,
                                      gaussian_idx_sorted=gaussian_idx_sorted, workload_ranges=workload_ranges,
                                      image_shape_wh=(W, H), depths=depths, cov2d_vecs=cov2d_vecs,
-                                     sh_to_rgb_ne_0=sh_ne0, splat_records=records)
+                                     sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order)
         return output, ctx
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
@@ -438,7 +443,7 @@ class GaussianSplatOp:
         dT = grad.dT
         if dT is not None:
             dT = dT.contiguous()
-        _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
+        _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(), _lib.ptr(ctx.tile_order),
                                             ctx.splat_records.data_ptr(), ctx.gaussian_idx_sorted.data_ptr(),
                                             out.color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,

@@ -180,20 +180,26 @@ int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges
 int32_t d3gs_pack_splats(const int32_t* sorted_values, int64_t n, const D3gsSplatContext* ctx, float alpha_eps,
                          float* records, void* stream);
 
+/* Optional schedule for the two raster launches (no counterpart in the reference, whose grid walks the tiles
+ * in index order, render.py:1380-1386): order[k] = the tile CTA k handles, tiles with the longest lists first.
+ * Raster results do not depend on it. */
+int32_t d3gs_tile_order(const int32_t* ranges, int64_t num_tiles, int32_t* order, void* stream);
+
 /* ---- K6 raster forward (render.py:1329-2316, is_bwd=False) ------------------------------- */
-/* color [B,H,W,3] (NHWC), final_T [B,H,W], n_contrib [B,H,W] */
-int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const float* records, float* color,
-                            float* final_T, int32_t* n_contrib, uint32_t* status, void* stream);
+/* color [B,H,W,3] (NHWC), final_T [B,H,W], n_contrib [B,H,W]; tile_order [B*tiles] from d3gs_tile_order or NULL */
+int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const int32_t* tile_order,
+                            const float* records, float* color, float* final_T, int32_t* n_contrib,
+                            uint32_t* status, void* stream);
 
 /* ---- K7 raster backward (render.py:1589-1676, 1774-2210) -------------------------------- */
 /* drgb [B,H,W,3], dT [B,H,W] or NULL.  The reference's four per-splat gradient tensors (duv, dconic,
  * dopacity, dcolor, render.py:1388-1401) are one packed array here so that the kernel can use 16-byte
  * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, 0 | duv x,y, 0, 0},
  * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort. */
-int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const float* records,
-                             const int32_t* sorted_values, const float* color, const float* final_T,
-                             const int32_t* n_contrib, const float* drgb, const float* dT, float* splat_grads,
-                             uint32_t* status, void* stream);
+int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const int32_t* tile_order,
+                             const float* records, const int32_t* sorted_values, const float* color,
+                             const float* final_T, const int32_t* n_contrib, const float* drgb, const float* dT,
+                             float* splat_grads, uint32_t* status, void* stream);
 
 /* ---- K8 preprocess backward (render.py:2779-3374) ---------------------------------------- */
 /* every gradient element is written (zeros for culled Gaussians); sums over the view batch */
