@@ -17,8 +17,10 @@
 namespace d3gs {
 namespace {
 
-constexpr int kRadixBits = 8;
-constexpr int kRadix = 1 << kRadixBits;
+// Digits are 8 bits wide, or 9 when that saves a pass (45 key bits: 5 passes instead of 6); the kernels are
+// templated on the width.  Tables on the host side are sized for the wider digit.
+constexpr int kMaxRadixBits = 9;
+constexpr int kMaxRadix = 1 << kMaxRadixBits;
 // 8192 pairs per CTA as 1024 threads x 8 items, one CTA per SM.  The ranking below is a chain of dependent
 // rounds, one per item, so few items per thread keep a tile's lifetime short (at a few million pairs the
 // sort is bound by latency, not by bytes), and a large tile amortises the per-tile phases (digit totals,
@@ -28,7 +30,6 @@ constexpr int kSortThreads = 1024;
 constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kSortItems = 8;
 constexpr int kSortTile = kSortThreads * kSortItems;   // 8192 pairs per CTA
-constexpr int kDigitWarps = kRadix / 32;               // warps that own one digit per thread
 constexpr int kMaxPasses = 8;
 
 constexpr uint32_t kLbAggregate = 1u << 30;
@@ -42,9 +43,11 @@ struct PassTable {
     int32_t num_passes;
 };
 
+template <int BITS>
 __global__ void __launch_bounds__(256)
 histogram_kernel(const uint64_t* __restrict__ keys, int64_t n, const __grid_constant__ PassTable pt,
-                 uint32_t* __restrict__ hist /* [passes][256] */) {
+                 uint32_t* __restrict__ hist /* [passes][radix] */) {
+    constexpr int kRadix = 1 << BITS;
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
     for (int k = threadIdx.x; k < pt.num_passes * kRadix; k += 256) s_hist[k] = 0;
     __syncthreads();
@@ -63,9 +66,11 @@ histogram_kernel(const uint64_t* __restrict__ keys, int64_t n, const __grid_cons
     }
 }
 
-// exclusive scan of each pass's 256 bins, in place; one CTA of 256 threads per pass
-__global__ void __launch_bounds__(256) digit_offsets_kernel(uint32_t* __restrict__ hist) {
-    __shared__ uint32_t s_w[8];
+// exclusive scan of each pass's bins, in place; one CTA of one thread per bin per pass
+template <int BITS>
+__global__ void __launch_bounds__(1 << BITS) digit_offsets_kernel(uint32_t* __restrict__ hist) {
+    constexpr int kRadix = 1 << BITS;
+    __shared__ uint32_t s_w[kRadix / 32];
     uint32_t* h = hist + (size_t)blockIdx.x * kRadix;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint32_t c = h[t];
@@ -88,13 +93,14 @@ __global__ void __launch_bounds__(256) digit_offsets_kernel(uint32_t* __restrict
 __device__ __forceinline__ int key_slot(int pos) { return pos + (pos >> 4); }
 __device__ __forceinline__ int val_slot(int pos) { return pos + (pos >> 5); }
 
-// Lanes of the warp that hold the same 9-bit value (digit, or kRadix for "no item"): nine ballots, one per
+// Lanes of the warp that hold the same (BITS+1)-bit value (digit, or the radix for "no item"): one ballot per
 // bit.  __match_any_sync gives the same mask, but its latency grows with the number of distinct values in
 // the warp, and with uniformly distributed digits (the low depth bits) all 32 lanes differ.
+template <int BITS>
 __device__ __forceinline__ uint32_t same_bin_lanes(uint32_t bin) {
     uint32_t peers = 0xffffffffu;
 #pragma unroll
-    for (int b = 0; b <= kRadixBits; ++b) {
+    for (int b = 0; b <= BITS; ++b) {
         const bool bit = (bin >> b) & 1u;
         const uint32_t vote = __ballot_sync(0xffffffffu, bit);
         peers &= bit ? vote : ~vote;
@@ -102,23 +108,27 @@ __device__ __forceinline__ uint32_t same_bin_lanes(uint32_t bin) {
     return peers;
 }
 
+template <int BITS>
 struct SweepSmem {
+    static constexpr int kRadix = 1 << BITS;
     uint64_t keys[kSortTile + kSortTile / 16];
     int32_t vals[kSortTile + kSortTile / 32];
     uint32_t warp_hist[kSortWarps][kRadix + 1];
     uint32_t digit_off[kRadix + 1];
     int64_t global_base[kRadix];
-    uint32_t scan_tmp[kDigitWarps];
+    uint32_t scan_tmp[kRadix / 32];
     uint32_t tile;
 };
 
+template <int BITS>
 __global__ void __launch_bounds__(kSortThreads, 1)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
                 const int32_t* __restrict__ vals_in, int32_t* __restrict__ vals_out, int64_t n, int shift,
                 uint32_t mask, const uint32_t* __restrict__ digit_base, uint32_t* __restrict__ ticket,
-                uint32_t* __restrict__ lookback /* [tiles][256] */, uint32_t* __restrict__ status) {
+                uint32_t* __restrict__ lookback /* [tiles][radix] */, uint32_t* __restrict__ status) {
+    constexpr int kRadix = 1 << BITS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    SweepSmem& sm = *reinterpret_cast<SweepSmem*>(smem_raw);
+    SweepSmem<BITS>& sm = *reinterpret_cast<SweepSmem<BITS>*>(smem_raw);
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     if (t == 0) sm.tile = atomicAdd(ticket, 1u);
     for (int k = t; k < kSortWarps * (kRadix + 1); k += kSortThreads) (&sm.warp_hist[0][0])[k] = 0;
@@ -143,7 +153,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ key
     for (int i = 0; i < kSortItems; ++i) {
         const int local = warp * (32 * kSortItems) + i * 32 + lane;
         const uint32_t bin = (local < count) ? (uint32_t)((key[i] >> shift) & mask) : (uint32_t)kRadix;
-        const uint32_t peers = same_bin_lanes(bin);
+        const uint32_t peers = same_bin_lanes<BITS>(bin);
         const uint32_t pre = sm.warp_hist[warp][bin];
         __syncwarp();
         if (lane == __ffs(peers) - 1) sm.warp_hist[warp][bin] = pre + __popc(peers);
@@ -153,7 +163,7 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ key
     __syncthreads();
 
     // ---- per-digit tile counts, publish, look back ---------------------------------------------
-    const int d = t;   // the first 256 threads own one digit each
+    const int d = t;   // the first `radix` threads own one digit each
     uint32_t tot = 0, inc = 0;
     uint32_t* my = lookback + (size_t)tile * kRadix + (d < kRadix ? d : 0);
     if (d < kRadix) {
@@ -260,12 +270,62 @@ SortLayout sort_layout(int64_t n) {
     SortLayout L;
     L.tiles = div_up64(n > 0 ? n : 1, kSortTile);
     L.hist_off = 0;
-    L.ticket_off = L.hist_off + sizeof(uint32_t) * kMaxPasses * kRadix;
+    L.ticket_off = L.hist_off + sizeof(uint32_t) * kMaxPasses * kMaxRadix;
     L.lookback_off = L.ticket_off + 256;
     // one look-back table per pass, all cleared by the single memset at the start: no memset node between
     // two passes' kernels
-    L.total = L.lookback_off + (size_t)kMaxPasses * L.tiles * kRadix * sizeof(uint32_t);
+    L.total = L.lookback_off + (size_t)kMaxPasses * L.tiles * kMaxRadix * sizeof(uint32_t);
     return L;
+}
+
+}  // namespace
+}  // namespace d3gs
+
+namespace d3gs {
+namespace {
+
+// 9-bit digits when they save a pass, 8-bit digits otherwise
+int digit_bits(int key_bits) {
+    return (key_bits + 8) / 9 < (key_bits + 7) / 8 ? 9 : 8;
+}
+
+template <int BITS>
+int32_t run_sort(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int32_t* values_alt, int64_t n, int begin_bit,
+                 int end_bit, int passes, const SortLayout& L, char* ws, uint32_t* status, cudaStream_t s) {
+    constexpr int kRadix = 1 << BITS;
+    uint32_t* hist = reinterpret_cast<uint32_t*>(ws + L.hist_off);
+    uint32_t* tickets = reinterpret_cast<uint32_t*>(ws + L.ticket_off);
+    uint32_t* lookback = reinterpret_cast<uint32_t*>(ws + L.lookback_off);
+    PassTable pt;
+    pt.num_passes = passes;
+    for (int p = 0; p < kMaxPasses; ++p) {
+        const int sh = begin_bit + p * BITS;
+        const int bits = p < passes ? (end_bit - sh < BITS ? end_bit - sh : BITS) : 0;
+        pt.shift[p] = p < passes ? sh : 0;
+        pt.mask[p] = bits > 0 ? ((1u << bits) - 1u) : 0u;
+    }
+    D3GS_CUDA(cudaFuncSetAttribute(onesweep_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)sizeof(SweepSmem<BITS>)));
+    const size_t lb_pass = (size_t)L.tiles * kRadix;         // look-back words per pass
+    D3GS_CUDA(cudaMemsetAsync(ws, 0, L.lookback_off + (size_t)passes * lb_pass * sizeof(uint32_t), s));
+    int hist_blocks = (int)(L.tiles < 148 * 8 ? L.tiles : 148 * 8);
+    histogram_kernel<BITS><<<hist_blocks, 256, 0, s>>>(keys, n, pt, hist);
+    D3GS_LAUNCH_CHECK("histogram_kernel");
+    digit_offsets_kernel<BITS><<<passes, kRadix, 0, s>>>(hist);
+    D3GS_LAUNCH_CHECK("digit_offsets_kernel");
+    uint64_t* kin = keys;
+    uint64_t* kout = keys_alt;
+    int32_t* vin = values;
+    int32_t* vout = values_alt;
+    for (int p = 0; p < passes; ++p) {
+        onesweep_kernel<BITS><<<(unsigned)L.tiles, kSortThreads, sizeof(SweepSmem<BITS>), s>>>(
+            kin, kout, vin, vout, n, pt.shift[p], pt.mask[p], hist + (size_t)p * kRadix, tickets + p,
+            lookback + (size_t)p * lb_pass, status);
+        D3GS_LAUNCH_CHECK("onesweep_kernel");
+        uint64_t* tk = kin; kin = kout; kout = tk;
+        int32_t* tv = vin; vin = vout; vout = tv;
+    }
+    return D3GS_OK;
 }
 
 }  // namespace
@@ -285,7 +345,8 @@ extern "C" int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* 
     D3GS_REQUIRE(n >= 0, "negative pair count");
     D3GS_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit <= end_bit, "bad bit range [%d,%d)", begin_bit, end_bit);
     D3GS_REQUIRE(result_in_alt != nullptr && status != nullptr, "result_in_alt/status is NULL");
-    const int passes = (end_bit - begin_bit + kRadixBits - 1) / kRadixBits;
+    const int bits = digit_bits(end_bit - begin_bit);
+    const int passes = (end_bit - begin_bit + bits - 1) / bits;
     *result_in_alt = passes & 1;
     if (n == 0 || passes == 0) {
         *result_in_alt = 0;
@@ -296,40 +357,10 @@ extern "C" int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* 
     const SortLayout L = sort_layout(n);
     D3GS_REQUIRE(workspace_bytes >= L.total, "sort workspace too small: %zu < %zu", workspace_bytes, L.total);
     D3GS_REQUIRE(((uintptr_t)workspace & 15) == 0, "sort workspace must be 16-byte aligned");
-    cudaStream_t s = (cudaStream_t)stream;
     char* ws = reinterpret_cast<char*>(workspace);
-    uint32_t* hist = reinterpret_cast<uint32_t*>(ws + L.hist_off);
-    uint32_t* tickets = reinterpret_cast<uint32_t*>(ws + L.ticket_off);
-    uint32_t* lookback = reinterpret_cast<uint32_t*>(ws + L.lookback_off);
-
-    PassTable pt;
-    pt.num_passes = passes;
-    for (int p = 0; p < kMaxPasses; ++p) {
-        const int sh = begin_bit + p * kRadixBits;
-        const int bits = p < passes ? (end_bit - sh < kRadixBits ? end_bit - sh : kRadixBits) : 0;
-        pt.shift[p] = p < passes ? sh : 0;
-        pt.mask[p] = bits > 0 ? ((1u << bits) - 1u) : 0u;
-    }
-    D3GS_CUDA(cudaFuncSetAttribute(onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)sizeof(SweepSmem)));
-    const size_t lb_pass = (size_t)L.tiles * kRadix;         // look-back words per pass
-    D3GS_CUDA(cudaMemsetAsync(ws, 0, L.lookback_off + (size_t)passes * lb_pass * sizeof(uint32_t), s));
-    int hist_blocks = (int)(L.tiles < 148 * 8 ? L.tiles : 148 * 8);
-    histogram_kernel<<<hist_blocks, 256, 0, s>>>(keys, n, pt, hist);
-    D3GS_LAUNCH_CHECK("histogram_kernel");
-    digit_offsets_kernel<<<passes, 256, 0, s>>>(hist);
-    D3GS_LAUNCH_CHECK("digit_offsets_kernel");
-    uint64_t* kin = keys;
-    uint64_t* kout = keys_alt;
-    int32_t* vin = values;
-    int32_t* vout = values_alt;
-    for (int p = 0; p < passes; ++p) {
-        onesweep_kernel<<<(unsigned)L.tiles, kSortThreads, sizeof(SweepSmem), s>>>(
-            kin, kout, vin, vout, n, pt.shift[p], pt.mask[p], hist + (size_t)p * kRadix, tickets + p,
-            lookback + (size_t)p * lb_pass, status);
-        D3GS_LAUNCH_CHECK("onesweep_kernel");
-        uint64_t* tk = kin; kin = kout; kout = tk;
-        int32_t* tv = vin; vin = vout; vout = tv;
-    }
-    return D3GS_OK;
+    if (bits == 9)
+        return run_sort<9>(keys, keys_alt, values, values_alt, n, begin_bit, end_bit, passes, L, ws, status,
+                           (cudaStream_t)stream);
+    return run_sort<8>(keys, keys_alt, values, values_alt, n, begin_bit, end_bit, passes, L, ws, status,
+                       (cudaStream_t)stream);
 }
