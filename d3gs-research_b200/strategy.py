@@ -100,7 +100,6 @@ class GaussianStrategyOrigin:
         origin/strategy.py:286 (tests); ``generator`` seeds that draw (identical on every rank of a
         data-parallel job)."""
         import ctypes as C
-        from .model import FLAT_ORDER, flat_layout
         lib = _lib.load()
         n, dev = len(model), model.xyz.device
         assert model.color_sh_base is not None, "refinement is built for the split SH layout (color_sh_base + color_sh)"
