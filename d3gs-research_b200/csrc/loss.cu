@@ -68,20 +68,35 @@ struct SsimArgs {
 // once; a register-staged loop had one load per thread in flight and was bound by DRAM latency.
 __device__ __forceinline__ void load_halo(float (*s)[kHY][kSX], const float* img, bool nhwc, int b, int by, int bx,
                                           int height, int width, int t) {
-    const int64_t plane = (int64_t)height * width;
+    // Every thread keeps one fixed column (and channel / row-in-group) and walks down the rows, so that the
+    // per-element work is an add and a compare instead of index divisions.
+    static_assert(kThreads >= kHX * 3, "one thread per element of a 42-pixel, 3-channel row");
     if (nhwc) {
-        for (int k = t; k < kHY * kHX * 3; k += kThreads) {
-            const int ly = k / (kHX * 3), r = k - ly * (kHX * 3), lx = r / 3, c = r - lx * 3;
-            const int gy = by + ly - kPad, gx = bx + lx - kPad;
-            const bool ok = gy >= 0 && gy < height && gx >= 0 && gx < width;
-            cp_async4(&s[c][ly][lx], ok ? img + (((int64_t)b * height + gy) * width + gx) * 3 + c : img, ok);
+        if (t < kHX * 3) {   // thread = one float of the 126-float row
+            const int lx = t / 3, c = t - lx * 3, gx = bx + lx - kPad;
+            const bool col_ok = gx >= 0 && gx < width;
+            const float* src = img + (((int64_t)b * height + (by - kPad)) * width + gx) * 3 + c;
+            float* dst = &s[c][0][lx];
+            for (int ly = 0; ly < kHY; ++ly) {
+                const int gy = by + ly - kPad;
+                const bool ok = col_ok && gy >= 0 && gy < height;
+                cp_async4(dst, ok ? src : img, ok);
+                src += (int64_t)width * 3;
+                dst += kSX;
+            }
         }
     } else {
-        for (int k = t; k < 3 * kHY * kHX; k += kThreads) {
-            const int c = k / (kHY * kHX), r = k - c * (kHY * kHX), ly = r / kHX, lx = r - ly * kHX;
-            const int gy = by + ly - kPad, gx = bx + lx - kPad;
-            const bool ok = gy >= 0 && gy < height && gx >= 0 && gx < width;
-            cp_async4(&s[c][ly][lx], ok ? img + ((int64_t)b * 3 + c) * plane + (int64_t)gy * width + gx : img, ok);
+        if (t < kHX * 3) {   // thread = one column of one of three consecutive rows
+            const int r3 = t / kHX, lx = t - r3 * kHX, gx = bx + lx - kPad;
+            const bool col_ok = gx >= 0 && gx < width;
+            for (int c = 0; c < 3; ++c) {
+                const float* plane0 = img + ((int64_t)b * 3 + c) * height * width;
+                for (int ly = r3; ly < kHY; ly += 3) {
+                    const int gy = by + ly - kPad;
+                    const bool ok = col_ok && gy >= 0 && gy < height;
+                    cp_async4(&s[c][ly][lx], ok ? plane0 + (int64_t)gy * width + gx : img, ok);
+                }
+            }
         }
     }
     for (int k = t; k < 3 * kHY * (kSX - kHX); k += kThreads) {   // the float4 loads touch the row padding

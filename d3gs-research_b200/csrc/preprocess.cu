@@ -17,12 +17,19 @@ struct TileGeom {
     float ts;
 };
 
+// x / ts for the tile size 16 (the only one the entry points accept): a division by a power of two and the
+// multiplication by its reciprocal round to the same float, and the multiplication is one instruction
+// instead of the ~10 of an IEEE division.
+__device__ __forceinline__ float div_ts(float x, const TileGeom& tg) {
+    return tg.ts == 16.0f ? x * 0.0625f : x / tg.ts;
+}
+
 __device__ __forceinline__ void tile_rect(const TileGeom& tg, float u, float v, float radius, int* rmin, int* rmax) {
     // render.py:472-473: clamp(int((uv -/+ r (+ 15)) / 16), 0, tiles); max is exclusive
-    rmin[0] = clampi(f2i_sat((u - radius) / tg.ts), 0, tg.tiles_x);
-    rmin[1] = clampi(f2i_sat((v - radius) / tg.ts), 0, tg.tiles_y);
-    rmax[0] = clampi(f2i_sat((u + radius + tg.ts - 1.0f) / tg.ts), 0, tg.tiles_x);
-    rmax[1] = clampi(f2i_sat((v + radius + tg.ts - 1.0f) / tg.ts), 0, tg.tiles_y);
+    rmin[0] = clampi(f2i_sat(div_ts(u - radius, tg)), 0, tg.tiles_x);
+    rmin[1] = clampi(f2i_sat(div_ts(v - radius, tg)), 0, tg.tiles_y);
+    rmax[0] = clampi(f2i_sat(div_ts(u + radius + tg.ts - 1.0f, tg)), 0, tg.tiles_x);
+    rmax[1] = clampi(f2i_sat(div_ts(v + radius + tg.ts - 1.0f, tg)), 0, tg.tiles_y);
 }
 
 struct Obb {
@@ -103,10 +110,10 @@ struct TileWalk {
         }
         float bound = 2.0f * act_log(alpha_eps / opacity);
         ellipse_bound_aabb(ca, cb, cc, bound, half);
-        bmin[0] = clampi(f2i_sat((u - half[0]) / tg.ts), 0, tg.tiles_x);
-        bmin[1] = clampi(f2i_sat((v - half[1]) / tg.ts), 0, tg.tiles_y);
-        bmax[0] = clampi(f2i_sat(ceilf((u + half[0]) / tg.ts)), 0, tg.tiles_x);
-        bmax[1] = clampi(f2i_sat(ceilf((v + half[1]) / tg.ts)), 0, tg.tiles_y);
+        bmin[0] = clampi(f2i_sat(div_ts(u - half[0], tg)), 0, tg.tiles_x);
+        bmin[1] = clampi(f2i_sat(div_ts(v - half[1], tg)), 0, tg.tiles_y);
+        bmax[0] = clampi(f2i_sat(ceilf(div_ts(u + half[0], tg))), 0, tg.tiles_x);
+        bmax[1] = clampi(f2i_sat(ceilf(div_ts(v + half[1], tg))), 0, tg.tiles_y);
         ox = u - (float)bmin[0] * tg.ts;
         oy = v - (float)bmin[1] * tg.ts;
         obb = ellipse_bound_obb(ca, cb, cc, bound);

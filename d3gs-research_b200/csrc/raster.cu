@@ -162,14 +162,13 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
 
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
-        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, n, b + 1);
         if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
-        // whole-tile early exit (render.py:1691-1694); an in-flight prefetch is drained first
+        // The one barrier of a batch: batch b has arrived for everybody, everybody has finished batch b-1
+        // (so the other buffer may be refilled), and the whole-tile early exit is decided (render.py:1691-1694).
+        // No copy is in flight here: the next one is issued below.
         const int num_done = __syncthreads_count(done || copy_failed);
-        if (num_done == 256) {
-            if (b + 1 < nb) mbar_wait_bounded(&s_bar[cur ^ 1], (uint32_t)(((b + 1) >> 1) & 1));
-            break;
-        }
+        if (num_done == 256) break;
+        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, n, b + 1);
         const int cnt = min(kBatch, n - b * kBatch);
         const float4* rec = s_rec[cur];
         // Cull the whole batch first, then every quarter (8 lanes, a 4x2 pixel sub-block) walks its own
@@ -210,7 +209,6 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
                 C2 = upd ? f_fma(w, q2.z, C2) : C2;
             }
         }
-        __syncthreads();   // everyone is done reading s_rec[cur] before it is refilled
     }
     if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
     if (pc.inside) {
@@ -286,19 +284,18 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
     const int slot = (h4 ? 4 : 0) + (h2 ? 2 : 0) + (h1 ? 1 : 0);
     float T = 1.0f;
     bool copy_failed = false;
+#pragma unroll
+    for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;   // row t is zeroed again by its owner after every flush
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
+        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        // First barrier of the batch: batch b has arrived for everybody and everybody has flushed and zeroed
+        // its accumulator row of batch b-1, so the other record buffer may be refilled.  No copy is in flight.
+        if (__syncthreads_or(copy_failed)) break;
         if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
         const int cnt = min(kBatch, bmax - b * kBatch);
         int32_t my_id = 0;
         if (t < cnt) my_id = a.sorted_ids[r0 + b * kBatch + t];
-#pragma unroll
-        for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;
-        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
-        if (__syncthreads_or(copy_failed)) {
-            if (b + 1 < nb) mbar_wait_bounded(&s_bar[cur ^ 1], (uint32_t)(((b + 1) >> 1) & 1));
-            break;
-        }
         const float4* rec = s_rec[cur];
         const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
         const int ng = (wlim + 31) >> 5;
@@ -382,9 +379,10 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
                 red_add_v4(dst, g0, g1, g2, g3);
                 red_add_v4(dst + 4, g4, g5, g6, 0.0f);
                 red_add_v2(dst + 8, g7, g8);
+#pragma unroll
+                for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;
             }
         }
-        __syncthreads();
     }
     if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
 }
