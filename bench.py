@@ -426,7 +426,7 @@ def main():
                       "all ranks' parameters" if trainer._peerset is not None else
                       "sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded else
                       "replicated after all-reduce")
-    launches_per_step = 19 if trainer.fused_adam else 20
+    launches_per_step = 18 if trainer.fused_adam else 19
     trainer.close()    # unmap the peer buffers (collective) before the process group goes away
     if rank != 0:
         if world > 1:
