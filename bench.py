@@ -196,12 +196,13 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
     K sort pairs, P pixels, Tn tiles."""
     passes = 6
     table = {
-        "preprocess_fwd": 44 * N + 192 * V + 8 * N + 53 * V,
+        "preprocess_fwd": 44 * N + 192 * V + 8 * N + 53 * V + 48 * V,   # + the 48-byte raster record per visible Gaussian
         "scan": 8 * N,
         "duplicate_keys": 8 * N + 28 * V + 12 * K,
         "sort": (8 + 24 * passes) * K,
         "tile_ranges": 8 * K + 8 * Tn,
-        "pack_splats": (4 + 40 + 48) * K,
+        "pack_splats": (4 + 40 + 48) * K,   # only when the records are packed per pair (GaussianSplatOp.gather_records off)
+        "tile_order": 16 * Tn,
         "raster_fwd": 48 * K + 8 * Tn + 20 * P,
         "l1_dssim": 24 * P + 12 * P,
         "raster_bwd": 48 * K + 36 * P + 36 * K,
@@ -362,7 +363,11 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), info
+        # only two numbers of the last step leave the loop: a returned `info` would keep that step's buffers alive
+        # through the next timed loop as a third generation beside the two the loop itself holds, and the caching
+        # allocator would have to cudaMalloc them (a 7-22 ms stall, seen in one run out of four)
+        counts = (int(info["num_rendered"]), int((info["out"].radii > 0).sum().item()))
+        return float(t.item()), counts
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -393,8 +398,9 @@ def main():
     for _ in range(3):      # the same pattern once more after the snapshot's allocations
         info = trainer.step(cam, target_dev)
     restore()
+    info = None    # the timed loops hold two generations of step buffers, like the warm-up: no third one from here
     sampler.begin()
-    ms_total, info = timed(args.steps, e2e=False, sample_clocks=rank == 0)
+    ms_total, (K, V) = timed(args.steps, e2e=False, sample_clocks=rank == 0)
     clocks = sampler.stop() if rank == 0 else None
     restore()
     ms_e2e, _ = timed(args.steps, e2e=True)
@@ -414,8 +420,6 @@ def main():
         dist.all_reduce(c_lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(c_hi, op=dist.ReduceOp.MAX)
         replicas_agree = bool((c_lo == c_hi).item())
-    K = int(info["num_rendered"])
-    V = int((info["out"].radii > 0).sum().item())
     P, Tn = W * H, ((W + 15) // 16) * ((H + 15) // 16)
     views = world
     value = views * args.steps / (ms_total / 1e3)
@@ -426,7 +430,7 @@ def main():
                       "all ranks' parameters" if trainer._peerset is not None else
                       "sharded: reduce-scatter, Adam on 1/N slice, all-gather" if trainer.sharded else
                       "replicated after all-reduce")
-    launches_per_step = 18 if trainer.fused_adam else 19
+    launches_per_step = 17 if trainer.fused_adam else 18
     trainer.close()    # unmap the peer buffers (collective) before the process group goes away
     if rank != 0:
         if world > 1:

@@ -48,7 +48,7 @@ class ModelGrad(C.Structure):
 class SplatContext(C.Structure):
     _fields_ = [("tiles_touched", C.c_void_p), ("radii", C.c_void_p), ("depths", C.c_void_p), ("uvs", C.c_void_p),
                 ("conic_opacity", C.c_void_p), ("rgb_gaussian", C.c_void_p), ("cov2d_vecs", C.c_void_p),
-                ("sh_to_rgb_ne_0", C.c_void_p), ("tile_mask", C.c_void_p)]
+                ("sh_to_rgb_ne_0", C.c_void_p), ("tile_mask", C.c_void_p), ("records", C.c_void_p)]
 
 
 class AdamSegment(C.Structure):
@@ -108,8 +108,8 @@ SIGNATURES = {
     "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
     "d3gs_tile_order": (_I32, [_P, _I64, _P, _P]),
-    "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P]),
-    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
                                         C.POINTER(ModelGrad), _P]),
     "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),

@@ -185,23 +185,11 @@ pack_splats_kernel(const int32_t* __restrict__ ids, int64_t n, const float* __re
     const float2 uv = __ldg(reinterpret_cast<const float2*>(uvs) + id);
     const float4 co = __ldg(reinterpret_cast<const float4*>(conic_opacity) + id);
     const float r = __ldg(rgb + (int64_t)id * 3), g = __ldg(rgb + (int64_t)id * 3 + 1), b = __ldg(rgb + (int64_t)id * 3 + 2);
-    float thr = -1.0e30f, hx = 1.0e30f, hy = 1.0e30f;
-    if (co.w > alpha_eps && co.w < 1.0e30f) {
-        thr = act_log(alpha_eps / co.w) - 0.01f;
-        // {a dx^2 + 2 b dx dy + c dy^2 <= R}, R = -2 thr: |dx| <= sqrt(R c / det), |dy| <= sqrt(R a / det)
-        const float det = co.x * co.z - co.y * co.y;
-        // Very elongated splats (a*c >> det) are left unculled: there the float evaluation of `power`
-        // cancels heavily and can exceed thr slightly outside the exact box.  Up to a*c/det = 1e3 the
-        // rounding error of power stays below 1e-3, a tenth of the 0.01 margin built into thr.
-        if (det > 0.0f && co.x * co.z < 1.0e3f * det) {
-            const float R = -2.0f * thr;
-            hx = sqrtf(R * co.z / det) * 1.0005f + 0.02f + 3.5f;
-            hy = sqrtf(R * co.x / det) * 1.0005f + 0.02f + 1.5f;
-        }
-    }
-    rec[i * 3] = make_float4(uv.x, uv.y, hx, hy);
-    rec[i * 3 + 1] = make_float4(-0.5f * co.x, -co.y, -0.5f * co.z, co.w);
-    rec[i * 3 + 2] = make_float4(r, g, b, thr);
+    float4 r0, r1, r2;
+    make_splat_record(uv, co, r, g, b, alpha_eps, r0, r1, r2);
+    rec[i * 3] = r0;
+    rec[i * 3 + 1] = r1;
+    rec[i * 3 + 2] = r2;
 }
 
 }  // namespace

@@ -117,6 +117,33 @@ __device__ __forceinline__ float blend_power(float ha, float nb, float hc, float
     return f_fma(t, dx, f_mul(u, dy));
 }
 
+// The 48-byte record the raster kernels read for a splat: [u v hx hy][ha nb hc o][r g b thr], where
+// (ha, nb, hc) = (-0.5 a, -b, -0.5 c) of the conic.  thr is a lower bound of the `power` at which the splat
+// still reaches alpha_eps: power < thr  =>  opacity*exp(power) < 0.99*alpha_eps, so the blend loop may skip
+// such a pixel without changing any result.  (hx, hy) are the half extents of the axis-aligned box around
+// {power >= thr}, slightly inflated and widened by the half size of an 8x4 pixel block (3.5, 1.5): a block
+// whose centre is further than (hx, hy) from (u, v) contains no pixel that the splat can touch.
+__device__ __forceinline__ void make_splat_record(float2 uv, float4 co, float r, float g, float b, float alpha_eps,
+                                                  float4& rec0, float4& rec1, float4& rec2) {
+    float thr = -1.0e30f, hx = 1.0e30f, hy = 1.0e30f;
+    if (co.w > alpha_eps && co.w < 1.0e30f) {
+        thr = act_log(alpha_eps / co.w) - 0.01f;
+        // {a dx^2 + 2 b dx dy + c dy^2 <= R}, R = -2 thr: |dx| <= sqrt(R c / det), |dy| <= sqrt(R a / det)
+        const float det = co.x * co.z - co.y * co.y;
+        // Very elongated splats (a*c >> det) are left unculled: there the float evaluation of `power`
+        // cancels heavily and can exceed thr slightly outside the exact box.  Up to a*c/det = 1e3 the
+        // rounding error of power stays below 1e-3, a tenth of the 0.01 margin built into thr.
+        if (det > 0.0f && co.x * co.z < 1.0e3f * det) {
+            const float R = -2.0f * thr;
+            hx = sqrtf(R * co.z / det) * 1.0005f + 0.02f + 3.5f;
+            hy = sqrtf(R * co.x / det) * 1.0005f + 0.02f + 1.5f;
+        }
+    }
+    rec0 = make_float4(uv.x, uv.y, hx, hy);
+    rec1 = make_float4(-0.5f * co.x, -co.y, -0.5f * co.z, co.w);
+    rec2 = make_float4(r, g, b, thr);
+}
+
 // ---- Adam (d3sim/csrc/optim.py:22-49), shared by the optimizer kernels and the fused backward -------------
 // per-tensor scalars with the uniform divisions hoisted out of the element loop
 struct SegConst {
@@ -221,6 +248,10 @@ __device__ __forceinline__ void cp_async4(void* dst_smem, const void* src_gmem, 
                  : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// 16-byte asynchronous global -> shared copy through L2 (both addresses 16-byte aligned)
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;

@@ -444,9 +444,19 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
     for (int ch = 0; ch < 3; ++ch) c3[ch] = c3[ch] + 0.5f;
     if (a.ctx.sh_to_rgb_ne_0 != nullptr)
         a.ctx.sh_to_rgb_ne_0[i] = (uint8_t)(((c3[0] < 0.0f) << 2) | ((c3[1] < 0.0f) << 1) | (c3[2] < 0.0f));
-    a.ctx.rgb_gaussian[i * 3] = fmaxf(c3[0], 0.0f);
-    a.ctx.rgb_gaussian[i * 3 + 1] = fmaxf(c3[1], 0.0f);
-    a.ctx.rgb_gaussian[i * 3 + 2] = fmaxf(c3[2], 0.0f);
+    const float cr = fmaxf(c3[0], 0.0f), cg = fmaxf(c3[1], 0.0f), cb = fmaxf(c3[2], 0.0f);
+    a.ctx.rgb_gaussian[i * 3] = cr;
+    a.ctx.rgb_gaussian[i * 3 + 1] = cg;
+    a.ctx.rgb_gaussian[i * 3 + 2] = cb;
+    if (a.ctx.records != nullptr) {
+        // the raster record of this Gaussian (this thread wrote uv and the conic above)
+        const float2 uv = *reinterpret_cast<const float2*>(a.ctx.uvs + i * 2);
+        const float4 co = *reinterpret_cast<const float4*>(a.ctx.conic_opacity + i * 4);
+        float4 r0, r1, r2;
+        make_splat_record(uv, co, cr, cg, cb, cf.alpha_eps, r0, r1, r2);
+        float4* dst = reinterpret_cast<float4*>(a.ctx.records) + i * 3;
+        dst[0] = r0; dst[1] = r1; dst[2] = r2;
+    }
 }
 
 struct DupArgs {
@@ -574,6 +584,7 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
                  "context tensor pointer is NULL");
     D3GS_REQUIRE(((uintptr_t)ctx->uvs & 7) == 0 && ((uintptr_t)ctx->conic_opacity & 15) == 0,
                  "uvs / conic_opacity must be 8 / 16-byte aligned");
+    D3GS_REQUIRE(((uintptr_t)ctx->records & 15) == 0, "records must be 16-byte aligned");
     D3GS_REQUIRE(!cfg->training || (ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0),
                  "training needs cov2d_vecs and sh_to_rgb_ne_0");
     const int64_t total = model->num * cfg->num_views;

@@ -78,6 +78,21 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
         mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
         bulk_copy_g2s(s_in, a.model.sh_rest + g0 * 45, (uint32_t)rows * 180u, &s_bar);
     }
+    if (ADAM && t >= 32 && t < 32 + 15) {
+        // The optimizer sweep at the end of the kernel reads parameters and both moments of the five small fields
+        // one field after the other, a dependent DRAM round trip each: ask for these 15 spans (1-4 KB each) now,
+        // so that they sit in L2 when the sweep gets there.  (Prefetching the 45-coefficient spans as well made
+        // the kernel slower: 444 resident CTAs x 138 KB no longer fit beside the streaming traffic.)
+        const int j = t - 32, fld = j % 5, arr = j / 5;
+        const int per = fld == 1 ? 4 : fld == 3 ? 1 : 3;
+        const float* base = arr == 1 ? a.exp_avg[fld] : arr == 2 ? a.exp_avg_sq[fld]
+                          : fld == 0 ? a.model.xyz : fld == 1 ? a.model.quaternion_xyzw : fld == 2 ? a.model.scale
+                          : fld == 3 ? a.model.opacity : a.model.sh_base;
+        const float* ptr = base + g0 * per;
+        const uint32_t bytes = (uint32_t)(rows * per) * 4u;
+        if ((bytes & 15u) == 0 && ((uintptr_t)ptr & 15) == 0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+    }
     __syncthreads();
     if constexpr (NR3 > 0) {
         if (bulk_in) {

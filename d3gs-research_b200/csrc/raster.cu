@@ -1,25 +1,26 @@
 // K6 raster forward and K7 raster backward: per-tile front-to-back alpha blending.
 //
 // Reference semantics: d3sim/algos/d3gs/render.py:1329-2316 (forward is_bwd=False; backward
-// 1589-1676 + 1774-2210).  One CTA of 256 threads per 16x16 tile, one pixel per thread, pixels laid
-// out 8x4 per warp (render.py:1503-1512).
+// 1589-1676 + 1774-2210).  One CTA per 16x16 tile like the reference, but four warps of 8x8 pixels with TWO
+// pixels per lane instead of eight warps of 8x4 pixels with one (render.py:1503-1512).
 //
 // What is different from the reference's kernel, and why:
-//  * The tile's sorted list of 48-byte splat records is streamed through shared memory with bulk
-//    async copies (cp.async.bulk + mbarrier, double buffered) instead of per-thread gathers
-//    (render.py:1699-1716).
-//  * Both kernels were instruction-issue bound when every warp walked every record.  Now the 32
-//    lanes of a warp first test 32 records at once (each record carries a conservative bounding
-//    box of its alpha >= 1/255 region) against the four 4x2 sub-blocks of the warp's 8x4 pixel
-//    block, ballot, and append the survivors of every sub-block to a compact index list in shared
-//    memory.  Then every QUARTER of the warp walks only the list of its own sub-block, front to
-//    back: one pass of the instruction stream serves up to four records.  The forward pass body is
-//    branch free (selects and predicates), which is cheaper than votes and divergent branches
-//    when nearly every pass has a contributing pixel.
-//  * Backward: the nine per-splat partial derivatives are reduced inside each quarter with a
-//    transposing butterfly (10 shuffles for four records instead of 45 for one), accumulated per
-//    CTA in shared memory, and leave the CTA as three vector atomic adds per (tile, splat) instead
-//    of the reference's nine scalar atomics per warp (render.py:2061-2148).
+//  * The tile's sorted list of 48-byte splat records is staged through shared memory in batches, double
+//    buffered, either with one bulk async copy per batch (cp.async.bulk + mbarrier) when the records were
+//    packed per (tile, splat) pair beforehand, or with per-thread 16-byte async gathers by sorted id from the
+//    per-Gaussian record table the preprocess writes (render.py:1699-1716 gathers per thread, synchronously).
+//  * Both kernels were instruction-issue bound when every warp walked every record.  The 32 lanes of a warp
+//    first test 32 records at once (each record carries a conservative bounding box of its
+//    alpha >= 1/255 region) against the eight 4x2 sub-blocks of the warp's 8x8 pixel block, ballot, and
+//    append the survivors of every sub-block to a compact index list in shared memory.  Then every GROUP
+//    of four lanes walks only the list of its own sub-block, front to back: one pass of the instruction
+//    stream serves up to eight records.  The pass bodies are branch free (selects and predicates), which
+//    is cheaper than votes and divergent branches when nearly every pass has a contributing pixel.
+//  * A lane owns two horizontally adjacent pixels and uses the packed fp32 instructions of sm_100 (see below).
+//  * Backward: the nine per-splat partial sums are reduced inside each group with a transposing butterfly
+//    (8 shuffles for eight records instead of 45 for one), accumulated per CTA in shared memory, and leave
+//    the CTA as three vector atomic adds per (tile, splat) instead of the reference's nine scalar atomics
+//    per warp (render.py:2061-2148).
 //
 // The arithmetic that decides n_contrib -- power, exp, alpha, the transmittance product and the
 // three threshold compares -- is written with explicit round-to-nearest intrinsics so that its
@@ -30,7 +31,6 @@
 namespace d3gs {
 namespace {
 
-constexpr int kBatch = 256;                        // records per staged batch
 constexpr int kRecFloat4 = 3;                      // 48 bytes: [u v hx hy][ha nb hc o][r g b thr]
 constexpr uint32_t kRecBytes = kRecFloat4 * 16;
 constexpr int kGradFloats = D3GS_SPLAT_GRAD_FLOATS;   // 12: [dconic a b c, dopacity][dcolor r g b, 0][duv x y, 0 0]
@@ -55,11 +55,6 @@ struct RasterArgs {
     float* splat_grads;
 };
 
-struct PixelCoord {
-    int px, py;
-    bool inside;
-};
-
 // The tile a CTA works on.  The grid is one-dimensional; with an order table the CTAs take the tiles by
 // decreasing list length, so that the last CTAs to start are the cheapest and the grid ends without a tail.
 struct TileId {
@@ -76,20 +71,69 @@ __device__ __forceinline__ TileId tile_of_cta(const RasterArgs& a) {
     return t;
 }
 
-// Pixel of a thread.  A warp covers an 8x4 pixel block of the tile (render.py:1503-1512 uses the same
-// block per warp); inside it every QUARTER of the warp (8 lanes) covers a 4x2 sub-block:
-//   quarter q = lane>>3: x half (q&1)*4, y half (q>>1)*2; inside the quarter lane&3 -> x, (lane>>2)&1 -> y.
-// Results do not depend on which thread owns which pixel.
-__device__ __forceinline__ PixelCoord pixel_of_thread(const RasterArgs& a, const TileId& tl) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane >> 3;
-    PixelCoord p;
-    p.px = tl.x * 16 + (warp & 1) * 8 + (q & 1) * 4 + (lane & 3);
-    p.py = tl.y * 16 + (warp >> 1) * 4 + (q >> 1) * 2 + ((lane >> 2) & 1);
-    p.inside = p.px < a.width && p.py < a.height;
+__device__ __forceinline__ float shfl_x(float v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float x, float y, float z, float w) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void red_add_v2(float* addr, float x, float y) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(x), "f"(y) : "memory");
+}
+
+// ---- two pixels per lane, packed fp32 arithmetic ---------------------------------------------------------
+// sm_100 executes add/mul/fma on pairs of fp32 values held in a 64-bit register pair as ONE instruction
+// (each half rounded to nearest like the scalar operation, so no result changes).  Both raster kernels are
+// bound by instruction issue, so here a lane owns two horizontally adjacent pixels: everything that depends
+// on the splat alone (record loads, list walk, dy-only terms) is done once for both, and the arithmetic on
+// values that already come in pairs (the exp polynomial, transmittance, gradient moments) is packed.
+// Operations that mix a per-splat scalar with a pair stay scalar: duplicating the scalar into a register
+// pair costs what the packing saves, and staging duplicated records in shared memory cost more
+// shared-memory bandwidth than it saved issue slots.  A warp covers an 8x8 pixel block, a CTA of four warps
+// the 16x16 tile.  A group of FOUR lanes covers a 4x2 sub-block (the culling granularity) and walks its own
+// survivor list, so one pass of the instruction stream serves up to eight records.
+using f2 = float2;
+__device__ __forceinline__ f2 f2_add(f2 a, f2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ f2 f2_mul(f2 a, f2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ f2 f2_dup(float x) { return make_float2(x, x); }
+
+// blend_exp on both halves: the same operations in the same order as the scalar version
+__device__ __forceinline__ f2 blend_exp2(f2 power) {
+    f2 t = f2_mul(power, f2_dup(1.44269504088896341f));
+    t.x = fminf(fmaxf(t.x, -125.0f), 125.0f);
+    t.y = fminf(fmaxf(t.y, -125.0f), 125.0f);
+    const f2 m = f2_add(t, f2_dup(12582912.0f));
+    const f2 n = f2_add(m, f2_dup(-12582912.0f));
+    const f2 f = f2_fma(n, f2_dup(-1.0f), t);           // t - n
+    f2 p = f2_dup(0.001327647129073739f);
+    p = f2_fma(p, f, f2_dup(0.009675540961325169f));
+    p = f2_fma(p, f, f2_dup(0.05550713092088699f));
+    p = f2_fma(p, f, f2_dup(0.24022120237350464f));
+    p = f2_fma(p, f, f2_dup(0.6931469440460205f));
+    p = f2_fma(p, f, f2_dup(1.0f));
+    p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(m.x) << 23));
+    p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(m.y) << 23));
     return p;
 }
 
-// Producer side of the staging pipeline (thread 0 only).
+// Adds (x, y) to two adjacent floats in shared memory (8-byte aligned) with one 64-bit compare-and-swap loop:
+// a float atomic add on shared memory is a compare-and-swap loop as well, so the pair costs one loop, not two.
+__device__ __forceinline__ void smem_add_pair(float* addr, float x, float y) {
+    unsigned long long* p = reinterpret_cast<unsigned long long*>(addr);
+    unsigned long long seen = *p, assumed;
+    do {
+        assumed = seen;
+        const f2 sum = f2_add(make_float2(__uint_as_float((uint32_t)assumed), __uint_as_float((uint32_t)(assumed >> 32))),
+                              make_float2(x, y));
+        const unsigned long long next =
+            (unsigned long long)__float_as_uint(sum.x) | ((unsigned long long)__float_as_uint(sum.y) << 32);
+        seen = atomicCAS(p, assumed, next);
+    } while (seen != assumed);
+}
+
+constexpr int kBatch = 128;                // records per staged batch
+constexpr int kListStride = kBatch + 8;    // bytes per group list (padded: the walk reads one entry ahead)
+
 __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, uint64_t* bar, int r0, int n, int batch) {
     const int cnt = min(kBatch, n - batch * kBatch);
     const uint32_t bytes = (uint32_t)cnt * kRecBytes;
@@ -97,48 +141,72 @@ __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, ui
     bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
 }
 
-constexpr int kListStride = kBatch + 8;   // bytes per quarter list; +8 keeps the four lists on different banks
-
-// The 32 lanes test the records [g*32, g*32+32) of the staged batch, one record per lane, against the
-// four 4x2 sub-blocks of this warp's pixel block and append the index of every record that touches
-// sub-block q to lists[q] (in list order); c[q] is the running length, the same in all lanes.
-// The record's (hx, hy) already include the half size of the 8x4 block (3.5, 1.5); a sub-block is
-// 2.0 / 1.0 smaller and its centre sits at (+-2, +-1) from the block centre (wcx, wcy).
-__device__ __forceinline__ void cull_to_lists(const float4* rec, int g, int limit, float wcx, float wcy,
-                                              uint8_t* lists, int& c0, int& c1, int& c2, int& c3) {
-    const int lane = threadIdx.x & 31;
-    const int j = g * 32 + lane;
-    bool left = false, right = false, top = false, bottom = false;
-    if (j < limit) {
-        const float4 q0 = rec[j * 3];
-        const float ddx = q0.x - wcx, ddy = q0.y - wcy, hxq = q0.z - 2.0f, hyq = q0.w - 1.0f;
-        left = fabsf(ddx + 2.0f) <= hxq;
-        right = fabsf(ddx - 2.0f) <= hxq;
-        top = fabsf(ddy + 1.0f) <= hyq;
-        bottom = fabsf(ddy - 1.0f) <= hyq;
-    }
-    const uint32_t lt = (1u << lane) - 1u;
-    const uint32_t m0 = __ballot_sync(0xffffffffu, left && top);
-    const uint32_t m1 = __ballot_sync(0xffffffffu, right && top);
-    const uint32_t m2 = __ballot_sync(0xffffffffu, left && bottom);
-    const uint32_t m3 = __ballot_sync(0xffffffffu, right && bottom);
-    if (left && top) lists[c0 + __popc(m0 & lt)] = (uint8_t)j;
-    if (right && top) lists[kListStride + c1 + __popc(m1 & lt)] = (uint8_t)j;
-    if (left && bottom) lists[2 * kListStride + c2 + __popc(m2 & lt)] = (uint8_t)j;
-    if (right && bottom) lists[3 * kListStride + c3 + __popc(m3 & lt)] = (uint8_t)j;
-    c0 += __popc(m0);
-    c1 += __popc(m1);
-    c2 += __popc(m2);
-    c3 += __popc(m3);
+// Gather staging: thread t of the CTA fetches record `id` of the per-Gaussian table into slot t of a batch
+// buffer with three 16-byte asynchronous copies (the thread waits for its own copies with cp.async.wait_all
+// before the batch's barrier).  Used when the records are not packed per (tile, splat) pair beforehand.
+__device__ __forceinline__ void gather_record(const RasterArgs& a, float4* buf, int slot, int32_t id) {
+    if (id < 0) return;
+    const float4* src = a.records + (int64_t)id * kRecFloat4;
+    cp_async16(buf + slot * 3, src);
+    cp_async16(buf + slot * 3 + 1, src + 1);
+    cp_async16(buf + slot * 3 + 2, src + 2);
+}
+// id of the record that thread t stages for batch `batch` of a list of n records starting at r0 (-1: none)
+__device__ __forceinline__ int32_t staged_id(const RasterArgs& a, int r0, int n, int batch, int t) {
+    const int k = batch * kBatch + t;
+    return k < n ? a.sorted_ids[r0 + k] : -1;
 }
 
-__global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
-    __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
+// The 32 lanes test the records [g*32, g*32+32) of the staged batch, one per lane, against the eight 4x2
+// sub-blocks of the warp's 8x8 pixel block (columns at -+2 from the block centre, rows at -3, -1, +1, +3)
+// and append every survivor of sub-block k to lists[k] (in list order).
+// The record's (hx, hy) include the half size (3.5, 1.5) of an 8x4 block; a 4x2 sub-block is 2.0 / 1.0 smaller.
+__device__ __forceinline__ void cull_to_lists(const float4* raw, int g, int limit, float wcx, float wcy,
+                                              uint8_t* lists, int (&c)[8]) {
+    const int lane = threadIdx.x & 31;
+    const int j = g * 32 + lane;
+    bool bx[2] = {false, false}, by[4] = {false, false, false, false};
+    if (j < limit) {
+        const float4 q0 = raw[j * 3];
+        const float ddx = q0.x - wcx, ddy = q0.y - wcy, hxq = q0.z - 2.0f, hyq = q0.w - 1.0f;
+        bx[0] = fabsf(ddx + 2.0f) <= hxq;
+        bx[1] = fabsf(ddx - 2.0f) <= hxq;
+        by[0] = fabsf(ddy + 3.0f) <= hyq;
+        by[1] = fabsf(ddy + 1.0f) <= hyq;
+        by[2] = fabsf(ddy - 1.0f) <= hyq;
+        by[3] = fabsf(ddy - 3.0f) <= hyq;
+    }
+    const uint32_t lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const bool in = bx[k & 1] && by[k >> 1];
+        const uint32_t m = __ballot_sync(0xffffffffu, in);
+        if (in) lists[k * kListStride + c[k] + __popc(m & lt)] = (uint8_t)j;
+        c[k] += __popc(m);
+    }
+}
+
+// power = dx*(ha*dx + nb*dy) + (hc*dy)*dy for two pixels of one row (blend_power's operations and order)
+__device__ __forceinline__ f2 blend_power2(const float4& q1, f2 dx, float dy) {
+    const float t0 = f_fma(q1.y, dy, f_mul(q1.x, dx.x)), t1 = f_fma(q1.y, dy, f_mul(q1.x, dx.y));
+    const float uu = f_mul(f_mul(q1.z, dy), dy);
+    return make_float2(f_fma(t0, dx.x, uu), f_fma(t1, dx.y, uu));
+}
+
+__device__ __forceinline__ int pick8(const int (&c)[8], int k) {
+    int v = c[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) v = k == i ? c[i] : v;
+    return v;
+}
+
+template <bool GATHER>
+__global__ void __launch_bounds__(128, 10) raster_forward_kernel(const __grid_constant__ RasterArgs a) {
+    __shared__ __align__(128) float4 s_raw[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
-    __shared__ uint8_t s_list[8][4 * kListStride];   // per warp: the four quarters' survivor lists
-    const int t = threadIdx.x;
+    __shared__ uint8_t s_list[4][8 * kListStride];   // per warp: the eight groups' survivor lists
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, group = lane >> 2;
     const TileId tl = tile_of_cta(a);
-    const PixelCoord pc = pixel_of_thread(a, tl);
     const int tile = tl.tile;
     const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
     const int n = r1 - r0;
@@ -149,117 +217,159 @@ __global__ void __launch_bounds__(256) raster_forward_kernel(const __grid_consta
         fence_mbar_init();
     }
     __syncthreads();
-    if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, n, 0);
+    int32_t id_next = -1;   // GATHER: the id this thread stages for the batch after the one in flight
+    if (GATHER) {
+        gather_record(a, s_raw[0], t, staged_id(a, r0, n, 0, t));
+        id_next = staged_id(a, r0, n, 1, t);
+    } else if (t == 0 && nb > 0) {
+        issue_batch(a, s_raw[0], &s_bar[0], r0, n, 0);
+    }
 
-    const float fpx = (float)pc.px, fpy = (float)pc.py;
-    const float wcx = (float)(tl.x * 16 + ((t >> 5) & 1) * 8) + 3.5f;
-    const float wcy = (float)(tl.y * 16 + (t >> 6) * 4) + 1.5f;
-    const int quarter = (t & 31) >> 3, warp = t >> 5;
-    bool done = !pc.inside;
-    float T = 1.0f, C0 = 0.0f, C1 = 0.0f, C2 = 0.0f;
-    int contributor = 0;
+    // pixel A = (px, py), pixel B = (px + 1, py)
+    const int bx0 = tl.x * 16 + (warp & 1) * 8, by0 = tl.y * 16 + (warp >> 1) * 8;
+    const int px = bx0 + (group & 1) * 4 + (lane & 1) * 2;
+    const int py = by0 + (group >> 1) * 2 + ((lane >> 1) & 1);
+    const bool insideA = px < a.width && py < a.height, insideB = px + 1 < a.width && py < a.height;
+    const float fpxA = (float)px, fpxB = (float)(px + 1), fpy = (float)py;
+    const float wcx = (float)bx0 + 3.5f, wcy = (float)by0 + 3.5f;
+    bool doneA = !insideA, doneB = !insideB;
+    f2 T = f2_dup(1.0f), C0 = f2_dup(0.0f), C1 = f2_dup(0.0f), C2 = f2_dup(0.0f);
+    int contribA = 0, contribB = 0;
     bool copy_failed = false;
 
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
-        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        if (GATHER) cp_async_wait_all();
+        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
         // The one barrier of a batch: batch b has arrived for everybody, everybody has finished batch b-1
-        // (so the other buffer may be refilled), and the whole-tile early exit is decided (render.py:1691-1694).
-        // No copy is in flight here: the next one is issued below.
-        const int num_done = __syncthreads_count(done || copy_failed);
-        if (num_done == 256) break;
-        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, n, b + 1);
+        // (so the other buffer may be refilled), and the whole-tile early exit is decided
+        // (render.py:1691-1694).  No copy is in flight here: the next is issued below.
+        const int num_done = __syncthreads_count((doneA && doneB) || copy_failed);
+        if (num_done == 128) break;
+        if (GATHER) {
+            if (b + 1 < nb) {
+                gather_record(a, s_raw[cur ^ 1], t, id_next);
+                id_next = staged_id(a, r0, n, b + 2, t);
+            }
+        } else if (t == 0 && b + 1 < nb) {
+            issue_batch(a, s_raw[cur ^ 1], &s_bar[cur ^ 1], r0, n, b + 1);
+        }
         const int cnt = min(kBatch, n - b * kBatch);
-        const float4* rec = s_rec[cur];
-        // Cull the whole batch first, then every quarter (8 lanes, a 4x2 pixel sub-block) walks its own
-        // survivor list front to back, independently of the other quarters: one pass of the instruction
-        // stream serves up to four different records.
         const int ng = (cnt + 31) >> 5;
-        if (!__all_sync(0xffffffffu, done)) {
-            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-            for (int g = 0; g < ng; ++g) cull_to_lists(rec, g, cnt, wcx, wcy, s_list[warp], c0, c1, c2, c3);
+        const float4* rec = s_raw[cur];
+        if (!__all_sync(0xffffffffu, doneA && doneB)) {
+            int c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int g = 0; g < ng; ++g) cull_to_lists(rec, g, cnt, wcx, wcy, s_list[warp], c);
             __syncwarp();
-            const int mine = quarter == 0 ? c0 : (quarter == 1 ? c1 : (quarter == 2 ? c2 : c3));
-            const uint8_t* lst = &s_list[warp][quarter * kListStride];
+            const int mine = pick8(c, group);
+            const uint8_t* lst = &s_list[warp][group * kListStride];
             const int base = b * kBatch;
+            // The list index of a pass is loaded one pass ahead (the lists are padded, so reading one past the
+            // end is in bounds).  Past the end of its list a group replays record 0 (always staged, finite);
+            // `live` masks the result.
+            int jn = 0 < mine ? (int)lst[0] : 0;
             for (int i = 0;; ++i) {
-                const bool live = i < mine && !done;
+                const bool live = i < mine && !(doneA && doneB);
                 if (!__any_sync(0xffffffffu, live)) break;
-                // past the end of its list a quarter reads a stale index (< kBatch); `live` masks the result
-                const int j = lst[i];
-                const float4 q0 = rec[j * 3];       // u, v, hx, hy
-                const float4 q1 = rec[j * 3 + 1];   // ha, nb, hc, opacity
-                const float4 q2 = rec[j * 3 + 2];   // r, g, b, thr
-                const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
-                const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
-                const float G = blend_exp(power);
-                const float alpha = fminf(0.99f, f_mul(q1.w, G));
-                const float nT = f_mul(T, f_sub(1.0f, alpha));
+                const int j = jn;
+                jn = i + 1 < mine ? (int)lst[i + 1] : 0;
+                const float2 uv = *reinterpret_cast<const float2*>(rec + j * 3);   // u, v
+                const float4 q1 = rec[j * 3 + 1];                                  // ha, nb, hc, opacity
+                const float4 q2 = rec[j * 3 + 2];                                  // r, g, b, thr
+                const f2 dx = make_float2(f_sub(uv.x, fpxA), f_sub(uv.x, fpxB));
+                const float dy = f_sub(uv.y, fpy);
+                const f2 power = blend_power2(q1, dx, dy);
+                const f2 G = blend_exp2(power);
+                const f2 alpha = make_float2(fminf(0.99f, f_mul(q1.w, G.x)), fminf(0.99f, f_mul(q1.w, G.y)));
+                const f2 oma = f2_fma(alpha, f2_dup(-1.0f), f2_dup(1.0f));   // 1 - alpha
+                const f2 nT = f2_mul(T, oma);
+                f2 w = f2_mul(alpha, T);
+                const float thr = q2.w;
                 // power < thr  =>  alpha < alpha_eps: the pixel skips this splat (render.py:1796-1798)
-                const bool ok = live && power >= q2.w && alpha >= a.alpha_eps;
-                const bool should_done = nT < a.t_eps;
+                const bool okA = live && !doneA && power.x >= thr && alpha.x >= a.alpha_eps;
+                const bool okB = live && !doneB && power.y >= thr && alpha.y >= a.alpha_eps;
+                const bool sdA = nT.x < a.t_eps, sdB = nT.y < a.t_eps;
                 // render.py:1803-1807: a splat with power > 0 or one that would end the pixel is not blended
-                const bool upd = ok && !(power > 0.0f) && !should_done;
-                done = done || (ok && should_done);
-                const float w = f_mul(alpha, T);
-                T = upd ? nT : T;
-                contributor = upd ? base + j : contributor;   // render.py:1836
-                C0 = upd ? f_fma(w, q2.x, C0) : C0;
-                C1 = upd ? f_fma(w, q2.y, C1) : C1;
-                C2 = upd ? f_fma(w, q2.z, C2) : C2;
+                const bool updA = okA && !(power.x > 0.0f) && !sdA;
+                const bool updB = okB && !(power.y > 0.0f) && !sdB;
+                doneA = doneA || (okA && sdA);
+                doneB = doneB || (okB && sdB);
+                T.x = updA ? nT.x : T.x;
+                T.y = updB ? nT.y : T.y;
+                contribA = updA ? base + j : contribA;   // render.py:1836
+                contribB = updB ? base + j : contribB;
+                w.x = updA ? w.x : 0.0f;                 // a zero weight leaves the colour sums unchanged
+                w.y = updB ? w.y : 0.0f;
+                C0 = make_float2(f_fma(w.x, q2.x, C0.x), f_fma(w.y, q2.x, C0.y));
+                C1 = make_float2(f_fma(w.x, q2.y, C1.x), f_fma(w.y, q2.y, C1.y));
+                C2 = make_float2(f_fma(w.x, q2.z, C2.x), f_fma(w.y, q2.z, C2.y));
             }
         }
     }
     if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
-    if (pc.inside) {
-        const int64_t pix = ((int64_t)tl.view * a.height + pc.py) * a.width + pc.px;
-        a.final_T[pix] = T;
-        a.n_contrib[pix] = contributor;
+    const int64_t pix = ((int64_t)tl.view * a.height + py) * a.width + px;
+    if (insideA) {
+        float c0 = C0.x, c1 = C1.x, c2 = C2.x;
+        a.final_T[pix] = T.x;
+        a.n_contrib[pix] = contribA;
         if (!a.training) {   // render.py:2259-2263: composite the background and clamp at inference
-            C0 = fminf(fmaxf(f_add(C0, f_mul(T, a.bg[0])), 0.0f), 1.0f);
-            C1 = fminf(fmaxf(f_add(C1, f_mul(T, a.bg[1])), 0.0f), 1.0f);
-            C2 = fminf(fmaxf(f_add(C2, f_mul(T, a.bg[2])), 0.0f), 1.0f);
+            c0 = fminf(fmaxf(f_add(c0, f_mul(T.x, a.bg[0])), 0.0f), 1.0f);
+            c1 = fminf(fmaxf(f_add(c1, f_mul(T.x, a.bg[1])), 0.0f), 1.0f);
+            c2 = fminf(fmaxf(f_add(c2, f_mul(T.x, a.bg[2])), 0.0f), 1.0f);
         }
-        a.color[pix * 3] = C0;
-        a.color[pix * 3 + 1] = C1;
-        a.color[pix * 3 + 2] = C2;
+        a.color[pix * 3] = c0; a.color[pix * 3 + 1] = c1; a.color[pix * 3 + 2] = c2;
+    }
+    if (insideB) {
+        float c0 = C0.y, c1 = C1.y, c2 = C2.y;
+        a.final_T[pix + 1] = T.y;
+        a.n_contrib[pix + 1] = contribB;
+        if (!a.training) {
+            c0 = fminf(fmaxf(f_add(c0, f_mul(T.y, a.bg[0])), 0.0f), 1.0f);
+            c1 = fminf(fmaxf(f_add(c1, f_mul(T.y, a.bg[1])), 0.0f), 1.0f);
+            c2 = fminf(fmaxf(f_add(c2, f_mul(T.y, a.bg[2])), 0.0f), 1.0f);
+        }
+        a.color[pix * 3 + 3] = c0; a.color[pix * 3 + 4] = c1; a.color[pix * 3 + 5] = c2;
     }
 }
 
-__device__ __forceinline__ float shfl_x(float v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
-
-__device__ __forceinline__ void red_add_v4(float* addr, float x, float y, float z, float w) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
-__device__ __forceinline__ void red_add_v2(float* addr, float x, float y) {
-    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(x), "f"(y) : "memory");
-}
-
-// Backward.  Per pixel the blend is replayed front to back (T from 1, colour suffix = final -
-// prefix, render.py:1868-1895).
-__global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
-    __shared__ __align__(128) float4 s_rec[2][kBatch * kRecFloat4];
+// Backward with two pixels per lane.  Per pass a lane adds its two pixels' nine moment values, then the
+// four lanes of a group reduce them with a transposing butterfly (8 shuffles) and every lane adds the two
+// components it ends up holding to the record's row in shared memory.
+template <bool GATHER>
+__global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
+    __shared__ __align__(128) float4 s_raw[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
-    __shared__ float s_acc[kBatch][9];   // per record: dconic a b c, dopacity, dcolor r g b, duv x y
-    __shared__ int s_max[8];
-    __shared__ uint8_t s_list[8][4 * kListStride];
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    // per record: sum m dx^2, m dx dy, m dy^2, m, dcolor r g b, m dx, m dy, (pad: rows stay 8-byte aligned)
+    __shared__ __align__(8) float s_acc[kBatch][10];
+    __shared__ int s_max[4];
+    __shared__ uint8_t s_list[4][8 * kListStride];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5, group = lane >> 2;
     const TileId tl = tile_of_cta(a);
-    const PixelCoord pc = pixel_of_thread(a, tl);
     const int tile = tl.tile;
     const int r0 = a.ranges[tile * 2], r1 = a.ranges[tile * 2 + 1];
     const int n = r1 - r0;
-    const int64_t pix = ((int64_t)tl.view * a.height + pc.py) * a.width + pc.px;
+    const int bx0 = tl.x * 16 + (warp & 1) * 8, by0 = tl.y * 16 + (warp >> 1) * 8;
+    const int px = bx0 + (group & 1) * 4 + (lane & 1) * 2;
+    const int py = by0 + (group >> 1) * 2 + ((lane >> 1) & 1);
+    const bool insideA = px < a.width && py < a.height, insideB = px + 1 < a.width && py < a.height;
+    const int64_t pix = ((int64_t)tl.view * a.height + py) * a.width + px;
     // render.py:1594: list positions [0, n_contrib] took part in the forward blend
-    int contributor = 0;
-    float rr0 = 0.0f, rr1 = 0.0f, rr2 = 0.0f, dr0 = 0.0f, dr1 = 0.0f, dr2 = 0.0f, dTT = 0.0f;
-    if (pc.inside && n > 0) {
-        contributor = min(a.n_contrib[pix] + 1, n);
-        rr0 = a.color[pix * 3]; rr1 = a.color[pix * 3 + 1]; rr2 = a.color[pix * 3 + 2];
-        dr0 = a.drgb[pix * 3]; dr1 = a.drgb[pix * 3 + 1]; dr2 = a.drgb[pix * 3 + 2];
-        dTT = a.dT != nullptr ? a.dT[pix] * a.final_T[pix] : 0.0f;   // render.py:1935
+    int contribA = 0, contribB = 0;
+    // nr = -(colour suffix): starts at -final colour and gains w*c per blended splat (render.py:1868-1895)
+    f2 nr0 = f2_dup(0.0f), nr1 = nr0, nr2 = nr0, dr0 = nr0, dr1 = nr0, dr2 = nr0, ndTT = nr0;
+    if (insideA && n > 0) {
+        contribA = min(a.n_contrib[pix] + 1, n);
+        nr0.x = -a.color[pix * 3]; nr1.x = -a.color[pix * 3 + 1]; nr2.x = -a.color[pix * 3 + 2];
+        dr0.x = a.drgb[pix * 3]; dr1.x = a.drgb[pix * 3 + 1]; dr2.x = a.drgb[pix * 3 + 2];
+        ndTT.x = a.dT != nullptr ? -(a.dT[pix] * a.final_T[pix]) : 0.0f;   // render.py:1935
     }
-    int wmax = contributor;
+    if (insideB && n > 0) {
+        contribB = min(a.n_contrib[pix + 1] + 1, n);
+        nr0.y = -a.color[pix * 3 + 3]; nr1.y = -a.color[pix * 3 + 4]; nr2.y = -a.color[pix * 3 + 5];
+        dr0.y = a.drgb[pix * 3 + 3]; dr1.y = a.drgb[pix * 3 + 4]; dr2.y = a.drgb[pix * 3 + 5];
+        ndTT.y = a.dT != nullptr ? -(a.dT[pix + 1] * a.final_T[pix + 1]) : 0.0f;
+    }
+    int wmax = max(contribA, contribB);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
     if (lane == 0) s_max[warp] = wmax;
@@ -269,95 +379,124 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
         fence_mbar_init();
     }
     __syncthreads();
-    int bmax = 0;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) bmax = max(bmax, s_max[w]);
+    const int bmax = max(max(s_max[0], s_max[1]), max(s_max[2], s_max[3]));
     const int nb = (bmax + kBatch - 1) / kBatch;     // batches anybody in the tile still needs
-    if (t == 0 && nb > 0) issue_batch(a, s_rec[0], &s_bar[0], r0, bmax, 0);
+    // GATHER: ids of the records this thread stages: of the current batch, the one in flight, the one after
+    int32_t id_cur = -1, id_flight = -1, id_next = -1;
+    if (GATHER) {
+        id_cur = staged_id(a, r0, bmax, 0, t);
+        gather_record(a, s_raw[0], t, id_cur);
+        id_next = staged_id(a, r0, bmax, 1, t);
+    } else if (t == 0 && nb > 0) {
+        issue_batch(a, s_raw[0], &s_bar[0], r0, bmax, 0);
+    }
 
-    const float fpx = (float)pc.px, fpy = (float)pc.py;
-    const float wcx = (float)(tl.x * 16 + (warp & 1) * 8) + 3.5f;
-    const float wcy = (float)(tl.y * 16 + (warp >> 1) * 4) + 1.5f;
-    const int quarter = lane >> 3;
-    const bool h4 = (lane & 4) != 0, h2 = (lane & 2) != 0, h1 = (lane & 1) != 0;
-    // after the butterfly, lane k of a quarter holds the quarter's total of component `slot`
-    const int slot = (h4 ? 4 : 0) + (h2 ? 2 : 0) + (h1 ? 1 : 0);
-    float T = 1.0f;
+    const float fpxA = (float)px, fpxB = (float)(px + 1), fpy = (float)py;
+    const float wcx = (float)bx0 + 3.5f, wcy = (float)by0 + 3.5f;
+    const bool h2 = (lane & 2) != 0, h1 = (lane & 1) != 0;
+    // after the butterfly a lane holds the group's totals of components slot and slot + 1
+    const int slot = (h2 ? 4 : 0) + (h1 ? 2 : 0);
+    f2 T = f2_dup(1.0f);
     bool copy_failed = false;
 #pragma unroll
     for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;   // row t is zeroed again by its owner after every flush
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
-        if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        if (GATHER) cp_async_wait_all();
+        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
         // First barrier of the batch: batch b has arrived for everybody and everybody has flushed and zeroed
         // its accumulator row of batch b-1, so the other record buffer may be refilled.  No copy is in flight.
         if (__syncthreads_or(copy_failed)) break;
-        if (t == 0 && b + 1 < nb) issue_batch(a, s_rec[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
         const int cnt = min(kBatch, bmax - b * kBatch);
         int32_t my_id = 0;
-        if (t < cnt) my_id = a.sorted_ids[r0 + b * kBatch + t];
-        const float4* rec = s_rec[cur];
+        if (GATHER) {
+            if (b > 0) id_cur = id_flight;
+            my_id = max(id_cur, 0);
+            if (b + 1 < nb) {
+                gather_record(a, s_raw[cur ^ 1], t, id_next);
+                id_flight = id_next;
+                id_next = staged_id(a, r0, bmax, b + 2, t);
+            }
+        } else {
+            if (t == 0 && b + 1 < nb) issue_batch(a, s_raw[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
+            if (t < cnt) my_id = a.sorted_ids[r0 + b * kBatch + t];
+        }
+        const float4* raw = s_raw[cur];
         const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
         const int ng = (wlim + 31) >> 5;
         if (ng > 0) {
-            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-            for (int g = 0; g < ng; ++g) cull_to_lists(rec, g, wlim, wcx, wcy, s_list[warp], c0, c1, c2, c3);
+            int c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int g = 0; g < ng; ++g) cull_to_lists(raw, g, wlim, wcx, wcy, s_list[warp], c);
             __syncwarp();
-            const int mine = quarter == 0 ? c0 : (quarter == 1 ? c1 : (quarter == 2 ? c2 : c3));
-            const int maxc = max(max(c0, c1), max(c2, c3));
-            const uint8_t* lst = &s_list[warp][quarter * kListStride];
+            const int mine = pick8(c, group);
+            const int maxc = max(max(max(c[0], c[1]), max(c[2], c[3])), max(max(c[4], c[5]), max(c[6], c[7])));
+            const uint8_t* lst = &s_list[warp][group * kListStride];
             const int base = b * kBatch;
-            // every quarter (8 lanes, 4x2 pixels) walks its own survivors; one pass serves up to four records
+            // The list index of a pass is loaded one pass ahead (the lists are padded, so reading one past the
+            // end is in bounds).  A group past the end of its list replays record 0 with zero weights: every
+            // value below stays finite, so the branch-free selects cannot leak a NaN into T or the colour suffix.
+            int jn = 0 < mine ? (int)lst[0] : 0;
             for (int i = 0; i < maxc; ++i) {
                 const bool act = i < mine;
-                // a quarter past the end of its list replays record 0 with zero weights: every value below
-                // stays finite, so the branch-free selects cannot leak a NaN into T or the colour suffix
-                const int j = act ? (int)lst[i] : 0;
-                const float4 q0 = rec[j * 3];
-                const float4 q1 = rec[j * 3 + 1];
-                const float4 q2 = rec[j * 3 + 2];
-                const float dx = f_sub(q0.x, fpx), dy = f_sub(q0.y, fpy);
-                const float power = blend_power(q1.x, q1.y, q1.z, dx, dy);
-                const float G = blend_exp(power);
-                const float alpha = fminf(0.99f, f_mul(q1.w, G));
+                const int j = jn;
+                jn = i + 1 < mine ? (int)lst[i + 1] : 0;
+                const float2 uv = *reinterpret_cast<const float2*>(raw + j * 3);   // u, v
+                const float4 q1 = raw[j * 3 + 1];                                  // ha, nb, hc, opacity
+                const float4 q2 = raw[j * 3 + 2];                                  // r, g, b, thr
+                const f2 dx = make_float2(f_sub(uv.x, fpxA), f_sub(uv.x, fpxB));
+                const float dy = f_sub(uv.y, fpy);
+                const f2 power = blend_power2(q1, dx, dy);
+                const f2 G = blend_exp2(power);
+                const f2 alpha = make_float2(fminf(0.99f, f_mul(q1.w, G.x)), fminf(0.99f, f_mul(q1.w, G.y)));
+                const float thr = q2.w;
                 // render.py:1777: valid = power <= 0 && alpha >= alpha_eps && position < contributor
-                const bool valid = act && (base + j < contributor) && power >= q2.w && power <= 0.0f &&
-                                   alpha >= a.alpha_eps;
-                const float oma = f_sub(1.0f, alpha);
-                const float w = valid ? f_mul(alpha, T) : 0.0f;
-                T = valid ? f_mul(T, oma) : T;
-                rr0 = fmaf(-w, q2.x, rr0); rr1 = fmaf(-w, q2.y, rr1); rr2 = fmaf(-w, q2.z, rr2);
-                float dl = dr0 * fmaf(T, q2.x, -rr0);
-                dl = fmaf(dr1, fmaf(T, q2.y, -rr1), dl);
-                dl = fmaf(dr2, fmaf(T, q2.z, -rr2), dl);
-                dl -= dTT;
+                const bool validA = act && (base + j < contribA) && power.x >= thr && power.x <= 0.0f &&
+                                    alpha.x >= a.alpha_eps;
+                const bool validB = act && (base + j < contribB) && power.y >= thr && power.y <= 0.0f &&
+                                    alpha.y >= a.alpha_eps;
+                const f2 oma = f2_fma(alpha, f2_dup(-1.0f), f2_dup(1.0f));
+                f2 w = f2_mul(alpha, T);
+                const f2 nT = f2_mul(T, oma);
+                w.x = validA ? w.x : 0.0f;
+                w.y = validB ? w.y : 0.0f;
+                T.x = validA ? nT.x : T.x;
+                T.y = validB ? nT.y : T.y;
+                nr0 = make_float2(fmaf(w.x, q2.x, nr0.x), fmaf(w.y, q2.x, nr0.y));
+                nr1 = make_float2(fmaf(w.x, q2.y, nr1.x), fmaf(w.y, q2.y, nr1.y));
+                nr2 = make_float2(fmaf(w.x, q2.z, nr2.x), fmaf(w.y, q2.z, nr2.y));
+                f2 dl = f2_mul(dr0, make_float2(fmaf(T.x, q2.x, nr0.x), fmaf(T.y, q2.x, nr0.y)));
+                dl = f2_fma(dr1, make_float2(fmaf(T.x, q2.y, nr1.x), fmaf(T.y, q2.y, nr1.y)), dl);
+                dl = f2_fma(dr2, make_float2(fmaf(T.x, q2.z, nr2.x), fmaf(T.y, q2.z, nr2.y)), dl);
+                dl = f2_add(dl, ndTT);
                 // m = dL/dalpha * G (render.py:1957, 2018).  The per-splat sums are kept as moments of m over
                 // the pixels; the record's constants (opacity, conic) are applied once when the batch is
                 // flushed: dL/dG * G = opacity * m (render.py:1995).
-                const float m = valid ? __fdividef(dl, oma) * G : 0.0f;
-                const float mx = m * dx, my = m * dy;
-                float v0 = mx * dx, v1 = mx * dy, v2 = my * dy, v3 = m;      // sum m dx^2, m dx dy, m dy^2, m
-                float v4 = w * dr0, v5 = w * dr1, v6 = w * dr2;              // dcolor, render.py:1962
-                float v7 = mx, v8 = my;                                      // sum m dx, m dy
-                const uint32_t vmask = __ballot_sync(0xffffffffu, valid);
+                f2 m;
+                m.x = validA ? __fdividef(dl.x, oma.x) : 0.0f;
+                m.y = validB ? __fdividef(dl.y, oma.y) : 0.0f;
+                m = f2_mul(m, G);
+                const f2 dy2 = f2_dup(dy);
+                const f2 mx = f2_mul(m, dx), my = f2_mul(m, dy2);
+                const f2 pxx = f2_mul(mx, dx), pxy = f2_mul(mx, dy2), pyy = f2_mul(my, dy2);
+                const f2 pc0 = f2_mul(w, dr0), pc1 = f2_mul(w, dr1), pc2 = f2_mul(w, dr2);
+                const uint32_t vmask = __ballot_sync(0xffffffffu, validA || validB);
                 if (vmask == 0) continue;
-                // transposing butterfly inside each quarter: 8 components in 7 shuffles, the ninth in 3
-                const float a0 = (h4 ? v4 : v0) + shfl_x(h4 ? v0 : v4, 4);
-                const float a1 = (h4 ? v5 : v1) + shfl_x(h4 ? v1 : v5, 4);
-                const float a2 = (h4 ? v6 : v2) + shfl_x(h4 ? v2 : v6, 4);
-                const float a3 = (h4 ? v7 : v3) + shfl_x(h4 ? v3 : v7, 4);
-                const float b0 = (h2 ? a2 : a0) + shfl_x(h2 ? a0 : a2, 2);
-                const float b1 = (h2 ? a3 : a1) + shfl_x(h2 ? a1 : a3, 2);
-                const float c = (h1 ? b1 : b0) + shfl_x(h1 ? b0 : b1, 1);
-                v8 += shfl_x(v8, 4);
+                const float v0 = pxx.x + pxx.y, v1 = pxy.x + pxy.y, v2 = pyy.x + pyy.y, v3 = m.x + m.y;
+                const float v4 = pc0.x + pc0.y, v5 = pc1.x + pc1.y, v6 = pc2.x + pc2.y, v7 = mx.x + mx.y;
+                float v8 = my.x + my.y;
+                // transposing butterfly inside each group of four lanes: 8 components in 6 shuffles, the ninth in 2
+                const f2 a01 = f2_add(make_float2(h2 ? v4 : v0, h2 ? v5 : v1),
+                                      make_float2(shfl_x(h2 ? v0 : v4, 2), shfl_x(h2 ? v1 : v5, 2)));
+                const f2 a23 = f2_add(make_float2(h2 ? v6 : v2, h2 ? v7 : v3),
+                                      make_float2(shfl_x(h2 ? v2 : v6, 2), shfl_x(h2 ? v3 : v7, 2)));
+                const f2 b01 = f2_add(make_float2(h1 ? a23.x : a01.x, h1 ? a23.y : a01.y),
+                                      make_float2(shfl_x(h1 ? a01.x : a23.x, 1), shfl_x(h1 ? a01.y : a23.y, 1)));
                 v8 += shfl_x(v8, 2);
                 v8 += shfl_x(v8, 1);
-                // quarters with at least one valid lane add their nine sums: lane k adds component k,
-                // the first lane of the quarter also the ninth
-                const bool qvalid = ((vmask >> (quarter * 8)) & 0xffu) != 0;
-                if (qvalid) {
-                    atomicAdd(&s_acc[j][slot], c);
-                    if ((lane & 7) == 0) atomicAdd(&s_acc[j][8], v8);
+                const bool gvalid = ((vmask >> (group * 4)) & 0xfu) != 0;
+                if (gvalid) {
+                    smem_add_pair(&s_acc[j][slot], b01.x, b01.y);
+                    if ((lane & 3) == 0) atomicAdd(&s_acc[j][8], v8);
                 }
             }
         }
@@ -370,7 +509,7 @@ __global__ void __launch_bounds__(256) raster_backward_kernel(const __grid_const
                              (g6 != 0.f) | (sx != 0.f) | (sy != 0.f);
             // conic = (-2 ha, -nb, -2 hc), render.py:2001-2017: d/dconic = -0.5 o sxx, -o sxy, -0.5 o syy;
             // d/duv = o (2 ha sx + nb sy, 2 hc sy + nb sx); d/dopacity = s0
-            const float4 k1 = rec[t * 3 + 1];   // ha, nb, hc, opacity
+            const float4 k1 = raw[t * 3 + 1];   // ha, nb, hc, opacity
             const float g0 = -0.5f * k1.w * sxx, g1 = -k1.w * sxy, g2 = -0.5f * k1.w * syy, g3 = s0;
             const float g7 = k1.w * fmaf(2.0f * k1.x, sx, k1.y * sy);
             const float g8 = k1.w * fmaf(2.0f * k1.z, sy, k1.y * sx);
@@ -409,8 +548,8 @@ int32_t fill_args(const D3gsOpConfig* cfg, RasterArgs& a) {
 using namespace d3gs;
 
 extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const int32_t* tile_order,
-                                       const float* records, float* color, float* final_T, int32_t* n_contrib,
-                                       uint32_t* status, void* stream) {
+                                       const float* records, const int32_t* sorted_values, float* color,
+                                       float* final_T, int32_t* n_contrib, uint32_t* status, void* stream) {
     RasterArgs a = {};
     int32_t rc = fill_args(cfg, a);
     if (rc != D3GS_OK) return rc;
@@ -424,13 +563,18 @@ extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* r
     a.final_T = final_T;
     a.n_contrib = n_contrib;
     const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
-    raster_forward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    if (sorted_values != nullptr) {   // records are the per-Gaussian table: gather by sorted id
+        a.sorted_ids = sorted_values;
+        raster_forward_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    } else {                          // records are packed per (tile, splat) pair, in list order
+        raster_forward_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    }
     D3GS_LAUNCH_CHECK("raster_forward_kernel");
     return D3GS_OK;
 }
 
 extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges,
-                                        const int32_t* tile_order, const float* records,
+                                        const int32_t* tile_order, const float* records, int32_t records_by_id,
                                         const int32_t* sorted_values, const float* color,
                                         const float* final_T, const int32_t* n_contrib, const float* drgb,
                                         const float* dT, float* splat_grads, uint32_t* status, void* stream) {
@@ -457,7 +601,8 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
     a.dT = dT;
     a.splat_grads = splat_grads;
     const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
-    raster_backward_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(a);
+    if (records_by_id) raster_backward_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    else raster_backward_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("raster_backward_kernel");
     return D3GS_OK;
 }

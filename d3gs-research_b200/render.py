@@ -47,6 +47,7 @@ class GaussianSplatOpContext:
     # order in which their CTAs take the tiles (longest lists first)
     splat_records: torch.Tensor | None = None
     tile_order: torch.Tensor | None = None
+    records_by_id: bool = False   # splat_records is the per-Gaussian table (gathered by sorted id), not per pair
 
 
 @dataclasses.dataclass
@@ -216,6 +217,10 @@ class GaussianSplatOp:
         self.last_num_rendered = 0
         # when True, forward() keeps copies of the intermediate binning arrays in ``self.debug`` (tests)
         self.debug_capture = False
+        # True: the preprocess writes one raster record per Gaussian and the raster kernels gather them by sorted
+        # id; False: d3gs_pack_splats writes one record per sorted (tile, splat) pair and the raster kernels stream
+        # them with bulk copies (one more pass over the pairs; same results)
+        self.gather_records = True
         self.debug: dict[str, torch.Tensor] = {}
         # optional StageTimer; None = no events recorded
         self.timer: StageTimer | None = None
@@ -295,12 +300,13 @@ class GaussianSplatOp:
 
     @staticmethod
     def _ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb, cov2d, ne0,
-                    tile_mask=None) -> _lib.SplatContext:
+                    tile_mask=None, records=None) -> _lib.SplatContext:
         s = _lib.SplatContext()
         s.tiles_touched, s.radii, s.depths = _lib.ptr(tiles_touched), _lib.ptr(radii), _lib.ptr(depths)
         s.uvs, s.conic_opacity, s.rgb_gaussian = _lib.ptr(uvs), _lib.ptr(conic_opacity), _lib.ptr(rgb)
         s.cov2d_vecs, s.sh_to_rgb_ne_0 = _lib.ptr(cov2d), _lib.ptr(ne0)
         s.tile_mask = _lib.ptr(tile_mask)
+        s.records = _lib.ptr(records)
         return s
 
     # ---- forward (render.py:169-1015) ---------------------------------------------------------
@@ -330,9 +336,12 @@ class GaussianSplatOp:
         sh_ne0 = torch.empty([BN], dtype=torch.uint8, device=dev) if training else None
         tiles_touched = torch.empty(BN, dtype=i32, device=dev)
         tile_mask = torch.empty(BN, dtype=torch.int64, device=dev)   # binning scratch, dropped after the key emission
+        # per-Gaussian raster records, written by the preprocess and gathered by sorted id in the raster kernels
+        gather = self.gather_records
+        records = torch.empty([BN, 12], dtype=f32, device=dev) if gather else None
         mstruct = self._model_struct(model)
         cstruct = self._ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb_gaussian, cov2d_vecs, sh_ne0,
-                                   tile_mask)
+                                   tile_mask, records)
         mask_u8 = None
         if mask is not None:
             mask_u8 = mask.to(torch.uint8).contiguous()
@@ -397,15 +406,20 @@ class GaussianSplatOp:
         self._mark("tile_ranges")
         if self.debug_capture:
             self.debug.update(ranges=workload_ranges)
-        records = torch.empty(cap * 12, dtype=f32, device=dev)[:num_rendered * 12].view(num_rendered, 12)
-        _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
-                                        float(self._cfg.alpha_eps), records.data_ptr(), stream), "d3gs_pack_splats")
+        if not gather:   # one record per sorted pair, in list order
+            records = torch.empty(cap * 12, dtype=f32, device=dev)[:num_rendered * 12].view(num_rendered, 12)
+            _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),
+                                            float(self._cfg.alpha_eps), records.data_ptr(), stream),
+                       "d3gs_pack_splats")
+            self._mark("pack_splats")
         tile_order = torch.empty(num_tiles, dtype=i32, device=dev)
         _lib.check(lib.d3gs_tile_order(workload_ranges.data_ptr(), num_tiles, tile_order.data_ptr(), stream),
                    "d3gs_tile_order")
-        self._mark("pack_splats")
+        self._mark("tile_order")
         _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), tile_order.data_ptr(),
-                                           records.data_ptr(), out_color.data_ptr(), final_T.data_ptr(),
+                                           records.data_ptr(),
+                                           gaussian_idx_sorted.data_ptr() if gather else None,
+                                           out_color.data_ptr(), final_T.data_ptr(),
                                            n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
         self._mark("raster_fwd")
         output = GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
@@ -415,7 +429,8 @@ class GaussianSplatOp:
         ctx = GaussianSplatOpContext(conic_opacity=conic_opacity, radii=radii, uvs=uvs, rgb_gaussian=rgb_gaussian,
                                      gaussian_idx_sorted=gaussian_idx_sorted, workload_ranges=workload_ranges,
                                      image_shape_wh=(W, H), depths=depths, cov2d_vecs=cov2d_vecs,
-                                     sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order)
+                                     sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order,
+                                     records_by_id=gather)
         return output, ctx
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
@@ -444,7 +459,8 @@ class GaussianSplatOp:
         if dT is not None:
             dT = dT.contiguous()
         _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(), _lib.ptr(ctx.tile_order),
-                                            ctx.splat_records.data_ptr(), ctx.gaussian_idx_sorted.data_ptr(),
+                                            ctx.splat_records.data_ptr(), int(ctx.records_by_id),
+                                            ctx.gaussian_idx_sorted.data_ptr(),
                                             out.color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
                                             stream), "d3gs_raster_backward")

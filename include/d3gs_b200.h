@@ -118,6 +118,10 @@ typedef struct D3gsSplatContext {
                                  accepted, as a row-major bit mask over the 3-sigma tile rect when that rect has at
                                  most 64 tiles.  Written by the preprocess, read by the key duplication, which then
                                  does not repeat the overlap tests. */
+    float* records;           /* [B*N,12] optional (may be NULL; not in the reference), 16-byte aligned: the 48-byte
+                                 raster record of every visible Gaussian, [u v hx hy][ha nb hc o][r g b thr].  Written
+                                 by the preprocess; with it the raster kernels gather their records by sorted id and
+                                 the per-pair packing pass (d3gs_pack_splats) is not needed. */
 } D3gsSplatContext;
 
 /* ---- helpers -------------------------------------------------------------------------- */
@@ -186,18 +190,22 @@ int32_t d3gs_pack_splats(const int32_t* sorted_values, int64_t n, const D3gsSpla
 int32_t d3gs_tile_order(const int32_t* ranges, int64_t num_tiles, int32_t* order, void* stream);
 
 /* ---- K6 raster forward (render.py:1329-2316, is_bwd=False) ------------------------------- */
-/* color [B,H,W,3] (NHWC), final_T [B,H,W], n_contrib [B,H,W]; tile_order [B*tiles] from d3gs_tile_order or NULL */
+/* color [B,H,W,3] (NHWC), final_T [B,H,W], n_contrib [B,H,W]; tile_order [B*tiles] from d3gs_tile_order or NULL.
+ * records: with sorted_values == NULL the per-pair records of d3gs_pack_splats, in list order; with
+ * sorted_values (the sorted value list of the sort) the per-Gaussian table D3gsSplatContext.records, from
+ * which the kernel gathers by id, like the reference's per-batch gathers (render.py:1702-1716). */
 int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, const int32_t* tile_order,
-                            const float* records, float* color, float* final_T, int32_t* n_contrib,
-                            uint32_t* status, void* stream);
+                            const float* records, const int32_t* sorted_values, float* color, float* final_T,
+                            int32_t* n_contrib, uint32_t* status, void* stream);
 
 /* ---- K7 raster backward (render.py:1589-1676, 1774-2210) -------------------------------- */
 /* drgb [B,H,W,3], dT [B,H,W] or NULL.  The reference's four per-splat gradient tensors (duv, dconic,
  * dopacity, dcolor, render.py:1388-1401) are one packed array here so that the kernel can use 16-byte
  * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, 0 | duv x,y, 0, 0},
- * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort. */
+ * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort.
+ * records_by_id != 0: records is the per-Gaussian table (see d3gs_raster_forward), else the per-pair records. */
 int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const int32_t* tile_order,
-                             const float* records, const int32_t* sorted_values, const float* color,
+                             const float* records, int32_t records_by_id, const int32_t* sorted_values, const float* color,
                              const float* final_T, const int32_t* n_contrib, const float* drgb, const float* dT,
                              float* splat_grads, uint32_t* status, void* stream);
 

@@ -129,6 +129,37 @@ def test_backward_gradients(cuda_device, early_filter, views, ref_order):
         assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
 
 
+@pytest.mark.parametrize("width,height,views", [(177, 121, 1), (64, 33, 2)])
+def test_record_staging_modes_agree(cuda_device, width, height, views):
+    """The raster kernels stage their records either by gathering from the per-Gaussian table the preprocess
+    writes (default) or by streaming per-pair records written by d3gs_pack_splats.  Both must give the same
+    image, transmittance and contributor counts bit for bit (odd image sizes: the second pixel of a lane
+    falls outside), the oracle's contributor counts, and the same gradients up to the order of the float atomics."""
+    sc = small_scene(n=4000, width=width, height=height, sh_degree=3, seed=33, views=views)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
+    g = torch.Generator().manual_seed(9)
+    drgb = torch.randn(views, height, width, 3, generator=g).to(cuda_device)
+    res = {}
+    for gather in (True, False):
+        op = d3.GaussianSplatOp(op_cfg)
+        op.gather_records = gather
+        model = gpu_model(sc, cuda_device)
+        model.act_applied = True
+        cams = gpu_cameras(sc, cuda_device)
+        out, ctx = op.forward(model, cams, training=True)
+        assert ctx.records_by_id == gather
+        gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=drgb, dT=None), return_uv_grad=True)
+        torch.cuda.synchronize()
+        res[gather] = (out.color.clone(), out.T.clone(), out.n_contrib.clone(), duv.clone(), gm.xyz.clone(),
+                       gm.color_sh.clone())
+    for k in range(3):
+        assert torch.equal(res[True][k], res[False][k])
+    for k, name in ((3, "duv"), (4, "xyz"), (5, "sh_rest")):
+        assert_close(res[True][k].cpu().numpy(), res[False][k].cpu().numpy(), GRAD_TOL, name)
+    ref = O.forward(oracle_cfg(sc, op_cfg), oracle_scene(sc))
+    np.testing.assert_array_equal(res[True][2].cpu().numpy(), ref.n_contrib)
+
+
 def test_autograd_api_and_unsplit_nonflat_models(cuda_device):
     """rasterize_gaussians + loss.backward() through the public API; non-flat tensors."""
     sc = small_scene(n=3000, width=128, height=96, sh_degree=2, seed=5)
