@@ -48,6 +48,7 @@ class GaussianSplatOpContext:
     splat_records: torch.Tensor | None = None
     tile_order: torch.Tensor | None = None
     records_by_id: bool = False   # splat_records is the per-Gaussian table (gathered by sorted id), not per pair
+    raster_color: torch.Tensor | None = None   # the kernels' [B,H,W,3] colour when out.color is a re-formatted copy
 
 
 @dataclasses.dataclass
@@ -309,6 +310,28 @@ class GaussianSplatOp:
         s.records = _lib.ptr(records)
         return s
 
+    # ---- output formats (render.py:696-705, 1623-1668, 2222-2300) ------------------------------------
+    def _format_color(self, color: torch.Tensor, final_T: torch.Tensor) -> torch.Tensor:
+        """The kernels write NHWC RGB.  ``render_rgba`` appends the accumulated opacity: the reference blends a
+        fourth channel of constant 1, sum_i alpha_i T_i, which telescopes to 1 - T_final (and stays inside [0,1],
+        so the inference clamp with a zero background alpha changes nothing).  ``use_nchw`` permutes."""
+        if self._cfg.render_rgba:
+            color = torch.cat([color, (1.0 - final_T).unsqueeze(-1)], dim=-1)
+        if self._cfg.use_nchw:
+            color = color.permute(0, 3, 1, 2).contiguous()
+        return color
+
+    def _unformat_grad(self, drgb: torch.Tensor, dT: torch.Tensor | None):
+        """Inverse of ``_format_color`` for the incoming gradient: back to NHWC RGB; the alpha channel's gradient
+        moves to the transmittance, d(1 - T)/dT = -1."""
+        if self._cfg.use_nchw:
+            drgb = drgb.permute(0, 2, 3, 1)
+        if self._cfg.render_rgba:
+            dalpha = drgb[..., 3]
+            dT = -dalpha if dT is None else dT - dalpha
+            drgb = drgb[..., :3]
+        return drgb.contiguous(), dT
+
     # ---- forward (render.py:169-1015) ---------------------------------------------------------
     def forward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
                 training: bool = False, instance2world_T: torch.Tensor | None = None,
@@ -371,8 +394,8 @@ class GaussianSplatOp:
         n_contrib = torch.empty([B, H, W], dtype=i32, device=dev)
         out_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
         if num_rendered == 0:   # render.py:706-729: outputs are left uninitialised, no context
-            return GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
-                                       n_contrib=n_contrib), None
+            return GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
+                                       depth=None, n_contrib=n_contrib), None
         # Pair-sized buffers are allocated with a capacity quantised to 2^20 pairs above 1.125 x the count: the
         # count changes a little every training step, and exact sizes would make the caching allocator miss
         # and fall back to cudaMalloc (a device-wide stall of milliseconds) every few steps.
@@ -422,15 +445,16 @@ class GaussianSplatOp:
                                            out_color.data_ptr(), final_T.data_ptr(),
                                            n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
         self._mark("raster_fwd")
-        output = GaussianSplatOutput(custom_features=None, T=final_T, color=out_color, depth=None,
-                                     n_contrib=n_contrib, radii=radii)
+        output = GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
+                                     depth=None, n_contrib=n_contrib, radii=radii)
         if not training:
             return output, None
         ctx = GaussianSplatOpContext(conic_opacity=conic_opacity, radii=radii, uvs=uvs, rgb_gaussian=rgb_gaussian,
                                      gaussian_idx_sorted=gaussian_idx_sorted, workload_ranges=workload_ranges,
                                      image_shape_wh=(W, H), depths=depths, cov2d_vecs=cov2d_vecs,
                                      sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order,
-                                     records_by_id=gather)
+                                     records_by_id=gather,
+                                     raster_color=out_color if output.color is not out_color else None)
         return output, ctx
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
@@ -448,6 +472,10 @@ class GaussianSplatOp:
         num = BN // B
         drgb = grad.drgb
         assert drgb.is_contiguous(), "drgb must be contiguous"
+        dT = grad.dT
+        if self._cfg.use_nchw or self._cfg.render_rgba:
+            drgb, dT = self._unformat_grad(drgb, dT)
+        color = ctx.raster_color if ctx.raster_color is not None else out.color
         # packed per-splat gradients [BN,12]: dconic a b c, dopacity | dcolor r g b, 0 | duv x y, 0 0
         packed = torch.empty([BN, 12], dtype=torch.float32, device=dev)
         ocfg = _lib.OpConfig()
@@ -455,13 +483,12 @@ class GaussianSplatOp:
         ocfg.alpha_eps, ocfg.transmittance_eps = self._cfg.alpha_eps, self._cfg.transmittance_eps
         ocfg.num_views, ocfg.training = B, 1
         sync = self._sync_words(dev)
-        dT = grad.dT
         if dT is not None:
             dT = dT.contiguous()
         _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(), _lib.ptr(ctx.tile_order),
                                             ctx.splat_records.data_ptr(), int(ctx.records_by_id),
                                             ctx.gaussian_idx_sorted.data_ptr(),
-                                            out.color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
+                                            color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
                                             stream), "d3gs_raster_backward")
         self._mark("raster_bwd")

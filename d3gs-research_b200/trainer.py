@@ -222,6 +222,9 @@ class SplatTrainer:
                 views[k].copy_(getattr(model, k).detach())
                 setattr(model, k, views[k])
             model.flat = flat
+        if op_cfg.use_nchw or op_cfg.render_rgba:
+            raise NotImplementedError("SplatTrainer's fused loss reads the operator's NHWC RGB output: "
+                                      "use_nchw / render_rgba are for GaussianSplatOp and rasterize_gaussians")
         self.op = GaussianSplatOp(op_cfg)
         self.fused_adam = (self.world == 1) if fuse_backward_adam is None else bool(fuse_backward_adam)
         assert not (self.fused_adam and self.world > 1), "the fused backward + Adam is the single-rank path"

@@ -160,6 +160,53 @@ def test_record_staging_modes_agree(cuda_device, width, height, views):
     np.testing.assert_array_equal(res[True][2].cpu().numpy(), ref.n_contrib)
 
 
+@pytest.mark.parametrize("nchw,rgba,training", [(True, False, True), (False, True, True), (True, True, True),
+                                                  (True, True, False)])
+def test_output_formats_nchw_rgba(cuda_device, nchw, rgba, training):
+    """use_nchw / render_rgba (render.py:696-705, 1623-1668, 2222-2300): the alpha channel is the blended
+    constant 1, sum of alpha_i T_i = 1 - T; its gradient reaches the splats like a colour channel's.  The
+    PER_GAUSSIAN backward choice of the reference gives the same gradients as DEFAULT and is accepted."""
+    from d3gs_research_b200.config_def import RasterizeBackwardAlgo
+    views = 2
+    sc = small_scene(n=3000, width=96, height=72, sh_degree=3, seed=11, views=views)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, use_nchw=nchw, render_rgba=rgba,
+                                    rasterize_backward_algo=RasterizeBackwardAlgo.PER_GAUSSIAN)
+    op = d3.GaussianSplatOp(op_cfg)
+    assert op.is_nchw == nchw and op.is_rgba == rgba
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    cams = gpu_cameras(sc, cuda_device)
+    out, ctx = op.forward(model, cams, training=training)
+    ch = 4 if rgba else 3
+    assert tuple(out.color.shape) == ((views, ch, 72, 96) if nchw else (views, 72, 96, ch))
+    ocfg = oracle_cfg(sc, op_cfg, training=training)
+    osc = oracle_scene(sc)
+    ref = O.forward(ocfg, osc)
+    if training:
+        ref_color, ref_T = ref.color, ref.T
+    else:
+        ref_color, ref_T, _ = O.raster_fwd(ocfg, views, ref.ranges, ref.sorted_ids, ref.prep, bg=op_cfg.bg_color)
+    expect = np.concatenate([ref_color, 1.0 - ref_T[..., None]], axis=-1) if rgba else ref_color
+    if nchw:
+        expect = np.ascontiguousarray(expect.transpose(0, 3, 1, 2))
+    assert_close(out.color.cpu().numpy(), expect, IMG_TOL, "formatted colour")
+    if not training:
+        assert ctx is None
+        return
+    g = torch.Generator().manual_seed(3)
+    dcol = torch.randn(out.color.shape, generator=g)
+    dT = torch.randn(views, 72, 96, generator=g)
+    gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=dcol.to(cuda_device), dT=dT.to(cuda_device)),
+                             return_uv_grad=True)
+    torch.cuda.synchronize()
+    d = dcol.permute(0, 2, 3, 1) if nchw else dcol
+    dT_ref = dT - d[..., 3] if rgba else dT
+    O.backward(ocfg, osc, ref, d[..., :3].contiguous().numpy(), dT_ref.contiguous().numpy())
+    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv")
+    for name, ours in (("xyz", gm.xyz), ("opacity", gm.opacity), ("sh_rest", gm.color_sh)):
+        assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
+
+
 def test_autograd_api_and_unsplit_nonflat_models(cuda_device):
     """rasterize_gaussians + loss.backward() through the public API; non-flat tensors."""
     sc = small_scene(n=3000, width=128, height=96, sh_degree=2, seed=5)
