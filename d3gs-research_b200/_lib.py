@@ -30,7 +30,8 @@ class OpConfig(C.Structure):
                 ("transmittance_eps", C.c_float), ("scale_global", C.c_float), ("early_filter_algo", C.c_int32),
                 ("sh_degree", C.c_int32), ("training", C.c_int32), ("clamp_mask_reference_order", C.c_int32),
                 ("fused_activations", C.c_int32),
-                ("bg_color", C.c_float * 3), ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS)]
+                ("bg_color", C.c_float * 3), ("key_shift_bits", C.c_int32), ("depth_32bit_prec", C.c_float),
+                ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS)]
 
 
 class Model(C.Structure):
@@ -105,7 +106,7 @@ SIGNATURES = {
     "d3gs_duplicate_keys": (_I32, [C.POINTER(OpConfig), _I64, _P, C.POINTER(SplatContext), _P, _P, _P]),
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
-    "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _P]),
+    "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _I32, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
     "d3gs_tile_order": (_I32, [_P, _I64, _P, _P]),
     "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P, _P]),

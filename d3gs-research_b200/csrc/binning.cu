@@ -123,14 +123,14 @@ scan_lookback_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, 
 }
 
 __global__ void __launch_bounds__(256)
-tile_ranges_kernel(const uint64_t* __restrict__ keys, int64_t n, int32_t* __restrict__ ranges) {
+tile_ranges_kernel(const uint64_t* __restrict__ keys, int64_t n, int32_t* __restrict__ ranges, int shift) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
-    const uint32_t t = (uint32_t)(keys[i] >> 32);
+    const uint32_t t = (uint32_t)(keys[i] >> shift);
     if (i == 0) {
         ranges[(int64_t)t * 2] = 0;
     } else {
-        const uint32_t lt = (uint32_t)(keys[i - 1] >> 32);
+        const uint32_t lt = (uint32_t)(keys[i - 1] >> shift);
         if (t != lt) {
             ranges[(int64_t)lt * 2 + 1] = (int32_t)i;
             ranges[(int64_t)t * 2] = (int32_t)i;
@@ -225,15 +225,18 @@ extern "C" int32_t d3gs_scan_tiles(const int32_t* in, int32_t* out, int64_t n, i
 }
 
 extern "C" int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges, int64_t num_tiles,
-                                    void* stream) {
+                                    int32_t key_shift_bits, void* stream) {
     D3GS_REQUIRE(n >= 0 && num_tiles >= 0, "negative count");
+    D3GS_REQUIRE(key_shift_bits == 0 || key_shift_bits == 32 || key_shift_bits == 18,
+                 "key_shift_bits must be 32 (64-bit keys) or 18 (32-bit keys), got %d", key_shift_bits);
     D3GS_REQUIRE(ranges != nullptr || num_tiles == 0, "ranges is NULL");
     cudaStream_t s = (cudaStream_t)stream;
     if (num_tiles > 0) D3GS_CUDA(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 2 * sizeof(int32_t), s));
     if (n == 0) return D3GS_OK;
     D3GS_REQUIRE(sorted_keys != nullptr, "sorted_keys is NULL");
     D3GS_REQUIRE(n < (int64_t)1 << 31, "pair count %lld does not fit the int32 ranges", (long long)n);
-    tile_ranges_kernel<<<(unsigned)div_up64(n, 256), 256, 0, s>>>(sorted_keys, n, ranges);
+    tile_ranges_kernel<<<(unsigned)div_up64(n, 256), 256, 0, s>>>(sorted_keys, n, ranges,
+                                                                  key_shift_bits == 18 ? 18 : 32);
     D3GS_LAUNCH_CHECK("tile_ranges_kernel");
     return D3GS_OK;
 }

@@ -476,6 +476,7 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
     tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
     tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
     tg.ts = (float)cf.tile_x;
+    const int shift = cf.key_shift_bits == 18 ? 18 : 32;
     const int r = i < total ? a.ctx.radii[i] : 0;
     bool big = false;        // emitted by the whole warp below
     WalkSeed seed = {};
@@ -488,7 +489,10 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
         const float2 uv = *reinterpret_cast<const float2*>(a.ctx.uvs + i * 2);
         int rmin[2], rmax[2];
         tile_rect(tg, uv.x, uv.y, (float)r, rmin, rmax);
-        dbits = __float_as_uint(a.ctx.depths[i]);
+        // 64-bit keys carry the depth's bits (depth > 0: bit order = numeric order); 32-bit keys an 18-bit
+        // quantised depth (render.py:767-773)
+        dbits = shift == 32 ? __float_as_uint(a.ctx.depths[i])
+                            : ((uint32_t)(a.ctx.depths[i] / cf.depth_32bit_prec) & 0x3FFFFu);
         tile_base = (uint64_t)b * (uint64_t)(tg.tiles_x * tg.tiles_y);
         const int rw = rmax[0] - rmin[0];
         if (a.ctx.tile_mask != nullptr && rw * (rmax[1] - rmin[1]) <= 64) {
@@ -499,7 +503,7 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
                 m &= m - 1;
                 const int y = rmin[1] + bit / rw, x = rmin[0] + bit % rw;
                 const uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
-                a.keys[off] = (key << 32) | dbits;
+                a.keys[off] = (key << shift) | dbits;
                 a.values[off] = (int32_t)i;
                 ++off;
             }
@@ -514,7 +518,7 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
             } else {
                 walk.for_each([&](int x, int y) {
                     uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
-                    a.keys[off] = (key << 32) | dbits;
+                    a.keys[off] = (key << shift) | dbits;
                     a.values[off] = (int32_t)i;
                     ++off;
                 });
@@ -543,7 +547,7 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
             const uint32_t m = __ballot_sync(0xffffffffu, ok);
             if (ok) {
                 const int64_t dst = o + __popc(m & ((1u << lane) - 1u));
-                a.keys[dst] = ((tb + (uint64_t)(y * tg.tiles_x + x)) << 32) | db;
+                a.keys[dst] = ((tb + (uint64_t)(y * tg.tiles_x + x)) << shift) | db;
                 a.values[dst] = id;
             }
             o += __popc(m);
@@ -562,6 +566,13 @@ int32_t check_cfg(const D3gsOpConfig* cfg) {
     D3GS_REQUIRE(cfg->early_filter_algo == 0 || cfg->early_filter_algo == 1 || cfg->early_filter_algo == 3 ||
                      cfg->early_filter_algo == 4,
                  "early_filter_algo %d unsupported (NONE=0, AABB=1, OBB=3, OBB_DFVT=4)", cfg->early_filter_algo);
+    D3GS_REQUIRE(cfg->key_shift_bits == 0 || cfg->key_shift_bits == 32 || cfg->key_shift_bits == 18,
+                 "key_shift_bits must be 32 (64-bit keys) or 18 (32-bit keys), got %d", cfg->key_shift_bits);
+    if (cfg->key_shift_bits == 18) {
+        const int64_t tiles = (int64_t)cfg->num_views * ((cfg->width + 15) / 16) * ((cfg->height + 15) / 16);
+        D3GS_REQUIRE(tiles < (1 << 14), "32-bit sort keys hold 14 bits of tile index: %lld tiles", (long long)tiles);
+        D3GS_REQUIRE(cfg->depth_32bit_prec > 0.0f, "depth_32bit_prec must be positive");
+    }
     return D3GS_OK;
 }
 

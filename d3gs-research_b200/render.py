@@ -272,7 +272,13 @@ class GaussianSplatOp:
         bg = np.asarray(cfg.bg_color, np.float32).reshape(-1)
         for k in range(3):
             c.bg_color[k] = float(bg[k])
+        # enable_32bit_sort (render.py:227-228, 737, 767-770): 14 bits of tile index over an 18-bit quantised depth
+        c.key_shift_bits = 18 if cfg.enable_32bit_sort else 32
+        c.depth_32bit_prec = float(cfg.depth_32bit_prec)
         c.num_views = rows.shape[0]
+        if cfg.enable_32bit_sort:
+            assert rows.shape[0] * div_up(int(w), 16) * div_up(int(h), 16) < 2 ** 14, \
+                "32bit sort only support 14 bits tile idx"
         for b in range(rows.shape[0]):
             cam = c.cameras[b]
             for k in range(12):
@@ -409,7 +415,7 @@ class GaussianSplatOp:
         self._mark("duplicate_keys")
         if self.debug_capture:
             self.debug.update(scan=tiles_touched.clone(), keys=keys.clone(), values=gaussian_idx.clone())
-        end_bit = 32 + lib.d3gs_bit_length(num_tiles)                       # render.py:851-852
+        end_bit = 32 if self._cfg.enable_32bit_sort else 32 + lib.d3gs_bit_length(num_tiles)   # render.py:851-854
         ws_sort = self._ws.get("sort", lib.d3gs_sort_workspace_bytes(num_rendered, 0, end_bit), dev)
         in_alt = C.c_int32(0)
         _lib.check(lib.d3gs_sort_pairs(keys.data_ptr(), keys_alt.data_ptr(), gaussian_idx.data_ptr(),
@@ -424,8 +430,8 @@ class GaussianSplatOp:
         if self.debug_capture:
             self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted)
         workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
-        _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles, stream),
-                   "d3gs_tile_ranges")
+        _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles,
+                                        ocfg.key_shift_bits, stream), "d3gs_tile_ranges")
         self._mark("tile_ranges")
         if self.debug_capture:
             self.debug.update(ranges=workload_ranges)

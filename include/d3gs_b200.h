@@ -70,6 +70,10 @@ typedef struct D3gsOpConfig {
     int32_t fused_activations;              /* 1: normalize/exp/sigmoid applied in-kernel (GaussianModelOriginFused,
                                                origin/model.py:453-462); 0: tensors are already activated */
     float bg_color[3];
+    int32_t key_shift_bits;                 /* 0 or 32: key = tile << 32 | depth bits (64-bit sort keys);
+                                               18: enable_32bit_sort (render.py:737, 767-770): key = tile << 18 |
+                                               (uint32(depth / depth_32bit_prec) & 0x3FFFF), sorted on 32 bits */
+    float depth_32bit_prec;                 /* 0.001, used with key_shift_bits == 18 */
     int32_t num_views;                      /* B */
     D3gsCamera cameras[D3GS_MAX_VIEWS];
 } D3gsOpConfig;
@@ -176,7 +180,8 @@ int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int
 
 /* ---- K5 tile ranges (render.py:896-939) --------------------------------------------------- */
 /* ranges [num_tiles,2] int32 is zero-filled by this call, then [start,end) written per tile */
-int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges, int64_t num_tiles, void* stream);
+int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges, int64_t num_tiles,
+                         int32_t key_shift_bits, void* stream);
 
 /* ---- staging for the rasteriser: gather splats into sorted, contiguous 48-byte records ------
  * (replaces the per-batch gathers of render.py:1702-1716; lets the raster kernels stream their

@@ -89,12 +89,15 @@ class OpConfig:
     scale_global: float = 1.0
     clamp_mask_reference_order: bool = True
     fused_activations: bool = True
+    key_shift: int = 32            # 18: enable_32bit_sort (render.py:737, 767-770)
+    depth_prec: float = 0.001      # depth_32bit_prec
 
     def vec(self) -> np.ndarray:
         return np.array([self.width, self.height, self.tile, self.near, self.far, self.eps, self.eigen_eps,
                          self.clamp_factor, self.sigma, self.lowpass, self.alpha_eps, self.t_eps,
                          self.early_filter, self.sh_degree, int(self.training), self.scale_global,
-                         int(self.clamp_mask_reference_order), int(self.fused_activations), 0, 0], dtype=np.float32)
+                         int(self.clamp_mask_reference_order), int(self.fused_activations), self.key_shift,
+                         self.depth_prec], dtype=np.float32)
 
     @property
     def tiles_xy(self):
@@ -162,9 +165,9 @@ def sort_pairs(keys, vals, end_bit: int):
     return ko, vo
 
 
-def tile_ranges(sorted_keys, num_tiles: int):
+def tile_ranges(sorted_keys, num_tiles: int, shift: int = 32):
     r = np.zeros((num_tiles, 2), np.int32)
-    lib().oracle_tile_ranges(ctypes.c_int64(sorted_keys.size), _p(sorted_keys), _p(r))
+    lib().oracle_tile_ranges(ctypes.c_int64(sorted_keys.size), _p(sorted_keys), _p(r), ctypes.c_int(shift))
     return r
 
 
@@ -262,10 +265,10 @@ def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None) -> IterationR
     scan, total = scan_inclusive(prep["tiles_touched"])
     keys, vals = duplicate_keys(cfg, sc.b, sc.n, scan, total, prep)
     t2 = time.perf_counter()
-    end_bit = 32 + bit_length(sc.b * tx * ty)
+    end_bit = 32 if cfg.key_shift == 18 else 32 + bit_length(sc.b * tx * ty)   # render.py:851-854
     sk, sv = sort_pairs(keys, vals, end_bit)
     t3 = time.perf_counter()
-    ranges = tile_ranges(sk, sc.b * tx * ty)
+    ranges = tile_ranges(sk, sc.b * tx * ty, cfg.key_shift)
     t4 = time.perf_counter()
     color, T, nc = raster_fwd(cfg, sc.b, ranges, sv, prep)
     t5 = time.perf_counter()

@@ -22,8 +22,8 @@ IMG_TOL = 1e-4
 GRAD_TOL = 1e-3
 
 
-def _run_forward(sc, device, early_filter, training=True):
-    op_cfg = d3.GaussianSplatConfig(early_filter_algo=early_filter)
+def _run_forward(sc, device, early_filter, training=True, **cfg_kw):
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=early_filter, **cfg_kw)
     op = d3.GaussianSplatOp(op_cfg)
     op.debug_capture = True
     model = gpu_model(sc, device)
@@ -67,6 +67,26 @@ def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views):
     np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
     assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
     assert_close(out.T.cpu().numpy(), ref.T, IMG_TOL, "T")
+
+
+@pytest.mark.parametrize("views", [1, 3])
+def test_binning_bit_exact_32bit_keys(cuda_device, views):
+    """enable_32bit_sort (render.py:227-228, 737, 767-770, 851-854): key = tile << 18 | 18-bit quantised depth,
+    sorted on 32 bits.  Keys, sorted lists, ranges and contributor counts must equal the oracle's bit for bit;
+    the image follows (a different depth order than with 64-bit keys, the same one as the oracle's)."""
+    sc = small_scene(n=6000, width=200, height=136, sh_degree=2, seed=17, views=views)
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, EarlyFilterAlgo.OBB_DFVT,
+                                                             enable_32bit_sort=True)
+    assert ocfg.key_shift == 18
+    dbg = {k: v.cpu().numpy() for k, v in op.debug.items()}
+    assert int(dbg["keys"].max()) < 2 ** 32 and op.last_num_rendered == ref.num_rendered
+    np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
+    np.testing.assert_array_equal(dbg["values"], ref.vals)
+    np.testing.assert_array_equal(dbg["sorted_keys"].view(np.uint64), ref.sorted_keys)
+    np.testing.assert_array_equal(dbg["sorted_values"], ref.sorted_ids)
+    np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+    assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
 
 
 @pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB_DFVT])

@@ -52,3 +52,22 @@ def test_view_batch_gradient_is_sum_over_views():
         acc = {k: r.grads[k].astype(np.float64) + (0 if acc is None else acc[k]) for k in r.grads}
     for k in acc:
         np.testing.assert_allclose(both.grads[k], acc[k], rtol=1e-4, atol=1e-6 * max(1e-12, np.abs(acc[k]).max()))
+
+
+def test_oracle_32bit_sort_keys():
+    """enable_32bit_sort (render.py:737, 767-770, 851-854): key = tile << 18 | (uint32(depth / 0.001) & 0x3FFFF),
+    sorted on 32 bits; same pairs and ranges as the 64-bit keys, tiles in the same order, depths quantised."""
+    sc = small_scene(n=800, width=96, height=64, sh_degree=1, seed=6, views=2)
+    osc = oracle_scene(sc)
+    r64 = O.forward(O.OpConfig(width=96, height=64, sh_degree=1, early_filter=4), osc)
+    r32 = O.forward(O.OpConfig(width=96, height=64, sh_degree=1, early_filter=4, key_shift=18), osc)
+    assert r32.num_rendered == r64.num_rendered and int(r32.keys.max()) < 2 ** 32
+    np.testing.assert_array_equal(r32.vals, r64.vals)
+    np.testing.assert_array_equal(r32.keys >> np.uint64(18), r64.keys >> np.uint64(32))
+    depth = r64.keys.astype(np.uint32).view(np.float32)      # low 32 bits of the 64-bit keys are the depth's bits
+    np.testing.assert_array_equal(r32.keys & np.uint64(0x3FFFF),
+                                  ((depth / np.float32(0.001)).astype(np.uint32) & 0x3FFFF).astype(np.uint64))
+    assert bool((r32.sorted_keys[1:] >= r32.sorted_keys[:-1]).all())
+    np.testing.assert_array_equal(r32.ranges, r64.ranges)     # the same tiles hold the same number of pairs
+    order = np.argsort(r32.keys, kind="stable")
+    np.testing.assert_array_equal(r32.sorted_ids, r32.vals[order])
