@@ -323,16 +323,29 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
             float cc = (U1[0] * T1[0] + U1[1] * T1[1]) + U1[2] * T1[2];
             ca += cf.gaussian_lowpass_filter;
             cc += cf.gaussian_lowpass_filter;
-            const float det = ca * cc - cb * cb;
-            const float det_inv = 1.0f / (det + cf.eps);
-            const float k0 = cc * det_inv, k1 = -cb * det_inv, k2 = ca * det_inv;
+            float det = ca * cc - cb * cb;
+            float k0, k1, k2, opq = opac;
+            if (cf.anti_aliasing) {
+                // gs3d.py:592-619, render.py:449-462: the conic inverts the low-passed covariance without the eps
+                // guard, `det` becomes the determinant BEFORE the low-pass (it feeds the radius and the validity
+                // test below, as in the reference), and the opacity is scaled by sqrt(det / det_lowpass)
+                const float a0 = ca - cf.gaussian_lowpass_filter, c0 = cc - cf.gaussian_lowpass_filter;
+                const float det_l = det;
+                det = a0 * c0 - cb * cb;
+                const float inv = 1.0f / det_l;
+                k0 = cc * inv; k1 = -cb * inv; k2 = ca * inv;
+                opq = opac * sqrtf(fmaxf(0.000025f, det / det_l));
+            } else {
+                const float det_inv = 1.0f / (det + cf.eps);
+                k0 = cc * det_inv; k1 = -cb * det_inv; k2 = ca * det_inv;
+            }
             const float mid = 0.5f * (ca + cc);
             const float sq = sqrtf(fmaxf(cf.cov2d_radii_eigen_eps, mid * mid - det));
             const float radius = ceilf(cf.gaussian_std_sigma * sqrtf(fmaxf(mid + sq, mid - sq)));
             int rmin[2], rmax[2];
             tile_rect(tg, u, v, radius, rmin, rmax);
             const int area = (rmax[0] - rmin[0]) * (rmax[1] - rmin[1]);
-            if (det <= 0.0f || area == 0 || opac <= cf.alpha_eps) {
+            if (det <= 0.0f || area == 0 || opq <= cf.alpha_eps) {
                 valid = false;
             } else {
                 int cnt = 0;
@@ -342,10 +355,10 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                 const int rw = rmax[0] - rmin[0];
                 const bool small_rect = area <= 64;
                 TileWalk walk;
-                walk.init(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opac, rmin, rmax);
+                walk.init(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, u, v, k0, k1, k2, opq, rmin, rmax);
                 if (walk.area() > kCoopTiles && !small_rect) {   // a small rect keeps its bit mask: walked here
                     big = true;   // counted by the whole warp below
-                    seed.u = u; seed.v = v; seed.ca = k0; seed.cb = k1; seed.cc = k2; seed.opacity = opac;
+                    seed.u = u; seed.v = v; seed.ca = k0; seed.cb = k1; seed.cc = k2; seed.opacity = opq;
                     seed.rmin0 = rmin[0]; seed.rmin1 = rmin[1]; seed.rmax0 = rmax[0]; seed.rmax1 = rmax[1];
                 } else {
                     walk.for_each([&](int x, int y) {
@@ -358,7 +371,7 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                 a.ctx.radii[i] = (int)radius;
                 a.ctx.depths[i] = z;
                 *reinterpret_cast<float2*>(a.ctx.uvs + i * 2) = make_float2(u, v);
-                *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opac);
+                *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opq);
                 if (a.ctx.cov2d_vecs != nullptr) {
                     a.ctx.cov2d_vecs[i * 3] = ca;
                     a.ctx.cov2d_vecs[i * 3 + 1] = cb;

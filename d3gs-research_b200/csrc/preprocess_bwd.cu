@@ -188,9 +188,24 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             const float g0c = gA.x, g1c = gA.y, g2c = gA.z;
             const float det = ca * cc - cb * cb;
             const float d2i = 1.0f / (det * det + 1e-8f);
-            const float da = d2i * (-cc * cc * g0c + cb * cc * g1c + (det - ca * cc) * g2c);
-            const float db = d2i * 2.0f * (cb * cc * g0c - (0.5f * det + cb * cb) * g1c + ca * cb * g2c);
-            const float dc = d2i * (-ca * ca * g2c + ca * cb * g1c + (det - ca * cc) * g0c);
+            float da = d2i * (-cc * cc * g0c + cb * cc * g1c + (det - ca * cc) * g2c);
+            float db = d2i * 2.0f * (cb * cc * g0c - (0.5f * det + cb * cb) * g1c + ca * cb * g2c);
+            float dc = d2i * (-ca * ca * g2c + ca * cb * g1c + (det - ca * cc) * g0c);
+            float gop = gA.w;   // d loss / d (opacity the rasteriser saw)
+            if (cf.anti_aliasing) {
+                // render.py:3295-3309, gs3d.py:621-683: the compensation sqrt(max(2.5e-5, det0 / det)) multiplied
+                // the activated opacity; its gradient reaches the covariance and scales the opacity's own
+                const float lf = cf.gaussian_lowpass_filter;
+                const float det0 = (ca - lf) * (cc - lf) - cb * cb;
+                const float comp = det0 / det;
+                const float cs = sqrtf(fmaxf(0.000025f, comp));
+                const float ddet = comp <= 0.000025f ? 0.0f : (gop * opac) * 0.5f / cs;
+                const float gm = ddet * d2i;
+                da += lf * (cc * cc + cb * cb - cc * lf) * gm;
+                db += -2.0f * cb * lf * (ca + cc - lf) * gm;
+                dc += lf * (ca * ca + cb * cb - ca * lf) * gm;
+                gop = gop * cs;
+            }
             // cov2d = T Sigma T^T (gs3d.py:472-532): dSigma = T^T G T, dT = 2 G T Sigma
             const float hb = 0.5f * db;
             float GT0[3], GT1[3];
@@ -225,7 +240,7 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             float dxyz[3];
 #pragma unroll
             for (int j = 0; j < 3; ++j) dxyz[j] = Rt[j] * dp0 + Rt[3 + j] * dp1 + Rt[6 + j] * dp2;
-            ao += gA.w;
+            ao += gop;
             // colour (render.py:3341-3355)
             const float dn = sqrtf(d0 * d0 + d1 * d1 + d2 * d2);
             const float dni = 1.0f / dn;

@@ -275,6 +275,7 @@ class GaussianSplatOp:
         # enable_32bit_sort (render.py:227-228, 737, 767-770): 14 bits of tile index over an 18-bit quantised depth
         c.key_shift_bits = 18 if cfg.enable_32bit_sort else 32
         c.depth_32bit_prec = float(cfg.depth_32bit_prec)
+        c.anti_aliasing = int(bool(cfg.enable_anti_aliasing))
         c.num_views = rows.shape[0]
         if cfg.enable_32bit_sort:
             assert rows.shape[0] * div_up(int(w), 16) * div_up(int(h), 16) < 2 ** 14, \

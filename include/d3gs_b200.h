@@ -74,6 +74,9 @@ typedef struct D3gsOpConfig {
                                                18: enable_32bit_sort (render.py:737, 767-770): key = tile << 18 |
                                                (uint32(depth / depth_32bit_prec) & 0x3FFFF), sorted on 32 bits */
     float depth_32bit_prec;                 /* 0.001, used with key_shift_bits == 18 */
+    int32_t anti_aliasing;                  /* enable_anti_aliasing (render.py:391-406, 449-462; gs3d.py:592-619):
+                                               conic = inverse of the low-passed covariance without the eps guard,
+                                               opacity *= sqrt(max(2.5e-5, det(cov) / det(cov + lowpass I))) */
     int32_t num_views;                      /* B */
     D3gsCamera cameras[D3GS_MAX_VIEWS];
 } D3gsOpConfig;

@@ -91,13 +91,14 @@ class OpConfig:
     fused_activations: bool = True
     key_shift: int = 32            # 18: enable_32bit_sort (render.py:737, 767-770)
     depth_prec: float = 0.001      # depth_32bit_prec
+    anti_aliasing: bool = False    # enable_anti_aliasing (render.py:391-406, 449-462)
 
     def vec(self) -> np.ndarray:
         return np.array([self.width, self.height, self.tile, self.near, self.far, self.eps, self.eigen_eps,
                          self.clamp_factor, self.sigma, self.lowpass, self.alpha_eps, self.t_eps,
                          self.early_filter, self.sh_degree, int(self.training), self.scale_global,
                          int(self.clamp_mask_reference_order), int(self.fused_activations), self.key_shift,
-                         self.depth_prec], dtype=np.float32)
+                         self.depth_prec, int(self.anti_aliasing), 0, 0, 0], dtype=np.float32)
 
     @property
     def tiles_xy(self):

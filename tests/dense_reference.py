@@ -35,7 +35,7 @@ def sh_basis(deg, d):
 
 
 def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True, tile=16, near=0.2, far=1e4,
-                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4):
+                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4, anti_aliasing=False):
     """params: dict of float64 leaf tensors (xyz, quat, scale, opacity, sh_base, sh_rest).
     Returns color [H,W,3], T [H,W], n_valid (visible mask [N])."""
     xyz, quat, scale, opac = params["xyz"], params["quat"], params["scale"], params["opacity"]
@@ -77,6 +77,13 @@ def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True
     # (gs3d.py:549 vs 575); on well-conditioned inputs both agree far below the test tolerance.
     det_inv = 1.0 / (det + 1e-6)
     ca, cb, ccn = cc * det_inv, -b * det_inv, a * det_inv
+    if anti_aliasing:
+        # d3sim/csrc/gs3d.py:592-619, d3sim/algos/d3gs/render.py:449-462: no eps guard on the inverse, the
+        # determinant before the low-pass drives radius and validity, opacity *= sqrt(max(2.5e-5, det/det_lowpass))
+        det_l = det
+        det = (a - lowpass) * (cc - lowpass) - b * b
+        ca, cb, ccn = cc / det_l, -b / det_l, a / det_l
+        o = o * torch.sqrt(torch.clamp(det / det_l, min=0.000025))
     with torch.no_grad():
         mid = 0.5 * (a + cc)
         sq = torch.sqrt(torch.clamp(mid * mid - det, min=0.1))

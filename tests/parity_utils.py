@@ -31,7 +31,8 @@ def oracle_cfg(sc, op_cfg: "d3.GaussianSplatConfig", training=True) -> O.OpConfi
     return O.OpConfig(width=c.width, height=c.height, sh_degree=c.sh_degree, early_filter=int(op_cfg.early_filter_algo),
                       training=training, clamp_mask_reference_order=op_cfg.clamp_mask_reference_order,
                       near=op_cfg.near, far=op_cfg.far, scale_global=op_cfg.scale_global,
-                      key_shift=18 if op_cfg.enable_32bit_sort else 32, depth_prec=op_cfg.depth_32bit_prec)
+                      key_shift=18 if op_cfg.enable_32bit_sort else 32, depth_prec=op_cfg.depth_32bit_prec,
+                      anti_aliasing=op_cfg.enable_anti_aliasing)
 
 
 def gpu_model(sc, device, flat=True, requires_grad=False):

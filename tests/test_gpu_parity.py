@@ -149,6 +149,38 @@ def test_backward_gradients(cuda_device, early_filter, views, ref_order):
         assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
 
 
+@pytest.mark.parametrize("early_filter,views", [(EarlyFilterAlgo.OBB_DFVT, 1), (EarlyFilterAlgo.NONE, 2)])
+def test_anti_aliasing_parity(cuda_device, early_filter, views):
+    """enable_anti_aliasing (render.py:391-406, 449-462, 3295-3309; gs3d.py:592-683): the compensated opacity and
+    the un-guarded conic must equal the oracle's bit for bit (they decide tile counts and contributors), the
+    gradients, including the compensation's path into the covariance, within the gradient tolerance."""
+    sc = small_scene(n=5000, width=176, height=120, sh_degree=3, seed=23, views=views)
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter, enable_anti_aliasing=True)
+    assert ocfg.anti_aliasing
+    base = O.forward(oracle_cfg(sc, d3.GaussianSplatConfig(early_filter_algo=early_filter)), osc)
+    assert not np.array_equal(base.prep["conic_opacity"], ref.prep["conic_opacity"])   # the option changes the result
+    dbg = {k: v.cpu().numpy() for k, v in op.debug.items()}
+    np.testing.assert_array_equal(dbg["tiles_touched"], ref.prep["tiles_touched"])
+    np.testing.assert_array_equal(ctx.radii.cpu().numpy(), ref.prep["radii"])
+    vis = ref.prep["radii"] > 0
+    np.testing.assert_array_equal(ctx.conic_opacity.cpu().numpy()[vis].view(np.uint32),
+                                  ref.prep["conic_opacity"][vis].view(np.uint32))
+    np.testing.assert_array_equal(dbg["sorted_values"], ref.sorted_ids)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+    assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
+    g = torch.Generator().manual_seed(7)
+    c = sc["cfg"]
+    drgb = torch.randn(views, c.height, c.width, 3, generator=g)
+    dT = torch.randn(views, c.height, c.width, generator=g)
+    gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=drgb.to(cuda_device), dT=dT.to(cuda_device)),
+                             return_uv_grad=True)
+    torch.cuda.synchronize()
+    O.backward(ocfg, osc, ref, drgb.numpy(), dT.numpy())
+    for name, ours in (("xyz", gm.xyz), ("quat", gm.quaternion_xyzw), ("scale", gm.scale), ("opacity", gm.opacity),
+                       ("sh_base", gm.color_sh_base), ("sh_rest", gm.color_sh)):
+        assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
+
+
 @pytest.mark.parametrize("width,height,views", [(177, 121, 1), (64, 33, 2)])
 def test_record_staging_modes_agree(cuda_device, width, height, views):
     """The raster kernels stage their records either by gathering from the per-Gaussian table the preprocess

@@ -9,12 +9,15 @@ from oracle import oracle as O
 from parity_utils import oracle_scene, small_scene
 
 
-@pytest.mark.parametrize("deg,early_filter,ref_order", [(0, 0, True), (3, 0, True), (3, 3, True), (2, 1, False)])
-def test_oracle_matches_dense_autograd(deg, early_filter, ref_order):
+@pytest.mark.parametrize("deg,early_filter,ref_order,aa", [(0, 0, True, False), (3, 0, True, False), (3, 3, True, False),
+                                                             (2, 1, False, False), (1, 0, True, True), (3, 4, True, True)])
+def test_oracle_matches_dense_autograd(deg, early_filter, ref_order, aa):
+    """aa: enable_anti_aliasing, the opacity compensation of render.py:449-462 and its gradient (3295-3309)."""
     W, H = 48, 40
     sc = small_scene(n=150, width=W, height=H, sh_degree=deg, seed=10 + deg, log_scale=("normal", -1.8, 0.5), sh_gain=6.0)
     osc = oracle_scene(sc)
-    cfg = O.OpConfig(width=W, height=H, sh_degree=deg, early_filter=early_filter, clamp_mask_reference_order=ref_order)
+    cfg = O.OpConfig(width=W, height=H, sh_degree=deg, early_filter=early_filter, clamp_mask_reference_order=ref_order,
+                     anti_aliasing=aa)
     res = O.forward(cfg, osc)
     g = torch.Generator().manual_seed(5)
     drgb = torch.randn(1, H, W, 3, generator=g).numpy().astype(np.float32)
@@ -22,7 +25,7 @@ def test_oracle_matches_dense_autograd(deg, early_filter, ref_order):
     O.backward(cfg, osc, res, drgb, dT)
     params = {k: torch.tensor(getattr(osc, k), dtype=torch.float64, requires_grad=True)
               for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")}
-    C, T, vis = render_dense(params, osc.cams[0], W, H, deg, clamp_mask_reference_order=ref_order)
+    C, T, vis = render_dense(params, osc.cams[0], W, H, deg, clamp_mask_reference_order=ref_order, anti_aliasing=aa)
     assert int(vis.sum()) == int((res.prep["radii"] > 0).sum())
     assert np.abs(C.detach().numpy() - res.color[0]).max() < 2e-5
     assert np.abs(T.detach().numpy() - res.T[0]).max() < 2e-5
