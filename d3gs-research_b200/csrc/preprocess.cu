@@ -511,10 +511,13 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
         if (a.ctx.tile_mask != nullptr && rw * (rmax[1] - rmin[1]) <= 64) {
             // the preprocess left the accepted tiles as a row-major bit mask over the 3-sigma rect
             uint64_t m = a.ctx.tile_mask[i];
+            // bit / rw by one multiplication: exact for bit < 64 and rw <= 64
+            const uint32_t rcp = (65536u + (uint32_t)max(rw, 1) - 1u) / (uint32_t)max(rw, 1);
             while (m) {
                 const int bit = __ffsll((long long)m) - 1;
                 m &= m - 1;
-                const int y = rmin[1] + bit / rw, x = rmin[0] + bit % rw;
+                const int by = (int)(((uint32_t)bit * rcp) >> 16);
+                const int y = rmin[1] + by, x = rmin[0] + (bit - by * rw);
                 const uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
                 a.keys[off] = (key << shift) | dbits;
                 a.values[off] = (int32_t)i;
