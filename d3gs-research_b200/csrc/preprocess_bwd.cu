@@ -29,7 +29,6 @@ struct BwdArgs {
     float* exp_avg[6];
     float* exp_avg_sq[6];
     int32_t has_stats;
-    int32_t variant;   // experiment switch
     D3gsDensifyStats stats;
 };
 
@@ -93,15 +92,6 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
         const uint32_t bytes = (uint32_t)(rows * per) * 4u;
         if ((bytes & 15u) == 0 && ((uintptr_t)ptr & 15) == 0)
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-    }
-    if (ADAM && (a.variant & 12) && (t == 64 || t == 65)) {
-        const int arr = t - 64;
-        if ((a.variant >> (2 + arr)) & 1) {
-            const float* ptr = (arr == 0 ? a.exp_avg[5] : a.exp_avg_sq[5]) + g0 * 45;
-            const uint32_t bytes = (uint32_t)(rows * 45) * 4u;
-            if ((bytes & 15u) == 0 && ((uintptr_t)ptr & 15) == 0)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-        }
     }
     __syncthreads();
     if constexpr (NR3 > 0) {
@@ -381,13 +371,8 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
                         const int q = q0 + u * 256;
                         if (q < count / 4) {
                             p[u] = reinterpret_cast<const float4*>(pp)[q];
-                            if (a.variant & 1) {
-                                m[u] = __ldcs(reinterpret_cast<const float4*>(pm) + q);
-                                v[u] = __ldcs(reinterpret_cast<const float4*>(pv) + q);
-                            } else {
-                                m[u] = reinterpret_cast<const float4*>(pm)[q];
-                                v[u] = reinterpret_cast<const float4*>(pv)[q];
-                            }
+                            m[u] = reinterpret_cast<const float4*>(pm)[q];
+                            v[u] = reinterpret_cast<const float4*>(pv)[q];
                         }
                     }
 #pragma unroll
@@ -406,15 +391,9 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
                             adam_update(gr.y, p[u].y, m[u].y, v[u].y, c);
                             adam_update(gr.z, p[u].z, m[u].z, v[u].z, c);
                             adam_update(gr.w, p[u].w, m[u].w, v[u].w, c);
-                            if (a.variant & 2) __stcs(reinterpret_cast<float4*>(pp) + q, p[u]);
-                            else reinterpret_cast<float4*>(pp)[q] = p[u];
-                            if (a.variant & 1) {
-                                __stcs(reinterpret_cast<float4*>(pm) + q, m[u]);
-                                __stcs(reinterpret_cast<float4*>(pv) + q, v[u]);
-                            } else {
-                                reinterpret_cast<float4*>(pm)[q] = m[u];
-                                reinterpret_cast<float4*>(pv)[q] = v[u];
-                            }
+                            reinterpret_cast<float4*>(pp)[q] = p[u];
+                            reinterpret_cast<float4*>(pm)[q] = m[u];
+                            reinterpret_cast<float4*>(pv)[q] = v[u];
                         }
                     }
                 }
@@ -569,7 +548,6 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
     a.model = *model;
     a.ctx = *ctx;
     a.splat_grads = splat_grads;
-    { const char* e = getenv("D3GS_BWD_VARIANT"); a.variant = e ? atoi(e) : 0; }
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)256 * (kRow + 14) * sizeof(float);   // SH rows + the 14 small-field gradients
