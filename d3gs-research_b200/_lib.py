@@ -30,7 +30,7 @@ class OpConfig(C.Structure):
                 ("transmittance_eps", C.c_float), ("scale_global", C.c_float), ("early_filter_algo", C.c_int32),
                 ("sh_degree", C.c_int32), ("training", C.c_int32), ("clamp_mask_reference_order", C.c_int32),
                 ("fused_activations", C.c_int32),
-                ("bg_color", C.c_float * 3), ("key_shift_bits", C.c_int32), ("depth_32bit_prec", C.c_float), ("anti_aliasing", C.c_int32),
+                ("bg_color", C.c_float * 3), ("key_shift_bits", C.c_int32), ("depth_32bit_prec", C.c_float), ("anti_aliasing", C.c_int32), ("inv_depth", C.c_int32),
                 ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS)]
 
 

@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                 if (a.ctx.tile_mask != nullptr) a.ctx.tile_mask[i] = tmask;
                 a.ctx.tiles_touched[i] = cnt;
                 a.ctx.radii[i] = (int)radius;
-                a.ctx.depths[i] = z;
+                a.ctx.depths[i] = cf.inv_depth ? 1.0f / z : z;   // render.py:582 (this array also feeds the sort keys)
                 *reinterpret_cast<float2*>(a.ctx.uvs + i * 2) = make_float2(u, v);
                 *reinterpret_cast<float4*>(a.ctx.conic_opacity + i * 4) = make_float4(k0, k1, k2, opq);
                 if (a.ctx.cov2d_vecs != nullptr) {

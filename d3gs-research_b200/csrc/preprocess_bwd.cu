@@ -23,7 +23,7 @@ struct BwdArgs {
     D3gsModel model;
     D3gsSplatContext ctx;
     D3gsModelGrad grad;
-    const float* splat_grads;   // [B*N, 12]: dconic a b c, dopacity | dcolor r g b, - | duv x y, - -
+    const float* splat_grads;   // [B*N, 12]: dconic a b c, dopacity | dcolor r g b, dz | duv x y, - -
     // fused optimizer step (ADAM variant): per field xyz, quaternion, scale, opacity, sh_base, sh_rest
     SegConst sc[6];
     float* exp_avg[6];
@@ -236,7 +236,10 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             // pinhole (camera.py:335-371)
             const float du = gC.x * cam.fx, dv = gC.y * cam.fy;
             const float dp0 = du * zi + dm0, dp1 = dv * zi + dm1;
-            const float dp2 = -(du * pc0 + dv * pc1) * z2i + dm2;
+            // gB.w: gradient of this splat's depth value when a depth image was rendered (zero otherwise);
+            // the depth value is z, or 1/z with render_inv_depth (render.py:3053-3057)
+            const float dzv = cf.inv_depth ? -gB.w * z2i : gB.w;
+            const float dp2 = -(du * pc0 + dv * pc1) * z2i + dm2 + dzv;
             float dxyz[3];
 #pragma unroll
             for (int j = 0; j < 3; ++j) dxyz[j] = Rt[j] * dp0 + Rt[3 + j] * dp1 + Rt[6 + j] * dp2;

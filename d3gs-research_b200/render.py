@@ -49,6 +49,8 @@ class GaussianSplatOpContext:
     tile_order: torch.Tensor | None = None
     records_by_id: bool = False   # splat_records is the per-Gaussian table (gathered by sorted id), not per pair
     raster_color: torch.Tensor | None = None   # the kernels' [B,H,W,3] colour when out.color is a re-formatted copy
+    depth_records: torch.Tensor | None = None  # render_depth: the records with (depth value, 0, 0) as the colour
+    depth_color: torch.Tensor | None = None    # render_depth: [B,H,W,3] blend of those records (channel 0 = depth sum)
 
 
 @dataclasses.dataclass
@@ -276,6 +278,7 @@ class GaussianSplatOp:
         c.key_shift_bits = 18 if cfg.enable_32bit_sort else 32
         c.depth_32bit_prec = float(cfg.depth_32bit_prec)
         c.anti_aliasing = int(bool(cfg.enable_anti_aliasing))
+        c.inv_depth = int(bool(cfg.render_inv_depth))
         c.num_views = rows.shape[0]
         if cfg.enable_32bit_sort:
             assert rows.shape[0] * div_up(int(w), 16) * div_up(int(h), 16) < 2 ** 14, \
@@ -452,8 +455,28 @@ class GaussianSplatOp:
                                            out_color.data_ptr(), final_T.data_ptr(),
                                            n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
         self._mark("raster_fwd")
+        depth = depth_records = depth_color = None
+        if self._cfg.render_depth:
+            # render.py:1824, 2244-2255: depth_accum += weight * depth_val.  The depth value is blended exactly like
+            # a colour channel, so the depth image is a second forward pass over the same lists with
+            # (depth value, 0, 0) in the records' colour slots (never composited or clamped: training mode).
+            depth_records = records.clone()
+            depth_records[:, 8] = depths if gather else depths[gaussian_idx_sorted.long()]
+            depth_records[:, 9:11] = 0.0
+            ocfg_d = _lib.OpConfig.from_buffer_copy(ocfg)
+            ocfg_d.training = 1
+            depth_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
+            _lib.check(lib.d3gs_raster_forward(C.byref(ocfg_d), workload_ranges.data_ptr(), tile_order.data_ptr(),
+                                               depth_records.data_ptr(),
+                                               gaussian_idx_sorted.data_ptr() if gather else None,
+                                               depth_color.data_ptr(), torch.empty_like(final_T).data_ptr(),
+                                               torch.empty_like(n_contrib).data_ptr(), sync.data_ptr() + 8, stream),
+                       "d3gs_raster_forward(depth)")
+            depth = depth_color[..., 0]
+            depth = depth.contiguous() if training else depth / (1e-10 + 1.0 - final_T)
+            self._mark("raster_fwd_depth")
         output = GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
-                                     depth=None, n_contrib=n_contrib, radii=radii)
+                                     depth=depth, n_contrib=n_contrib, radii=radii)
         if not training:
             return output, None
         ctx = GaussianSplatOpContext(conic_opacity=conic_opacity, radii=radii, uvs=uvs, rgb_gaussian=rgb_gaussian,
@@ -461,7 +484,8 @@ class GaussianSplatOp:
                                      image_shape_wh=(W, H), depths=depths, cov2d_vecs=cov2d_vecs,
                                      sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order,
                                      records_by_id=gather,
-                                     raster_color=out_color if output.color is not out_color else None)
+                                     raster_color=out_color if output.color is not out_color else None,
+                                     depth_records=depth_records, depth_color=depth_color)
         return output, ctx
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
@@ -499,9 +523,28 @@ class GaussianSplatOp:
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
                                             stream), "d3gs_raster_backward")
         self._mark("raster_bwd")
+        dz = None
+        if grad.ddepth is not None:
+            # render.py:1948-1967: the raster backward is linear in (drgb, ddepth, dT); the depth channel's share
+            # is a second pass with the depth records, whose "colour" gradient of channel 0 is dL/d(depth value)
+            assert ctx.depth_records is not None, "ddepth needs an operator configured with render_depth"
+            dcol = torch.zeros([B, H, W, 3], dtype=torch.float32, device=dev)
+            dcol[..., 0] = grad.ddepth
+            packed2 = torch.empty([BN, 12], dtype=torch.float32, device=dev)
+            _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
+                                                _lib.ptr(ctx.tile_order), ctx.depth_records.data_ptr(),
+                                                int(ctx.records_by_id), ctx.gaussian_idx_sorted.data_ptr(),
+                                                ctx.depth_color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
+                                                dcol.data_ptr(), None, packed2.data_ptr(), sync.data_ptr() + 8,
+                                                stream), "d3gs_raster_backward(depth)")
+            packed[:, 0:4] += packed2[:, 0:4]
+            packed[:, 8:10] += packed2[:, 8:10]
+            packed[:, 7] = packed2[:, 4]     # slot 7: dz, consumed by the preprocess backward
+            dz = packed[:, 7]
+            self._mark("raster_bwd_depth")
         # the reference's four tensors (render.py:1412-1418) are views of the packed array
         return RasterizeGradientOutput(duv=packed[:, 8:10], dconic=packed[:, 0:3], dopacity=packed[:, 3],
-                                       dcolor=packed[:, 4:7], packed=packed)
+                                       dcolor=packed[:, 4:7], dz=dz, packed=packed)
 
     # ---- backward (render.py:2779-3374) --------------------------------------------------------
     def backward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
@@ -612,7 +655,7 @@ class _RasterizeGaussians(torch.autograd.Function):
             drgb = torch.zeros_like(ctx.out.color)
         if not drgb.is_contiguous():
             drgb = drgb.contiguous()
-        gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=None, dcustom_features=None)
+        gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=ddepth, dcustom_features=None)
         gm, duv, _ = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad)
         return (gm.xyz, gm.color_sh, gm.color_sh_base, gm.scale, gm.quaternion_xyzw, gm.opacity, None, None, None,
                 None, None, None, None, None, None, None, None, duv)

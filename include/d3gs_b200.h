@@ -77,6 +77,8 @@ typedef struct D3gsOpConfig {
     int32_t anti_aliasing;                  /* enable_anti_aliasing (render.py:391-406, 449-462; gs3d.py:592-619):
                                                conic = inverse of the low-passed covariance without the eps guard,
                                                opacity *= sqrt(max(2.5e-5, det(cov) / det(cov + lowpass I))) */
+    int32_t inv_depth;                      /* render_inv_depth (render.py:582): ctx.depths holds 1/z, which, as in the
+                                               reference, is also the value the sort keys are built from */
     int32_t num_views;                      /* B */
     D3gsCamera cameras[D3GS_MAX_VIEWS];
 } D3gsOpConfig;
@@ -209,7 +211,7 @@ int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, cons
 /* ---- K7 raster backward (render.py:1589-1676, 1774-2210) -------------------------------- */
 /* drgb [B,H,W,3], dT [B,H,W] or NULL.  The reference's four per-splat gradient tensors (duv, dconic,
  * dopacity, dcolor, render.py:1388-1401) are one packed array here so that the kernel can use 16-byte
- * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, 0 | duv x,y, 0, 0},
+ * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, dz | duv x,y, 0, 0},
  * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort.
  * records_by_id != 0: records is the per-Gaussian table (see d3gs_raster_forward), else the per-pair records. */
 int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const int32_t* tile_order,
@@ -218,7 +220,9 @@ int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t
                              float* splat_grads, uint32_t* status, void* stream);
 
 /* ---- K8 preprocess backward (render.py:2779-3374) ---------------------------------------- */
-/* every gradient element is written (zeros for culled Gaussians); sums over the view batch */
+/* every gradient element is written (zeros for culled Gaussians); sums over the view batch.  Slot 7 of a
+ * splat_grads row (zero after d3gs_raster_backward) is dz, the gradient of the splat's depth value when a
+ * depth image was rendered (render.py:3053-3057): it joins the camera-space z gradient. */
 int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
                                  const float* splat_grads, const D3gsModelGrad* grad, void* stream);
 

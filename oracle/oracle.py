@@ -13,7 +13,7 @@ import ctypes
 import os
 import subprocess
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace as dataclass_replace
 
 import numpy as np
 
@@ -92,13 +92,14 @@ class OpConfig:
     key_shift: int = 32            # 18: enable_32bit_sort (render.py:737, 767-770)
     depth_prec: float = 0.001      # depth_32bit_prec
     anti_aliasing: bool = False    # enable_anti_aliasing (render.py:391-406, 449-462)
+    inv_depth: bool = False        # render_inv_depth: the depth array holds 1/z (render.py:582)
 
     def vec(self) -> np.ndarray:
         return np.array([self.width, self.height, self.tile, self.near, self.far, self.eps, self.eigen_eps,
                          self.clamp_factor, self.sigma, self.lowpass, self.alpha_eps, self.t_eps,
                          self.early_filter, self.sh_degree, int(self.training), self.scale_global,
                          int(self.clamp_mask_reference_order), int(self.fused_activations), self.key_shift,
-                         self.depth_prec, int(self.anti_aliasing), 0, 0, 0], dtype=np.float32)
+                         self.depth_prec, int(self.anti_aliasing), int(self.inv_depth), 0, 0], dtype=np.float32)
 
     @property
     def tiles_xy(self):
@@ -198,8 +199,9 @@ def raster_bwd(cfg: OpConfig, b: int, bn: int, ranges, sorted_ids, prep, color, 
     return dict(duv=duv, dconic=dconic, dopacity=dop, dcolor=dcol)
 
 
-def preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg):
+def preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg, dz=None):
     n = sc.n
+    dz = None if dz is None else _f32(dz)   # [B*N]: d loss / d depth value of every splat (render_depth)
     g = dict(xyz=np.zeros((n, 3), np.float32), quat=np.zeros((n, 4), np.float32),
              scale=np.zeros((n, 3), np.float32), opacity=np.zeros(n, np.float32),
              sh_base=np.zeros((n, 3), np.float32), sh_rest=np.zeros((n, 15, 3), np.float32))
@@ -207,7 +209,8 @@ def preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg):
     lib().oracle_preprocess_bwd(_p(cv), ctypes.c_int(sc.b), ctypes.c_int(n), _p(sc.cams), _p(sc.xyz), _p(sc.quat),
                                 _p(sc.scale), _p(sc.opacity), _p(sc.sh_rest), _p(prep["radii"]), _p(prep["cov2d"]),
                                 _p(prep["ne0"]), _p(rg["duv"]), _p(rg["dconic"]), _p(rg["dopacity"]),
-                                _p(rg["dcolor"]), _p(g["xyz"]), _p(g["quat"]), _p(g["scale"]), _p(g["opacity"]),
+                                _p(rg["dcolor"]), _p(dz), _p(g["xyz"]), _p(g["quat"]),
+                                _p(g["scale"]), _p(g["opacity"]),
                                 _p(g["sh_base"]), _p(g["sh_rest"]))
     return g
 
@@ -249,6 +252,7 @@ class IterationResult:
     color: np.ndarray
     T: np.ndarray
     n_contrib: np.ndarray
+    depth: np.ndarray | None = None          # render_depth: [B,H,W]
     loss: np.ndarray | None = None
     drgb: np.ndarray | None = None
     raster_grads: dict | None = None
@@ -256,7 +260,24 @@ class IterationResult:
     timings: dict = field(default_factory=dict)
 
 
-def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None) -> IterationResult:
+def _depth_prep(prep):
+    """The depth channel is blended like a colour (render.py:1824: depth_accum += weight * depth_val): a copy of
+    the per-Gaussian context whose colour is (depth value, 0, 0)."""
+    p2 = dict(prep)
+    rgb = np.zeros_like(prep["rgb"])
+    rgb[:, 0] = prep["depths"]
+    p2["rgb"] = rgb
+    return p2
+
+
+def raster_depth(cfg: OpConfig, b: int, ranges, sorted_ids, prep, T):
+    """render.py:2244-2255: sum_i w_i depth_i in training, divided by (1e-10 + 1 - T) at inference."""
+    acc, _, _ = raster_fwd(dataclass_replace(cfg, training=True), b, ranges, sorted_ids, _depth_prep(prep))
+    acc = np.ascontiguousarray(acc[..., 0])
+    return acc if cfg.training else acc / (np.float32(1e-10) + np.float32(1.0) - T)
+
+
+def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None, render_depth: bool = False) -> IterationResult:
     """preprocess -> scan -> keys -> sort -> ranges -> raster (render.py:169-1015)."""
     tm = {} if timings is None else timings
     tx, ty = cfg.tiles_xy
@@ -274,17 +295,33 @@ def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None) -> IterationR
     color, T, nc = raster_fwd(cfg, sc.b, ranges, sv, prep)
     t5 = time.perf_counter()
     tm.update(preprocess=t1 - t0, scan_keys=t2 - t1, sort=t3 - t2, ranges=t4 - t3, raster_fwd=t5 - t4)
-    return IterationResult(prep, scan, total, keys, vals, sk, sv, ranges, color, T, nc, timings=tm)
+    depth = raster_depth(cfg, sc.b, ranges, sv, prep, T) if render_depth else None
+    return IterationResult(prep, scan, total, keys, vals, sk, sv, ranges, color, T, nc, depth=depth, timings=tm)
 
 
-def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None) -> IterationResult:
-    """raster backward -> preprocess backward (render.py:2779-3374)."""
+def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None, ddepth=None) -> IterationResult:
+    """raster backward -> preprocess backward (render.py:2779-3374).  ddepth [B,H,W]: gradient of the rendered
+    depth (training output, the un-normalised sum); the raster backward is linear in (drgb, ddepth, dT), so the
+    depth channel's part is a second pass with the depth value as the colour (render.py:1948-1967)."""
     t0 = time.perf_counter()
     res.drgb = _f32(drgb)
     res.raster_grads = raster_bwd(cfg, sc.b, sc.b * sc.n, res.ranges, res.sorted_ids, res.prep, res.color, res.T,
                                   res.n_contrib, res.drgb, dT)
+    dz = None
+    if ddepth is not None:
+        assert res.depth is not None and cfg.training
+        col = np.zeros(res.color.shape, np.float32)
+        col[..., 0] = res.depth
+        dcol = np.zeros(res.color.shape, np.float32)
+        dcol[..., 0] = ddepth
+        rg2 = raster_bwd(cfg, sc.b, sc.b * sc.n, res.ranges, res.sorted_ids, _depth_prep(res.prep), col, res.T,
+                         res.n_contrib, dcol, None)
+        for k in ("duv", "dconic", "dopacity"):
+            res.raster_grads[k] = res.raster_grads[k] + rg2[k]
+        dz = np.ascontiguousarray(rg2["dcolor"][:, 0])
+        res.raster_grads["dz"] = dz
     t1 = time.perf_counter()
-    res.grads = preprocess_bwd(cfg, sc, res.prep, res.raster_grads)
+    res.grads = preprocess_bwd(cfg, sc, res.prep, res.raster_grads, dz)
     t2 = time.perf_counter()
     res.timings.update(raster_bwd=t1 - t0, preprocess_bwd=t2 - t1)
     return res

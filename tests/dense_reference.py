@@ -35,9 +35,11 @@ def sh_basis(deg, d):
 
 
 def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True, tile=16, near=0.2, far=1e4,
-                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4, anti_aliasing=False):
+                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4, anti_aliasing=False, depth_mode=None):
     """params: dict of float64 leaf tensors (xyz, quat, scale, opacity, sh_base, sh_rest).
-    Returns color [H,W,3], T [H,W], n_valid (visible mask [N])."""
+    Returns color [H,W,3], T [H,W], n_valid (visible mask [N]); with depth_mode "z" or "inv" also the blended
+    depth value sum_i w_i d_i [H,W] (d3sim/algos/d3gs/render.py:1824, 2244-2255 in training).  "inv": the depth
+    value is 1/z AND, as in the reference, that value is what the splats are sorted by (render.py:582, 773)."""
     xyz, quat, scale, opac = params["xyz"], params["quat"], params["scale"], params["opacity"]
     cam16 = torch.as_tensor(cam16, dtype=torch.float64)
     Rt = cam16[:9].reshape(3, 3)            # rows: columns of R_c2w  == world->cam rotation
@@ -107,11 +109,13 @@ def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True
         gate = torch.stack([neg[:, 2], neg[:, 1], neg[:, 0]], dim=1)
         rgb_val = rgb.detach()
         rgb = torch.where(gate, rgb_val, rgb_val + (rgb_raw - rgb_raw.detach()))
-    order = torch.argsort(z.detach(), stable=True)
+    dval = (1.0 / z) if depth_mode == "inv" else z
+    order = torch.argsort((dval if depth_mode == "inv" else z).detach(), stable=True)
     ys, xs = torch.meshgrid(torch.arange(H, dtype=torch.float64), torch.arange(W, dtype=torch.float64), indexing="ij")
     tyi, txi = (ys // tile), (xs // tile)
     T = torch.ones(H, W, dtype=torch.float64)
     C = torch.zeros(H, W, 3, dtype=torch.float64)
+    D = torch.zeros(H, W, dtype=torch.float64)
     done = torch.zeros(H, W, dtype=torch.bool)
     for g in order.tolist():
         if not bool(visible[g]):
@@ -129,7 +133,10 @@ def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True
             ok = ok & ~should_done & (power <= 0)
         w = torch.where(ok, alpha * T, torch.zeros_like(T))
         C = C + w[:, :, None] * rgb[g]
+        D = D + w * dval[g]
         T = torch.where(ok, T * (1 - alpha), T)
+    if depth_mode is not None:
+        return C, T, visible, D
     return C, T, visible
 
 

@@ -32,7 +32,7 @@ def oracle_cfg(sc, op_cfg: "d3.GaussianSplatConfig", training=True) -> O.OpConfi
                       training=training, clamp_mask_reference_order=op_cfg.clamp_mask_reference_order,
                       near=op_cfg.near, far=op_cfg.far, scale_global=op_cfg.scale_global,
                       key_shift=18 if op_cfg.enable_32bit_sort else 32, depth_prec=op_cfg.depth_32bit_prec,
-                      anti_aliasing=op_cfg.enable_anti_aliasing)
+                      anti_aliasing=op_cfg.enable_anti_aliasing, inv_depth=op_cfg.render_inv_depth)
 
 
 def gpu_model(sc, device, flat=True, requires_grad=False):

@@ -181,6 +181,46 @@ def test_anti_aliasing_parity(cuda_device, early_filter, views):
         assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
 
 
+@pytest.mark.parametrize("inv,gather,views", [(False, True, 2), (True, True, 1), (False, False, 1)])
+def test_render_depth_parity(cuda_device, inv, gather, views):
+    """render_depth / render_inv_depth (render.py:582, 1824, 1948-1967, 2244-2255, 3053-3057): the blended depth
+    value in training, its normalised form at inference, and the gradient a depth loss sends to the parameters.
+    With render_inv_depth the depth array holds 1/z and, as in the reference, the sort keys are built from it."""
+    sc = small_scene(n=4000, width=160, height=104, sh_degree=2, seed=29, views=views)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, render_depth=True, render_inv_depth=inv)
+    op = d3.GaussianSplatOp(op_cfg)
+    op.gather_records = gather
+    op.debug_capture = True
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    cams = gpu_cameras(sc, cuda_device)
+    out, ctx = op.forward(model, cams, training=True)
+    ocfg = oracle_cfg(sc, op_cfg)
+    osc = oracle_scene(sc)
+    ref = O.forward(ocfg, osc, render_depth=True)
+    np.testing.assert_array_equal(op.debug["sorted_values"].cpu().numpy(), ref.sorted_ids)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+    assert_close(out.depth.cpu().numpy(), ref.depth, IMG_TOL, "depth")
+    assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
+    # inference: depth_accum / (1e-10 + 1 - T)
+    out_inf, _ = op.forward(model, cams, training=False)
+    ref_inf = O.forward(oracle_cfg(sc, op_cfg, training=False), osc, render_depth=True)
+    assert_close(out_inf.depth.cpu().numpy(), ref_inf.depth, 5e-4, "normalised depth")
+    g = torch.Generator().manual_seed(13)
+    c = sc["cfg"]
+    drgb = torch.randn(views, c.height, c.width, 3, generator=g)
+    ddepth = torch.randn(views, c.height, c.width, generator=g)
+    gm, duv, _ = op.backward(model, cams, ctx, out,
+                             GaussianSplatGradients(drgb=drgb.to(cuda_device), dT=None, ddepth=ddepth.to(cuda_device)),
+                             return_uv_grad=True)
+    torch.cuda.synchronize()
+    O.backward(ocfg, osc, ref, drgb.numpy(), None, ddepth.numpy())
+    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv")
+    for name, ours in (("xyz", gm.xyz), ("quat", gm.quaternion_xyzw), ("scale", gm.scale), ("opacity", gm.opacity),
+                       ("sh_base", gm.color_sh_base), ("sh_rest", gm.color_sh)):
+        assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
+
+
 @pytest.mark.parametrize("width,height,views", [(177, 121, 1), (64, 33, 2)])
 def test_record_staging_modes_agree(cuda_device, width, height, views):
     """The raster kernels stage their records either by gathering from the per-Gaussian table the preprocess

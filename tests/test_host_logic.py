@@ -22,7 +22,7 @@ def test_config_defaults_follow_reference():
     assert t.iterations == 7500 and t.optim.position_lr_max_steps == 7500 and t.strategy.refine_every == 25
 
 
-@pytest.mark.parametrize("kw", [dict(transmittance_is_double=True), dict(render_depth=True), dict(render_inv_depth=True),
+@pytest.mark.parametrize("kw", [dict(transmittance_is_double=True), dict(move_opacity_in_grad_to_prep=True),
                                 dict(sparse_mode=True), dict(tile_size=(8, 8)), dict(use_int64_tile_touched=True),
                                 dict(early_filter_algo=d3.EarlyFilterAlgo.ELLIPSE), dict(disable_builtin_rgb=True)])
 def test_unsupported_options_raise_at_construction(kw):
@@ -33,6 +33,7 @@ def test_unsupported_options_raise_at_construction(kw):
 
 def test_output_format_options_are_accepted():
     c = d3.GaussianSplatConfig(use_nchw=True, render_rgba=True, enable_32bit_sort=True, enable_anti_aliasing=True,
+                               render_depth=True, render_inv_depth=True,
                                rasterize_backward_algo=d3.RasterizeBackwardAlgo.PER_GAUSSIAN)
     assert c.unsupported_options() == [] and c.num_channels == 4
 

@@ -74,3 +74,30 @@ def test_oracle_32bit_sort_keys():
     np.testing.assert_array_equal(r32.ranges, r64.ranges)     # the same tiles hold the same number of pairs
     order = np.argsort(r32.keys, kind="stable")
     np.testing.assert_array_equal(r32.sorted_ids, r32.vals[order])
+
+
+@pytest.mark.parametrize("inv", [False, True])
+def test_oracle_depth_matches_dense_autograd(inv):
+    """render_depth / render_inv_depth: the blended depth value and the gradient it sends to every parameter
+    (render.py:582, 1824, 1948-1967, 3053-3057)."""
+    W, H, deg = 48, 40, 1
+    sc = small_scene(n=150, width=W, height=H, sh_degree=deg, seed=12, log_scale=("normal", -1.8, 0.5), sh_gain=6.0)
+    osc = oracle_scene(sc)
+    cfg = O.OpConfig(width=W, height=H, sh_degree=deg, early_filter=0, inv_depth=inv)
+    res = O.forward(cfg, osc, render_depth=True)
+    g = torch.Generator().manual_seed(8)
+    drgb = torch.randn(1, H, W, 3, generator=g).numpy().astype(np.float32)
+    ddepth = torch.randn(1, H, W, generator=g).numpy().astype(np.float32)
+    O.backward(cfg, osc, res, drgb, None, ddepth)
+    params = {k: torch.tensor(getattr(osc, k), dtype=torch.float64, requires_grad=True)
+              for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")}
+    C, T, vis, D = render_dense(params, osc.cams[0], W, H, deg, depth_mode="inv" if inv else "z")
+    assert np.abs(C.detach().numpy() - res.color[0]).max() < 2e-5
+    scale_d = np.abs(D.detach().numpy()).max()
+    assert np.abs(D.detach().numpy() - res.depth[0]).max() < 2e-5 * max(scale_d, 1.0)
+    loss = (C * torch.tensor(drgb[0], dtype=torch.float64)).sum() + (D * torch.tensor(ddepth[0], dtype=torch.float64)).sum()
+    loss.backward()
+    for k, p in params.items():
+        ref = p.grad.numpy()
+        scale = np.abs(ref).max()
+        assert np.abs(res.grads[k] - ref).max() / scale < 2e-4, k
