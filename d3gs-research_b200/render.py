@@ -49,8 +49,10 @@ class GaussianSplatOpContext:
     tile_order: torch.Tensor | None = None
     records_by_id: bool = False   # splat_records is the per-Gaussian table (gathered by sorted id), not per pair
     raster_color: torch.Tensor | None = None   # the kernels' [B,H,W,3] colour when out.color is a re-formatted copy
-    depth_records: torch.Tensor | None = None  # render_depth: the records with (depth value, 0, 0) as the colour
-    depth_color: torch.Tensor | None = None    # render_depth: [B,H,W,3] blend of those records (channel 0 = depth sum)
+    # Quantities blended like a colour (render_depth, custom_features), three channels per extra raster pass:
+    # for every pass (records with those values in the colour slots, their [B,H,W,3] blend)
+    aux_passes: list | None = None
+    num_custom_feat: int = 0
 
 
 @dataclasses.dataclass
@@ -348,8 +350,8 @@ class GaussianSplatOp:
                 custom_features: torch.Tensor | None = None, mask: torch.Tensor | None = None,
                 prep_user_inputs: dict[str, Any] | None = None):
         assert model.act_applied, "model must be activated before render"
-        if instance2world_T is not None or custom_features is not None or prep_user_inputs is not None:
-            raise NotImplementedError("instance transforms, custom features and proxy inputs are not built")
+        if instance2world_T is not None or prep_user_inputs is not None:
+            raise NotImplementedError("instance transforms and proxy inputs are not built")
         lib = self._lib
         dev = model.xyz.device
         stream = torch.cuda.current_stream(dev).cuda_stream
@@ -455,27 +457,45 @@ class GaussianSplatOp:
                                            out_color.data_ptr(), final_T.data_ptr(),
                                            n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
         self._mark("raster_fwd")
-        depth = depth_records = depth_color = None
+        # render.py:1824, 1920-1923, 2244-2270: the depth value and the custom features are blended exactly like
+        # colour channels (accum += weight * value, never composited or clamped).  Each group of three channels
+        # is one more forward pass over the same lists with the values in the records' colour slots.
+        depth = out_feat = None
+        aux_values = []
         if self._cfg.render_depth:
-            # render.py:1824, 2244-2255: depth_accum += weight * depth_val.  The depth value is blended exactly like
-            # a colour channel, so the depth image is a second forward pass over the same lists with
-            # (depth value, 0, 0) in the records' colour slots (never composited or clamped: training mode).
-            depth_records = records.clone()
-            depth_records[:, 8] = depths if gather else depths[gaussian_idx_sorted.long()]
-            depth_records[:, 9:11] = 0.0
-            ocfg_d = _lib.OpConfig.from_buffer_copy(ocfg)
-            ocfg_d.training = 1
-            depth_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
-            _lib.check(lib.d3gs_raster_forward(C.byref(ocfg_d), workload_ranges.data_ptr(), tile_order.data_ptr(),
-                                               depth_records.data_ptr(),
-                                               gaussian_idx_sorted.data_ptr() if gather else None,
-                                               depth_color.data_ptr(), torch.empty_like(final_T).data_ptr(),
+            aux_values.append(torch.stack([depths, torch.zeros_like(depths), torch.zeros_like(depths)], dim=1))
+        nfeat = 0
+        if custom_features is not None:
+            assert not self._cfg.use_nchw, "custom feat don't support nchw, set use_nchw=False in config."
+            nfeat = custom_features.shape[-1]
+            assert custom_features.shape[0] == BN and custom_features.dim() == 2
+            feat = custom_features.detach().to(f32)
+            pad = (-nfeat) % 3
+            if pad:
+                feat = torch.cat([feat, torch.zeros([BN, pad], dtype=f32, device=dev)], dim=1)
+            aux_values += [feat[:, k:k + 3] for k in range(0, nfeat + pad, 3)]
+        aux_passes = []
+        for vals in aux_values:
+            recs = records.clone()
+            recs[:, 8:11] = vals if gather else vals[gaussian_idx_sorted.long()]
+            ocfg_a = _lib.OpConfig.from_buffer_copy(ocfg)
+            ocfg_a.training = 1
+            blend = torch.empty([B, H, W, 3], dtype=f32, device=dev)
+            _lib.check(lib.d3gs_raster_forward(C.byref(ocfg_a), workload_ranges.data_ptr(), tile_order.data_ptr(),
+                                               recs.data_ptr(), gaussian_idx_sorted.data_ptr() if gather else None,
+                                               blend.data_ptr(), torch.empty_like(final_T).data_ptr(),
                                                torch.empty_like(n_contrib).data_ptr(), sync.data_ptr() + 8, stream),
-                       "d3gs_raster_forward(depth)")
-            depth = depth_color[..., 0]
+                       "d3gs_raster_forward(aux)")
+            aux_passes.append((recs, blend))
+        if aux_passes:
+            self._mark("raster_fwd_aux")
+        if self._cfg.render_depth:
+            depth = aux_passes[0][1][..., 0]
             depth = depth.contiguous() if training else depth / (1e-10 + 1.0 - final_T)
-            self._mark("raster_fwd_depth")
-        output = GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
+        if nfeat:
+            groups = aux_passes[1:] if self._cfg.render_depth else aux_passes
+            out_feat = torch.cat([b for _, b in groups], dim=-1)[..., :nfeat].contiguous()
+        output = GaussianSplatOutput(custom_features=out_feat, T=final_T, color=self._format_color(out_color, final_T),
                                      depth=depth, n_contrib=n_contrib, radii=radii)
         if not training:
             return output, None
@@ -485,7 +505,7 @@ class GaussianSplatOp:
                                      sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order,
                                      records_by_id=gather,
                                      raster_color=out_color if output.color is not out_color else None,
-                                     depth_records=depth_records, depth_color=depth_color)
+                                     aux_passes=aux_passes, num_custom_feat=nfeat)
         return output, ctx
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
@@ -523,28 +543,55 @@ class GaussianSplatOp:
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
                                             stream), "d3gs_raster_backward")
         self._mark("raster_bwd")
-        dz = None
-        if grad.ddepth is not None:
-            # render.py:1948-1967: the raster backward is linear in (drgb, ddepth, dT); the depth channel's share
-            # is a second pass with the depth records, whose "colour" gradient of channel 0 is dL/d(depth value)
-            assert ctx.depth_records is not None, "ddepth needs an operator configured with render_depth"
-            dcol = torch.zeros([B, H, W, 3], dtype=torch.float32, device=dev)
-            dcol[..., 0] = grad.ddepth
+        # render.py:1948-1971: the raster backward is linear in the image gradients of all blended channels; the
+        # share of every auxiliary group is one more pass with that group's records, whose "colour" gradient is
+        # the gradient of the blended values (dz for the depth, dcustom_features for the features)
+        dz = dfeat = None
+        aux = list(ctx.aux_passes or [])
+        aux_grads = []
+        if self._cfg.render_depth and aux:
+            dd = None
+            if grad.ddepth is not None:
+                dd = torch.zeros([B, H, W, 3], dtype=torch.float32, device=dev)
+                dd[..., 0] = grad.ddepth
+            aux_grads.append(dd)
+        else:
+            assert grad.ddepth is None, "ddepth needs an operator configured with render_depth"
+        nfeat = ctx.num_custom_feat
+        if nfeat:
+            df = grad.dcustom_features
+            if df is not None:
+                pad = (-nfeat) % 3
+                if pad:
+                    df = torch.cat([df, torch.zeros([B, H, W, pad], dtype=torch.float32, device=dev)], dim=-1)
+            aux_grads += [None if df is None else df[..., k:k + 3].contiguous() for k in range(0, nfeat + (-nfeat) % 3, 3)]
+        per_splat = []
+        for (recs, blend), dimg in zip(aux, aux_grads):
+            if dimg is None:
+                per_splat.append(None)
+                continue
             packed2 = torch.empty([BN, 12], dtype=torch.float32, device=dev)
             _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
-                                                _lib.ptr(ctx.tile_order), ctx.depth_records.data_ptr(),
-                                                int(ctx.records_by_id), ctx.gaussian_idx_sorted.data_ptr(),
-                                                ctx.depth_color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
-                                                dcol.data_ptr(), None, packed2.data_ptr(), sync.data_ptr() + 8,
-                                                stream), "d3gs_raster_backward(depth)")
+                                                _lib.ptr(ctx.tile_order), recs.data_ptr(), int(ctx.records_by_id),
+                                                ctx.gaussian_idx_sorted.data_ptr(), blend.data_ptr(), out.T.data_ptr(),
+                                                out.n_contrib.data_ptr(), dimg.data_ptr(), None, packed2.data_ptr(),
+                                                sync.data_ptr() + 8, stream), "d3gs_raster_backward(aux)")
             packed[:, 0:4] += packed2[:, 0:4]
             packed[:, 8:10] += packed2[:, 8:10]
-            packed[:, 7] = packed2[:, 4]     # slot 7: dz, consumed by the preprocess backward
-            dz = packed[:, 7]
-            self._mark("raster_bwd_depth")
+            per_splat.append(packed2[:, 4:7])
+        if per_splat:
+            self._mark("raster_bwd_aux")
+        if self._cfg.render_depth and per_splat:
+            if per_splat[0] is not None:
+                packed[:, 7] = per_splat[0][:, 0]     # slot 7: dz, consumed by the preprocess backward
+                dz = packed[:, 7]
+            per_splat = per_splat[1:]
+        if nfeat and any(p is not None for p in per_splat):
+            dfeat = torch.cat([p if p is not None else torch.zeros([BN, 3], dtype=torch.float32, device=dev)
+                               for p in per_splat], dim=1)[:, :nfeat].contiguous()
         # the reference's four tensors (render.py:1412-1418) are views of the packed array
         return RasterizeGradientOutput(duv=packed[:, 8:10], dconic=packed[:, 0:3], dopacity=packed[:, 3],
-                                       dcolor=packed[:, 4:7], dz=dz, packed=packed)
+                                       dcolor=packed[:, 4:7], dcustom_features=dfeat, dz=dz, packed=packed)
 
     # ---- backward (render.py:2779-3374) --------------------------------------------------------
     def backward(self, model: GaussianModelOriginBase, cameras: BasicPinholeCamera | CameraBundle,
@@ -580,7 +627,7 @@ class GaussianSplatOp:
                                                          C.byref(stats) if stats is not None else None, stream),
                        "d3gs_preprocess_backward_adam")
             self._mark("preprocess_bwd_adam")
-            return None, (duv if return_uv_grad else None), None
+            return None, (duv if return_uv_grad else None), rg.dcustom_features
         if grad_out is None:
             if model.flat is not None or (model.color_sh_base is not None and model.color_sh.shape[1] == 15):
                 flat = torch.zeros(flat_layout(num)[1], dtype=torch.float32, device=dev)
@@ -609,8 +656,8 @@ class GaussianSplatOp:
         self._mark("preprocess_bwd")
         if return_uv_grad:
             # [B,N,2] strided view of the packed array (the reference returns duv.view(B,-1,2), render.py:3373)
-            return grad_out, rg.packed.view(B, -1, 12)[:, :, 8:10], None
-        return grad_out, None, None
+            return grad_out, rg.packed.view(B, -1, 12)[:, :, 8:10], rg.dcustom_features
+        return grad_out, None, rg.dcustom_features
 
 
 class _RasterizeGaussians(torch.autograd.Function):
@@ -655,9 +702,9 @@ class _RasterizeGaussians(torch.autograd.Function):
             drgb = torch.zeros_like(ctx.out.color)
         if not drgb.is_contiguous():
             drgb = drgb.contiguous()
-        gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=ddepth, dcustom_features=None)
-        gm, duv, _ = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad)
-        return (gm.xyz, gm.color_sh, gm.color_sh_base, gm.scale, gm.quaternion_xyzw, gm.opacity, None, None, None,
+        gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=ddepth, dcustom_features=dcustom_features)
+        gm, duv, dfeat = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad)
+        return (gm.xyz, gm.color_sh, gm.color_sh_base, gm.scale, gm.quaternion_xyzw, gm.opacity, None, None, dfeat,
                 None, None, None, None, None, None, None, None, duv)
 
 

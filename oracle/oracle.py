@@ -253,6 +253,8 @@ class IterationResult:
     T: np.ndarray
     n_contrib: np.ndarray
     depth: np.ndarray | None = None          # render_depth: [B,H,W]
+    custom_features: np.ndarray | None = None   # [B*N,F] input
+    custom_image: np.ndarray | None = None      # [B,H,W,F] blend
     loss: np.ndarray | None = None
     drgb: np.ndarray | None = None
     raster_grads: dict | None = None
@@ -260,24 +262,43 @@ class IterationResult:
     timings: dict = field(default_factory=dict)
 
 
-def _depth_prep(prep):
-    """The depth channel is blended like a colour (render.py:1824: depth_accum += weight * depth_val): a copy of
-    the per-Gaussian context whose colour is (depth value, 0, 0)."""
+def _aux_prep(prep, values3):
+    """Depth and custom features are blended like a colour (render.py:1824, 1920-1923: accum += weight * value):
+    a copy of the per-Gaussian context whose colour is the given [B*N,3] values."""
     p2 = dict(prep)
-    rgb = np.zeros_like(prep["rgb"])
-    rgb[:, 0] = prep["depths"]
-    p2["rgb"] = rgb
+    p2["rgb"] = _f32(values3)
     return p2
+
+
+def _depth_values(prep):
+    v = np.zeros_like(prep["rgb"])
+    v[:, 0] = prep["depths"]
+    return v
+
+
+def _feature_groups(feat):
+    """[B*N,F] -> list of [B*N,3] (zero padded)."""
+    feat = _f32(feat)
+    pad = (-feat.shape[1]) % 3
+    if pad:
+        feat = np.concatenate([feat, np.zeros((feat.shape[0], pad), np.float32)], axis=1)
+    return [np.ascontiguousarray(feat[:, k:k + 3]) for k in range(0, feat.shape[1], 3)]
+
+
+def raster_aux(cfg: OpConfig, b: int, ranges, sorted_ids, prep, values3):
+    """Un-composited, un-clamped blend of three per-Gaussian channels."""
+    acc, _, _ = raster_fwd(dataclass_replace(cfg, training=True), b, ranges, sorted_ids, _aux_prep(prep, values3))
+    return acc
 
 
 def raster_depth(cfg: OpConfig, b: int, ranges, sorted_ids, prep, T):
     """render.py:2244-2255: sum_i w_i depth_i in training, divided by (1e-10 + 1 - T) at inference."""
-    acc, _, _ = raster_fwd(dataclass_replace(cfg, training=True), b, ranges, sorted_ids, _depth_prep(prep))
-    acc = np.ascontiguousarray(acc[..., 0])
+    acc = np.ascontiguousarray(raster_aux(cfg, b, ranges, sorted_ids, prep, _depth_values(prep))[..., 0])
     return acc if cfg.training else acc / (np.float32(1e-10) + np.float32(1.0) - T)
 
 
-def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None, render_depth: bool = False) -> IterationResult:
+def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None, render_depth: bool = False,
+            custom_features=None) -> IterationResult:
     """preprocess -> scan -> keys -> sort -> ranges -> raster (render.py:169-1015)."""
     tm = {} if timings is None else timings
     tx, ty = cfg.tiles_xy
@@ -296,17 +317,35 @@ def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None, render_depth:
     t5 = time.perf_counter()
     tm.update(preprocess=t1 - t0, scan_keys=t2 - t1, sort=t3 - t2, ranges=t4 - t3, raster_fwd=t5 - t4)
     depth = raster_depth(cfg, sc.b, ranges, sv, prep, T) if render_depth else None
-    return IterationResult(prep, scan, total, keys, vals, sk, sv, ranges, color, T, nc, depth=depth, timings=tm)
+    feat_img = None
+    if custom_features is not None:   # [B*N,F] -> [B,H,W,F] (render.py:241-245, 2268-2270)
+        nf = custom_features.shape[1]
+        feat_img = np.concatenate([raster_aux(cfg, sc.b, ranges, sv, prep, v) for v in _feature_groups(custom_features)],
+                                  axis=-1)[..., :nf]
+        feat_img = np.ascontiguousarray(feat_img)
+    res = IterationResult(prep, scan, total, keys, vals, sk, sv, ranges, color, T, nc, depth=depth, timings=tm)
+    res.custom_features, res.custom_image = custom_features, feat_img
+    return res
 
 
-def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None, ddepth=None) -> IterationResult:
-    """raster backward -> preprocess backward (render.py:2779-3374).  ddepth [B,H,W]: gradient of the rendered
-    depth (training output, the un-normalised sum); the raster backward is linear in (drgb, ddepth, dT), so the
-    depth channel's part is a second pass with the depth value as the colour (render.py:1948-1967)."""
+def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None, ddepth=None, dcustom=None) -> IterationResult:
+    """raster backward -> preprocess backward (render.py:2779-3374).  ddepth [B,H,W] / dcustom [B,H,W,F]: gradients
+    of the rendered depth (training output, the un-normalised sum) and of the blended custom features; the raster
+    backward is linear in the image gradients, so every extra channel group is one more pass with its values as
+    the colour (render.py:1948-1971)."""
     t0 = time.perf_counter()
     res.drgb = _f32(drgb)
-    res.raster_grads = raster_bwd(cfg, sc.b, sc.b * sc.n, res.ranges, res.sorted_ids, res.prep, res.color, res.T,
+    bn = sc.b * sc.n
+    res.raster_grads = raster_bwd(cfg, sc.b, bn, res.ranges, res.sorted_ids, res.prep, res.color, res.T,
                                   res.n_contrib, res.drgb, dT)
+
+    def aux_pass(values3, blend3, dimg3):
+        rg2 = raster_bwd(cfg, sc.b, bn, res.ranges, res.sorted_ids, _aux_prep(res.prep, values3), _f32(blend3), res.T,
+                         res.n_contrib, _f32(dimg3), None)
+        for k in ("duv", "dconic", "dopacity"):
+            res.raster_grads[k] = res.raster_grads[k] + rg2[k]
+        return rg2["dcolor"]
+
     dz = None
     if ddepth is not None:
         assert res.depth is not None and cfg.training
@@ -314,12 +353,16 @@ def backward(cfg: OpConfig, sc: Scene, res: IterationResult, drgb, dT=None, ddep
         col[..., 0] = res.depth
         dcol = np.zeros(res.color.shape, np.float32)
         dcol[..., 0] = ddepth
-        rg2 = raster_bwd(cfg, sc.b, sc.b * sc.n, res.ranges, res.sorted_ids, _depth_prep(res.prep), col, res.T,
-                         res.n_contrib, dcol, None)
-        for k in ("duv", "dconic", "dopacity"):
-            res.raster_grads[k] = res.raster_grads[k] + rg2[k]
-        dz = np.ascontiguousarray(rg2["dcolor"][:, 0])
+        dz = np.ascontiguousarray(aux_pass(_depth_values(res.prep), col, dcol)[:, 0])
         res.raster_grads["dz"] = dz
+    if dcustom is not None:
+        nf = res.custom_features.shape[1]
+        pad = (-nf) % 3
+        img = np.concatenate([res.custom_image, np.zeros(res.custom_image.shape[:3] + (pad,), np.float32)], axis=-1)
+        dimg = np.concatenate([_f32(dcustom), np.zeros(res.custom_image.shape[:3] + (pad,), np.float32)], axis=-1)
+        parts = [aux_pass(v, img[..., 3 * k:3 * k + 3], dimg[..., 3 * k:3 * k + 3])
+                 for k, v in enumerate(_feature_groups(res.custom_features))]
+        res.raster_grads["dcustom"] = np.ascontiguousarray(np.concatenate(parts, axis=1)[:, :nf])
     t1 = time.perf_counter()
     res.grads = preprocess_bwd(cfg, sc, res.prep, res.raster_grads, dz)
     t2 = time.perf_counter()

@@ -35,11 +35,12 @@ def sh_basis(deg, d):
 
 
 def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True, tile=16, near=0.2, far=1e4,
-                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4, anti_aliasing=False, depth_mode=None):
+                 lowpass=0.3, alpha_eps=1.0 / 255.0, t_eps=1e-4, anti_aliasing=False, depth_mode=None, custom=None):
     """params: dict of float64 leaf tensors (xyz, quat, scale, opacity, sh_base, sh_rest).
     Returns color [H,W,3], T [H,W], n_valid (visible mask [N]); with depth_mode "z" or "inv" also the blended
     depth value sum_i w_i d_i [H,W] (d3sim/algos/d3gs/render.py:1824, 2244-2255 in training).  "inv": the depth
-    value is 1/z AND, as in the reference, that value is what the splats are sorted by (render.py:582, 773)."""
+    value is 1/z AND, as in the reference, that value is what the splats are sorted by (render.py:582, 773).
+    custom: [N,F] float64 features blended like colours; their image [H,W,F] is appended to the result."""
     xyz, quat, scale, opac = params["xyz"], params["quat"], params["scale"], params["opacity"]
     cam16 = torch.as_tensor(cam16, dtype=torch.float64)
     Rt = cam16[:9].reshape(3, 3)            # rows: columns of R_c2w  == world->cam rotation
@@ -116,6 +117,7 @@ def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True
     T = torch.ones(H, W, dtype=torch.float64)
     C = torch.zeros(H, W, 3, dtype=torch.float64)
     D = torch.zeros(H, W, dtype=torch.float64)
+    Fi = None if custom is None else torch.zeros(H, W, custom.shape[1], dtype=torch.float64)
     done = torch.zeros(H, W, dtype=torch.bool)
     for g in order.tolist():
         if not bool(visible[g]):
@@ -134,10 +136,11 @@ def render_dense(params, cam16, W, H, sh_degree, clamp_mask_reference_order=True
         w = torch.where(ok, alpha * T, torch.zeros_like(T))
         C = C + w[:, :, None] * rgb[g]
         D = D + w * dval[g]
+        if custom is not None:
+            Fi = Fi + w[:, :, None] * custom[g]
         T = torch.where(ok, T * (1 - alpha), T)
-    if depth_mode is not None:
-        return C, T, visible, D
-    return C, T, visible
+    extra = (() if depth_mode is None else (D,)) + (() if custom is None else (Fi,))
+    return (C, T, visible) + extra
 
 
 def ssim_l1_loss_torch(x_nchw, y_nchw, lambda_dssim=0.2, window_size=11, sigma=1.5):

@@ -221,6 +221,46 @@ def test_render_depth_parity(cuda_device, inv, gather, views):
         assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
 
 
+@pytest.mark.parametrize("nfeat,depth,views", [(4, False, 1), (3, True, 2), (1, False, 1)])
+def test_custom_features_parity(cuda_device, nfeat, depth, views):
+    """custom_features [B*N,F] -> out.custom_features [B,H,W,F] (render.py:241-245, 1920-1923, 2268-2270) and the
+    gradients of a loss on that image: dcustom_features per Gaussian and the share that reaches the Gaussians'
+    parameters through the blend weights (1952-1971); through the operator and through rasterize_gaussians."""
+    sc = small_scene(n=3000, width=128, height=88, sh_degree=1, seed=31, views=views)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, render_depth=depth)
+    op = d3.GaussianSplatOp(op_cfg)
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    cams = gpu_cameras(sc, cuda_device)
+    g = torch.Generator().manual_seed(17)
+    c = sc["cfg"]
+    feat = torch.randn(views * 3000, nfeat, generator=g)
+    out, ctx = op.forward(model, cams, training=True, custom_features=feat.to(cuda_device))
+    assert tuple(out.custom_features.shape) == (views, c.height, c.width, nfeat)
+    ocfg = oracle_cfg(sc, op_cfg)
+    osc = oracle_scene(sc)
+    ref = O.forward(ocfg, osc, render_depth=depth, custom_features=feat.numpy())
+    assert_close(out.custom_features.cpu().numpy(), ref.custom_image, IMG_TOL, "custom features")
+    drgb = torch.randn(views, c.height, c.width, 3, generator=g)
+    dfi = torch.randn(views, c.height, c.width, nfeat, generator=g)
+    dd = torch.randn(views, c.height, c.width, generator=g) if depth else None
+    grads = GaussianSplatGradients(drgb=drgb.to(cuda_device), dT=None, ddepth=None if dd is None else dd.to(cuda_device),
+                                   dcustom_features=dfi.to(cuda_device))
+    gm, duv, dfeat = op.backward(model, cams, ctx, out, grads, return_uv_grad=True)
+    torch.cuda.synchronize()
+    O.backward(ocfg, osc, ref, drgb.numpy(), None, None if dd is None else dd.numpy(), dfi.numpy())
+    assert_close(dfeat.cpu().numpy(), ref.raster_grads["dcustom"], GRAD_TOL, "dcustom_features")
+    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv")
+    for name, ours in (("xyz", gm.xyz), ("scale", gm.scale), ("opacity", gm.opacity), ("sh_base", gm.color_sh_base)):
+        assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
+    if views == 1 and not depth:   # the autograd entry point carries the features and their gradient
+        m2 = gpu_model(sc, cuda_device, requires_grad=True)
+        f2 = feat.to(cuda_device).requires_grad_(True)
+        o2 = d3.rasterize_gaussians(m2, cams, d3.GaussianSplatOp(op_cfg), training=True, custom_features=f2)
+        ((o2.color * drgb.to(cuda_device)).sum() + (o2.custom_features * dfi.to(cuda_device)).sum()).backward()
+        assert_close(f2.grad.cpu().numpy(), ref.raster_grads["dcustom"], GRAD_TOL, "autograd dcustom_features")
+
+
 @pytest.mark.parametrize("width,height,views", [(177, 121, 1), (64, 33, 2)])
 def test_record_staging_modes_agree(cuda_device, width, height, views):
     """The raster kernels stage their records either by gathering from the per-Gaussian table the preprocess

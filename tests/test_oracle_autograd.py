@@ -101,3 +101,30 @@ def test_oracle_depth_matches_dense_autograd(inv):
         ref = p.grad.numpy()
         scale = np.abs(ref).max()
         assert np.abs(res.grads[k] - ref).max() / scale < 2e-4, k
+
+
+def test_oracle_custom_features_match_dense_autograd():
+    """custom_features [B*N,F] blended into [B,H,W,F] and the gradients of a loss on that image: to the features
+    themselves and, through the blend weights, to the Gaussians (render.py:241-245, 1920-1923, 1952-1971)."""
+    W, H, deg, F = 48, 40, 0, 4
+    sc = small_scene(n=150, width=W, height=H, sh_degree=deg, seed=14, log_scale=("normal", -1.8, 0.5), sh_gain=6.0)
+    osc = oracle_scene(sc)
+    cfg = O.OpConfig(width=W, height=H, sh_degree=deg, early_filter=3)
+    g = torch.Generator().manual_seed(9)
+    feat = torch.randn(150, F, generator=g).numpy().astype(np.float32)
+    res = O.forward(cfg, osc, custom_features=feat)
+    drgb = torch.randn(1, H, W, 3, generator=g).numpy().astype(np.float32)
+    dfeat_img = torch.randn(1, H, W, F, generator=g).numpy().astype(np.float32)
+    O.backward(cfg, osc, res, drgb, None, None, dfeat_img)
+    params = {k: torch.tensor(getattr(osc, k), dtype=torch.float64, requires_grad=True)
+              for k in ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")}
+    ft = torch.tensor(feat, dtype=torch.float64, requires_grad=True)
+    C, T, vis, Fi = render_dense(params, osc.cams[0], W, H, deg, custom=ft)
+    assert np.abs(Fi.detach().numpy() - res.custom_image[0]).max() < 2e-5
+    loss = (C * torch.tensor(drgb[0], dtype=torch.float64)).sum() + (Fi * torch.tensor(dfeat_img[0], dtype=torch.float64)).sum()
+    loss.backward()
+    ref = ft.grad.numpy()
+    assert np.abs(res.raster_grads["dcustom"] - ref).max() / np.abs(ref).max() < 2e-4
+    for k in ("xyz", "quat", "scale", "opacity"):
+        ref = params[k].grad.numpy()
+        assert np.abs(res.grads[k] - ref).max() / np.abs(ref).max() < 2e-4, k
