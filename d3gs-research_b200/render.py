@@ -327,6 +327,9 @@ class GaussianSplatOp:
         """The kernels write NHWC RGB.  ``render_rgba`` appends the accumulated opacity: the reference blends a
         fourth channel of constant 1, sum_i alpha_i T_i, which telescopes to 1 - T_final (and stays inside [0,1],
         so the inference clamp with a zero background alpha changes nothing).  ``use_nchw`` permutes."""
+        if self._cfg.disable_builtin_rgb:   # config_def.py:127-132: 0 colour channels, or the alpha alone
+            assert not self._cfg.use_nchw, "only support nhwc if disable builtin rgb."   # render.py:667
+            color = color[..., :0]
         if self._cfg.render_rgba:
             color = torch.cat([color, (1.0 - final_T).unsqueeze(-1)], dim=-1)
         if self._cfg.use_nchw:
@@ -339,9 +342,11 @@ class GaussianSplatOp:
         if self._cfg.use_nchw:
             drgb = drgb.permute(0, 2, 3, 1)
         if self._cfg.render_rgba:
-            dalpha = drgb[..., 3]
+            dalpha = drgb[..., -1]
             dT = -dalpha if dT is None else dT - dalpha
-            drgb = drgb[..., :3]
+            drgb = drgb[..., :-1]
+        if self._cfg.disable_builtin_rgb:   # no colour channels: the splat colours receive no gradient
+            drgb = torch.zeros(drgb.shape[:3] + (3,), dtype=drgb.dtype, device=drgb.device)
         return drgb.contiguous(), dT
 
     # ---- forward (render.py:169-1015) ---------------------------------------------------------
@@ -524,7 +529,7 @@ class GaussianSplatOp:
         drgb = grad.drgb
         assert drgb.is_contiguous(), "drgb must be contiguous"
         dT = grad.dT
-        if self._cfg.use_nchw or self._cfg.render_rgba:
+        if self._cfg.use_nchw or self._cfg.render_rgba or self._cfg.disable_builtin_rgb:
             drgb, dT = self._unformat_grad(drgb, dT)
         color = ctx.raster_color if ctx.raster_color is not None else out.color
         # packed per-splat gradients [BN,12]: dconic a b c, dopacity | dcolor r g b, 0 | duv x y, 0 0

@@ -222,7 +222,7 @@ class SplatTrainer:
                 views[k].copy_(getattr(model, k).detach())
                 setattr(model, k, views[k])
             model.flat = flat
-        if op_cfg.use_nchw or op_cfg.render_rgba:
+        if op_cfg.use_nchw or op_cfg.render_rgba or op_cfg.disable_builtin_rgb:
             raise NotImplementedError("SplatTrainer's fused loss reads the operator's NHWC RGB output: "
                                       "use_nchw / render_rgba are for GaussianSplatOp and rasterize_gaussians")
         self.op = GaussianSplatOp(op_cfg)

@@ -221,6 +221,39 @@ def test_render_depth_parity(cuda_device, inv, gather, views):
         assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
 
 
+@pytest.mark.parametrize("rgba", [False, True])
+def test_disable_builtin_rgb(cuda_device, rgba):
+    """disable_builtin_rgb (config_def.py:116-132, render.py:667): the colour output has no channels (or the alpha
+    alone) and the custom features carry the appearance; the SH coefficients receive no gradient."""
+    sc = small_scene(n=2000, width=96, height=64, sh_degree=1, seed=37)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, disable_builtin_rgb=True, render_rgba=rgba)
+    assert op_cfg.num_channels == (1 if rgba else 0)
+    op = d3.GaussianSplatOp(op_cfg)
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    cams = gpu_cameras(sc, cuda_device)
+    g = torch.Generator().manual_seed(19)
+    feat = torch.randn(2000, 3, generator=g)
+    out, ctx = op.forward(model, cams, training=True, custom_features=feat.to(cuda_device))
+    assert tuple(out.color.shape) == (1, 64, 96, 1 if rgba else 0)
+    ocfg = oracle_cfg(sc, op_cfg)
+    osc = oracle_scene(sc)
+    ref = O.forward(ocfg, osc, custom_features=feat.numpy())
+    if rgba:
+        assert_close(out.color[..., 0].cpu().numpy(), 1.0 - ref.T, IMG_TOL, "alpha")
+    assert_close(out.custom_features.cpu().numpy(), ref.custom_image, IMG_TOL, "custom features")
+    dcol = torch.randn(out.color.shape, generator=g)
+    dfi = torch.randn(1, 64, 96, 3, generator=g)
+    gm, _, dfeat = op.backward(model, cams, ctx, out, GaussianSplatGradients(
+        drgb=dcol.to(cuda_device), dT=None, dcustom_features=dfi.to(cuda_device)))
+    torch.cuda.synchronize()
+    O.backward(ocfg, osc, ref, np.zeros((1, 64, 96, 3), np.float32), -dcol[..., 0].numpy() if rgba else None, None, dfi.numpy())
+    assert float(gm.color_sh.abs().max()) == 0.0 and float(gm.color_sh_base.abs().max()) == 0.0
+    assert_close(dfeat.cpu().numpy(), ref.raster_grads["dcustom"], GRAD_TOL, "dcustom_features")
+    for name, ours in (("xyz", gm.xyz), ("opacity", gm.opacity)):
+        assert_close(ours.cpu().numpy(), ref.grads[name], GRAD_TOL, f"grad {name}")
+
+
 @pytest.mark.parametrize("nfeat,depth,views", [(4, False, 1), (3, True, 2), (1, False, 1)])
 def test_custom_features_parity(cuda_device, nfeat, depth, views):
     """custom_features [B*N,F] -> out.custom_features [B,H,W,F] (render.py:241-245, 1920-1923, 2268-2270) and the
