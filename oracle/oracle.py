@@ -294,7 +294,10 @@ def raster_aux(cfg: OpConfig, b: int, ranges, sorted_ids, prep, values3):
 def raster_depth(cfg: OpConfig, b: int, ranges, sorted_ids, prep, T):
     """render.py:2244-2255: sum_i w_i depth_i in training, divided by (1e-10 + 1 - T) at inference."""
     acc = np.ascontiguousarray(raster_aux(cfg, b, ranges, sorted_ids, prep, _depth_values(prep))[..., 0])
-    return acc if cfg.training else acc / (np.float32(1e-10) + np.float32(1.0) - T)
+    if cfg.training:
+        return acc
+    with np.errstate(invalid="ignore", divide="ignore"):   # in float32 1e-10 + 1 - T is 0 where nothing was blended: 0/0, as in the reference
+        return acc / (np.float32(1e-10) + np.float32(1.0) - T)
 
 
 def forward(cfg: OpConfig, sc: Scene, timings: dict | None = None, render_depth: bool = False,
