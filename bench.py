@@ -222,7 +222,7 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int) -> fl
 # workload by the ratio of algorithmic bytes (traffic of these kernels grows with the units processed).
 NCU_SMALL_CASE = dict(N=750000, V=574917, K=1068256, P=2073600, Tn=8160)
 NCU_SMALL_TRAFFIC = {"raster_bwd": 151.38e6, "raster_fwd": 43.82e6, "adam_stats": 1244.93e6, "preprocess_bwd": 351.21e6,
-                     "preprocess_fwd": 252.27e6, "preprocess_bwd_adam": 1145.16e6, "l1_dssim": 224.19e6, "pack_splats": 35.39e6, "duplicate_keys": 21.03e6}
+                     "preprocess_fwd": 252.27e6, "preprocess_bwd_adam": 1103.29e6, "l1_dssim": 224.19e6, "pack_splats": 35.39e6, "duplicate_keys": 21.03e6}
 
 
 def ncu_traffic(stage: str, N: int, V: int, K: int, P: int, Tn: int):
