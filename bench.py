@@ -469,6 +469,12 @@ def main():
                      "traffic_source": "ncu dram bytes of the 750k-Gaussian case scaled by algorithmic bytes",
                      "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": dom_bytes,
+                     # the fused backward + Adam launch is credited with the bytes of the two stages it replaces (the
+                     # per-stage figures the iteration total is defined on); what it has to move itself is less:
+                     # no gradient tensor is written or read back.  Both fractions are reported.
+                     "moved_bytes_per_launch": (89 * V + 1456 * N) if dom == "preprocess_bwd_adam" else dom_bytes,
+                     "frac_of_moved_bytes": ((89 * V + 1456 * N) if dom == "preprocess_bwd_adam" else dom_bytes)
+                     / (kernel_stages[dom] * 1e-3) / 1e9 / peak,
                      "iteration": {"algorithmic_bytes": iter_bytes,
                                    "achieved": iter_bytes / (ms_total / args.steps * 1e-3) / 1e9,
                                    "frac": iter_bytes / (ms_total / args.steps * 1e-3) / 1e9 / peak}},
