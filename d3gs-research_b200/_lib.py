@@ -67,6 +67,8 @@ class DensifyStats(C.Structure):
 
 
 MAX_PEERS = 8
+RASTER_RECORDS_BY_ID = 1
+RASTER_DIRECT_ATOMICS = 2
 PEER_HANDLE_BYTES = 64
 
 
@@ -98,6 +100,7 @@ SIGNATURES = {
     "d3gs_last_error": (_SZ, [C.c_char_p, _SZ]),
     "d3gs_bit_length": (_I32, [C.c_uint32]),
     "d3gs_struct_size": (_SZ, [_I32]),
+    "d3gs_kernel_launch_count": (C.c_uint64, []),
     "d3gs_preprocess_forward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), _P, C.POINTER(SplatContext), _P]),
     "d3gs_scan_workspace_bytes": (_SZ, [_I64]),
     "d3gs_scan_tiles": (_I32, [_P, _P, _I64, _P, _P, _SZ, _P, _P]),

@@ -1,4 +1,5 @@
 // Error plumbing and small helpers of the d3gs_b200 C ABI.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -19,7 +20,12 @@ int32_t cuda_fail(cudaError_t e, const char* what) {
     return D3GS_ERR_CUDA;
 }
 
+static std::atomic<uint64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 }  // namespace d3gs
+
+extern "C" uint64_t d3gs_kernel_launch_count(void) { return d3gs::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* d3gs_version(void) { return "d3gs_b200 0.1.0 (sm_100a)"; }
 

@@ -14,6 +14,7 @@ namespace d3gs {
 // ---- host-side error plumbing ------------------------------------------------------------
 void set_error(const char* fmt, ...);
 int32_t cuda_fail(cudaError_t e, const char* what);
+void count_launch();
 
 #define D3GS_REQUIRE(cond, ...)                 \
     do {                                        \
@@ -29,8 +30,10 @@ int32_t cuda_fail(cudaError_t e, const char* what);
         if (e__ != cudaSuccess) return ::d3gs::cuda_fail(e__, #expr); \
     } while (0)
 
+// every kernel launch of the library passes here once: the launch is counted (d3gs_kernel_launch_count)
 #define D3GS_LAUNCH_CHECK(name)                                  \
     do {                                                         \
+        ::d3gs::count_launch();                                  \
         cudaError_t e__ = cudaGetLastError();                    \
         if (e__ != cudaSuccess) return ::d3gs::cuda_fail(e__, name); \
     } while (0)

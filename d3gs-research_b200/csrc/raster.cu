@@ -18,9 +18,12 @@
 //    is cheaper than votes and divergent branches when nearly every pass has a contributing pixel.
 //  * A lane owns two horizontally adjacent pixels and uses the packed fp32 instructions of sm_100 (see below).
 //  * Backward: the nine per-splat partial sums are reduced inside each group with a transposing butterfly
-//    (8 shuffles for eight records instead of 45 for one), accumulated per CTA in shared memory, and leave
-//    the CTA as three vector atomic adds per (tile, splat) instead of the reference's nine scalar atomics
-//    per warp (render.py:2061-2148).
+//    (8 shuffles for eight records instead of 45 for one).  Then either (a) they are accumulated per CTA in
+//    shared memory and leave the CTA as three vector atomic adds per (tile, splat), or (b) the four lanes of
+//    the group add them to global memory at once (four 8-byte and one 4-byte atomic per group and record).
+//    (b) has no shared-memory atomics, no flush and one barrier less per batch and is faster while a splat is
+//    seen by one or two groups of a tile (small splats: 0.89 -> 0.77 ms at 3 M Gaussians, 1080p); (a) wins when
+//    splats cover many 4x2 sub-blocks.  The reference issues nine scalar atomics per warp (render.py:2061-2148).
 //
 // The arithmetic that decides n_contrib -- power, exp, alpha, the transmittance product and the
 // three threshold compares -- is written with explicit round-to-nearest intrinsics so that its
@@ -337,12 +340,13 @@ __global__ void __launch_bounds__(128, 8) raster_forward_kernel(const __grid_con
 // four lanes of a group reduce them with a transposing butterfly (8 shuffles) and every lane adds the two
 // components it ends up holding to the record's row in shared memory.
 // 8 CTAs per SM (64 registers): measured faster than 9 / 10 CTAs (56 / 48 registers) and than 6 / 5 (72 / 77)
-template <bool GATHER>
+template <bool GATHER, bool DIRECT>
 __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_raw[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
     // per record: sum m dx^2, m dx dy, m dy^2, m, dcolor r g b, m dx, m dy, (pad: rows stay 8-byte aligned)
-    __shared__ __align__(8) float s_acc[kBatch][10];
+    __shared__ __align__(8) float s_acc[DIRECT ? 1 : kBatch][10];
+    __shared__ int32_t s_ids[2][DIRECT ? kBatch : 1];   // DIRECT: sorted id of every staged record
     __shared__ int s_max[4];
     __shared__ uint8_t s_list[4][8 * kListStride];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5, group = lane >> 2;
@@ -389,8 +393,10 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
         id_cur = staged_id(a, r0, bmax, 0, t);
         gather_record(a, s_raw[0], t, id_cur);
         id_next = staged_id(a, r0, bmax, 1, t);
-    } else if (t == 0 && nb > 0) {
-        issue_batch(a, s_raw[0], &s_bar[0], r0, bmax, 0);
+        if (DIRECT) s_ids[0][t] = id_cur;
+    } else {
+        if (t == 0 && nb > 0) issue_batch(a, s_raw[0], &s_bar[0], r0, bmax, 0);
+        if (DIRECT) s_ids[0][t] = staged_id(a, r0, bmax, 0, t);
     }
 
     const float fpxA = (float)px, fpxB = (float)(px + 1), fpy = (float)py;
@@ -400,8 +406,10 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
     const int slot = (h2 ? 4 : 0) + (h1 ? 2 : 0);
     f2 T = f2_dup(1.0f);
     bool copy_failed = false;
+    if (!DIRECT) {
 #pragma unroll
-    for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;   // row t is zeroed again by its owner after every flush
+        for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;   // row t is zeroed again by its owner after every flush
+    }
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
         if (GATHER) cp_async_wait_all();
@@ -416,12 +424,17 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
             my_id = max(id_cur, 0);
             if (b + 1 < nb) {
                 gather_record(a, s_raw[cur ^ 1], t, id_next);
+                if (DIRECT) s_ids[cur ^ 1][t] = id_next;
                 id_flight = id_next;
                 id_next = staged_id(a, r0, bmax, b + 2, t);
             }
         } else {
             if (t == 0 && b + 1 < nb) issue_batch(a, s_raw[cur ^ 1], &s_bar[cur ^ 1], r0, bmax, b + 1);
-            if (t < cnt) my_id = a.sorted_ids[r0 + b * kBatch + t];
+            if (DIRECT) {
+                if (b + 1 < nb) s_ids[cur ^ 1][t] = staged_id(a, r0, bmax, b + 1, t);
+            } else if (t < cnt) {
+                my_id = a.sorted_ids[r0 + b * kBatch + t];
+            }
         }
         const float4* raw = s_raw[cur];
         const int wlim = min(cnt, wmax - b * kBatch);   // warp-uniform: nobody in the warp goes further
@@ -496,12 +509,28 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
                 v8 += shfl_x(v8, 2);
                 v8 += shfl_x(v8, 1);
                 const bool gvalid = ((vmask >> (group * 4)) & 0xfu) != 0;
-                if (gvalid) {
+                if (DIRECT) {
+                    // No accumulation in shared memory: a record is touched by one or two groups of the tile on
+                    // average, so the group's totals leave as they are.  The four lanes hold (sxx, sxy),
+                    // (syy, s0), (dcolor r, g), (dcolor b, sx); sy is on every lane.  The record's conic and
+                    // opacity are applied here (see the flush of the other variant for the formulas).
+                    if (gvalid) {
+                        float* dst = a.splat_grads + (int64_t)s_ids[cur][j] * kGradFloats;
+                        const float o = q1.w;
+                        const float sx = b01.y, sy = v8;
+                        const float gu = o * fmaf(2.0f * q1.x, sx, q1.y * sy), gv = o * fmaf(2.0f * q1.z, sy, q1.y * sx);
+                        const float x = h2 ? (h1 ? gu : b01.x) : -0.5f * o * b01.x;
+                        const float y = h2 ? (h1 ? gv : b01.y) : (h1 ? b01.y : -o * b01.y);
+                        red_add_v2(dst + (h2 ? (h1 ? 8 : 4) : (h1 ? 2 : 0)), x, y);
+                        if (h2 && h1) atomicAdd(dst + 6, b01.x);
+                    }
+                } else if (gvalid) {
                     smem_add_pair(&s_acc[j][slot], b01.x, b01.y);
                     if ((lane & 3) == 0) atomicAdd(&s_acc[j][8], v8);
                 }
             }
         }
+        if (DIRECT) continue;
         __syncthreads();
         if (t < cnt) {
             const float* acc = s_acc[t];
@@ -576,7 +605,7 @@ extern "C" int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* r
 }
 
 extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges,
-                                        const int32_t* tile_order, const float* records, int32_t records_by_id,
+                                        const int32_t* tile_order, const float* records, int32_t mode,
                                         const int32_t* sorted_values, const float* color,
                                         const float* final_T, const int32_t* n_contrib, const float* drgb,
                                         const float* dT, float* splat_grads, uint32_t* status, void* stream) {
@@ -603,8 +632,14 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
     a.dT = dT;
     a.splat_grads = splat_grads;
     const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
-    if (records_by_id) raster_backward_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
-    else raster_backward_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    const bool records_by_id = (mode & D3GS_RASTER_RECORDS_BY_ID) != 0;
+    if (mode & D3GS_RASTER_DIRECT_ATOMICS) {
+        if (records_by_id) raster_backward_kernel<true, true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+        else raster_backward_kernel<false, true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    } else {
+        if (records_by_id) raster_backward_kernel<true, false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+        else raster_backward_kernel<false, false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    }
     D3GS_LAUNCH_CHECK("raster_backward_kernel");
     return D3GS_OK;
 }

@@ -211,6 +211,9 @@ class StageTimer:
 class GaussianSplatOp:
     """render.py:152-167.  ``cfg`` is deep-copied: create a new op to change options."""
 
+    # sort pairs per (view, Gaussian) below which the raster backward skips its shared-memory accumulation
+    DIRECT_ATOMICS_PAIRS_PER_GAUSSIAN = 3.0
+
     def __init__(self, cfg: GaussianSplatConfig) -> None:
         self._cfg = copy.deepcopy(cfg)
         bad = self._cfg.unsupported_options()
@@ -226,6 +229,10 @@ class GaussianSplatOp:
         # id; False: d3gs_pack_splats writes one record per sorted (tile, splat) pair and the raster kernels stream
         # them with bulk copies (one more pass over the pairs; same results)
         self.gather_records = True
+        # Raster backward: True = every group of four lanes adds its per-splat sums to global memory directly,
+        # False = per-tile accumulation in shared memory first, None = chosen per call from the number of sort
+        # pairs per Gaussian (small splats -> direct).  Same gradients up to the order of the float additions.
+        self.raster_grad_direct: bool | None = None
         self.debug: dict[str, torch.Tensor] = {}
         # optional StageTimer; None = no events recorded
         self.timer: StageTimer | None = None
@@ -250,6 +257,20 @@ class GaussianSplatOp:
             t = torch.zeros(2, dtype=torch.int64, device=device)
             self._sync[device] = t
         return t
+
+    def check_status(self, device=None) -> None:
+        """Read the device status word (one 8-byte copy), clear it and raise if a bounded wait of any kernel
+        launched through this operator gave up.  ``forward`` checks the word with its own read-back, which
+        covers everything launched before it; call this after the LAST forward / backward / optimizer launch of
+        a run, where no further forward follows."""
+        for dev, sync in self._sync.items():
+            if device is not None and dev != device:
+                continue
+            status = int(sync[1].item())
+            if status != 0:
+                sync[1] = 0
+                raise RuntimeError(f"d3gs_b200 device status {status:#x}: a bounded wait gave up "
+                                   "(1 scan, 2 sort, 4 bulk copy); results of the previous call are invalid")
 
     def _op_config(self, model: GaussianModelOriginBase, cameras, training: bool) -> _lib.OpConfig:
         cfg = self._cfg
@@ -541,8 +562,12 @@ class GaussianSplatOp:
         sync = self._sync_words(dev)
         if dT is not None:
             dT = dT.contiguous()
+        direct = self.raster_grad_direct
+        if direct is None:
+            direct = ctx.gaussian_idx_sorted.shape[0] < self.DIRECT_ATOMICS_PAIRS_PER_GAUSSIAN * BN
+        mode = (_lib.RASTER_RECORDS_BY_ID if ctx.records_by_id else 0) | (_lib.RASTER_DIRECT_ATOMICS if direct else 0)
         _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(), _lib.ptr(ctx.tile_order),
-                                            ctx.splat_records.data_ptr(), int(ctx.records_by_id),
+                                            ctx.splat_records.data_ptr(), mode,
                                             ctx.gaussian_idx_sorted.data_ptr(),
                                             color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
                                             drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
@@ -577,7 +602,7 @@ class GaussianSplatOp:
                 continue
             packed2 = torch.empty([BN, 12], dtype=torch.float32, device=dev)
             _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(),
-                                                _lib.ptr(ctx.tile_order), recs.data_ptr(), int(ctx.records_by_id),
+                                                _lib.ptr(ctx.tile_order), recs.data_ptr(), mode,
                                                 ctx.gaussian_idx_sorted.data_ptr(), blend.data_ptr(), out.T.data_ptr(),
                                                 out.n_contrib.data_ptr(), dimg.data_ptr(), None, packed2.data_ptr(),
                                                 sync.data_ptr() + 8, stream), "d3gs_raster_backward(aux)")

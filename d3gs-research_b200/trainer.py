@@ -450,6 +450,18 @@ class SplatTrainer:
             torch.distributed.all_reduce(self.state.count, group=self.pg)
             torch.distributed.all_reduce(self.state.max_radii, op=torch.distributed.ReduceOp.MAX, group=self.pg)
 
+    def update_path_name(self) -> str:
+        """Which of the update paths this trainer takes (for logs and benchmark records)."""
+        if self.world == 1:
+            return "single rank, Adam inside the preprocess backward" if self.fused_adam else \
+                "single rank, gradient buffer + optimizer kernel"
+        if self._peerset is not None:
+            return ("sharded, one kernel over NVLink peer memory: sum of all ranks' gradient slices, Adam, store to "
+                    "all ranks' parameters")
+        if self.sharded:
+            return "sharded: reduce-scatter, Adam on 1/N slice, all-gather"
+        return "replicated after all-reduce"
+
     def parameter_checksum(self) -> torch.Tensor:
         """Sum of the raw parameter bits; replicas must agree after every update."""
         return self.model.flat[:self.flat_total].view(torch.int32).sum(dtype=torch.int64)

@@ -139,6 +139,9 @@ const char* d3gs_version(void);
 size_t d3gs_last_error(char* buf, size_t cap);
 /* DeviceSort.get_higher_msb (csrc/devsort.py:129-149): number of bits needed for n */
 int32_t d3gs_bit_length(uint32_t n);
+/* Number of kernels this library has launched in the calling process since it was loaded (every entry point
+ * counts its own launches; memsets and copies are not counted).  For accounting, e.g. launches per step. */
+uint64_t d3gs_kernel_launch_count(void);
 /* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
  * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet,
  * 8 D3gsRefineConfig, 9 D3gsRefineMoments */
@@ -213,9 +216,15 @@ int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, cons
  * dopacity, dcolor, render.py:1388-1401) are one packed array here so that the kernel can use 16-byte
  * vector atomics: splat_grads [B*N, 12] = {dconic a,b,c, dopacity | dcolor r,g,b, dz | duv x,y, 0, 0},
  * 16-byte aligned, zero-filled by this call.  sorted_values: the sorted value list of the sort.
- * records_by_id != 0: records is the per-Gaussian table (see d3gs_raster_forward), else the per-pair records. */
+ * mode: bit flags.  D3GS_RASTER_RECORDS_BY_ID: records is the per-Gaussian table (see d3gs_raster_forward), else
+ * the per-pair records.  D3GS_RASTER_DIRECT_ATOMICS: every group of four lanes adds its sums for a splat to
+ * splat_grads directly instead of accumulating them per tile in shared memory first; faster while a splat
+ * overlaps few 4x2 pixel blocks of a tile (about three sort pairs per Gaussian or fewer), slower for scenes of
+ * large splats.  Same gradients up to the order of the float additions. */
+#define D3GS_RASTER_RECORDS_BY_ID 1
+#define D3GS_RASTER_DIRECT_ATOMICS 2
 int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const int32_t* tile_order,
-                             const float* records, int32_t records_by_id, const int32_t* sorted_values, const float* color,
+                             const float* records, int32_t mode, const int32_t* sorted_values, const float* color,
                              const float* final_T, const int32_t* n_contrib, const float* drgb, const float* dT,
                              float* splat_grads, uint32_t* status, void* stream);
 

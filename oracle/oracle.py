@@ -57,6 +57,18 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int | None = None) -> int:
+    """Use ``n`` OpenMP threads from now on (default: every core this process may run on), whatever
+    OMP_NUM_THREADS says -- torch.distributed.run exports OMP_NUM_THREADS=1 to its workers."""
+    if n is None:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except AttributeError:
+            n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(ctypes.c_int(int(n)))
+    return num_threads()
+
+
 def _p(a):
     if a is None:
         return None

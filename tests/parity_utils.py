@@ -74,3 +74,53 @@ def assert_close(a, b, tol, name, floor_frac=1e-3):
     bad = err > bound
     assert not bad.any(), (f"{name}: {int(bad.sum())}/{bad.size} elements off, max err {err.max():.3e} "
                            f"(scale {scale:.3e}, rel-inf {err.max() / scale:.3e}, tol {tol})")
+
+
+def assert_bit_equal(got, ref, name):
+    """Integer / bit-pattern equality with the mismatch count in the message (the target is 0)."""
+    g = got.cpu().numpy() if hasattr(got, "cpu") else np.asarray(got)
+    r = np.asarray(ref)
+    assert g.shape == r.shape, f"{name}: shape {g.shape} vs {r.shape}"
+    if g.dtype != r.dtype:
+        assert g.dtype.itemsize == r.dtype.itemsize, f"{name}: dtype {g.dtype} vs {r.dtype}"
+        g = g.view(r.dtype)
+    bad = int(np.count_nonzero(g != r))
+    assert bad == 0, f"{name}: {bad} of {g.size} elements differ from the oracle (first at {np.flatnonzero(g != r)[:5]})"
+
+
+def assert_update_close(dp, dp_ref, g_ref, lr, name, tol=1e-3, first_step=True, resolved_frac=None,
+                        max_unresolved=0.02, p_before=None, ulps=1.0):
+    """Adam update ``p_after - p_before`` against the oracle's, relative to the update's own scale.
+
+    Adam normalises the gradient (``lr * m_hat / (sqrt(v_hat) + eps)``; the very first step is ``lr * sign(g)``),
+    so an element whose gradient lies below the resolution of the fp32 sums -- where the gradient tolerance itself
+    admits a sign change -- can legitimately move by a different amount.  Elements whose oracle gradient exceeds
+    ``resolved_frac * max|g|`` must match within ``tol * max(|update|, 0.01 * lr)``; the others may differ, but
+    must stay within the step bound (first step: ``|update| <= lr``) and must be few.  ``resolved_frac`` defaults
+    to 1e-5 for a first step (only the gradient's sign matters there) and to 1e-3 afterwards (the floor below
+    which the gradient comparison itself is absolute, not relative).  ``p_before``: the parameter is stored in
+    fp32, so its update is quantised by the spacing of the parameter itself (one ulp of a position near 16 is
+    1.2 % of the position learning rate); ``ulps`` spacings of ``p_before`` are added to the bound."""
+    if resolved_frac is None:
+        resolved_frac = 1e-5 if first_step else 1e-3
+    dp = np.asarray(dp, np.float64)
+    dp_ref = np.asarray(dp_ref, np.float64)
+    g = np.abs(np.asarray(g_ref, np.float64))
+    assert dp.shape == dp_ref.shape == g.shape, f"{name}: shapes {dp.shape} {dp_ref.shape} {g.shape}"
+    assert np.abs(dp_ref).max() > 0.5 * lr, f"{name}: the oracle's update is empty"
+    assert np.abs(dp).max() > 0.5 * lr, f"{name}: the parameters did not move"
+    resolved = g > resolved_frac * g.max()
+    err = np.abs(dp - dp_ref)
+    bound = tol * np.maximum(np.abs(dp_ref), 1e-2 * lr)
+    if p_before is not None:
+        bound = bound + ulps * np.spacing(np.abs(np.asarray(p_before, np.float32))).astype(np.float64)
+    bad = resolved & (err > bound)
+    assert not bad.any(), (f"{name}: {int(bad.sum())}/{int(resolved.sum())} resolved elements off, max err "
+                           f"{err[resolved].max():.3e} against lr {lr:.3e}")
+    loose = ~resolved
+    if first_step:
+        assert (np.abs(dp[loose]) <= lr * (1.0 + 1e-3)).all(), f"{name}: an update exceeds the first-step bound lr"
+    differing = loose & (err > bound)
+    moved = max(int(np.count_nonzero(dp_ref)), 1)
+    assert differing.sum() <= max_unresolved * moved, \
+        f"{name}: {int(differing.sum())} unresolved elements differ ({differing.sum() / moved:.2%} of the moved ones)"

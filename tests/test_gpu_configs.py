@@ -1,0 +1,177 @@
+"""GPU parity on the five named benchmark configurations, at their full sizes, against the CPU oracle.
+
+Every scene is the one ``scenes.make_scene(name, seed=0)`` generates (camera 0 of the configuration).  Bars:
+bit-exact tile-touch counts, unsorted and sorted key/value lists, tile ranges and per-pixel contributor counts
+(the mismatch count is reported, the target is 0); <= 1e-4 relative for the rendered image; <= 1e-3 relative
+for the 59 per-Gaussian gradients, ``duv``, the densification statistics and the Adam moments; the Adam UPDATE
+``p_after - p_before`` within 1e-3 of the update's own scale.
+
+cfg0: 10 k Gaussians, SH degree 0, 256x256, L1 loss, forward + backward.
+cfg1: 100 k, SH degree 3, 800x800, L1 loss, one Adam step + statistics (and a second step from a common state,
+      where Adam's normalisation no longer hides the gradient's magnitude).
+cfg2: 1 M, 1297x840, 0.8 L1 + 0.2 D-SSIM, the full iteration.
+cfg3: 3 M, 1920x1080, the full iteration of one data-parallel rank (the benchmark's workload).
+cfg4: 6 M, 3840x2160, forward only (inference), binning bit-exact for one of the 64 cameras.
+"""
+import numpy as np
+import pytest
+import torch
+
+import d3gs_research_b200 as d3
+from d3gs_research_b200 import scenes
+from d3gs_research_b200.config_def import EarlyFilterAlgo
+from d3gs_research_b200.fused_ssim import l1_dssim_forward_backward
+from d3gs_research_b200.render import GaussianSplatGradients
+from d3gs_research_b200.trainer import SplatTrainer
+from oracle import oracle as O
+from parity_utils import (assert_bit_equal, assert_close, assert_update_close, gpu_cameras, gpu_model, oracle_cfg,
+                          oracle_scene)
+
+pytestmark = pytest.mark.gpu
+
+IMG_TOL = 1e-4
+GRAD_TOL = 1e-3
+FIELDS = ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")
+MODEL_ATTR = dict(xyz="xyz", quat="quaternion_xyzw", scale="scale", opacity="opacity", sh_base="color_sh_base",
+                  sh_rest="color_sh")
+LAMBDA = {"cfg0": 0.0, "cfg1": 0.0, "cfg2": 0.2, "cfg3": 0.2}
+
+
+def _op_cfg():
+    return d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
+
+
+def _fresh_adam(osc):
+    return {k: (np.zeros_like(getattr(osc, k)), np.zeros_like(getattr(osc, k))) for k in FIELDS}
+
+
+def _check_binning(op, out, ref):
+    dbg = op.debug
+    assert op.last_num_rendered == ref.num_rendered, (op.last_num_rendered, ref.num_rendered)
+    assert_bit_equal(dbg["tiles_touched"], ref.prep["tiles_touched"], "tiles_touched")
+    assert_bit_equal(dbg["scan"], ref.scan, "scan")
+    assert_bit_equal(dbg["keys"], ref.keys.view(np.int64), "unsorted keys")
+    assert_bit_equal(dbg["values"], ref.vals, "unsorted values")
+    assert_bit_equal(dbg["sorted_keys"], ref.sorted_keys.view(np.int64), "sorted keys")
+    assert_bit_equal(dbg["sorted_values"], ref.sorted_ids, "sorted values")
+    assert_bit_equal(dbg["ranges"], ref.ranges, "workload_ranges")
+    assert_bit_equal(out.n_contrib, ref.n_contrib, "n_contrib")
+    assert_bit_equal(out.radii, ref.prep["radii"], "radii")
+
+
+def _full_config_parity(name, device, second_step=False):
+    """Forward, loss, backward, Adam and statistics of one named configuration against the oracle."""
+    sc = scenes.make_scene(name, seed=0, views=1)
+    cfg = sc["cfg"]
+    lam = LAMBDA[name]
+    op_cfg = _op_cfg()
+    target = sc["target"][:1].contiguous()
+    n = cfg.n
+
+    # ---- oracle: the whole iteration, parameters updated in place ---------------------------------------
+    osc = oracle_scene(sc)
+    before = {k: getattr(osc, k).copy() for k in FIELDS}
+    adam_state = _fresh_adam(osc)
+    ostats = dict(duv_ndc_length=np.zeros(n, np.float32), count=np.zeros(n, np.float32), max_radii=np.zeros(n, np.float32))
+    ref = O.run_iteration(oracle_cfg(sc, op_cfg), osc, target.numpy(), lam, adam_state=adam_state, step=1, stats=ostats)
+    assert ref.num_rendered > 0
+
+    # ---- run A: the operator API, gradients visible --------------------------------------------------------
+    cams = gpu_cameras(sc, device)
+    tgt = target.to(device)
+    model = gpu_model(sc, device)
+    model.act_applied = True
+    op = d3.GaussianSplatOp(op_cfg)
+    op.debug_capture = True
+    out, ctx = op.forward(model, cams, training=True)
+    _check_binning(op, out, ref)
+    assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
+    assert_close(out.T.cpu().numpy(), ref.T, IMG_TOL, "T")
+    loss, dcolor = l1_dssim_forward_backward(out.color, tgt, lam)
+    assert abs(loss.item() - float(ref.loss[0])) <= 1e-5 * max(1.0, abs(float(ref.loss[0])))
+    # a gradient: the separable fp32 filters here and the oracle's 121-tap fp32 window round differently, and the
+    # variance terms of a smooth image cancel heavily (measured 1.4e-4 .. 2.3e-4 of the largest element)
+    assert_close(dcolor.cpu().numpy(), ref.drgb, GRAD_TOL, "dL/dcolor", floor_frac=1e-2)
+    gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None), return_uv_grad=True)
+    torch.cuda.synchronize()
+    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv")
+    for k in FIELDS:
+        assert_close(getattr(gm, MODEL_ATTR[k]).cpu().numpy(), ref.grads[k], GRAD_TOL, f"grad {k}")
+    del op, out, ctx, gm, duv, dcolor, model
+    if name == "cfg0":      # forward + backward under the L1 loss is the whole configuration
+        return
+
+    # ---- runs B and C: the training step, first with a gradient buffer + optimizer kernel (the path every rank of a
+    # data-parallel run takes), then with Adam inside the preprocess backward (the single-GPU default)
+    for fused in (False, True):
+        model = gpu_model(sc, device)
+        tr = SplatTrainer(model, op_cfg, lambda_dssim=lam, batch_size=1, fuse_backward_adam=fused)
+        assert tr.fused_adam == fused
+        info = tr.step(cams, tgt)
+        tr.op.check_status()
+        torch.cuda.synchronize()
+        assert abs(info["loss"].item() - float(ref.loss[0])) <= 1e-5 * max(1.0, abs(float(ref.loss[0])))
+        m_views, v_views = tr._field_views(tr.exp_avg), tr._field_views(tr.exp_avg_sq)
+        for k in FIELDS:
+            after = getattr(model, MODEL_ATTR[k]).detach().cpu().numpy()
+            assert_update_close(after - before[k], getattr(osc, k) - before[k], ref.grads[k], O.ADAM_LRS[k],
+                                f"{name} fused={fused} Adam update {k}", p_before=before[k])
+            assert_close(m_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][0], GRAD_TOL, f"exp_avg {k}")
+            assert_close(v_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][1], GRAD_TOL, f"exp_avg_sq {k}")
+        for k in ostats:
+            assert_close(getattr(tr.state, k).cpu().numpy(), ostats[k], GRAD_TOL, f"stats {k}")
+        if second_step and fused:
+            # Second step from a COMMON state: the GPU takes the oracle's parameters and moments, so that the only
+            # difference between the two second updates is the second gradient.  With non-zero moments the update
+            # depends on the gradient's magnitude, not only on its sign.
+            mid = {k: getattr(osc, k).copy() for k in FIELDS}
+            with torch.no_grad():
+                for k in FIELDS:
+                    getattr(model, MODEL_ATTR[k]).copy_(torch.from_numpy(mid[k]).to(device))
+                    m_views[MODEL_ATTR[k]].copy_(torch.from_numpy(adam_state[k][0]).to(device))
+                    v_views[MODEL_ATTR[k]].copy_(torch.from_numpy(adam_state[k][1]).to(device))
+            ref2 = O.run_iteration(oracle_cfg(sc, op_cfg), osc, target.numpy(), lam, adam_state=adam_state, step=2)
+            tr.step(cams, tgt)
+            tr.op.check_status()
+            torch.cuda.synchronize()
+            for k in FIELDS:
+                after = getattr(model, MODEL_ATTR[k]).detach().cpu().numpy()
+                assert_update_close(after - mid[k], getattr(osc, k) - mid[k], ref2.grads[k], O.ADAM_LRS[k],
+                                    f"{name} second Adam update {k}", first_step=False, p_before=mid[k])
+        del tr, model
+
+
+def test_cfg0_tiny_forward_backward(cuda_device):
+    _full_config_parity("cfg0", cuda_device)
+
+
+def test_cfg1_adam_step_and_stats(cuda_device):
+    _full_config_parity("cfg1", cuda_device, second_step=True)
+
+
+def test_cfg2_full_iteration(cuda_device):
+    _full_config_parity("cfg2", cuda_device)
+
+
+def test_cfg3_full_iteration_one_rank(cuda_device):
+    _full_config_parity("cfg3", cuda_device)
+
+
+def test_cfg4_binning_one_camera(cuda_device):
+    """6 M Gaussians, 3840x2160, forward only: keys, sorted lists, ranges and contributor counts of camera 0."""
+    sc = scenes.make_scene("cfg4", seed=0, views=1)
+    op_cfg = _op_cfg()
+    op = d3.GaussianSplatOp(op_cfg)
+    op.debug_capture = True
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    out, ctx = op.forward(model, gpu_cameras(sc, cuda_device), training=False)
+    op.check_status()
+    torch.cuda.synchronize()
+    assert ctx is None
+    ocfg = oracle_cfg(sc, op_cfg, training=False)
+    ref = O.forward(ocfg, oracle_scene(sc))
+    assert ref.num_rendered > 10_000_000
+    _check_binning(op, out, ref)
+    color, _, _ = O.raster_fwd(ocfg, 1, ref.ranges, ref.sorted_ids, ref.prep, bg=op_cfg.bg_color)
+    assert_close(out.color.cpu().numpy(), color, IMG_TOL, "color")
