@@ -67,6 +67,9 @@ def parse():
     ap.add_argument("--long-steps", type=int, default=300,
                     help="also time one loop of this many steps from the snapshot (value_300: the work per step "
                          "drifts as training moves the Gaussians); 0 = skip")
+    ap.add_argument("--binning", default="bucket", choices=["bucket", "sort"],
+                    help="sorted per-tile lists from per-tile buckets sorted in shared memory, or from key "
+                         "duplication + global radix sort + range extraction like the reference")
     ap.add_argument("--raster-grad-mode", default="auto", choices=["auto", "direct", "shared"],
                     help="raster backward: direct global atomics per lane group, per-tile accumulation in shared "
                          "memory, or chosen from the pairs per Gaussian")
@@ -238,11 +241,25 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, train
     return float(table.get(stage, 0.0))
 
 
+BUCKET_BINNING = False    # set by the bench from the binning path the operator took
+
+
 def moved_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, training: bool = True) -> float:
     """Bytes the launch of a stage itself has to move.  Equal to the algorithmic bytes except for the fused
-    backward + Adam launch, which neither writes nor re-reads the 236-byte-per-Gaussian gradient."""
+    backward + Adam launch, which neither writes nor re-reads the 236-byte-per-Gaussian gradient, and for the
+    tile-bucket binning: the scan runs over the tiles, a pair is one 8-byte entry, the per-tile sort reads the
+    entries once and writes 4-byte indices, and there is no range extraction."""
     if stage == "preprocess_bwd_adam":
         return float(89 * V + 1456 * N)
+    if BUCKET_BINNING:
+        if stage == "scan":
+            return float(8 * Tn + 20 * Tn)
+        if stage == "duplicate_keys":
+            return float(4 * N + 28 * V + 8 * K + 8 * K)    # + one cursor atomic per pair
+        if stage == "sort":
+            return float(8 * K + 4 * K + 8 * Tn)
+        if stage == "preprocess_fwd":
+            return algorithmic_bytes(stage, N, V, K, P, Tn, training) + 4 * K   # one count atomic per pair
     return algorithmic_bytes(stage, N, V, K, P, Tn, training)
 
 
@@ -323,9 +340,11 @@ def cpu_baseline(cfg_name: str, sample: int, check: dict | None = None):
     cores = O.set_num_threads()
     full = scenes.CONFIGS[cfg_name]
     n = max(full.n // sample, 1000)
-    sc = scenes.make_scene(cfg_name, seed=0, n=n, views=1)
-    osc = _oracle_scene(sc)
     render_only = cfg_name == "cfg4"
+    # camera 0 of the configuration's camera set (the render sweep's cameras lie on a sphere whose sampling
+    # depends on the number of views; the training configurations use their first camera)
+    sc = scenes.make_scene(cfg_name, seed=0, n=n, views=None if render_only else 1)
+    osc = _oracle_scene(sc)
     ocfg = O.OpConfig(width=full.width, height=full.height, sh_degree=full.sh_degree, early_filter=4,
                       training=not render_only)
     scale = full.n / n
@@ -412,6 +431,7 @@ def _dist_setup():
 
 # ---------------------------------------------------------------------------------------------
 def bench_train(args):
+    global BUCKET_BINNING
     import torch
     import torch.distributed as dist
 
@@ -437,6 +457,7 @@ def bench_train(args):
                            peer_update=False if (args.nccl_update or args.replicated_adam) else None,
                            fuse_backward_adam=False if (args.separate_adam or world > 1 or not do_update) else None)
     trainer.op.raster_grad_direct = {"auto": None, "direct": True, "shared": False}[args.raster_grad_mode]
+    trainer.op.binning = args.binning
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
     target_host = sc["target"][rank % sc["target"].shape[0]][None].contiguous().pin_memory()
@@ -562,6 +583,8 @@ def bench_train(args):
     direct = trainer.op.raster_grad_direct
     if direct is None:
         direct = K < trainer.op.DIRECT_ATOMICS_PAIRS_PER_GAUSSIAN * N
+    BUCKET_BINNING = trainer.op.last_binning == "bucket"
+    binning_taken = trainer.op.last_binning
     trainer.close()    # unmap the peer buffers (collective) before the process group goes away
     if rank != 0:
         if world > 1:
@@ -576,6 +599,8 @@ def bench_train(args):
                    "parallelism": f"dp{world} over views, replicated Gaussians",
                    "optimizer": optimizer_kind,
                    "raster_backward": "direct global atomics per lane group" if direct else "per-tile accumulation in shared memory",
+                   "binning": "per-tile buckets sorted in shared memory" if binning_taken == "bucket" else
+                              "key duplication + global radix sort + range extraction",
                    "replicas_agree": replicas_agree, "early_filter": "OBB_DFVT",
                    "l2": "inputs larger than L2 (params+grads+Adam state 2.8 GB per step)" if N >= 1_000_000 else
                          "working set below the 126 MB L2 at this size; no flush between steps (a training loop "
@@ -607,6 +632,7 @@ def bench_render(args):
     """cfg4: forward-only rendering of the configuration's 64 cameras, 64/N views per GPU in launches of up to
     8 views (one ``CameraBundle`` per launch; sort key = (view * tiles + tile) << 32 | depth).  A step is one pass
     over this rank's cameras.  No collective: the ranks render disjoint cameras."""
+    global BUCKET_BINNING
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -631,6 +657,7 @@ def bench_render(args):
                                                      sc["sh_rest"], device=dev, cur_sh_degree=scfg.sh_degree)
     model.act_applied = True
     op = d3.GaussianSplatOp(d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT))
+    op.binning = args.binning
     fx, fy, cx, cy = sc["intrinsics"]
     my_cams = [d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank * per_rank + k], fx, fy, cx, cy, W, H)
                for k in range(per_rank)]
@@ -713,6 +740,8 @@ def bench_render(args):
     stage_ms = op.timer.summary(median=False)
     op.timer = None
     op.check_status()
+    BUCKET_BINNING = op.last_binning == "bucket"
+    binning_taken = op.last_binning
     # camera 0 of the whole set, rendered alone, for the bit-exact comparison with the CPU oracle
     check = None
     if rank == 0 and not args.no_cpu_baseline and not n_override:
@@ -744,6 +773,8 @@ def bench_render(args):
                    "sort_pairs_per_launch": K, "visible_per_launch": V, "resolution": [W, H],
                    "sort_key_bits": 32 + int(Tn).bit_length(),
                    "parallelism": f"{world} ranks render disjoint cameras, replicated Gaussians, no collective",
+                   "binning": "per-tile buckets sorted in shared memory" if binning_taken == "bucket" else
+                              "key duplication + global radix sort + range extraction",
                    "early_filter": "OBB_DFVT", "l2": "inputs larger than L2 (several GB per launch)"},
         "repeats": {"count": repeats, "ms_per_step_min": min(dev_ms) / args.steps, "ms_per_step_max": max(dev_ms) / args.steps,
                     "ms_per_step_median": ms_total / args.steps},

@@ -49,7 +49,8 @@ class ModelGrad(C.Structure):
 class SplatContext(C.Structure):
     _fields_ = [("tiles_touched", C.c_void_p), ("radii", C.c_void_p), ("depths", C.c_void_p), ("uvs", C.c_void_p),
                 ("conic_opacity", C.c_void_p), ("rgb_gaussian", C.c_void_p), ("cov2d_vecs", C.c_void_p),
-                ("sh_to_rgb_ne_0", C.c_void_p), ("tile_mask", C.c_void_p), ("records", C.c_void_p)]
+                ("sh_to_rgb_ne_0", C.c_void_p), ("tile_mask", C.c_void_p), ("records", C.c_void_p),
+                ("tile_counts", C.c_void_p)]
 
 
 class AdamSegment(C.Structure):
@@ -109,6 +110,10 @@ SIGNATURES = {
     "d3gs_duplicate_keys": (_I32, [C.POINTER(OpConfig), _I64, _P, C.POINTER(SplatContext), _P, _P, _P]),
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
+    "d3gs_bucket_sort_capacity": (_I64, []),
+    "d3gs_bucket_prepare": (_I32, [_P, _P, _I64, _P, _P, _P, _P]),
+    "d3gs_bucket_emit": (_I32, [C.POINTER(OpConfig), _I64, C.POINTER(SplatContext), _P, _P, _P]),
+    "d3gs_bucket_sort": (_I32, [_P, _P, _I64, _I64, _P, _P, _P]),
     "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _I32, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
     "d3gs_tile_order": (_I32, [_P, _I64, _P, _P]),

@@ -211,8 +211,9 @@ constexpr int kRow = 45;   // shared-memory row length in floats (odd: conflict-
 // the SURVIVING Gaussians only (180 bytes each) are then brought into shared memory with coalesced
 // loads and evaluated per thread from there: per-thread global loads with a 180-byte stride cost ~22
 // sectors per request.
+// 64 registers (4 CTAs of 256 threads per SM): with 78 the kernel lost a fifth of its throughput
 template <int DEG>
-__global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+__global__ void __launch_bounds__(256, 4) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
     constexpr int NB = (DEG + 1) * (DEG + 1);
     constexpr int NR3 = (NB - 1) * 3;
     __shared__ __align__(128) float s_rest[NR3 > 0 ? 256 * kRow : 4];
@@ -361,9 +362,12 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                     seed.u = u; seed.v = v; seed.ca = k0; seed.cb = k1; seed.cc = k2; seed.opacity = opq;
                     seed.rmin0 = rmin[0]; seed.rmin1 = rmin[1]; seed.rmax0 = rmax[0]; seed.rmax1 = rmax[1];
                 } else {
+                    int32_t* tcount = a.ctx.tile_counts != nullptr ? a.ctx.tile_counts + (int64_t)b * (tg.tiles_x * tg.tiles_y)
+                                                                   : nullptr;
                     walk.for_each([&](int x, int y) {
                         ++cnt;
                         if (small_rect) tmask |= 1ull << ((y - rmin[1]) * rw + (x - rmin[0]));
+                        if (tcount != nullptr) atomicAdd(tcount + (y * tg.tiles_x + x), 1);
                     });
                 }
                 if (a.ctx.tile_mask != nullptr) a.ctx.tile_mask[i] = tmask;
@@ -401,11 +405,18 @@ __global__ void __launch_bounds__(256) preprocess_fwd_kernel(const __grid_consta
                 walk.init(cf.early_filter_algo, tg, cf.tile_x, cf.alpha_eps, sd.u, sd.v, sd.ca, sd.cb, sd.cc, sd.opacity,
                           rmin, rmax);
                 const int bw = walk.width(), n_tiles = walk.area();
+                int32_t* tcount = nullptr;
+                if (a.ctx.tile_counts != nullptr) {
+                    const int64_t isrc = i0 + (t & ~31) + src;     // flat index of the lane whose walk this is
+                    tcount = a.ctx.tile_counts + (isrc / N) * (int64_t)(tg.tiles_x * tg.tiles_y);
+                }
                 int cnt = 0;
                 for (int q0 = 0; q0 < n_tiles; q0 += 32) {
                     const int q = q0 + lane;
-                    const bool ok = q < n_tiles && walk.test(walk.bmin[0] + q % bw, walk.bmin[1] + q / bw);
+                    const int x = walk.bmin[0] + q % bw, y = walk.bmin[1] + q / bw;
+                    const bool ok = q < n_tiles && walk.test(x, y);
                     cnt += __popc(__ballot_sync(0xffffffffu, ok));
+                    if (ok && tcount != nullptr) atomicAdd(tcount + (y * tg.tiles_x + x), 1);
                 }
                 if (lane == src) a.ctx.tiles_touched[i] = cnt;
             }
@@ -478,9 +489,15 @@ struct DupArgs {
     const int32_t* scan;
     uint64_t* keys;
     int32_t* values;
+    int32_t* cursor;      // BUCKET: next free position of every tile's range
+    uint64_t* entries;    // BUCKET: depth bits << 32 | flat index, one per pair, in the tile's range
     int64_t num;
 };
 
+// BUCKET == false: key = tile << shift | depth bits and value = flat index at the Gaussian's scanned offset
+// (render.py:739-840).  BUCKET == true: the pair becomes one 8-byte entry, depth bits << 32 | flat index, at a
+// position drawn from the tile's cursor inside the tile's range.
+template <bool BUCKET>
 __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_constant__ DupArgs a) {
     const int64_t total = a.num * a.cfg.num_views;
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -498,7 +515,7 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
     uint64_t tile_base = 0;
     if (r > 0) {
         const int b = (int)(i / a.num);
-        off = i == 0 ? 0 : (int64_t)a.scan[i - 1];
+        if (!BUCKET) off = i == 0 ? 0 : (int64_t)a.scan[i - 1];
         const float2 uv = *reinterpret_cast<const float2*>(a.ctx.uvs + i * 2);
         int rmin[2], rmax[2];
         tile_rect(tg, uv.x, uv.y, (float)r, rmin, rmax);
@@ -513,15 +530,43 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
             uint64_t m = a.ctx.tile_mask[i];
             // bit / rw by one multiplication: exact for bit < 64 and rw <= 64
             const uint32_t rcp = (65536u + (uint32_t)max(rw, 1) - 1u) / (uint32_t)max(rw, 1);
-            while (m) {
-                const int bit = __ffsll((long long)m) - 1;
-                m &= m - 1;
-                const int by = (int)(((uint32_t)bit * rcp) >> 16);
-                const int y = rmin[1] + by, x = rmin[0] + (bit - by * rw);
-                const uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
-                a.keys[off] = (key << shift) | dbits;
-                a.values[off] = (int32_t)i;
-                ++off;
+            if (BUCKET) {
+                // The position of an entry comes back from an atomic on its tile's cursor: four tiles at a time, so
+                // that the four round trips to L2 overlap instead of following one another.
+                const uint64_t e = ((uint64_t)dbits << 32) | (uint32_t)i;
+                while (m) {
+                    int32_t* cur[4];
+                    int nt = 0;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        cur[u] = a.cursor;
+                        if (m) {
+                            const int bit = __ffsll((long long)m) - 1;
+                            m &= m - 1;
+                            const int by = (int)(((uint32_t)bit * rcp) >> 16);
+                            cur[u] = a.cursor + (tile_base + (uint64_t)((rmin[1] + by) * tg.tiles_x + rmin[0] + (bit - by * rw)));
+                            nt = u + 1;
+                        }
+                    }
+                    int pos[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (u < nt) pos[u] = atomicAdd(cur[u], 1);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (u < nt) a.entries[pos[u]] = e;
+                }
+            } else {
+                while (m) {
+                    const int bit = __ffsll((long long)m) - 1;
+                    m &= m - 1;
+                    const int by = (int)(((uint32_t)bit * rcp) >> 16);
+                    const int y = rmin[1] + by, x = rmin[0] + (bit - by * rw);
+                    const uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
+                    a.keys[off] = (key << shift) | dbits;
+                    a.values[off] = (int32_t)i;
+                    ++off;
+                }
             }
         } else {
             const float4 co = *reinterpret_cast<const float4*>(a.ctx.conic_opacity + i * 4);
@@ -534,9 +579,13 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
             } else {
                 walk.for_each([&](int x, int y) {
                     uint64_t key = tile_base + (uint64_t)(y * tg.tiles_x + x);
-                    a.keys[off] = (key << shift) | dbits;
-                    a.values[off] = (int32_t)i;
-                    ++off;
+                    if (BUCKET) {
+                        a.entries[atomicAdd(a.cursor + key, 1)] = ((uint64_t)dbits << 32) | (uint32_t)i;
+                    } else {
+                        a.keys[off] = (key << shift) | dbits;
+                        a.values[off] = (int32_t)i;
+                        ++off;
+                    }
                 });
             }
         }
@@ -562,9 +611,14 @@ __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_consta
             const bool ok = q < n_tiles && walk.test(x, y);
             const uint32_t m = __ballot_sync(0xffffffffu, ok);
             if (ok) {
-                const int64_t dst = o + __popc(m & ((1u << lane) - 1u));
-                a.keys[dst] = ((tb + (uint64_t)(y * tg.tiles_x + x)) << shift) | db;
-                a.values[dst] = id;
+                if (BUCKET) {
+                    a.entries[atomicAdd(a.cursor + (tb + (uint64_t)(y * tg.tiles_x + x)), 1)] =
+                        ((uint64_t)db << 32) | (uint32_t)id;
+                } else {
+                    const int64_t dst = o + __popc(m & ((1u << lane) - 1u));
+                    a.keys[dst] = ((tb + (uint64_t)(y * tg.tiles_x + x)) << shift) | db;
+                    a.values[dst] = id;
+                }
             }
             o += __popc(m);
         }
@@ -615,6 +669,11 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
     D3GS_REQUIRE(!cfg->training || (ctx->cov2d_vecs && ctx->sh_to_rgb_ne_0),
                  "training needs cov2d_vecs and sh_to_rgb_ne_0");
     const int64_t total = model->num * cfg->num_views;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (ctx->tile_counts != nullptr) {
+        const size_t tiles = (size_t)cfg->num_views * ((cfg->width + 15) / 16) * ((cfg->height + 15) / 16);
+        D3GS_CUDA(cudaMemsetAsync(ctx->tile_counts, 0, tiles * sizeof(int32_t), s));
+    }
     if (total == 0) return D3GS_OK;
     D3GS_REQUIRE(total < (int64_t)1 << 31, "B*N = %lld does not fit int32 indexing", (long long)total);
     PrepArgs a;
@@ -624,7 +683,6 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
     a.ctx = *ctx;
     a.mask = mask;
     dim3 grid((unsigned)div_up64(total, 256));
-    cudaStream_t s = (cudaStream_t)stream;
     switch (cfg->sh_degree) {
         case 0: preprocess_fwd_kernel<0><<<grid, 256, 0, s>>>(a); break;
         case 1: preprocess_fwd_kernel<1><<<grid, 256, 0, s>>>(a); break;
@@ -651,7 +709,31 @@ extern "C" int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, con
     a.keys = keys;
     a.values = values;
     a.num = num;
-    duplicate_keys_kernel<<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    duplicate_keys_kernel<false><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("duplicate_keys_kernel");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const D3gsSplatContext* ctx, int32_t* cursor,
+                                    uint64_t* entries, void* stream) {
+    int32_t rc = check_cfg(cfg);
+    if (rc != D3GS_OK) return rc;
+    D3GS_REQUIRE(cfg->key_shift_bits == 0 || cfg->key_shift_bits == 32,
+                 "tile-bucket binning orders by the 32 depth bits (64-bit sort keys); got key_shift_bits %d",
+                 cfg->key_shift_bits);
+    D3GS_REQUIRE(ctx != nullptr, "ctx is NULL");
+    const int64_t total = num * cfg->num_views;
+    if (total == 0) return D3GS_OK;
+    D3GS_REQUIRE(cursor != nullptr && entries != nullptr, "cursor/entries is NULL");
+    D3GS_REQUIRE(ctx->radii && ctx->depths && ctx->uvs && ctx->conic_opacity, "context tensor pointer is NULL");
+    DupArgs a = {};
+    a.cfg = *cfg;
+    if (a.cfg.early_filter_algo == 4) a.cfg.early_filter_algo = 3;
+    a.ctx = *ctx;
+    a.cursor = cursor;
+    a.entries = entries;
+    a.num = num;
+    duplicate_keys_kernel<true><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    D3GS_LAUNCH_CHECK("duplicate_keys_kernel<bucket>");
     return D3GS_OK;
 }

@@ -233,6 +233,13 @@ class GaussianSplatOp:
         # False = per-tile accumulation in shared memory first, None = chosen per call from the number of sort
         # pairs per Gaussian (small splats -> direct).  Same gradients up to the order of the float additions.
         self.raster_grad_direct: bool | None = None
+        # How the sorted per-tile lists are built.  "bucket": the preprocess counts the pairs of every tile, the
+        # pairs are written straight into their tile's range and every tile's list is sorted in shared memory
+        # (d3gs_bucket_*); "sort": key duplication, global radix sort and range extraction like the reference.
+        # Same lists and ranges bit for bit.  "bucket" falls back to "sort" for a launch whose longest list does
+        # not fit one CTA's shared memory, and is not used with 32-bit sort keys.
+        self.binning = "bucket"
+        self.last_binning = ""
         self.debug: dict[str, torch.Tensor] = {}
         # optional StageTimer; None = no events recorded
         self.timer: StageTimer | None = None
@@ -251,10 +258,10 @@ class GaussianSplatOp:
 
     # ---- plumbing ---------------------------------------------------------------------------
     def _sync_words(self, device) -> torch.Tensor:
-        """int64[2] on the device: [num_rendered, status bits]; read back with one copy."""
+        """int64[4] on the device: [num_rendered, status bits, longest tile list, unused]; read back with one copy."""
         t = self._sync.get(device)
         if t is None:
-            t = torch.zeros(2, dtype=torch.int64, device=device)
+            t = torch.zeros(4, dtype=torch.int64, device=device)
             self._sync[device] = t
         return t
 
@@ -334,13 +341,14 @@ class GaussianSplatOp:
 
     @staticmethod
     def _ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb, cov2d, ne0,
-                    tile_mask=None, records=None) -> _lib.SplatContext:
+                    tile_mask=None, records=None, tile_counts=None) -> _lib.SplatContext:
         s = _lib.SplatContext()
         s.tiles_touched, s.radii, s.depths = _lib.ptr(tiles_touched), _lib.ptr(radii), _lib.ptr(depths)
         s.uvs, s.conic_opacity, s.rgb_gaussian = _lib.ptr(uvs), _lib.ptr(conic_opacity), _lib.ptr(rgb)
         s.cov2d_vecs, s.sh_to_rgb_ne_0 = _lib.ptr(cov2d), _lib.ptr(ne0)
         s.tile_mask = _lib.ptr(tile_mask)
         s.records = _lib.ptr(records)
+        s.tile_counts = _lib.ptr(tile_counts)
         return s
 
     # ---- output formats (render.py:696-705, 1623-1668, 2222-2300) ------------------------------------
@@ -400,9 +408,11 @@ class GaussianSplatOp:
         # per-Gaussian raster records, written by the preprocess and gathered by sorted id in the raster kernels
         gather = self.gather_records
         records = torch.empty([BN, 12], dtype=f32, device=dev) if gather else None
+        use_bucket = self.binning == "bucket" and not self._cfg.enable_32bit_sort
+        tile_counts = torch.empty(num_tiles, dtype=i32, device=dev) if use_bucket else None
         mstruct = self._model_struct(model)
         cstruct = self._ctx_struct(tiles_touched, radii, depths, uvs, conic_opacity, rgb_gaussian, cov2d_vecs, sh_ne0,
-                                   tile_mask, records)
+                                   tile_mask, records, tile_counts)
         mask_u8 = None
         if mask is not None:
             mask_u8 = mask.to(torch.uint8).contiguous()
@@ -412,19 +422,35 @@ class GaussianSplatOp:
         self._mark("preprocess_fwd")
         if self.debug_capture:
             self.debug = {"tiles_touched": tiles_touched.clone()}
-        # cumsum + total (render.py:694-695): one device->host read per forward, as in the reference
         sync = self._sync_words(dev)
-        ws_scan = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(BN), dev)
-        _lib.check(lib.d3gs_scan_tiles(tiles_touched.data_ptr(), tiles_touched.data_ptr(), BN, sync.data_ptr(),
-                                       ws_scan.data_ptr(), ws_scan.numel(), sync.data_ptr() + 8, stream),
-                   "d3gs_scan_tiles")
+        workload_ranges = cursor = None
+
+        def scan_tiles_touched():   # cumsum + total (render.py:694-695)
+            ws = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(BN), dev)
+            _lib.check(lib.d3gs_scan_tiles(tiles_touched.data_ptr(), tiles_touched.data_ptr(), BN, sync.data_ptr(),
+                                           ws.data_ptr(), ws.numel(), sync.data_ptr() + 8, stream), "d3gs_scan_tiles")
+
+        if use_bucket:
+            # the pair count is the total of the per-tile counts; their scan is every tile's range
+            tile_scan = torch.empty(num_tiles, dtype=i32, device=dev)
+            ws = self._ws.get("scan_tiles", lib.d3gs_scan_workspace_bytes(num_tiles), dev)
+            _lib.check(lib.d3gs_scan_tiles(tile_counts.data_ptr(), tile_scan.data_ptr(), num_tiles, sync.data_ptr(),
+                                           ws.data_ptr(), ws.numel(), sync.data_ptr() + 8, stream), "d3gs_scan_tiles")
+            workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
+            cursor = torch.empty(num_tiles, dtype=i32, device=dev)
+            _lib.check(lib.d3gs_bucket_prepare(tile_counts.data_ptr(), tile_scan.data_ptr(), num_tiles,
+                                               workload_ranges.data_ptr(), cursor.data_ptr(), sync.data_ptr() + 16,
+                                               stream), "d3gs_bucket_prepare")
+        else:
+            scan_tiles_touched()
         self._mark("scan")
-        num_rendered, status = (int(v) for v in sync.tolist())
+        # one device->host read per forward, as in the reference (render.py:695)
+        num_rendered, status, longest, _ = (int(v) for v in sync.tolist())
         self._mark("host_readback_idle")
         if status != 0:
             sync[1] = 0
             raise RuntimeError(f"d3gs_b200 device status {status:#x}: a bounded wait gave up "
-                               "(1 scan, 2 sort, 4 bulk copy); results of the previous call are invalid")
+                               "(1 scan, 2 sort, 4 bulk copy, 8 peer flag); results of the previous call are invalid")
         if num_rendered >= 2 ** 31:
             raise RuntimeError(f"num_rendered {num_rendered} does not fit the int32 offsets")
         self.last_num_rendered = num_rendered
@@ -434,39 +460,56 @@ class GaussianSplatOp:
         if num_rendered == 0:   # render.py:706-729: outputs are left uninitialised, no context
             return GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
                                        depth=None, n_contrib=n_contrib), None
+        if use_bucket and longest > lib.d3gs_bucket_sort_capacity():
+            use_bucket = False          # a list too long for one CTA's shared memory: radix-sort path for this launch
+            scan_tiles_touched()
+        self.last_binning = "bucket" if use_bucket else "sort"
         # Pair-sized buffers are allocated with a capacity quantised to 2^20 pairs above 1.125 x the count: the
         # count changes a little every training step, and exact sizes would make the caching allocator miss
         # and fall back to cudaMalloc (a device-wide stall of milliseconds) every few steps.
         cap = _pair_capacity(num_rendered)
-        keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
-        keys_alt = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
-        gaussian_idx = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
-        gaussian_idx_alt = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
-        _lib.check(lib.d3gs_duplicate_keys(C.byref(ocfg), num, tiles_touched.data_ptr(), C.byref(cstruct),
-                                           keys.data_ptr(), gaussian_idx.data_ptr(), stream), "d3gs_duplicate_keys")
-        self._mark("duplicate_keys")
-        if self.debug_capture:
-            self.debug.update(scan=tiles_touched.clone(), keys=keys.clone(), values=gaussian_idx.clone())
-        end_bit = 32 if self._cfg.enable_32bit_sort else 32 + lib.d3gs_bit_length(num_tiles)   # render.py:851-854
-        ws_sort = self._ws.get("sort", lib.d3gs_sort_workspace_bytes(num_rendered, 0, end_bit), dev)
-        in_alt = C.c_int32(0)
-        _lib.check(lib.d3gs_sort_pairs(keys.data_ptr(), keys_alt.data_ptr(), gaussian_idx.data_ptr(),
-                                       gaussian_idx_alt.data_ptr(), num_rendered, 0, end_bit, ws_sort.data_ptr(),
-                                       ws_sort.numel(), C.byref(in_alt), sync.data_ptr() + 8, stream),
-                   "d3gs_sort_pairs")
-        self._mark("sort")
-        if in_alt.value:                                                   # render.py:884-887
-            keys, keys_alt = keys_alt, keys
-            gaussian_idx, gaussian_idx_alt = gaussian_idx_alt, gaussian_idx
-        gaussian_idx_sorted = gaussian_idx
-        if self.debug_capture:
-            self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted)
-        workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
-        _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles,
-                                        ocfg.key_shift_bits, stream), "d3gs_tile_ranges")
-        self._mark("tile_ranges")
-        if self.debug_capture:
-            self.debug.update(ranges=workload_ranges)
+        if use_bucket:
+            entries = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
+            gaussian_idx_sorted = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
+            keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered] if self.debug_capture else None
+            _lib.check(lib.d3gs_bucket_emit(C.byref(ocfg), num, C.byref(cstruct), cursor.data_ptr(), entries.data_ptr(),
+                                            stream), "d3gs_bucket_emit")
+            self._mark("duplicate_keys")
+            _lib.check(lib.d3gs_bucket_sort(entries.data_ptr(), workload_ranges.data_ptr(), num_tiles, longest,
+                                            gaussian_idx_sorted.data_ptr(), _lib.ptr(keys), stream), "d3gs_bucket_sort")
+            self._mark("sort")
+            if self.debug_capture:
+                self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted, ranges=workload_ranges)
+        else:
+            keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
+            keys_alt = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
+            gaussian_idx = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
+            gaussian_idx_alt = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
+            _lib.check(lib.d3gs_duplicate_keys(C.byref(ocfg), num, tiles_touched.data_ptr(), C.byref(cstruct),
+                                               keys.data_ptr(), gaussian_idx.data_ptr(), stream), "d3gs_duplicate_keys")
+            self._mark("duplicate_keys")
+            if self.debug_capture:
+                self.debug.update(scan=tiles_touched.clone(), keys=keys.clone(), values=gaussian_idx.clone())
+            end_bit = 32 if self._cfg.enable_32bit_sort else 32 + lib.d3gs_bit_length(num_tiles)   # render.py:851-854
+            ws_sort = self._ws.get("sort", lib.d3gs_sort_workspace_bytes(num_rendered, 0, end_bit), dev)
+            in_alt = C.c_int32(0)
+            _lib.check(lib.d3gs_sort_pairs(keys.data_ptr(), keys_alt.data_ptr(), gaussian_idx.data_ptr(),
+                                           gaussian_idx_alt.data_ptr(), num_rendered, 0, end_bit, ws_sort.data_ptr(),
+                                           ws_sort.numel(), C.byref(in_alt), sync.data_ptr() + 8, stream),
+                       "d3gs_sort_pairs")
+            self._mark("sort")
+            if in_alt.value:                                                   # render.py:884-887
+                keys, keys_alt = keys_alt, keys
+                gaussian_idx, gaussian_idx_alt = gaussian_idx_alt, gaussian_idx
+            gaussian_idx_sorted = gaussian_idx
+            if self.debug_capture:
+                self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted)
+            workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
+            _lib.check(lib.d3gs_tile_ranges(keys.data_ptr(), num_rendered, workload_ranges.data_ptr(), num_tiles,
+                                            ocfg.key_shift_bits, stream), "d3gs_tile_ranges")
+            self._mark("tile_ranges")
+            if self.debug_capture:
+                self.debug.update(ranges=workload_ranges)
         if not gather:   # one record per sorted pair, in list order
             records = torch.empty(cap * 12, dtype=f32, device=dev)[:num_rendered * 12].view(num_rendered, 12)
             _lib.check(lib.d3gs_pack_splats(gaussian_idx_sorted.data_ptr(), num_rendered, C.byref(cstruct),

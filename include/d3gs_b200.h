@@ -131,6 +131,9 @@ typedef struct D3gsSplatContext {
                                  raster record of every visible Gaussian, [u v hx hy][ha nb hc o][r g b thr].  Written
                                  by the preprocess; with it the raster kernels gather their records by sorted id and
                                  the per-pair packing pass (d3gs_pack_splats) is not needed. */
+    int32_t* tile_counts;     /* [B*tiles] optional (may be NULL; not in the reference): zero-filled by the preprocess,
+                                 which then adds 1 to the entry of every (view, tile) an accepted Gaussian touches:
+                                 the per-tile list lengths, known before any key exists (tile-bucket binning below) */
 } D3gsSplatContext;
 
 /* ---- helpers -------------------------------------------------------------------------- */
@@ -190,6 +193,28 @@ int32_t d3gs_sort_pairs(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int
 /* ranges [num_tiles,2] int32 is zero-filled by this call, then [start,end) written per tile */
 int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges, int64_t num_tiles,
                          int32_t key_shift_bits, void* stream);
+
+/* ---- tile-bucket binning (no counterpart in the reference; produces what render.py:739-939 produces) -----------
+ * The same sorted per-tile lists and tile ranges as d3gs_duplicate_keys + d3gs_sort_pairs + d3gs_tile_ranges,
+ * without a global sort: the upper key bits only name the tile, and the preprocess has already counted the pairs
+ * of every tile (D3gsSplatContext.tile_counts).  Call order:
+ *   d3gs_scan_tiles(tile_counts -> tile_scan, total = number of pairs)
+ *   d3gs_bucket_prepare: ranges [num_tiles,2] ({0,0} for empty tiles, like d3gs_tile_ranges), cursor [num_tiles] =
+ *       every tile's start, *max_count (device int64) = the longest list;
+ *   (the caller reads total and max_count, allocates entries [total] uint64 and sorted_values [total] int32)
+ *   d3gs_bucket_emit: one entry per pair, depth bits << 32 | flat index, at a position drawn from its tile's cursor;
+ *   d3gs_bucket_sort: every tile's entries sorted in shared memory; sorted_values receives the flat indices,
+ *       sorted_keys (optional, may be NULL) the reference's keys tile << 32 | depth bits.
+ * Entries are unique, so their order is the reference's: by depth, ties by ascending flat index (a stable sort of
+ * pairs emitted in index order).  d3gs_bucket_sort returns D3GS_ERR_UNSUPPORTED when max_count exceeds
+ * d3gs_bucket_sort_capacity() (16384): take the radix-sort path for that launch.  64-bit sort keys only. */
+int64_t d3gs_bucket_sort_capacity(void);
+int32_t d3gs_bucket_prepare(const int32_t* tile_counts, const int32_t* tile_scan, int64_t num_tiles, int32_t* ranges,
+                            int32_t* cursor, int64_t* max_count, void* stream);
+int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const D3gsSplatContext* ctx, int32_t* cursor,
+                         uint64_t* entries, void* stream);
+int32_t d3gs_bucket_sort(const uint64_t* entries, const int32_t* ranges, int64_t num_tiles, int64_t max_count,
+                         int32_t* sorted_values, uint64_t* sorted_keys, void* stream);
 
 /* ---- staging for the rasteriser: gather splats into sorted, contiguous 48-byte records ------
  * (replaces the per-batch gathers of render.py:1702-1716; lets the raster kernels stream their

@@ -31,6 +31,12 @@ pytestmark = pytest.mark.gpu
 
 IMG_TOL = 1e-4
 GRAD_TOL = 1e-3
+# Gradients are sums over pixels (and over tiles, through float atomics) of terms of both signs.  Elements of at
+# least a quarter of the tensor's largest magnitude must agree to GRAD_TOL relative; below that the comparison is
+# absolute, GRAD_TOL * 0.25 * scale: a sum that cancels to a small value carries the rounding noise of its large
+# terms (measured at these sizes: up to 1.1e-4 of the tensor's scale, one quaternion gradient of 12 million), and
+# no relative bound can hold for it.
+GRAD_FLOOR = 0.25
 FIELDS = ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")
 MODEL_ATTR = dict(xyz="xyz", quat="quaternion_xyzw", scale="scale", opacity="opacity", sh_base="color_sh_base",
                   sh_rest="color_sh")
@@ -49,9 +55,10 @@ def _check_binning(op, out, ref):
     dbg = op.debug
     assert op.last_num_rendered == ref.num_rendered, (op.last_num_rendered, ref.num_rendered)
     assert_bit_equal(dbg["tiles_touched"], ref.prep["tiles_touched"], "tiles_touched")
-    assert_bit_equal(dbg["scan"], ref.scan, "scan")
-    assert_bit_equal(dbg["keys"], ref.keys.view(np.int64), "unsorted keys")
-    assert_bit_equal(dbg["values"], ref.vals, "unsorted values")
+    if op.last_binning == "sort":    # the bucket path has no scan over the Gaussians and no unsorted key list
+        assert_bit_equal(dbg["scan"], ref.scan, "scan")
+        assert_bit_equal(dbg["keys"], ref.keys.view(np.int64), "unsorted keys")
+        assert_bit_equal(dbg["values"], ref.vals, "unsorted values")
     assert_bit_equal(dbg["sorted_keys"], ref.sorted_keys.view(np.int64), "sorted keys")
     assert_bit_equal(dbg["sorted_values"], ref.sorted_ids, "sorted values")
     assert_bit_equal(dbg["ranges"], ref.ranges, "workload_ranges")
@@ -81,22 +88,26 @@ def _full_config_parity(name, device, second_step=False):
     tgt = target.to(device)
     model = gpu_model(sc, device)
     model.act_applied = True
-    op = d3.GaussianSplatOp(op_cfg)
-    op.debug_capture = True
-    out, ctx = op.forward(model, cams, training=True)
-    _check_binning(op, out, ref)
+    for binning in ("sort", "bucket"):   # the reference's pipeline stage by stage, then the default path
+        op = d3.GaussianSplatOp(op_cfg)
+        op.binning = binning
+        op.debug_capture = True
+        out, ctx = op.forward(model, cams, training=True)
+        assert op.last_binning == binning, "a tile list outgrew the bucket sort's capacity"
+        _check_binning(op, out, ref)
     assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
     assert_close(out.T.cpu().numpy(), ref.T, IMG_TOL, "T")
     loss, dcolor = l1_dssim_forward_backward(out.color, tgt, lam)
     assert abs(loss.item() - float(ref.loss[0])) <= 1e-5 * max(1.0, abs(float(ref.loss[0])))
-    # a gradient: the separable fp32 filters here and the oracle's 121-tap fp32 window round differently, and the
-    # variance terms of a smooth image cancel heavily (measured 1.4e-4 .. 2.3e-4 of the largest element)
-    assert_close(dcolor.cpu().numpy(), ref.drgb, GRAD_TOL, "dL/dcolor", floor_frac=1e-2)
+    # A gradient, compared relative to the tensor's own scale: in fp32 the variance terms E[x^2] - E[x]^2 of a smooth
+    # image cancel to ~1e-4 of their operands, so the separable filters here and the oracle's 121-tap window (the
+    # reference's formulation) both carry rounding noise of ~1e-4 of the largest element (measured 1.4e-4 .. 2.3e-4)
+    assert_close(dcolor.cpu().numpy(), ref.drgb, GRAD_TOL, "dL/dcolor", floor_frac=1.0)
     gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None), return_uv_grad=True)
     torch.cuda.synchronize()
-    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv")
+    assert_close(duv.reshape(-1, 2).cpu().numpy(), ref.raster_grads["duv"], GRAD_TOL, "duv", floor_frac=GRAD_FLOOR)
     for k in FIELDS:
-        assert_close(getattr(gm, MODEL_ATTR[k]).cpu().numpy(), ref.grads[k], GRAD_TOL, f"grad {k}")
+        assert_close(getattr(gm, MODEL_ATTR[k]).cpu().numpy(), ref.grads[k], GRAD_TOL, f"grad {k}", floor_frac=GRAD_FLOOR)
     del op, out, ctx, gm, duv, dcolor, model
     if name == "cfg0":      # forward + backward under the L1 loss is the whole configuration
         return
@@ -116,10 +127,11 @@ def _full_config_parity(name, device, second_step=False):
             after = getattr(model, MODEL_ATTR[k]).detach().cpu().numpy()
             assert_update_close(after - before[k], getattr(osc, k) - before[k], ref.grads[k], O.ADAM_LRS[k],
                                 f"{name} fused={fused} Adam update {k}", p_before=before[k])
-            assert_close(m_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][0], GRAD_TOL, f"exp_avg {k}")
-            assert_close(v_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][1], GRAD_TOL, f"exp_avg_sq {k}")
+            assert_close(m_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][0], GRAD_TOL, f"exp_avg {k}", floor_frac=GRAD_FLOOR)
+            assert_close(v_views[MODEL_ATTR[k]].cpu().numpy(), adam_state[k][1], 2 * GRAD_TOL, f"exp_avg_sq {k}",
+                         floor_frac=GRAD_FLOOR)      # the square of the gradient: twice its relative error
         for k in ostats:
-            assert_close(getattr(tr.state, k).cpu().numpy(), ostats[k], GRAD_TOL, f"stats {k}")
+            assert_close(getattr(tr.state, k).cpu().numpy(), ostats[k], GRAD_TOL, f"stats {k}", floor_frac=GRAD_FLOOR)
         if second_step and fused:
             # Second step from a COMMON state: the GPU takes the oracle's parameters and moments, so that the only
             # difference between the two second updates is the second gradient.  With non-zero moments the update
@@ -161,17 +173,20 @@ def test_cfg4_binning_one_camera(cuda_device):
     """6 M Gaussians, 3840x2160, forward only: keys, sorted lists, ranges and contributor counts of camera 0."""
     sc = scenes.make_scene("cfg4", seed=0, views=1)
     op_cfg = _op_cfg()
-    op = d3.GaussianSplatOp(op_cfg)
-    op.debug_capture = True
     model = gpu_model(sc, cuda_device)
     model.act_applied = True
-    out, ctx = op.forward(model, gpu_cameras(sc, cuda_device), training=False)
-    op.check_status()
-    torch.cuda.synchronize()
-    assert ctx is None
     ocfg = oracle_cfg(sc, op_cfg, training=False)
     ref = O.forward(ocfg, oracle_scene(sc))
     assert ref.num_rendered > 10_000_000
-    _check_binning(op, out, ref)
+    for binning in ("sort", "bucket"):
+        op = d3.GaussianSplatOp(op_cfg)
+        op.binning = binning
+        op.debug_capture = True
+        out, ctx = op.forward(model, gpu_cameras(sc, cuda_device), training=False)
+        op.check_status()
+        torch.cuda.synchronize()
+        assert ctx is None
+        print("cfg4 binning", binning, "->", op.last_binning)
+        _check_binning(op, out, ref)
     color, _, _ = O.raster_fwd(ocfg, 1, ref.ranges, ref.sorted_ids, ref.prep, bg=op_cfg.bg_color)
     assert_close(out.color.cpu().numpy(), color, IMG_TOL, "color")

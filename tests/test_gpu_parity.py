@@ -22,9 +22,10 @@ IMG_TOL = 1e-4
 GRAD_TOL = 1e-3
 
 
-def _run_forward(sc, device, early_filter, training=True, **cfg_kw):
+def _run_forward(sc, device, early_filter, training=True, binning="sort", **cfg_kw):
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=early_filter, **cfg_kw)
     op = d3.GaussianSplatOp(op_cfg)
+    op.binning = binning
     op.debug_capture = True
     model = gpu_model(sc, device)
     model.act_applied = True
@@ -40,9 +41,13 @@ def _run_forward(sc, device, early_filter, training=True, **cfg_kw):
 @pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB,
                                           EarlyFilterAlgo.OBB_DFVT])
 @pytest.mark.parametrize("sh_degree,views", [(3, 1), (0, 1), (2, 3)])
-def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views):
+@pytest.mark.parametrize("binning", ["sort", "bucket"])
+def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views, binning):
+    """Both ways of building the sorted per-tile lists -- key duplication + radix sort + range extraction like the
+    reference, and per-tile buckets sorted in shared memory -- against the oracle, bit for bit."""
     sc = small_scene(n=6000, width=200, height=136, sh_degree=sh_degree, seed=3 + sh_degree, views=views)
-    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter)
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter, binning=binning)
+    assert op.last_binning == binning
     dbg = {k: v.cpu().numpy() for k, v in op.debug.items()}
     # K1: integer outputs bit-exact, float context bit-exact on visible Gaussians
     np.testing.assert_array_equal(dbg["tiles_touched"], ref.prep["tiles_touched"])
@@ -56,10 +61,11 @@ def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views):
         np.testing.assert_array_equal(g.view(np.uint32), r.view(np.uint32), err_msg=name)
     np.testing.assert_array_equal(ctx.sh_to_rgb_ne_0.cpu().numpy()[vis], ref.prep["ne0"][vis])
     # K2/K3/K4/K5
-    np.testing.assert_array_equal(dbg["scan"], ref.scan)
     assert op.last_num_rendered == ref.num_rendered
-    np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
-    np.testing.assert_array_equal(dbg["values"], ref.vals)
+    if binning == "sort":     # the bucket path has no scan over the Gaussians and no unsorted key list
+        np.testing.assert_array_equal(dbg["scan"], ref.scan)
+        np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
+        np.testing.assert_array_equal(dbg["values"], ref.vals)
     np.testing.assert_array_equal(dbg["sorted_keys"].view(np.uint64), ref.sorted_keys)
     np.testing.assert_array_equal(dbg["sorted_values"], ref.sorted_ids)
     np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
@@ -90,17 +96,20 @@ def test_binning_bit_exact_32bit_keys(cuda_device, views):
 
 
 @pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB_DFVT])
-def test_binning_bit_exact_large_gaussians(cuda_device, early_filter):
+@pytest.mark.parametrize("binning", ["sort", "bucket"])
+def test_binning_bit_exact_large_gaussians(cuda_device, early_filter, binning):
     """Gaussians that cover hundreds of tiles take the warp-cooperative paths of the tile count and of the key
     emission; the unsorted key list must still come out in the reference's per-Gaussian row-major order."""
     sc = small_scene(n=500, width=400, height=304, sh_degree=1, seed=11, log_scale=("normal", -0.9, 0.8))
-    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter)
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, early_filter, binning=binning)
+    assert op.last_binning == binning
     dbg = {k: v.cpu().numpy() for k, v in op.debug.items()}
     assert ref.prep["tiles_touched"].max() > 200, "the scene has no screen-filling Gaussian"
     np.testing.assert_array_equal(dbg["tiles_touched"], ref.prep["tiles_touched"])
-    np.testing.assert_array_equal(dbg["scan"], ref.scan)
-    np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
-    np.testing.assert_array_equal(dbg["values"], ref.vals)
+    if binning == "sort":
+        np.testing.assert_array_equal(dbg["scan"], ref.scan)
+        np.testing.assert_array_equal(dbg["keys"].view(np.uint64), ref.keys)
+        np.testing.assert_array_equal(dbg["values"], ref.vals)
     np.testing.assert_array_equal(dbg["sorted_keys"].view(np.uint64), ref.sorted_keys)
     np.testing.assert_array_equal(dbg["sorted_values"], ref.sorted_ids)
     np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
@@ -458,6 +467,67 @@ def test_radix_sort_stable_bit_range(cuda_device, n, end_bit):
     np.testing.assert_array_equal(vs.cpu().numpy(), vals[order])
 
 
+def test_bucket_sort_every_list_length(cuda_device):
+    """d3gs_bucket_prepare + d3gs_bucket_sort through the C ABI: tiles whose lists have every interesting length
+    (empty, one entry, the class boundaries of the three kernel instances, the capacity) come out ordered by
+    (depth bits, index) with the reference's keys and ranges; a list beyond the capacity is refused."""
+    lib = _lib.load()
+    cap = int(lib.d3gs_bucket_sort_capacity())
+    lengths = [0, 1, 2, 3, 31, 0, 511, 512, 513, 1000, 2047, 2048, 2049, 5000, 0, cap - 1, cap, 7]
+    rng = np.random.default_rng(5)
+    counts = np.array(lengths, np.int32)
+    incl = np.cumsum(counts).astype(np.int32)
+    total = int(incl[-1])
+    # few distinct depths -> many ties, broken by the index; entries shuffled inside every tile's range
+    depth = rng.integers(0, 200, size=total, dtype=np.uint64) + np.uint64(0x3F000000)
+    ids = rng.permutation(total).astype(np.uint64)
+    entries = (depth << np.uint64(32)) | ids
+    st = torch.cuda.current_stream().cuda_stream
+    dev = cuda_device
+    d_counts, d_incl = torch.from_numpy(counts).to(dev), torch.from_numpy(incl).to(dev)
+    ranges = torch.empty(len(lengths), 2, dtype=torch.int32, device=dev)
+    cursor = torch.empty(len(lengths), dtype=torch.int32, device=dev)
+    maxc = torch.zeros(1, dtype=torch.int64, device=dev)
+    _lib.check(lib.d3gs_bucket_prepare(d_counts.data_ptr(), d_incl.data_ptr(), len(lengths), ranges.data_ptr(),
+                                       cursor.data_ptr(), maxc.data_ptr(), st), "prepare")
+    assert int(maxc.item()) == cap
+    start = incl - counts
+    exp_ranges = np.stack([np.where(counts > 0, start, 0), np.where(counts > 0, incl, 0)], axis=1).astype(np.int32)
+    np.testing.assert_array_equal(ranges.cpu().numpy(), exp_ranges)
+    np.testing.assert_array_equal(cursor.cpu().numpy(), start)
+    d_entries = torch.from_numpy(entries.view(np.int64)).to(dev)
+    vals = torch.full((total,), -1, dtype=torch.int32, device=dev)
+    keys = torch.zeros(total, dtype=torch.int64, device=dev)
+    _lib.check(lib.d3gs_bucket_sort(d_entries.data_ptr(), ranges.data_ptr(), len(lengths), cap, vals.data_ptr(),
+                                    keys.data_ptr(), st), "sort")
+    got_v, got_k = vals.cpu().numpy(), keys.cpu().numpy().view(np.uint64)
+    for t, (a, b) in enumerate(zip(start, incl)):
+        e = np.sort(entries[a:b])
+        np.testing.assert_array_equal(got_v[a:b], (e & np.uint64(0xFFFFFFFF)).astype(np.int32), err_msg=f"tile {t}")
+        np.testing.assert_array_equal(got_k[a:b], (np.uint64(t) << np.uint64(32)) | (e >> np.uint64(32)), err_msg=f"tile {t}")
+    # keys are optional
+    vals2 = torch.empty_like(vals)
+    _lib.check(lib.d3gs_bucket_sort(d_entries.data_ptr(), ranges.data_ptr(), len(lengths), cap, vals2.data_ptr(), None, st),
+               "sort without keys")
+    assert torch.equal(vals, vals2)
+    assert lib.d3gs_bucket_sort(d_entries.data_ptr(), ranges.data_ptr(), len(lengths), cap + 1, vals2.data_ptr(), None,
+                                st) == -3
+    assert "radix" in _lib.last_error() or "sort_pairs" in _lib.last_error()
+
+
+def test_bucket_binning_falls_back_on_long_lists(cuda_device):
+    """A tile list longer than the bucket sort's shared-memory capacity makes the operator take the radix-sort
+    path for that launch; the result is the oracle's either way."""
+    sc = small_scene(n=40000, width=64, height=48, sh_degree=0, seed=41, pos=("uniform", 0.4), log_scale=("normal", -3.0, 0.3))
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, EarlyFilterAlgo.OBB_DFVT, binning="bucket")
+    longest = int((ref.ranges[:, 1] - ref.ranges[:, 0]).max())
+    assert longest > _lib.load().d3gs_bucket_sort_capacity(), longest
+    assert op.last_binning == "sort"
+    np.testing.assert_array_equal(op.debug["sorted_values"].cpu().numpy(), ref.sorted_ids)
+    np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+
+
 @pytest.mark.parametrize("shape", [(1, 40, 56), (2, 97, 130), (1, 16, 16), (1, 5, 7)])
 def test_l1_dssim_loss_and_gradient(cuda_device, shape):
     b, h, w = shape
@@ -579,6 +649,7 @@ def _full_size_invariants(cuda_device, cfg_name, training):
     from d3gs_research_b200 import scenes
     sc = scenes.make_scene(cfg_name, seed=0, views=1)
     op = d3.GaussianSplatOp(d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT))
+    op.binning = "sort"     # the invariants below involve the unsorted key list
     op.debug_capture = True
     model = gpu_model(sc, cuda_device)
     model.act_applied = True
