@@ -53,6 +53,10 @@ def parse():
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--n", type=int, default=0, help="override the Gaussian count (profiling on small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "symm", "symm-nomc", "ipc", "nccl"],
+                    help="N>1: how gradients are summed and parameters broadcast: one kernel over torch symmetric "
+                         "memory (switch multicast when available; -nomc: plain peer accesses), one kernel over CUDA "
+                         "IPC buffers with NCCL barriers, or NCCL reduce-scatter / all-gather")
     ap.add_argument("--nccl-update", action="store_true",
                     help="N>1: sharded optimizer through NCCL reduce-scatter / all-gather instead of the peer-memory kernel")
     ap.add_argument("--separate-adam", action="store_true",
@@ -452,9 +456,12 @@ def bench_train(args):
                                                      sc["sh_rest"], device=dev, cur_sh_degree=scfg.sh_degree)
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
     do_update = args.config != "cfg0"           # cfg0 is forward + backward only
+    peer_update = {"auto": None, "symm": "symm", "symm-nomc": "symm", "ipc": "ipc", "nccl": False}[args.exchange]
+    if args.nccl_update or args.replicated_adam or world == 1:
+        peer_update = False if world > 1 else None
     trainer = SplatTrainer(model, op_cfg, lambda_dssim=LAMBDA_DSSIM[args.config], batch_size=world,
                            shard_optimizer=False if args.replicated_adam else None,
-                           peer_update=False if (args.nccl_update or args.replicated_adam) else None,
+                           peer_update=peer_update, multicast=False if args.exchange == "symm-nomc" else None,
                            fuse_backward_adam=False if (args.separate_adam or world > 1 or not do_update) else None)
     trainer.op.raster_grad_direct = {"auto": None, "direct": True, "shared": False}[args.raster_grad_mode]
     trainer.op.binning = args.binning

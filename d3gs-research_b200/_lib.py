@@ -71,11 +71,15 @@ MAX_PEERS = 8
 RASTER_RECORDS_BY_ID = 1
 RASTER_DIRECT_ATOMICS = 2
 PEER_HANDLE_BYTES = 64
+PEER_FLAG_WORDS = 32
+STATUS_PEER_TIMEOUT = 8
 
 
 class PeerSet(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("grad", C.c_void_p * MAX_PEERS),
-                ("param", C.c_void_p * MAX_PEERS), ("status", C.c_void_p)]
+                ("param", C.c_void_p * MAX_PEERS), ("status", C.c_void_p), ("grad_mc", C.c_void_p),
+                ("param_mc", C.c_void_p), ("flags", C.c_void_p * MAX_PEERS), ("epoch", C.c_uint32),
+                ("wait_limit", C.c_uint32)]
 
 
 class RefineConfig(C.Structure):

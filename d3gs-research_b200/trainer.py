@@ -17,10 +17,13 @@ parameter buffer together with its Adam moments, updates only that slice, and an
 brings the updated slices back to every replica.  The bytes on the wire equal those of an all-reduce,
 while the Adam launch, which is bound by HBM bandwidth, shrinks by the number of ranks.
 With ``peer_update`` (the default on NCCL when the buffers can be mapped) the three steps are one kernel
-over NVLink peer memory: ``PeerBuffer`` gives every process a mapping of every rank's gradient and
-parameter buffer, the Adam launch sums its slice of all gradient buffers with peer loads and stores the
-new parameters into all parameter buffers, and two one-element all-reduces order it against the other
-ranks (all gradients written / all parameters written).
+over NVLink memory of all ranks.  Preferred form (``"symm"``): the gradient, parameter and flag buffers are
+torch symmetric memory (``SymmBuffer``); when the switch offers a multicast mapping the launch pulls its
+slice of the gradient sum with one ``multimem.ld_reduce`` per element and pushes the new parameters with
+one ``multimem.st``; without multicast it uses plain peer loads and stores.  The launches of the ranks are
+ordered by flags inside the kernel (gradients ready / update done), so the step contains no host-side
+collective at all.  Fallback form (``"ipc"``): ``PeerBuffer`` maps cudaMalloc buffers through CUDA IPC and
+two one-element all-reduces order the launches.
 Optimizer hyper-parameters are scaled with the global batch like tools.py:146-163.
 """
 from __future__ import annotations
@@ -142,6 +145,44 @@ class PeerBuffer:
         self.tensor = None
 
 
+class SymmBuffer:
+    """One buffer per rank in torch symmetric memory (``torch.distributed._symmetric_memory``): every rank's
+    copy is mapped into every process (``ptrs[q]``), and where the NVLink switch supports it the copies are also
+    bound to one multicast address (``multicast_ptr``; 0 otherwise).  Construction is collective."""
+
+    def __init__(self, numel: int, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        dist = torch.distributed
+        group = group if group is not None else dist.group.WORLD
+        self.numel, self.device, self.group = numel, device, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass      # newer torch enables the group on first use
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert self.ptrs[self.rank] == self.tensor.data_ptr(), "symmetric memory: local pointer mismatch"
+        mc = 0
+        try:
+            if self.handle.has_multicast_support(device.type, device.index):
+                mc = int(self.handle.multicast_ptr)
+        except Exception:
+            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)     # every rank's buffer is zero before anybody writes into a peer's
+
+    def close(self, collective: bool = True):
+        torch.cuda.synchronize(self.device)
+        if collective:
+            torch.distributed.barrier(group=self.group)
+        self.handle = None
+        self.tensor = None
+
+
 class HostFeed:
     """Uploads per-step inputs that live in pinned host memory on a side stream, double buffered.
 
@@ -174,12 +215,16 @@ class SplatTrainer:
     def __init__(self, model: GaussianModelOriginBase, op_cfg: config_def.GaussianSplatConfig,
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
                  spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False,
-                 shard_optimizer: bool | None = None, peer_update: bool | None = None,
-                 fuse_backward_adam: bool | None = None):
+                 shard_optimizer: bool | None = None, peer_update: "bool | str | None" = None,
+                 fuse_backward_adam: bool | None = None, multicast: bool | None = None):
         """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs).
         ``shard_optimizer``: reduce-scatter + sliced Adam + all-gather instead of all-reduce + replicated
         Adam; default on when there is more than one rank.  ``peer_update``: do the sharded update as one
-        kernel over mapped peer buffers; default: tried on NCCL, NCCL collectives when mapping fails.
+        kernel over the ranks' mapped buffers: ``"symm"`` (torch symmetric memory, ordering by flags inside the
+        kernel, switch multicast when available and ``multicast`` is not False), ``"ipc"`` / ``True`` (CUDA IPC
+        buffers, plain peer accesses, two one-element all-reduces around the launch), ``False`` (NCCL
+        reduce-scatter / all-gather).  Default on NCCL: ``"symm"``, then ``"ipc"``, then NCCL, whichever can be
+        set up on every rank.
         ``fuse_backward_adam`` (single rank, one view per step; default on): the preprocess backward applies
         Adam as it produces the gradients, which are then never stored; ``grad_flat`` is not written."""
         assert model.has_fused_activations, "the trainer drives the fused-activation model"
@@ -195,22 +240,30 @@ class SplatTrainer:
         layout, total = flat_layout(n)
         self.flat_total = total
         self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)
-        self.peer_param = self.peer_grad = None
-        want_peer = self.sharded and dev.type == "cuda" and self.world <= _lib.MAX_PEERS and \
+        self.peer_param = self.peer_grad = self.peer_flags = None
+        self.multicast = False
+        self.exchange = "nccl"      # how the gradient sum and the parameter broadcast travel: symm | ipc | nccl
+        self._multicast_wanted = multicast
+        can_peer = self.sharded and dev.type == "cuda" and self.world <= _lib.MAX_PEERS and \
             torch.distributed.get_backend(process_group) == "nccl"
-        if peer_update is not None:
-            assert not peer_update or want_peer, "peer_update needs a sharded optimizer on NCCL with at most 8 ranks"
-            want_peer = bool(peer_update)
-        if want_peer:
+        if peer_update is True:
+            peer_update = "ipc"
+        if peer_update in ("symm", "ipc"):
+            assert can_peer, "peer_update needs a sharded optimizer on NCCL with at most 8 ranks"
+            modes = [peer_update]
+        elif peer_update is None and can_peer:
+            modes = ["symm", "ipc"]
+        else:
+            modes = []
+        for mode in modes:
             try:
-                self.peer_param = PeerBuffer(padded, dev, process_group)
-                self.peer_grad = PeerBuffer(padded, dev, process_group)
-            except RuntimeError:
-                if peer_update:
+                self._create_peer_buffers(mode, padded, dev)
+                self.exchange = mode
+                break
+            except Exception:
+                if peer_update is not None:
                     raise
-                if self.peer_param is not None:
-                    self.peer_param.close()
-                self.peer_param = self.peer_grad = None
+                self._release_peer_buffers()
         if self.peer_param is not None or model.flat is None or model.flat.numel() < padded:
             # move the parameters into one flat buffer (padded to a whole number of slices when the
             # optimizer is sharded, inside the mapped buffer for the peer update); the model's tensors
@@ -234,13 +287,10 @@ class SplatTrainer:
         self.grad_flat = self.peer_grad.tensor if self.peer_grad is not None else \
             torch.zeros(padded, dtype=torch.float32, device=dev)
         self._peerset = None
+        self._epoch = 0
+        self.peer_wait_limit = 0      # polls before a flag wait inside the exchange kernel gives up; 0 = default
         if self.peer_param is not None:
-            ps = _lib.PeerSet()
-            ps.world, ps.rank = self.world, self.rank
-            for q in range(self.world):
-                ps.grad[q], ps.param[q] = self.peer_grad.ptrs[q], self.peer_param.ptrs[q]
-            ps.status = self.op._sync_words(dev).data_ptr() + 8   # the word every forward pass checks
-            self._peerset = ps
+            self._peerset = self._make_peerset(dev)
             self._bar = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
@@ -270,6 +320,53 @@ class SplatTrainer:
         self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
 
     # ------------------------------------------------------------------------------------------
+    def _create_peer_buffers(self, mode: str, padded: int, dev) -> None:
+        """Collective.  Raises on every rank when any rank could not set the buffers up."""
+        dist = torch.distributed
+        ok = torch.ones(1, dtype=torch.int32, device=dev)
+        err = None
+        try:
+            if mode == "symm":
+                self.peer_param = SymmBuffer(padded, torch.float32, dev, self.pg)
+                self.peer_grad = SymmBuffer(padded, torch.float32, dev, self.pg)
+                self.peer_flags = SymmBuffer(_lib.PEER_FLAG_WORDS, torch.int32, dev, self.pg)
+            else:
+                self.peer_param = PeerBuffer(padded, dev, self.pg)
+                self.peer_grad = PeerBuffer(padded, dev, self.pg)
+        except Exception as e:      # noqa: BLE001 -- any failure means "this mode is not available here"
+            err = e
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.pg)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"peer buffers ({mode}) could not be set up on some rank: {err or 'not this one'}")
+
+    def _release_peer_buffers(self) -> None:
+        for b in (self.peer_flags, self.peer_grad, self.peer_param):
+            if b is not None:
+                try:
+                    b.close(collective=False)
+                except Exception:   # noqa: BLE001
+                    pass
+        self.peer_param = self.peer_grad = self.peer_flags = None
+
+    def _make_peerset(self, dev) -> "_lib.PeerSet":
+        ps = _lib.PeerSet()
+        ps.world, ps.rank = self.world, self.rank
+        for q in range(self.world):
+            ps.grad[q], ps.param[q] = self.peer_grad.ptrs[q], self.peer_param.ptrs[q]
+        ps.status = self.op._sync_words(dev).data_ptr() + 8   # the word every forward pass checks
+        self.multicast = False
+        if self.exchange == "symm":
+            for q in range(self.world):
+                ps.flags[q] = self.peer_flags.ptrs[q]
+            gmc, pmc = self.peer_grad.multicast_ptr, self.peer_param.multicast_ptr
+            if self._multicast_wanted is not False and gmc and pmc:
+                ps.grad_mc, ps.param_mc = gmc, pmc
+                self.multicast = True
+            assert not (self._multicast_wanted is True and not self.multicast), \
+                "multicast=True, but the symmetric buffers have no multicast mapping here"
+        return ps
+
     def _field_views(self, flat: torch.Tensor) -> dict:
         """Views of a flat buffer in this trainer's layout, shaped like the model's tensors."""
         return {name: flat[off:off + cnt].view(getattr(self.model, name).shape) for name, (off, cnt) in self._offsets.items()}
@@ -280,43 +377,103 @@ class SplatTrainer:
         d3sim/algos/d3gs/origin/strategy.py:159-363; the trainer calls it every ``refine_every`` iterations
         between ``refine_start_iter`` and ``refine_stop_iter``, origin/trainer.py:377-386).  The model's tensors,
         the Adam moments, the gradient buffer and the statistics are rebuilt for the new Gaussian count.
-        Single rank only: with several ranks the peer-mapped buffers would have to be re-created for the new
-        count on every rank, which is not built.  Returns ``(n_keep, n_dup_kept, n_split_kept, n_split)``."""
-        assert self.world == 1, "SplatTrainer.refine is built for one rank"
+
+        With several ranks the call is collective: the statistics are summed over the ranks first, every rank
+        then takes the same decisions on its replica (the split children's normals come from a device generator
+        seeded alike on all ranks), the sharded Adam moments are gathered for the call and cut into the new
+        slices afterwards, and the buffers the ranks share (symmetric memory or CUDA IPC) are released and
+        re-created for the new count.  Returns ``(n_keep, n_dup_kept, n_split_kept, n_split)``."""
         model, dev = self.model, self.model.xyz.device
-        m_views, v_views = self._field_views(self.exp_avg), self._field_views(self.exp_avg_sq)
+        dist = torch.distributed
+        old_padded = self.shard_len * self.world if self.sharded else self.flat_total
+        if self.world > 1:
+            self.reduce_stats()
+            if generator is None:
+                generator = torch.Generator(device=dev)
+                generator.manual_seed(0x5EED0000 + int(step))
+        if self.sharded:   # the moments of the whole model, for the gather by source index
+            full_m = torch.empty(old_padded, dtype=torch.float32, device=dev)
+            full_v = torch.empty(old_padded, dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(full_m, self.exp_avg, group=self.pg)
+            dist.all_gather_into_tensor(full_v, self.exp_avg_sq, group=self.pg)
+        else:
+            full_m, full_v = self.exp_avg, self.exp_avg_sq
+        m_views, v_views = self._field_views(full_m), self._field_views(full_v)
         moments = {name: (m_views[name], v_views[name]) for name in self._offsets}
         new_model, new_moments, _, totals = strategy.refine_tensors(model, moments, self.state, step, generator)
         n = len(new_model)
+        if self.world > 1:   # the replicas must have taken the same decisions
+            t = torch.tensor(list(totals), dtype=torch.int64, device=dev)
+            lo, hi = t.clone(), t.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.pg)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.pg)
+            assert bool((lo == hi).all().item()), f"ranks disagree on the refinement: {totals}"
         layout, total = flat_layout(n)
-        for k in FLAT_ORDER:
-            setattr(model, k, getattr(new_model, k))
-        model.flat = new_model.flat
-        self.flat_total, self.shard_len = total, total
+        self.flat_total = total
+        self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)
         self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
-        self.exp_avg = torch.zeros(total, dtype=torch.float32, device=dev)
-        self.exp_avg_sq = torch.zeros(total, dtype=torch.float32, device=dev)
-        m_views, v_views = self._field_views(self.exp_avg), self._field_views(self.exp_avg_sq)
+        if self.peer_param is not None:
+            # the shared buffers have the old size: release them on every rank, then map new ones
+            mode = self.exchange
+            for k in FLAT_ORDER:
+                setattr(model, k, None)
+            model.flat = None
+            self.grad_flat = self.grad_model = self._peerset = None
+            for b in (self.peer_flags, self.peer_grad, self.peer_param):
+                if b is not None:
+                    b.close()
+            self.peer_param = self.peer_grad = self.peer_flags = None
+            self._create_peer_buffers(mode, padded, dev)
+            flat = self.peer_param.tensor
+            self.grad_flat = self.peer_grad.tensor
+        else:
+            flat = torch.zeros(padded, dtype=torch.float32, device=dev)
+            self.grad_flat = torch.zeros(padded, dtype=torch.float32, device=dev)
+        views = carve_flat(flat, n)
+        for k in FLAT_ORDER:
+            views[k].copy_(getattr(new_model, k))
+            setattr(model, k, views[k])
+        model.flat = flat
+        if self.peer_param is not None:
+            self._peerset = self._make_peerset(dev)
+            self._epoch = 0          # the new flag blocks start at zero
+        # the new moments, in the flat layout, cut to this rank's slice
+        new_m = torch.zeros(padded, dtype=torch.float32, device=dev)
+        new_v = torch.zeros(padded, dtype=torch.float32, device=dev)
         for name, (m, v) in new_moments.items():
-            m_views[name].copy_(m)
-            v_views[name].copy_(v)
-        self.grad_flat = torch.zeros(total, dtype=torch.float32, device=dev)
+            off, cnt = self._offsets[name]
+            new_m[off:off + cnt].copy_(m.reshape(-1))
+            new_v[off:off + cnt].copy_(v.reshape(-1))
+        self.state_lo = self.rank * self.shard_len if self.sharded else 0
+        self.exp_avg = new_m[self.state_lo:self.state_lo + self.shard_len].clone()
+        self.exp_avg_sq = new_v[self.state_lo:self.state_lo + self.shard_len].clone()
+        self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) \
+            if (self.sharded and self._peerset is None) else None
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
         self.state = GaussianTrainState.create(n, self.state.scene_scale, device=dev)   # reset, origin/strategy.py:349
+        if self.world > 1:
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=self.pg)     # nobody starts a step before every replica is in place
         return totals
 
     @torch.no_grad()
     def reset_opacity(self, strategy) -> None:
-        """origin/trainer.py:388-417 on the trainer's buffers: clamp the opacities, zero their Adam moments."""
-        assert not self.sharded, "the opacity moments of a sharded optimizer live on several ranks"
+        """origin/trainer.py:388-417 on the trainer's buffers: clamp the opacities, zero their Adam moments.  With a
+        sharded optimizer every rank clamps its own replica and zeroes the part of the opacity moments it holds."""
         off, cnt = self._offsets["opacity"]
         lib = _lib.load()
         dev = self.model.opacity.device
+        lo, hi = max(off, self.state_lo), min(off + cnt, self.state_lo + self.shard_len)
+        whole = lo == off and hi == off + cnt       # this rank holds the moments of every opacity
         _lib.check(lib.d3gs_reset_opacity(self.model.opacity.data_ptr(), cnt, float(strategy.reset_opacity_thresh),
                                           int(self.model.has_fused_activations),
-                                          self.exp_avg.data_ptr() + off * 4, self.exp_avg_sq.data_ptr() + off * 4,
+                                          self.exp_avg.data_ptr() + (off - self.state_lo) * 4 if whole else None,
+                                          self.exp_avg_sq.data_ptr() + (off - self.state_lo) * 4 if whole else None,
                                           torch.cuda.current_stream(dev).cuda_stream), "d3gs_reset_opacity")
+        if not whole and hi > lo:
+            self.exp_avg[lo - self.state_lo:hi - self.state_lo].zero_()
+            self.exp_avg_sq[lo - self.state_lo:hi - self.state_lo].zero_()
 
     def _adam_segments(self):
         self.step_count += 1
@@ -397,7 +554,14 @@ class SplatTrainer:
     def apply_gradients(self, stats=None, update: bool = True) -> None:
         """Sum ``grad_flat`` over the ranks and take the Adam step (second half of ``step``)."""
         model = self.model
-        if self._peerset is not None and update:
+        if self._peerset is not None and update and self.exchange == "symm":
+            # ordering by flags inside the launch: no host-side collective in the step
+            self._epoch += 1
+            self._peerset.epoch = self._epoch
+            self._peerset.wait_limit = int(self.peer_wait_limit)
+            _launch_adam(self._adam_segments(), stats, model.xyz.device, peers=self._peerset)
+            self.op._mark("adam_stats")
+        elif self._peerset is not None and update:
             torch.distributed.all_reduce(self._bar, group=self.pg)    # every rank's gradient is complete
             self.op._mark("barrier_grads")
             _launch_adam(self._adam_segments(), stats, model.xyz.device, peers=self._peerset)
@@ -439,9 +603,10 @@ class SplatTrainer:
         self.model.flat = flat
         self.grad_flat = self.grad_model = None
         self._peerset = None
-        self.peer_grad.close()
-        self.peer_param.close()
-        self.peer_param = self.peer_grad = None
+        for b in (self.peer_flags, self.peer_grad, self.peer_param):
+            if b is not None:
+                b.close()
+        self.peer_param = self.peer_grad = self.peer_flags = None
 
     def reduce_stats(self):
         """All-reduce the densification statistics (each rank accumulates its own views' share)."""
@@ -455,9 +620,14 @@ class SplatTrainer:
         if self.world == 1:
             return "single rank, Adam inside the preprocess backward" if self.fused_adam else \
                 "single rank, gradient buffer + optimizer kernel"
+        if self._peerset is not None and self.exchange == "symm":
+            how = ("multimem.ld_reduce / multimem.st through the NVLink switch" if self.multicast else
+                   "plain peer loads and stores (no multicast mapping)")
+            return ("sharded, one kernel over symmetric memory: gradient slice summed and parameters broadcast by "
+                    f"{how}, Adam on the slice, launches ordered by flags inside the kernel")
         if self._peerset is not None:
-            return ("sharded, one kernel over NVLink peer memory: sum of all ranks' gradient slices, Adam, store to "
-                    "all ranks' parameters")
+            return ("sharded, one kernel over NVLink peer memory (CUDA IPC): sum of all ranks' gradient slices, Adam, "
+                    "store to all ranks' parameters; two one-element all-reduces order the launches")
         if self.sharded:
             return "sharded: reduce-scatter, Adam on 1/N slice, all-gather"
         return "replicated after all-reduce"

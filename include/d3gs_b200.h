@@ -41,6 +41,7 @@ extern "C" {
 #define D3GS_STATUS_SCAN_TIMEOUT 1u
 #define D3GS_STATUS_SORT_TIMEOUT 2u
 #define D3GS_STATUS_COPY_TIMEOUT 4u
+#define D3GS_STATUS_PEER_TIMEOUT 8u   /* another rank's flag (gradients ready / update done) did not arrive */
 
 /* One pinhole camera: cam2world[:3].T flattened ([4,3]: rows 0..2 are the columns of the
  * camera-to-world rotation, row 3 the camera centre; render.py:136, 205-206) and intrinsics. */
@@ -341,7 +342,26 @@ typedef struct D3gsPeerSet {
     float* param[D3GS_MAX_PEERS];        /* each rank's flat parameter buffer as mapped in this process */
     uint32_t* status;                    /* optional device word: D3GS_STATUS_COPY_TIMEOUT is OR-ed in when a
                                             staged copy did not arrive in time (that chunk is left unchanged) */
+    /* Optional: multicast addresses of the SAME buffers (a switch multicast mapping over all ranks' copies, e.g.
+     * torch symmetric memory's multicast_ptr).  With them the launch takes the path through the NVLink switch: one
+     * multimem.ld_reduce per gradient element (the switch adds the ranks' copies) and one multimem.st per new
+     * parameter, so that S/world + S bytes enter and leave every GPU instead of 2 (world-1)/world S. */
+    const float* grad_mc;
+    float* param_mc;
+    /* Optional: ordering inside the launch instead of by the caller's collectives.  flags[q] = rank q's block of
+     * D3GS_PEER_FLAG_WORDS uint32 words as mapped in this process (zero-filled once, before the first launch);
+     * epoch = number of this launch: 1, 2, 3, ... the same on every rank.  A launch then (1) announces "my
+     * gradients are complete" to all ranks and waits for everybody's announcement before it reads, (2) after its
+     * last store announces "done" with its status bits and waits for everybody's, so that when the kernel ends the
+     * whole parameter buffer of this rank is up to date.  Every rank must launch epoch e before any rank can
+     * finish it; a wait gives up after wait_limit polls (0 = a default of seconds) and sets
+     * D3GS_STATUS_PEER_TIMEOUT, and a status bit set on any rank is OR-ed into every rank's status word.
+     * With flags[0] == NULL the caller orders the launches as described above. */
+    uint32_t* flags[D3GS_MAX_PEERS];
+    uint32_t epoch;
+    uint32_t wait_limit;
 } D3gsPeerSet;
+#define D3GS_PEER_FLAG_WORDS 32
 int32_t d3gs_adam_stats_step_peers(const D3gsAdamSegment* segments, int32_t num_segments,
                                    const D3gsDensifyStats* stats, const D3gsPeerSet* peers, void* stream);
 
