@@ -53,10 +53,13 @@ def parse():
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--n", type=int, default=0, help="override the Gaussian count (profiling on small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "symm", "symm-nomc", "ipc", "nccl"],
-                    help="N>1: how gradients are summed and parameters broadcast: one kernel over torch symmetric "
-                         "memory (switch multicast when available; -nomc: plain peer accesses), one kernel over CUDA "
-                         "IPC buffers with NCCL barriers, or NCCL reduce-scatter / all-gather")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "symm", "symm-nomc", "ipc", "nccl"],
+                    help="N>1: how gradients are summed and parameters broadcast.  fused (the default when symmetric "
+                         "memory can be set up): one launch does the preprocess backward of all ranks' views from their "
+                         "raster gradients, the sum, Adam and the parameter broadcast; symm: gradient buffers summed by "
+                         "one kernel over symmetric memory (switch multicast when available; -nomc: plain peer "
+                         "accesses); ipc: the same over CUDA IPC buffers with NCCL barriers; nccl: reduce-scatter / "
+                         "all-gather")
     ap.add_argument("--nccl-update", action="store_true",
                     help="N>1: sharded optimizer through NCCL reduce-scatter / all-gather instead of the peer-memory kernel")
     ap.add_argument("--separate-adam", action="store_true",
@@ -246,6 +249,7 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, train
 
 
 BUCKET_BINNING = False    # set by the bench from the binning path the operator took
+WORLD = 1                 # ranks of the run (the fused backward + exchange launch covers 1/WORLD of the Gaussians)
 
 
 def moved_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, training: bool = True) -> float:
@@ -255,6 +259,13 @@ def moved_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, training: b
     entries once and writes 4-byte indices, and there is no range extraction."""
     if stage == "preprocess_bwd_adam":
         return float(89 * V + 1456 * N)
+    if stage == "preprocess_bwd_adam_peers":
+        # HBM side of one rank's launch: its share of parameters and moments, the raster gradients and context of
+        # its Gaussians in every view (its own from HBM, the others' over NVLink), and the other ranks' parameter
+        # stores arriving in this replica
+        return float(89 * V + 1456 * N / WORLD + 236 * N * (WORLD - 1) / WORLD)
+    if stage == "densify_stats":
+        return float(24 * N + 12 * V)
     if BUCKET_BINNING:
         if stage == "scan":
             return float(8 * Tn + 20 * Tn)
@@ -435,7 +446,7 @@ def _dist_setup():
 
 # ---------------------------------------------------------------------------------------------
 def bench_train(args):
-    global BUCKET_BINNING
+    global BUCKET_BINNING, WORLD
     import torch
     import torch.distributed as dist
 
@@ -456,17 +467,23 @@ def bench_train(args):
                                                      sc["sh_rest"], device=dev, cur_sh_degree=scfg.sh_degree)
     op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
     do_update = args.config != "cfg0"           # cfg0 is forward + backward only
-    peer_update = {"auto": None, "symm": "symm", "symm-nomc": "symm", "ipc": "ipc", "nccl": False}[args.exchange]
+    peer_update = {"auto": None, "fused": "symm", "symm": "symm", "symm-nomc": "symm", "ipc": "ipc",
+                   "nccl": False}[args.exchange]
+    fuse_exchange = {"auto": None, "fused": True}.get(args.exchange, False)
     if args.nccl_update or args.replicated_adam or world == 1:
         peer_update = False if world > 1 else None
     trainer = SplatTrainer(model, op_cfg, lambda_dssim=LAMBDA_DSSIM[args.config], batch_size=world,
                            shard_optimizer=False if args.replicated_adam else None,
                            peer_update=peer_update, multicast=False if args.exchange == "symm-nomc" else None,
+                           fuse_exchange=fuse_exchange if world > 1 else False,
                            fuse_backward_adam=False if (args.separate_adam or world > 1 or not do_update) else None)
     trainer.op.raster_grad_direct = {"auto": None, "direct": True, "shared": False}[args.raster_grad_mode]
     trainer.op.binning = args.binning
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
+    # the cameras of all ranks of this step's batch, in rank order (a training loop knows the batch it draws)
+    all_cams = [d3.BasicPinholeCamera.from_params(sc["cam2worlds"][r % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
+                for r in range(world)] if world > 1 else None
     target_host = sc["target"][rank % sc["target"].shape[0]][None].contiguous().pin_memory()
     target_dev = target_host.to(dev)
     repeats = args.repeats if args.repeats > 0 else 9
@@ -496,10 +513,10 @@ def bench_train(args):
                 tgt, ready = nxt
                 if k + 1 < steps:
                     nxt = feed.push(target_host)
-                info = trainer.step(cam, tgt, update=do_update, target_ready=ready)
+                info = trainer.step(cam, tgt, update=do_update, target_ready=ready, all_cameras=all_cams)
                 loss_host[k].copy_(trainer._loss_sums, non_blocking=True)   # this step's loss sums -> host
             else:
-                info = trainer.step(cam, target_dev, update=do_update)
+                info = trainer.step(cam, target_dev, update=do_update, all_cameras=all_cams)
         e1.record()
         launches = lib.d3gs_kernel_launch_count() - launches0
         if sample_clocks:   # everything is enqueued and the GPU is still executing: the query delays no launch
@@ -524,10 +541,10 @@ def bench_train(args):
     # timed loop paid a cudaMalloc of up to 9 ms in its second step, one run out of four).
     info = None
     for _ in range(max(args.warmup, 3)):
-        info = trainer.step(cam, target_dev, update=do_update)
+        info = trainer.step(cam, target_dev, update=do_update, all_cameras=all_cams)
     for _ in range(3):      # warm the host-buffer path (side stream, staging buffers) as well
         tgt, ready = feed.push(target_host)
-        info = trainer.step(cam, tgt, update=do_update, target_ready=ready)
+        info = trainer.step(cam, tgt, update=do_update, target_ready=ready, all_cameras=all_cams)
     # Every timed loop starts from the same parameters and optimizer state: training moves the Gaussians, so
     # the work per step drifts with the step count and the loops would not measure the same steps.
     snap = {"flat": trainer.model.flat.clone(), "m": trainer.exp_avg.clone(), "v": trainer.exp_avg_sq.clone(),
@@ -543,7 +560,7 @@ def bench_train(args):
         trainer.step_count = snap["step"]
 
     for _ in range(3):      # the same pattern once more after the snapshot's allocations
-        info = trainer.step(cam, target_dev, update=do_update)
+        info = trainer.step(cam, target_dev, update=do_update, all_cameras=all_cams)
     restore()
     info = None    # the timed loops hold two generations of step buffers, like the warm-up: no third one from here
     sampler.begin()
@@ -590,6 +607,7 @@ def bench_train(args):
     direct = trainer.op.raster_grad_direct
     if direct is None:
         direct = K < trainer.op.DIRECT_ATOMICS_PAIRS_PER_GAUSSIAN * N
+    WORLD = world
     BUCKET_BINNING = trainer.op.last_binning == "bucket"
     binning_taken = trainer.op.last_binning
     trainer.close()    # unmap the peer buffers (collective) before the process group goes away

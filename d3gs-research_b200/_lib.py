@@ -82,6 +82,11 @@ class PeerSet(C.Structure):
                 ("wait_limit", C.c_uint32)]
 
 
+class PeerViews(C.Structure):
+    _fields_ = [("splat_grads", C.c_void_p * MAX_PEERS), ("radii", C.c_void_p * MAX_PEERS),
+                ("cov2d_vecs", C.c_void_p * MAX_PEERS), ("sh_to_rgb_ne_0", C.c_void_p * MAX_PEERS)]
+
+
 class RefineConfig(C.Structure):
     _fields_ = [("prune_opacity_thresh", C.c_float), ("grow_grad2d", C.c_float), ("grow_scale3d", C.c_float),
                 ("grow_scale2d", C.c_float), ("prune_scale3d", C.c_float), ("prune_scale2d", C.c_float),
@@ -95,7 +100,7 @@ class RefineMoments(C.Structure):
 
 
 _STRUCTS = [Camera, OpConfig, Model, ModelGrad, SplatContext, AdamSegment, DensifyStats, PeerSet, RefineConfig,
-            RefineMoments]
+            RefineMoments, PeerViews]
 
 _P, _I32, _I64, _F, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
 
@@ -124,7 +129,7 @@ SIGNATURES = {
     "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
-                                        C.POINTER(ModelGrad), _P]),
+                                        C.POINTER(ModelGrad), _P, _P]),
     "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "d3gs_ssim_backward": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I32, _I32, _I32, _P, _P]),
     "d3gs_l1_dssim_scratch_bytes": (_SZ, [_I32, _I32, _I32]),
@@ -132,7 +137,10 @@ SIGNATURES = {
     "d3gs_adam_stats_step": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), _P]),
     "d3gs_densify_stats": (_I32, [C.POINTER(DensifyStats), _P]),
     "d3gs_preprocess_backward_adam": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
-                                             C.POINTER(AdamSegment), C.POINTER(DensifyStats), _P]),
+                                             C.POINTER(AdamSegment), C.POINTER(DensifyStats), _P, _P]),
+    "d3gs_preprocess_backward_adam_peers": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(PeerViews), _I64, _I64,
+                                                   C.POINTER(AdamSegment), C.POINTER(DensifyStats), C.POINTER(PeerSet),
+                                                   _P]),
     "d3gs_adam_stats_step_peers": (_I32, [C.POINTER(AdamSegment), _I32, C.POINTER(DensifyStats), C.POINTER(PeerSet), _P]),
     "d3gs_refine_classify": (_I32, [C.POINTER(Model), C.POINTER(RefineConfig), _P, _P, _P, _P, _P, _P]),
     "d3gs_refine_apply": (_I32, [C.POINTER(Model), C.POINTER(Model), C.POINTER(RefineConfig), C.POINTER(RefineMoments),

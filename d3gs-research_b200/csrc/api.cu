@@ -61,6 +61,7 @@ extern "C" size_t d3gs_struct_size(int32_t which) {
         case 7: return sizeof(D3gsPeerSet);
         case 8: return sizeof(D3gsRefineConfig);
         case 9: return sizeof(D3gsRefineMoments);
+        case 10: return sizeof(D3gsPeerViews);
         default: return 0;
     }
 }

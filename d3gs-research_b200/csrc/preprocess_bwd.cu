@@ -14,6 +14,7 @@
 // 236-byte-per-Gaussian gradient.  The rasteriser's per-splat gradients arrive packed, 48 bytes per
 // (view, Gaussian).
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace d3gs {
 namespace {
@@ -21,9 +22,20 @@ namespace {
 struct BwdArgs {
     D3gsOpConfig cfg;
     D3gsModel model;
-    D3gsSplatContext ctx;
     D3gsModelGrad grad;
-    const float* splat_grads;   // [B*N, 12]: dconic a b c, dopacity | dcolor r g b, dz | duv x y, - -
+    // Per view b, indexed by the Gaussian: what the backward reads of that view.  One process, B views: slices of
+    // the [B*N, .] context arrays.  Data parallel (PEER): view b is rank b's, and the pointers are rank b's
+    // buffers as mapped in this process -- the loads cross NVLink.
+    const float* v_grads[D3GS_MAX_VIEWS];     // [N, 12]: dconic a b c, dopacity | dcolor r g b, dz | duv x y, - -
+    const int32_t* v_radii[D3GS_MAX_VIEWS];   // [N]
+    const float* v_cov2d[D3GS_MAX_VIEWS];     // [N, 3]
+    const uint8_t* v_ne0[D3GS_MAX_VIEWS];     // [N]
+    int64_t g_begin, g_count;                 // the Gaussians this launch covers (PEER: this rank's share)
+    // PEER: where the updated parameters go -- every rank's flat parameter buffer, and the element offset of each
+    // field inside it; the flags that order the ranks' launches
+    D3gsPeerSet peers;
+    int64_t field_off[6];
+    uint32_t* status;                         // optional device word for D3GS_STATUS_COPY_TIMEOUT
     // fused optimizer step (ADAM variant): per field xyz, quaternion, scale, opacity, sh_base, sh_rest
     SegConst sc[6];
     float* exp_avg[6];
@@ -49,32 +61,31 @@ __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.457045
 // higher-order SH coefficients with coalesced accesses, taking the gradient rows from shared memory.  Compared
 // with a gradient buffer followed by the optimizer kernel this removes one write and one read of the whole
 // 236-byte-per-Gaussian gradient.
-template <int DEG, bool MULTI, bool ADAM>
-__global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
-    extern __shared__ __align__(16) float smem[];
-    __shared__ uint8_t s_vis[256];
-    __shared__ __align__(8) uint64_t s_bar;
+//
+// One tile of 256 Gaussians starting at Gaussian g0.  Returns false when the CTA must stop (a staging copy never
+// arrived).  `phase`: parity of the staging barrier, toggled per staged tile.
+template <int DEG, bool MULTI, bool ADAM, bool PEER>
+__device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t* s_vis, uint64_t& s_bar, uint32_t& phase,
+                                         const int64_t tile) {
     float* s_in = smem;
     float* s_out = MULTI ? smem + 256 * kRow : smem;
-    const int64_t N = a.model.num;
     const int t = threadIdx.x;
-    const int64_t g0 = (int64_t)blockIdx.x * 256;
-    const int64_t g = g0 + t;
     const D3gsOpConfig& cf = a.cfg;
     constexpr int NB = (DEG + 1) * (DEG + 1);
     constexpr int NR3 = (NB - 1) * 3;
+    const int64_t range_end = a.g_begin + a.g_count;
+    const int64_t g0 = a.g_begin + tile * 256;
+    const int64_t g = g0 + t;
 
     bool any_view = false;
-    if (g < N)
-        for (int b = 0; b < cf.num_views; ++b) any_view |= a.ctx.radii[(int64_t)b * N + g] != 0;
+    if (g < range_end)
+        for (int b = 0; b < cf.num_views; ++b) any_view |= a.v_radii[b][g] != 0;
     s_vis[t] = any_view ? 1 : 0;
-    const int rows = (int)min((int64_t)256, N - g0);
+    const int rows = (int)min((int64_t)256, range_end - g0);
     // contiguous degree-3 layout: the CTA's rows are one 16-byte aligned span -> one bulk async copy
     const bool bulk_in = NR3 > 0 && a.model.sh_rest_stride == 45 && (rows & 3) == 0 &&
                          ((uintptr_t)(a.model.sh_rest + g0 * 45) & 15) == 0;
     if (bulk_in && t == 0) {
-        mbar_init(&s_bar, 1);
-        fence_mbar_init();
         mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
         bulk_copy_g2s(s_in, a.model.sh_rest + g0 * 45, (uint32_t)rows * 180u, &s_bar);
     }
@@ -94,9 +105,11 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
     }
     __syncthreads();
+    bool copy_ok = true;
     if constexpr (NR3 > 0) {
         if (bulk_in) {
-            mbar_wait_bounded(&s_bar, 0);
+            copy_ok = mbar_wait_bounded(&s_bar, phase);
+            phase ^= 1u;
         } else {
             const float* src = a.model.sh_rest;
             const int64_t stride = a.model.sh_rest_stride;
@@ -118,6 +131,14 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             }
             __syncthreads();
         }
+    }
+    if (__syncthreads_or(!copy_ok)) {
+        // The coefficient rows never arrived: flag it, give the copy one more bounded wait (the shared memory must
+        // not be released while it may still land), and change nothing for this CTA's Gaussians -- no gradient is
+        // written and, in the fused variants, no optimizer step is taken.
+        if (!copy_ok) mbar_wait_bounded(&s_bar, phase ^ 1u);
+        if (t == 0 && a.status != nullptr) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
+        return false;
     }
     float* my_in = s_in + t * kRow;
     float* my_out = s_out + t * kRow;
@@ -158,13 +179,16 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
 #pragma unroll
             for (int c = r; c < 3; ++c) Sg[r][c] = Sg[c][r] = M[r][0] * M[c][0] + M[r][1] * M[c][1] + M[r][2] * M[c][2];
         float dSacc[3][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};   // sum over views of dL/dSigma
+        // PEER: the densification statistics of this Gaussian over ALL views (origin/strategy.py:93-122); the owner
+        // of a Gaussian sees every view's duv and radius here, so the statistics come out already summed over ranks
+        float st_len = 0.f, st_cnt = 0.f, st_rad = 0.f;
 
         for (int b = 0; b < cf.num_views; ++b) {
-            const int64_t i = (int64_t)b * N + g;
-            if (a.ctx.radii[i] == 0) continue;
+            const int rad_b = a.v_radii[b][g];
+            if (rad_b == 0) continue;
             const D3gsCamera& cam = cf.cameras[b];
             const float* Rt = cam.cam2world_T;
-            const float4* sg4 = reinterpret_cast<const float4*>(a.splat_grads + i * D3GS_SPLAT_GRAD_FLOATS);
+            const float4* sg4 = reinterpret_cast<const float4*>(a.v_grads[b] + g * D3GS_SPLAT_GRAD_FLOATS);
             const float4 gA = sg4[0], gB = sg4[1], gC = sg4[2];
             const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
             const float pc0 = Rt[0] * d0 + Rt[1] * d1 + Rt[2] * d2;
@@ -184,7 +208,8 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
                 T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
             }
             // conic -> cov2d (gs3d.py:559-588)
-            const float ca = a.ctx.cov2d_vecs[i * 3], cb = a.ctx.cov2d_vecs[i * 3 + 1], cc = a.ctx.cov2d_vecs[i * 3 + 2];
+            const float* cv = a.v_cov2d[b] + g * 3;
+            const float ca = cv[0], cb = cv[1], cc = cv[2];
             const float g0c = gA.x, g1c = gA.y, g2c = gA.z;
             const float det = ca * cc - cb * cb;
             const float d2i = 1.0f / (det * det + 1e-8f);
@@ -233,6 +258,13 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             const float dm0 = xg * -dJ02 * cam.fx * z2i;
             const float dm1 = yg * -dJ12 * cam.fy * z2i;
             const float dm2 = -(cam.fx * dJ00 + cam.fy * dJ11) * z2i + 2.0f * (dJ02 * txf + dJ12 * tyf) * z2i * zi;
+            if (PEER && a.has_stats) {
+                const float lb = (float)(a.stats.loss_batch > 0 ? a.stats.loss_batch : cf.num_views);
+                const float ax = gC.x * (0.5f * (float)a.stats.width * lb), ay = gC.y * (0.5f * (float)a.stats.height * lb);
+                st_len += sqrtf(ax * ax + ay * ay);
+                st_cnt += 1.0f;
+                st_rad = fmaxf(st_rad, (float)rad_b / (float)max(a.stats.width, a.stats.height));
+            }
             // pinhole (camera.py:335-371)
             const float du = gC.x * cam.fx, dv = gC.y * cam.fy;
             const float dp0 = du * zi + dm0, dp1 = dv * zi + dm1;
@@ -249,7 +281,7 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             const float dni = 1.0f / dn;
             const float x = d0 * dni, y = d1 * dni, zz_ = d2 * dni;
             float cg[3] = {gB.x, gB.y, gB.z};
-            const uint8_t m = a.ctx.sh_to_rgb_ne_0[i];
+            const uint8_t m = a.v_ne0[b][g];
             if (cf.clamp_mask_reference_order) {   // bit k gates channel k (render.py:3344-3350)
                 if (m & 1) cg[0] = 0.f;
                 if (m & 2) cg[1] = 0.f;
@@ -338,14 +370,20 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
         aq[0] = (dq[0] - qx * dot) * qni; aq[1] = (dq[1] - qy * dot) * qni;
         aq[2] = (dq[2] - qz * dot) * qni; aq[3] = (dq[3] - qw * dot) * qni;
         if (fused) ao = ao * opac * (1.0f - opac);   // sigmoid_grad_out: g * out * (1 - out)
+        if (PEER && a.has_stats) {
+            a.stats.duv_ndc_length[g] += st_len;
+            a.stats.count[g] += st_cnt;
+            if (a.stats.need_max_radii) a.stats.max_radii[g] = fmaxf(a.stats.max_radii[g], st_rad);
+        }
     }
     if (ADAM) {
         // The 14 small-field gradients of every thread join the SH rows in shared memory, then the CTA walks
         // the six parameter spans of its 256 Gaussians with coalesced float4 accesses (several in flight per
         // thread), exactly like the stand-alone optimizer kernel but with the gradient coming from shared
         // memory.  The parameters are updated in place: a CTA reads and writes only its own Gaussians'.
-        if (a.has_stats && g < N) stats_update(a.stats, g);
-        float* s_small = smem + 256 * kRow;   // [xyz 768 | quaternion 1024 | scale 768 | opacity 256 | sh_base 768]
+        if (!PEER && a.has_stats && g < range_end) stats_update(a.stats, g);
+        // [xyz 768 | quaternion 1024 | scale 768 | opacity 256 | sh_base 768]
+        float* s_small = smem + (MULTI ? 2 : 1) * 256 * kRow;
         s_small[t * 3] = axyz[0]; s_small[t * 3 + 1] = axyz[1]; s_small[t * 3 + 2] = axyz[2];
         *reinterpret_cast<float4*>(s_small + 768 + t * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
         s_small[1792 + t * 3] = as[0]; s_small[1792 + t * 3 + 1] = as[1]; s_small[1792 + t * 3 + 2] = as[2];
@@ -394,7 +432,13 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
                             adam_update(gr.y, p[u].y, m[u].y, v[u].y, c);
                             adam_update(gr.z, p[u].z, m[u].z, v[u].z, c);
                             adam_update(gr.w, p[u].w, m[u].w, v[u].w, c);
-                            reinterpret_cast<float4*>(pp)[q] = p[u];
+                            if (PEER) {   // every replica receives the new value (this rank's own through its own mapping)
+                                const int64_t fo = a.field_off[fld] + g0 * per[fld];
+                                for (int r = 0; r < a.peers.world; ++r)
+                                    reinterpret_cast<float4*>(a.peers.param[r] + fo)[q] = p[u];
+                            } else {
+                                reinterpret_cast<float4*>(pp)[q] = p[u];
+                            }
                             reinterpret_cast<float4*>(pm)[q] = m[u];
                             reinterpret_cast<float4*>(pv)[q] = v[u];
                         }
@@ -406,13 +450,19 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
                     if (fld == 5 && NR3 < 45 && f % 45 >= NR3) gr = 0.0f;
                     float p = pp[f], m = pm[f], v = pv[f];
                     adam_update(gr, p, m, v, c);
-                    pp[f] = p; pm[f] = m; pv[f] = v;
+                    if (PEER) {
+                        const int64_t fo = a.field_off[fld] + g0 * per[fld];
+                        for (int r = 0; r < a.peers.world; ++r) a.peers.param[r][fo + f] = p;
+                    } else {
+                        pp[f] = p;
+                    }
+                    pm[f] = m; pv[f] = v;
                 }
             }
         }
-        return;
+        return true;
     }
-    if (g < N) {
+    if (g < range_end) {
         a.grad.xyz[g * 3] = axyz[0]; a.grad.xyz[g * 3 + 1] = axyz[1]; a.grad.xyz[g * 3 + 2] = axyz[2];
         *reinterpret_cast<float4*>(a.grad.quaternion_xyzw + g * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
         a.grad.scale[g * 3] = as[0]; a.grad.scale[g * 3 + 1] = as[1]; a.grad.scale[g * 3 + 2] = as[2];
@@ -445,12 +495,61 @@ __global__ void __launch_bounds__(256, 3) preprocess_bwd_kernel(const __grid_con
             }
         }
     }
+    return true;
+}
+
+// PEER (data parallel, one view per rank; implies MULTI and ADAM): the launch covers this rank's share of the
+// Gaussians.  For them it reads EVERY rank's per-splat raster gradients and context over NVLink, runs the
+// backward through projection and SH for all views, sums in registers, applies Adam with this rank's moments and
+// stores the new parameters into EVERY rank's parameter buffer.  The 236-byte-per-Gaussian parameter gradient
+// never exists: what crosses the links is the rasteriser's 48 bytes per (view, Gaussian) plus 17 bytes of
+// context inbound, and the parameters outbound.  The launches of the ranks are ordered by flags (exchange.cuh).
+template <int DEG, bool MULTI, bool ADAM, bool PEER = false>
+__global__ void __launch_bounds__(256, PEER ? 2 : 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ uint8_t s_vis[256];
+    __shared__ __align__(8) uint64_t s_bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&s_bar, 1);
+        fence_mbar_init();
+    }
+    uint32_t phase = 0;
+    if constexpr (PEER) {
+        // a resident grid that strides over the tiles: the flag exchange and the system-wide fence at the end are
+        // paid once per CTA
+        const bool ready = exchange_begin(a.peers);   // every rank's raster gradients are complete (contains a barrier)
+        const int64_t num_tiles = (a.g_count + 255) / 256;
+        if (ready) {      // else a rank never announced its gradients: change nothing
+            for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                if (!bwd_tile<DEG, MULTI, ADAM, PEER>(a, smem, s_vis, s_bar, phase, tile)) break;
+                __syncthreads();      // the next tile reuses the shared memory
+            }
+        }
+        exchange_end(a.peers);        // all parameters of every rank's share have arrived when the kernel ends
+    } else {
+        __syncthreads();
+        bwd_tile<DEG, MULTI, ADAM, PEER>(a, smem, s_vis, s_bar, phase, blockIdx.x);
+    }
 }
 
 }  // namespace
 }  // namespace d3gs
 
 using namespace d3gs;
+
+// one process, B views: view b's arrays are slices of the [B*N, .] context
+static void fill_views(BwdArgs& a, const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
+                       const float* splat_grads) {
+    const int64_t N = model->num;
+    for (int b = 0; b < cfg->num_views; ++b) {
+        a.v_grads[b] = splat_grads + (int64_t)b * N * D3GS_SPLAT_GRAD_FLOATS;
+        a.v_radii[b] = ctx->radii + (int64_t)b * N;
+        a.v_cov2d[b] = ctx->cov2d_vecs + (int64_t)b * N * 3;
+        a.v_ne0[b] = ctx->sh_to_rgb_ne_0 + (int64_t)b * N;
+    }
+    a.g_begin = 0;
+    a.g_count = N;
+}
 
 static int32_t check_backward_inputs(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
                                      const float* splat_grads) {
@@ -466,7 +565,7 @@ static int32_t check_backward_inputs(const D3gsOpConfig* cfg, const D3gsModel* m
 
 extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model,
                                             const D3gsSplatContext* ctx, const float* splat_grads,
-                                            const D3gsModelGrad* grad, void* stream) {
+                                            const D3gsModelGrad* grad, uint32_t* status, void* stream) {
     D3GS_REQUIRE(grad != nullptr, "NULL argument");
     int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
     if (rc != D3GS_OK) return rc;
@@ -483,9 +582,9 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     BwdArgs a = {};
     a.cfg = *cfg;
     a.model = *model;
-    a.ctx = *ctx;
     a.grad = *grad;
-    a.splat_grads = splat_grads;
+    a.status = status;
+    fill_views(a, cfg, model, ctx, splat_grads);
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
     const bool multi = cfg->num_views > 1;
@@ -511,32 +610,43 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     return D3GS_OK;
 }
 
+// the six optimizer segments of a fused backward: xyz, quaternion, scale, opacity, sh_base, sh_rest over
+// `count` Gaussians starting at Gaussian `begin` of the model
+static int32_t fill_segments(BwdArgs& a, const D3gsModel* model, const D3gsAdamSegment* segments, int64_t begin,
+                             int64_t count, bool params_are_slices) {
+    const float* params[6] = {model->xyz, model->quaternion_xyzw, model->scale, model->opacity, model->sh_base,
+                              model->sh_rest};
+    const int64_t per[6] = {3, 4, 3, 1, 3, 45};
+    for (int k = 0; k < 6; ++k) {
+        const D3gsAdamSegment& sg = segments[k];
+        D3GS_REQUIRE(sg.param == params[k] + (params_are_slices ? begin * per[k] : 0),
+                     "segment %d does not point at the model's tensor", k);
+        D3GS_REQUIRE(sg.count == per[k] * count, "segment %d: %lld elements, expected %lld", k, (long long)sg.count,
+                     (long long)(per[k] * count));
+        D3GS_REQUIRE(sg.exp_avg && sg.exp_avg_sq, "segment %d: NULL moment tensor", k);
+        D3GS_REQUIRE(sg.grad_scale != 0.0f && sg.bias_correction1 != 0.0f && sg.bias_correction2_sqrt != 0.0f,
+                     "segment %d: zero grad_scale / bias correction", k);
+        a.sc[k] = make_seg_const(sg);
+        // the kernel indexes the moments by the Gaussian's index in the whole model
+        a.exp_avg[k] = sg.exp_avg - begin * per[k];
+        a.exp_avg_sq[k] = sg.exp_avg_sq - begin * per[k];
+    }
+    return D3GS_OK;
+}
+
 extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const D3gsModel* model,
                                                  const D3gsSplatContext* ctx, const float* splat_grads,
                                                  const D3gsAdamSegment* segments, const D3gsDensifyStats* stats,
-                                                 void* stream) {
+                                                 uint32_t* status, void* stream) {
     int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(segments != nullptr, "segments is NULL");
     D3GS_REQUIRE(cfg->num_views == 1, "the fused backward + Adam handles one view per launch (got %d)", cfg->num_views);
     D3GS_REQUIRE(model->sh_rest != nullptr && model->sh_rest_stride == 45 && model->sh_base_stride == 3,
                  "the fused backward + Adam needs the split degree-3 SH layout (strides 3 and 45)");
-    const float* params[6] = {model->xyz, model->quaternion_xyzw, model->scale, model->opacity, model->sh_base,
-                              model->sh_rest};
-    const int64_t per[6] = {3, 4, 3, 1, 3, 45};
     BwdArgs a = {};
-    for (int k = 0; k < 6; ++k) {
-        const D3gsAdamSegment& sg = segments[k];
-        D3GS_REQUIRE(sg.param == params[k], "segment %d does not point at the model's tensor", k);
-        D3GS_REQUIRE(sg.count == per[k] * model->num, "segment %d: %lld elements, expected %lld", k, (long long)sg.count,
-                     (long long)(per[k] * model->num));
-        D3GS_REQUIRE(sg.exp_avg && sg.exp_avg_sq, "segment %d: NULL moment tensor", k);
-        D3GS_REQUIRE(sg.grad_scale != 0.0f && sg.bias_correction1 != 0.0f && sg.bias_correction2_sqrt != 0.0f,
-                     "segment %d: zero grad_scale / bias correction", k);
-        a.sc[k] = make_seg_const(sg);
-        a.exp_avg[k] = sg.exp_avg;
-        a.exp_avg_sq[k] = sg.exp_avg_sq;
-    }
+    rc = fill_segments(a, model, segments, 0, model->num, false);
+    if (rc != D3GS_OK) return rc;
     if (stats != nullptr) {
         D3GS_REQUIRE(stats->num == model->num && stats->batch == 1, "statistics shape does not match the model / one view");
         D3GS_REQUIRE(stats->duv && stats->radii && stats->duv_ndc_length && stats->count, "NULL stats tensor");
@@ -549,8 +659,8 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
     if (model->num == 0) return D3GS_OK;
     a.cfg = *cfg;
     a.model = *model;
-    a.ctx = *ctx;
-    a.splat_grads = splat_grads;
+    a.status = status;
+    fill_views(a, cfg, model, ctx, splat_grads);
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)256 * (kRow + 14) * sizeof(float);   // SH rows + the 14 small-field gradients
@@ -568,5 +678,83 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
     }
 #undef D3GS_LAUNCH_BWD_ADAM
     D3GS_LAUNCH_CHECK("preprocess_bwd_kernel<adam>");
+    return D3GS_OK;
+}
+
+extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, const D3gsModel* model,
+                                                       const D3gsPeerViews* views, int64_t g_begin, int64_t g_count,
+                                                       const D3gsAdamSegment* segments, const D3gsDensifyStats* stats,
+                                                       const D3gsPeerSet* peers, void* stream) {
+    D3GS_REQUIRE(cfg && model && views && segments && peers, "NULL argument");
+    D3GS_REQUIRE(peers->world >= 1 && peers->world <= D3GS_MAX_PEERS && peers->rank >= 0 && peers->rank < peers->world,
+                 "bad world / rank");
+    D3GS_REQUIRE(cfg->num_views == peers->world, "one view per rank: num_views %d, world %d", cfg->num_views, peers->world);
+    D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
+    D3GS_REQUIRE(model->sh_rest != nullptr && model->sh_rest_stride == 45 && model->sh_base_stride == 3,
+                 "the fused backward + Adam needs the split degree-3 SH layout (strides 3 and 45)");
+    D3GS_REQUIRE(g_begin >= 0 && g_count >= 0 && g_begin + g_count <= model->num, "Gaussian range [%lld, +%lld) outside the model",
+                 (long long)g_begin, (long long)g_count);
+    D3GS_REQUIRE((g_begin & 3) == 0, "the range must start at a multiple of four Gaussians (16-byte aligned spans)");
+    D3GS_REQUIRE(((uintptr_t)model->quaternion_xyzw & 15) == 0, "quaternion tensors must be 16-byte aligned");
+    const bool with_flags = peers->flags[0] != nullptr;
+    D3GS_REQUIRE(!with_flags || peers->epoch != 0, "epoch must be positive when flag blocks are given");
+    BwdArgs a = {};
+    const float* params[6] = {model->xyz, model->quaternion_xyzw, model->scale, model->opacity, model->sh_base,
+                              model->sh_rest};
+    for (int b = 0; b < peers->world; ++b) {
+        D3GS_REQUIRE(views->splat_grads[b] && views->radii[b] && views->cov2d_vecs[b] && views->sh_to_rgb_ne_0[b],
+                     "view %d: NULL buffer", b);
+        D3GS_REQUIRE(((uintptr_t)views->splat_grads[b] & 15) == 0, "view %d: splat_grads not 16-byte aligned", b);
+        D3GS_REQUIRE(peers->param[b] != nullptr, "rank %d: NULL parameter buffer", b);
+        D3GS_REQUIRE((peers->flags[b] != nullptr) == with_flags, "flag blocks must be given for all ranks or none");
+        a.v_grads[b] = views->splat_grads[b];
+        a.v_radii[b] = views->radii[b];
+        a.v_cov2d[b] = views->cov2d_vecs[b];
+        a.v_ne0[b] = views->sh_to_rgb_ne_0[b];
+    }
+    for (int k = 0; k < 6; ++k) {
+        a.field_off[k] = params[k] - peers->param[peers->rank];
+        D3GS_REQUIRE(a.field_off[k] >= 0 && (a.field_off[k] & 3) == 0,
+                     "field %d does not lie 16-byte aligned inside this rank's flat parameter buffer", k);
+    }
+    int32_t rc = fill_segments(a, model, segments, g_begin, g_count, true);
+    if (rc != D3GS_OK) return rc;
+    if (stats != nullptr) {
+        D3GS_REQUIRE(stats->num == model->num, "statistics shape does not match the model");
+        D3GS_REQUIRE(stats->duv_ndc_length && stats->count && stats->width > 0 && stats->height > 0, "bad stats struct");
+        D3GS_REQUIRE(!stats->need_max_radii || stats->max_radii, "max_radii is NULL");
+        a.has_stats = 1;
+        a.stats = *stats;
+    }
+    a.cfg = *cfg;
+    a.model = *model;
+    a.peers = *peers;
+    for (int q = peers->world; q < D3GS_MAX_PEERS; ++q) a.peers.flags[q] = nullptr;
+    a.status = peers->status;
+    a.g_begin = g_begin;
+    a.g_count = g_count;
+    const int64_t tiles = div_up64(g_count, 256);
+    // every rank launches, even with an empty share: the flag exchange needs all ranks
+    int dev = 0, sms = 0;
+    D3GS_CUDA(cudaGetDevice(&dev));
+    D3GS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int64_t grid = tiles < (int64_t)sms * 2 ? tiles : (int64_t)sms * 2;
+    if (grid < 1) grid = 1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)256 * (2 * kRow + 14) * sizeof(float);   // SH rows in, gradient rows, small fields
+#define D3GS_LAUNCH_BWD_PEER(DEG)                                                                               \
+    do {                                                                                                        \
+        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, true, true, true>,                            \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
+        preprocess_bwd_kernel<DEG, true, true, true><<<(unsigned)grid, 256, smem, s>>>(a);                      \
+    } while (0)
+    switch (cfg->sh_degree) {
+        case 0: D3GS_LAUNCH_BWD_PEER(0); break;
+        case 1: D3GS_LAUNCH_BWD_PEER(1); break;
+        case 2: D3GS_LAUNCH_BWD_PEER(2); break;
+        default: D3GS_LAUNCH_BWD_PEER(3); break;
+    }
+#undef D3GS_LAUNCH_BWD_PEER
+    D3GS_LAUNCH_CHECK("preprocess_bwd_kernel<peers>");
     return D3GS_OK;
 }

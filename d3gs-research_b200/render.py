@@ -240,6 +240,10 @@ class GaussianSplatOp:
         # not fit one CTA's shared memory, and is not used with 32-bit sort keys.
         self.binning = "bucket"
         self.last_binning = ""
+        # Optional caller-owned tensors for what a later stage on ANOTHER GPU reads (data-parallel training with
+        # the backward fused into the exchange): keys "radii" [N] int32, "cov2d_vecs" [N,3], "sh_to_rgb_ne_0" [N]
+        # uint8 (written by forward) and "packed" [N,12] (written by the raster backward); single-view launches.
+        self.external: dict[str, torch.Tensor] | None = None
         self.debug: dict[str, torch.Tensor] = {}
         # optional StageTimer; None = no events recorded
         self.timer: StageTimer | None = None
@@ -396,13 +400,16 @@ class GaussianSplatOp:
         tiles_x, tiles_y = div_up(W, 16), div_up(H, 16)
         num_tiles = B * tiles_x * tiles_y
         i32, f32 = torch.int32, torch.float32
+        ext = self.external if (self.external is not None and training and B == 1) else None
         depths = torch.empty(BN, dtype=f32, device=dev)
-        radii = torch.empty(BN, dtype=i32, device=dev)
+        radii = ext["radii"] if ext else torch.empty(BN, dtype=i32, device=dev)
         uvs = torch.empty([BN, 2], dtype=f32, device=dev)
         conic_opacity = torch.empty([BN, 4], dtype=f32, device=dev)
         rgb_gaussian = torch.empty([BN, 3], dtype=f32, device=dev)
-        cov2d_vecs = torch.empty([BN, 3], dtype=f32, device=dev) if training else None
-        sh_ne0 = torch.empty([BN], dtype=torch.uint8, device=dev) if training else None
+        cov2d_vecs = (ext["cov2d_vecs"] if ext else torch.empty([BN, 3], dtype=f32, device=dev)) if training else None
+        sh_ne0 = (ext["sh_to_rgb_ne_0"] if ext else torch.empty([BN], dtype=torch.uint8, device=dev)) if training else None
+        if ext:
+            assert radii.shape == (BN,) and cov2d_vecs.shape == (BN, 3) and sh_ne0.shape == (BN,)
         tiles_touched = torch.empty(BN, dtype=i32, device=dev)
         tile_mask = torch.empty(BN, dtype=torch.int64, device=dev)   # binning scratch, dropped after the key emission
         # per-Gaussian raster records, written by the preprocess and gathered by sorted id in the raster kernels
@@ -597,7 +604,11 @@ class GaussianSplatOp:
             drgb, dT = self._unformat_grad(drgb, dT)
         color = ctx.raster_color if ctx.raster_color is not None else out.color
         # packed per-splat gradients [BN,12]: dconic a b c, dopacity | dcolor r g b, 0 | duv x y, 0 0
-        packed = torch.empty([BN, 12], dtype=torch.float32, device=dev)
+        if self.external is not None and B == 1 and "packed" in self.external:
+            packed = self.external["packed"]
+            assert packed.shape == (BN, 12) and packed.is_contiguous()
+        else:
+            packed = torch.empty([BN, 12], dtype=torch.float32, device=dev)
         ocfg = _lib.OpConfig()
         ocfg.width, ocfg.height, ocfg.tile_x, ocfg.tile_y = W, H, 16, 16
         ocfg.alpha_eps, ocfg.transmittance_eps = self._cfg.alpha_eps, self._cfg.transmittance_eps
@@ -697,7 +708,8 @@ class GaussianSplatOp:
             stats = stats_fn(duv) if stats_fn is not None else None
             _lib.check(lib.d3gs_preprocess_backward_adam(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct),
                                                          rg.packed.data_ptr(), arr,
-                                                         C.byref(stats) if stats is not None else None, stream),
+                                                         C.byref(stats) if stats is not None else None,
+                                                         self._sync_words(dev).data_ptr() + 8, stream),
                        "d3gs_preprocess_backward_adam")
             self._mark("preprocess_bwd_adam")
             return None, (duv if return_uv_grad else None), rg.dcustom_features
@@ -725,12 +737,33 @@ class GaussianSplatOp:
         cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
                                    ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
         _lib.check(lib.d3gs_preprocess_backward(C.byref(ocfg), C.byref(mstruct), C.byref(cstruct),
-                                                rg.packed.data_ptr(), C.byref(g), stream), "d3gs_preprocess_backward")
+                                                rg.packed.data_ptr(), C.byref(g), self._sync_words(dev).data_ptr() + 8,
+                                                stream), "d3gs_preprocess_backward")
         self._mark("preprocess_bwd")
         if return_uv_grad:
             # [B,N,2] strided view of the packed array (the reference returns duv.view(B,-1,2), render.py:3373)
             return grad_out, rg.packed.view(B, -1, 12)[:, :, 8:10], rg.dcustom_features
         return grad_out, None, rg.dcustom_features
+
+
+    def backward_adam_peers(self, model: GaussianModelOriginBase, all_cameras, views: "_lib.PeerViews", g_begin: int,
+                            g_count: int, adam_segments, peerset: "_lib.PeerSet", stats: "_lib.DensifyStats | None" = None) -> None:
+        """Data-parallel training, one view per rank: the preprocess backward of ALL ranks' views for this rank's
+        share of the Gaussians, the gradient sum, Adam and the parameter broadcast in one launch
+        (``d3gs_preprocess_backward_adam_peers``).  ``all_cameras``: the cameras of all ranks in rank order;
+        ``views``: every rank's raster gradients and context as mapped here (written by ``forward`` and
+        ``rasterize_forward_backward`` of the ranks through ``external``)."""
+        dev = model.xyz.device
+        ocfg = self._op_config(model, all_cameras, True)
+        assert ocfg.num_views == peerset.world and len(adam_segments) == 6
+        mstruct = self._model_struct(model)
+        arr = (_lib.AdamSegment * 6)(*adam_segments)
+        _lib.check(self._lib.d3gs_preprocess_backward_adam_peers(C.byref(ocfg), C.byref(mstruct), C.byref(views), g_begin,
+                                                                 g_count, arr, C.byref(stats) if stats is not None else None,
+                                                                 C.byref(peerset),
+                                                                 torch.cuda.current_stream(dev).cuda_stream),
+                   "d3gs_preprocess_backward_adam_peers")
+        self._mark("preprocess_bwd_adam_peers")
 
 
 class _RasterizeGaussians(torch.autograd.Function):

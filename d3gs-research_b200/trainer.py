@@ -216,7 +216,8 @@ class SplatTrainer:
                  lambda_dssim: float = 0.2, batch_size: int = 1, optim_cfg: config_def.Optimizer | None = None,
                  spatial_lr_scale: float = 1.0, process_group=None, need_max_radii: bool = False,
                  shard_optimizer: bool | None = None, peer_update: "bool | str | None" = None,
-                 fuse_backward_adam: bool | None = None, multicast: bool | None = None):
+                 fuse_backward_adam: bool | None = None, multicast: bool | None = None,
+                 fuse_exchange: bool | None = None):
         """``batch_size`` is the GLOBAL number of views per iteration (= world size in data-parallel runs).
         ``shard_optimizer``: reduce-scatter + sliced Adam + all-gather instead of all-reduce + replicated
         Adam; default on when there is more than one rank.  ``peer_update``: do the sharded update as one
@@ -225,6 +226,11 @@ class SplatTrainer:
         buffers, plain peer accesses, two one-element all-reduces around the launch), ``False`` (NCCL
         reduce-scatter / all-gather).  Default on NCCL: ``"symm"``, then ``"ipc"``, then NCCL, whichever can be
         set up on every rank.
+        ``fuse_exchange`` (with ``"symm"``; default on): the preprocess backward moves INTO the exchange launch.
+        Every rank owns a contiguous range of the Gaussians; its launch reads every rank's per-splat raster
+        gradients for that range over NVLink (65 bytes per Gaussian and peer instead of the 236 of the parameter
+        gradient), runs the backward of all views, applies Adam and stores the new parameters into every
+        replica.  ``step`` then needs the cameras of all ranks (``all_cameras``).
         ``fuse_backward_adam`` (single rank, one view per step; default on): the preprocess backward applies
         Adam as it produces the gradients, which are then never stored; ``grad_flat`` is not written."""
         assert model.has_fused_activations, "the trainer drives the fused-activation model"
@@ -289,15 +295,25 @@ class SplatTrainer:
         self._peerset = None
         self._epoch = 0
         self.peer_wait_limit = 0      # polls before a flag wait inside the exchange kernel gives up; 0 = default
+        self.fused_exchange = False
+        self.peer_views = None
         if self.peer_param is not None:
             self._peerset = self._make_peerset(dev)
             self._bar = torch.zeros(1, dtype=torch.float32, device=dev)
+        want_fx = self.exchange == "symm" if fuse_exchange is None else bool(fuse_exchange)
+        assert not want_fx or self.exchange == "symm", "fuse_exchange needs the symmetric-memory exchange"
+        if want_fx:
+            self._setup_fused_exchange(n, dev)
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
         # Adam moments: the whole buffer on one rank, only this rank's slice when sharded
         self.state_lo = self.rank * self.shard_len if self.sharded else 0
         self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) \
             if (self.sharded and self._peerset is None) else None
+        if self.fused_exchange:     # moments of this rank's range of Gaussians, in the flat layout of that many Gaussians
+            self.shard_len = flat_layout(self.range_len)[1]
+            self.state_lo = 0
+            self.grad_shard = None
         self.exp_avg = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
         self.state = GaussianTrainState.create(n, device=dev)
@@ -367,6 +383,59 @@ class SplatTrainer:
                 "multicast=True, but the symmetric buffers have no multicast mapping here"
         return ps
 
+    def _setup_fused_exchange(self, n: int, dev) -> None:
+        """Collective.  Ranges of Gaussians per rank (multiples of 256, the kernel's tile) and the symmetric buffer
+        every rank writes its view's raster gradients and backward context into."""
+        s = -(-n // self.world)
+        self.range_len = -(-s // 256) * 256
+        self.g_begin = min(self.rank * self.range_len, n)
+        self.g_count = max(0, min(self.range_len, n - self.g_begin))
+        sec = lambda nbytes: -(-nbytes // 256) * 256
+        off_cov, off_rad = sec(n * 48), sec(n * 48) + sec(n * 12)
+        off_ne0 = off_rad + sec(n * 4)
+        total = off_ne0 + sec(n)
+        self.peer_views = SymmBuffer(total // 4, torch.float32, dev, self.pg)
+        raw = self.peer_views.tensor.view(torch.uint8)
+        self.op.external = {
+            "packed": raw[:n * 48].view(torch.float32).view(n, 12),
+            "cov2d_vecs": raw[off_cov:off_cov + n * 12].view(torch.float32).view(n, 3),
+            "radii": raw[off_rad:off_rad + n * 4].view(torch.int32),
+            "sh_to_rgb_ne_0": raw[off_ne0:off_ne0 + n],
+        }
+        v = _lib.PeerViews()
+        for q in range(self.world):
+            base = self.peer_views.ptrs[q]
+            v.splat_grads[q], v.cov2d_vecs[q] = base, base + off_cov
+            v.radii[q], v.sh_to_rgb_ne_0[q] = base + off_rad, base + off_ne0
+        self._views_struct = v
+        self.fused_exchange = True
+
+    def _fused_segments(self):
+        """Six segments over this rank's range of Gaussians, moments in the range's own flat layout."""
+        self.step_count += 1
+        t = float(self.step_count)
+        b1, b2 = self.betas
+        bc1 = 1.0 - math.pow(b1, t)
+        bc2s = math.sqrt(1.0 - math.pow(b2, t))
+        if self.use_xyz_schedule:
+            self.lrs["xyz"] = float(self.xyz_schedule(self.step_count))
+        layout, _ = flat_layout(self.range_len)
+        per = {"xyz": 3, "quaternion_xyzw": 4, "scale": 3, "opacity": 1, "color_sh_base": 3, "color_sh": 45}
+        segs = []
+        for name in FLAT_ORDER:
+            off, _, _ = layout[name]
+            s = _lib.AdamSegment()
+            s.param = getattr(self.model, name).data_ptr() + self.g_begin * per[name] * 4
+            s.grad = None
+            s.exp_avg = self.exp_avg.data_ptr() + off * 4
+            s.exp_avg_sq = self.exp_avg_sq.data_ptr() + off * 4
+            s.count = per[name] * self.g_count
+            s.lr, s.beta1, s.beta2, s.eps = float(self.lrs[name]), b1, b2, self.eps
+            s.bias_correction1, s.bias_correction2_sqrt = bc1, bc2s
+            s.grad_scale, s.weight_decay = 1.0, 0.0
+            segs.append(s)
+        return segs
+
     def _field_views(self, flat: torch.Tensor) -> dict:
         """Views of a flat buffer in this trainer's layout, shaped like the model's tensors."""
         return {name: flat[off:off + cnt].view(getattr(self.model, name).shape) for name, (off, cnt) in self._offsets.items()}
@@ -385,19 +454,12 @@ class SplatTrainer:
         re-created for the new count.  Returns ``(n_keep, n_dup_kept, n_split_kept, n_split)``."""
         model, dev = self.model, self.model.xyz.device
         dist = torch.distributed
-        old_padded = self.shard_len * self.world if self.sharded else self.flat_total
         if self.world > 1:
             self.reduce_stats()
             if generator is None:
                 generator = torch.Generator(device=dev)
                 generator.manual_seed(0x5EED0000 + int(step))
-        if self.sharded:   # the moments of the whole model, for the gather by source index
-            full_m = torch.empty(old_padded, dtype=torch.float32, device=dev)
-            full_v = torch.empty(old_padded, dtype=torch.float32, device=dev)
-            dist.all_gather_into_tensor(full_m, self.exp_avg, group=self.pg)
-            dist.all_gather_into_tensor(full_v, self.exp_avg_sq, group=self.pg)
-        else:
-            full_m, full_v = self.exp_avg, self.exp_avg_sq
+        full_m, full_v = self._gather_full_moments()   # the moments of the whole model, for the gather by source index
         m_views, v_views = self._field_views(full_m), self._field_views(full_v)
         moments = {name: (m_views[name], v_views[name]) for name in self._offsets}
         new_model, new_moments, _, totals = strategy.refine_tensors(model, moments, self.state, step, generator)
@@ -412,6 +474,7 @@ class SplatTrainer:
         self.flat_total = total
         self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)
         self._offsets = {name: (off, cnt) for name, (off, cnt, _) in layout.items()}
+        was_fused = self.fused_exchange
         if self.peer_param is not None:
             # the shared buffers have the old size: release them on every rank, then map new ones
             mode = self.exchange
@@ -419,10 +482,12 @@ class SplatTrainer:
                 setattr(model, k, None)
             model.flat = None
             self.grad_flat = self.grad_model = self._peerset = None
-            for b in (self.peer_flags, self.peer_grad, self.peer_param):
+            self.op.external = None
+            for b in (self.peer_views, self.peer_flags, self.peer_grad, self.peer_param):
                 if b is not None:
                     b.close()
-            self.peer_param = self.peer_grad = self.peer_flags = None
+            self.peer_param = self.peer_grad = self.peer_flags = self.peer_views = None
+            self.fused_exchange = False
             self._create_peer_buffers(mode, padded, dev)
             flat = self.peer_param.tensor
             self.grad_flat = self.peer_grad.tensor
@@ -437,18 +502,34 @@ class SplatTrainer:
         if self.peer_param is not None:
             self._peerset = self._make_peerset(dev)
             self._epoch = 0          # the new flag blocks start at zero
-        # the new moments, in the flat layout, cut to this rank's slice
-        new_m = torch.zeros(padded, dtype=torch.float32, device=dev)
-        new_v = torch.zeros(padded, dtype=torch.float32, device=dev)
-        for name, (m, v) in new_moments.items():
-            off, cnt = self._offsets[name]
-            new_m[off:off + cnt].copy_(m.reshape(-1))
-            new_v[off:off + cnt].copy_(v.reshape(-1))
-        self.state_lo = self.rank * self.shard_len if self.sharded else 0
-        self.exp_avg = new_m[self.state_lo:self.state_lo + self.shard_len].clone()
-        self.exp_avg_sq = new_v[self.state_lo:self.state_lo + self.shard_len].clone()
-        self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) \
-            if (self.sharded and self._peerset is None) else None
+            if was_fused:
+                self._setup_fused_exchange(n, dev)
+        if self.fused_exchange:
+            # this rank's range of Gaussians, field by field, into the range's own flat layout
+            per = {"xyz": 3, "quaternion_xyzw": 4, "scale": 3, "opacity": 1, "color_sh_base": 3, "color_sh": 45}
+            layout_s, self.shard_len = flat_layout(self.range_len)
+            self.state_lo = 0
+            self.exp_avg = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
+            self.exp_avg_sq = torch.zeros(self.shard_len, dtype=torch.float32, device=dev)
+            for name, (m, v) in new_moments.items():
+                off_s = layout_s[name][0]
+                lo, cnt = self.g_begin * per[name], self.g_count * per[name]
+                self.exp_avg[off_s:off_s + cnt].copy_(m.reshape(-1)[lo:lo + cnt])
+                self.exp_avg_sq[off_s:off_s + cnt].copy_(v.reshape(-1)[lo:lo + cnt])
+            self.grad_shard = None
+        else:
+            # the new moments, in the flat layout, cut to this rank's slice
+            new_m = torch.zeros(padded, dtype=torch.float32, device=dev)
+            new_v = torch.zeros(padded, dtype=torch.float32, device=dev)
+            for name, (m, v) in new_moments.items():
+                off, cnt = self._offsets[name]
+                new_m[off:off + cnt].copy_(m.reshape(-1))
+                new_v[off:off + cnt].copy_(v.reshape(-1))
+            self.state_lo = self.rank * self.shard_len if self.sharded else 0
+            self.exp_avg = new_m[self.state_lo:self.state_lo + self.shard_len].clone()
+            self.exp_avg_sq = new_v[self.state_lo:self.state_lo + self.shard_len].clone()
+            self.grad_shard = torch.zeros(self.shard_len, dtype=torch.float32, device=dev) \
+                if (self.sharded and self._peerset is None) else None
         self.grad_model = type(model)(**carve_flat(self.grad_flat, n), cur_sh_degree=model.cur_sh_degree,
                                       act_applied=True, flat=self.grad_flat)
         self.state = GaussianTrainState.create(n, self.state.scene_scale, device=dev)   # reset, origin/strategy.py:349
@@ -457,6 +538,33 @@ class SplatTrainer:
             dist.barrier(group=self.pg)     # nobody starts a step before every replica is in place
         return totals
 
+    def _gather_full_moments(self):
+        """Both Adam moments of the whole model in the flat layout (collective when the optimizer is sharded)."""
+        if not self.sharded:
+            return self.exp_avg, self.exp_avg_sq
+        dist, dev = torch.distributed, self.model.xyz.device
+        if not self.fused_exchange:      # equal slices of the flat buffer
+            out = []
+            for src in (self.exp_avg, self.exp_avg_sq):
+                full = torch.empty(self.shard_len * self.world, dtype=torch.float32, device=dev)
+                dist.all_gather_into_tensor(full, src, group=self.pg)
+                out.append(full)
+            return out
+        # ranges of Gaussians: the ranks' pieces of a field, in rank order, are the field
+        layout_g, total = flat_layout(len(self.model))
+        layout_s, _ = flat_layout(self.range_len)
+        out = []
+        for src in (self.exp_avg, self.exp_avg_sq):
+            full = torch.zeros(total, dtype=torch.float32, device=dev)
+            for name in FLAT_ORDER:
+                off_s, cnt_s, _ = layout_s[name]
+                off_g, cnt_g, _ = layout_g[name]
+                gathered = torch.empty(self.world * cnt_s, dtype=torch.float32, device=dev)
+                dist.all_gather_into_tensor(gathered, src[off_s:off_s + cnt_s].contiguous(), group=self.pg)
+                full[off_g:off_g + cnt_g].copy_(gathered[:cnt_g])
+            out.append(full)
+        return out
+
     @torch.no_grad()
     def reset_opacity(self, strategy) -> None:
         """origin/trainer.py:388-417 on the trainer's buffers: clamp the opacities, zero their Adam moments.  With a
@@ -464,6 +572,14 @@ class SplatTrainer:
         off, cnt = self._offsets["opacity"]
         lib = _lib.load()
         dev = self.model.opacity.device
+        if self.fused_exchange:      # this rank holds the opacity moments of its own range of Gaussians
+            _lib.check(lib.d3gs_reset_opacity(self.model.opacity.data_ptr(), cnt, float(strategy.reset_opacity_thresh),
+                                              int(self.model.has_fused_activations), None, None,
+                                              torch.cuda.current_stream(dev).cuda_stream), "d3gs_reset_opacity")
+            off_s = flat_layout(self.range_len)[0]["opacity"][0]
+            self.exp_avg[off_s:off_s + self.range_len].zero_()
+            self.exp_avg_sq[off_s:off_s + self.range_len].zero_()
+            return
         lo, hi = max(off, self.state_lo), min(off + cnt, self.state_lo + self.shard_len)
         whole = lo == off and hi == off + cnt       # this rank holds the moments of every opacity
         _lib.check(lib.d3gs_reset_opacity(self.model.opacity.data_ptr(), cnt, float(strategy.reset_opacity_thresh),
@@ -505,8 +621,12 @@ class SplatTrainer:
 
     @torch.no_grad()
     def step(self, cameras, target_nchw: torch.Tensor, update: bool = True,
-             target_ready: "torch.cuda.Event | None" = None) -> dict:
+             target_ready: "torch.cuda.Event | None" = None, all_cameras=None) -> dict:
         """One iteration on this rank's view(s).  Returns ``{"out", "loss" (lazy), "num_rendered"}``.
+
+        ``all_cameras`` (data parallel with the backward fused into the exchange): the cameras of all ranks in
+        rank order, as a list of ``BasicPinholeCamera`` or a ``CameraBundle``.  Without it the ranks exchange
+        their camera parameters through the process group every step (a small blocking collective).
 
         ``target_ready``: an event recorded after an asynchronous upload of ``target_nchw`` on another
         stream; the loss kernels wait for it, so the upload overlaps the forward pass."""
@@ -519,6 +639,9 @@ class SplatTrainer:
             self.grad_flat.zero_()
             loss = None
             duv = None
+            if self.fused_exchange and update:     # this view contributes nothing: radii == 0 everywhere
+                self.op.external["radii"].zero_()
+                return self._step_fused_exchange(cameras, all_cameras, None, out, None, None)
         else:
             b, h, w, _ = out.color.shape
             nbytes = 3 * b * 3 * h * w * 4
@@ -533,6 +656,8 @@ class SplatTrainer:
                                                      grad_scale=1.0 / self.world, scratch=self._loss_scratch,
                                                      sums=self._loss_sums, dcolor=self._dcolor)
             self.op._mark("l1_dssim")
+            if self.fused_exchange and update:
+                return self._step_fused_exchange(cameras, all_cameras, ctx, out, dcolor, loss)
             fuse = self.fused_adam and update and out.color.shape[0] == 1
             w, h = out.image_shape_wh
             stats_fn = (lambda d: make_stats_struct(self.state, out.radii, d, w, h, self.need_max_radii,
@@ -548,6 +673,47 @@ class SplatTrainer:
             stats = make_stats_struct(self.state, out.radii, duv, w, h, self.need_max_radii,
                                       loss_batch=duv.shape[0] * self.world)
         self.apply_gradients(stats, update)
+        return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
+
+    def _all_cameras(self, cameras, all_cameras):
+        from .render import CameraBundle, _camera_rows
+        if all_cameras is None:
+            rows = torch.from_numpy(_camera_rows(cameras)).to(self.model.xyz.device)
+            gathered = torch.empty(self.world * rows.numel(), dtype=rows.dtype, device=rows.device)
+            torch.distributed.all_gather_into_tensor(gathered, rows.reshape(-1), group=self.pg)
+            host = gathered.view(self.world, 16).cpu().numpy()
+            return CameraBundle(None, cameras.image_shape_wh, None, None, host)
+        if isinstance(all_cameras, (list, tuple)):
+            key = id(all_cameras[0]), len(all_cameras)
+            cached = getattr(self, "_cam_cache", None)
+            if cached is None or cached[0] != key or cached[1] is not all_cameras:
+                import numpy as np
+                host = np.concatenate([_camera_rows(c) for c in all_cameras], axis=0)
+                self._cam_cache = (key, all_cameras, CameraBundle(None, all_cameras[0].image_shape_wh, None, None, host))
+            return self._cam_cache[2]
+        return all_cameras
+
+    def _step_fused_exchange(self, cameras, all_cameras, ctx, out, dcolor, loss) -> dict:
+        """Raster backward of this rank's view into the shared buffer, then one launch that does the preprocess
+        backward of all views for this rank's Gaussians, the gradient sum, Adam and the parameter broadcast."""
+        model = self.model
+        bundle = self._all_cameras(cameras, all_cameras)
+        if ctx is not None:
+            self.op.rasterize_forward_backward(model, ctx, out, GaussianSplatGradients(drgb=dcolor, dT=None), training=True)
+        # The launch accumulates the statistics of this rank's Gaussians over ALL views (it reads every view's duv and
+        # radii anyway): they come out summed over the ranks, each rank holding its own range; reduce_stats() (a
+        # sum / max over ranks, the other ranges being zero here) puts them together when a refinement needs them.
+        w, h = bundle.image_shape_wh
+        st = _lib.DensifyStats()
+        st.duv_ndc_length, st.count, st.max_radii = (self.state.duv_ndc_length.data_ptr(), self.state.count.data_ptr(),
+                                                     self.state.max_radii.data_ptr())
+        st.num, st.batch, st.width, st.height = len(model), self.world, int(w), int(h)
+        st.need_max_radii, st.loss_batch = int(self.need_max_radii), self.world
+        self._epoch += 1
+        self._peerset.epoch = self._epoch
+        self._peerset.wait_limit = int(self.peer_wait_limit)
+        self.op.backward_adam_peers(model, bundle, self._views_struct, self.g_begin, self.g_count,
+                                    self._fused_segments(), self._peerset, st)
         return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
 
     @torch.no_grad()
@@ -603,10 +769,11 @@ class SplatTrainer:
         self.model.flat = flat
         self.grad_flat = self.grad_model = None
         self._peerset = None
-        for b in (self.peer_flags, self.peer_grad, self.peer_param):
+        self.op.external = None
+        for b in (self.peer_views, self.peer_flags, self.peer_grad, self.peer_param):
             if b is not None:
                 b.close()
-        self.peer_param = self.peer_grad = self.peer_flags = None
+        self.peer_param = self.peer_grad = self.peer_flags = self.peer_views = None
 
     def reduce_stats(self):
         """All-reduce the densification statistics (each rank accumulates its own views' share)."""
@@ -620,6 +787,10 @@ class SplatTrainer:
         if self.world == 1:
             return "single rank, Adam inside the preprocess backward" if self.fused_adam else \
                 "single rank, gradient buffer + optimizer kernel"
+        if self.fused_exchange:
+            return ("sharded by Gaussian range, ONE launch over symmetric memory: preprocess backward of all ranks' views "
+                    "from their raster gradients (peer loads), gradient sum, Adam, parameters stored to every replica; "
+                    "launches ordered by flags inside the kernel")
         if self._peerset is not None and self.exchange == "symm":
             how = ("multimem.ld_reduce / multimem.st through the NVLink switch" if self.multicast else
                    "plain peer loads and stores (no multicast mapping)")

@@ -148,7 +148,7 @@ int32_t d3gs_bit_length(uint32_t n);
 uint64_t d3gs_kernel_launch_count(void);
 /* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
  * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet,
- * 8 D3gsRefineConfig, 9 D3gsRefineMoments */
+ * 8 D3gsRefineConfig, 9 D3gsRefineMoments, 10 D3gsPeerViews */
 size_t d3gs_struct_size(int32_t which);
 
 /* ---- K1 preprocess forward (render.py:250-681) ------------------------------------------- */
@@ -258,8 +258,10 @@ int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t
 /* every gradient element is written (zeros for culled Gaussians); sums over the view batch.  Slot 7 of a
  * splat_grads row (zero after d3gs_raster_backward) is dz, the gradient of the splat's depth value when a
  * depth image was rendered (render.py:3053-3057): it joins the camera-space z gradient. */
+/* status: optional device word; D3GS_STATUS_COPY_TIMEOUT is OR-ed in when the staging copy of a CTA's SH rows did not
+ * arrive (that CTA then writes no gradient). */
 int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
-                                 const float* splat_grads, const D3gsModelGrad* grad, void* stream);
+                                 const float* splat_grads, const D3gsModelGrad* grad, uint32_t* status, void* stream);
 
 /* ---- K9/K10 SSIM map and fused L1 + D-SSIM (fused_ssim.py:93-416, losses.py:19-20) ---------- */
 /* ssim map forward: x NHWC or NCHW [B,3,H,W]/[B,H,W,3], y NCHW; outputs NCHW; dmu* may be NULL */
@@ -316,10 +318,11 @@ int32_t d3gs_densify_stats(const D3gsDensifyStats* stats, void* stream);
  * segments[0..5] = xyz, quaternion_xyzw, scale, opacity, sh_base, sh_rest in this order; segment.param must be
  * the model's tensor (updated in place), segment.count its element count, segment.grad is ignored.  Needs the
  * split degree-3 layout (sh_base_stride 3, sh_rest_stride 45) and cfg->num_views == 1.  stats (may be NULL):
- * the densification statistics of the same iteration, accumulated by the same launch. */
+ * the densification statistics of the same iteration, accumulated by the same launch.
+ * status: as for d3gs_preprocess_backward; a CTA whose copy did not arrive takes no optimizer step. */
 int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsSplatContext* ctx,
                                       const float* splat_grads, const D3gsAdamSegment* segments,
-                                      const D3gsDensifyStats* stats, void* stream);
+                                      const D3gsDensifyStats* stats, uint32_t* status, void* stream);
 
 /* ---- data-parallel update over peer memory (no counterpart in the reference, which trains on one GPU;
  * the batch semantics it implements are those of train.py:170-172 and tools.py:146-163) ------------
@@ -364,6 +367,32 @@ typedef struct D3gsPeerSet {
 #define D3GS_PEER_FLAG_WORDS 32
 int32_t d3gs_adam_stats_step_peers(const D3gsAdamSegment* segments, int32_t num_segments,
                                    const D3gsDensifyStats* stats, const D3gsPeerSet* peers, void* stream);
+
+/* K8 + gradient sum over the ranks + K11 + parameter broadcast in ONE launch (no counterpart in the reference; batch
+ * semantics of train.py:170-172, render.py:3182-3199).  One view per rank.  Rank r owns the Gaussians
+ * [g_begin, g_begin + g_count) and their Adam moments.  Its launch reads, for those Gaussians, EVERY rank's per-splat
+ * raster gradients and context (views->...[b] = rank b's buffers of ITS view, each indexed by the Gaussian, as mapped
+ * in this process), runs the backward through projection and SH for all views (cfg->cameras[b] = rank b's camera,
+ * cfg->num_views = world), sums over the views in registers, applies Adam and stores the new parameters into every
+ * rank's flat parameter buffer (peers->param[q]; model's tensors lie inside peers->param[rank]).  The parameter
+ * gradient (236 bytes per Gaussian) is never formed: per Gaussian and peer 65 bytes come in over NVLink instead of
+ * 236, and the backward arithmetic overlaps the transfers.  segments[0..5]: xyz, quaternion_xyzw, scale, opacity,
+ * sh_base, sh_rest; param = the model's tensor + g_begin * floats-per-Gaussian, count = floats-per-Gaussian * g_count,
+ * exp_avg / exp_avg_sq = this rank's moments for its share.  peers->flags / epoch / wait_limit order the ranks'
+ * launches as for d3gs_adam_stats_step_peers (with flags[0] == NULL the caller does); peers->grad is not used.
+ * stats (may be NULL): the densification statistics of the rank's Gaussians over ALL views are accumulated in the
+ * same launch (duv_ndc_length, count, max_radii indexed by the Gaussian; width, height, loss_batch, need_max_radii as
+ * usual; duv and radii are not read -- the views carry them), i.e. already summed over the ranks, for the rank's own
+ * range only.  g_begin must be a multiple of 4.  Every rank must launch, also with g_count == 0. */
+typedef struct D3gsPeerViews {
+    const float* splat_grads[D3GS_MAX_PEERS];        /* [N,12] packed raster gradients of rank b's view */
+    const int32_t* radii[D3GS_MAX_PEERS];            /* [N] */
+    const float* cov2d_vecs[D3GS_MAX_PEERS];         /* [N,3] */
+    const uint8_t* sh_to_rgb_ne_0[D3GS_MAX_PEERS];   /* [N] */
+} D3gsPeerViews;
+int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, const D3gsModel* model, const D3gsPeerViews* views,
+                                            int64_t g_begin, int64_t g_count, const D3gsAdamSegment* segments,
+                                            const D3gsDensifyStats* stats, const D3gsPeerSet* peers, void* stream);
 
 /* Buffers another process on the same node can map.  create: cudaMalloc on the current device, zero-filled,
  * plus a 64-byte handle to send to the peers; open: map a peer's buffer into this process (enables peer

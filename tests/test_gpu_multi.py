@@ -1,5 +1,8 @@
-"""Data-parallel update on two GPUs.  Five ways to sum the ranks' gradients and apply Adam:
+"""Data-parallel update on two GPUs.  Six ways to sum the ranks' gradients and apply Adam:
 
+    fused       ONE launch per rank over torch symmetric memory: the preprocess backward of both ranks' views for the
+                rank's range of Gaussians (peer loads of the raster gradients), gradient sum, Adam, parameters
+                stored to both replicas; launches ordered by flags inside the kernel (the default with > 1 rank)
     symm-mc     one kernel over torch symmetric memory, gradient slice summed and parameters broadcast by the
                 NVLink switch (multimem.ld_reduce / multimem.st), launches ordered by flags inside the kernel
     symm        the same kernel and flags with plain peer loads and stores (no multicast)
@@ -28,7 +31,9 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-PATHS = (("symm-mc", dict(peer_update="symm", multicast=None)), ("symm", dict(peer_update="symm", multicast=False)),
+PATHS = (("fused", dict(peer_update="symm", fuse_exchange=True)),
+         ("symm-mc", dict(peer_update="symm", multicast=None, fuse_exchange=False)),
+         ("symm", dict(peer_update="symm", multicast=False, fuse_exchange=False)),
          ("ipc", dict(peer_update="ipc")), ("nccl", dict(peer_update=False)), ("replicated", dict(shard_optimizer=False)))
 
 
@@ -78,14 +83,16 @@ def _worker(rank, world, port, q):
             model = gpu_model(sc, dev)
             tr = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world, **kw)
             check(tr.sharded == (name != "replicated"), f"{name}: sharded = {tr.sharded}")
-            check(tr.exchange == {"symm-mc": "symm", "symm": "symm", "ipc": "ipc"}.get(name, "nccl"),
+            check(tr.exchange == {"fused": "symm", "symm-mc": "symm", "symm": "symm", "ipc": "ipc"}.get(name, "nccl"),
                   f"{name}: exchange = {tr.exchange}")
+            check(tr.fused_exchange == (name == "fused"), f"{name}: fused_exchange = {tr.fused_exchange}")
+            all_cams = [d3.BasicPinholeCamera.from_params(m, fx, fy, cx, cy, 160, 112) for m in sc["cam2worlds"]]
             if name == "symm-mc" and not tr.multicast:
                 notes.append("no multicast mapping on this box: symm-mc ran with plain peer accesses")
             # (c) one real step against the oracle; then back to the initial state (a real step's gradients come
             # out of float atomics and differ in their last bits from run to run, which (a) must not see)
             start = model.flat.clone()
-            tr.step(cam, target)
+            tr.step(cam, target, all_cameras=all_cams if n_gauss == 6000 else None)
             tr.op.check_status()
             torch.cuda.synchronize()
             if rank == 0:
@@ -106,16 +113,17 @@ def _worker(rank, world, port, q):
                 t.zero_()
             torch.cuda.synchronize()
             dist.barrier()
-            # (a) fixed gradients
-            for t in range(3):
-                gen = torch.Generator().manual_seed(1000 * t + rank)
-                tr.grad_flat[:tr.flat_total].copy_(torch.randn(tr.flat_total, generator=gen))
-                tr.apply_gradients(None, True)
+            # (a) fixed gradients (the fused path has no gradient buffer to put them in)
+            if name != "fused":
+                for t in range(3):
+                    gen = torch.Generator().manual_seed(1000 * t + rank)
+                    tr.grad_flat[:tr.flat_total].copy_(torch.randn(tr.flat_total, generator=gen))
+                    tr.apply_gradients(None, True)
             torch.cuda.synchronize()
             fixed = model.flat[:tr.flat_total].clone()
             # (b) real steps on top
             for _ in range(2):
-                tr.step(cam, target)
+                tr.step(cam, target, all_cameras=all_cams)
             tr.reduce_stats()
             tr.op.check_status()
             torch.cuda.synchronize()
@@ -129,7 +137,7 @@ def _worker(rank, world, port, q):
         init = gpu_model(sc, dev).flat[:results["ipc"][0].numel()]
         ok = True
         for name, _ in PATHS:
-            if name == "ipc":
+            if name in ("ipc", "fused"):      # fused: no fixed-gradient updates, so a different state; it has (c)
                 continue
             exact = bool(torch.equal(results["ipc"][0], results[name][0]))               # (a) exact
             counts = bool(torch.equal(results["ipc"][2], results[name][2]))             # visibility counts
@@ -157,18 +165,19 @@ def _worker(rank, world, port, q):
     target = torch.rand(1, 3, 112, 160, generator=torch.Generator().manual_seed(10 + rank)).to(dev)
     strategy = d3.GaussianStrategyOrigin(grow_grad2d=2e-5)      # low enough that this small scene grows
     counts = {}
-    for name, kw in (PATHS[0], PATHS[2], PATHS[3]):
+    all_cams = [d3.BasicPinholeCamera.from_params(m, fx, fy, cx, cy, 160, 112) for m in sc["cam2worlds"]]
+    for name, kw in (PATHS[0], PATHS[1], PATHS[3], PATHS[4]):
         model = gpu_model(sc, dev)
         tr = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world, **kw)
         for _ in range(4):
-            tr.step(cam, target)
+            tr.step(cam, target, all_cameras=all_cams)
         totals = tr.refine(strategy, step=600)
         n_new = len(tr.model)
         check(n_new == totals[0] + totals[1] + 2 * totals[2] and n_new != 6000, f"{name}: refine totals {totals}")
         check(tr.exp_avg.numel() == tr.shard_len and tr.grad_flat.numel() >= tr.flat_total, f"{name}: buffer sizes")
         tr.reset_opacity(strategy)
         for _ in range(2):
-            tr.step(cam, target)
+            tr.step(cam, target, all_cameras=all_cams)
         tr.op.check_status()
         torch.cuda.synchronize()
         chk = torch.stack([tr.parameter_checksum(), torch.tensor(n_new, device=dev)])
