@@ -111,7 +111,8 @@ SIGNATURES = {
     "d3gs_bit_length": (_I32, [C.c_uint32]),
     "d3gs_struct_size": (_SZ, [_I32]),
     "d3gs_kernel_launch_count": (C.c_uint64, []),
-    "d3gs_preprocess_forward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), _P, C.POINTER(SplatContext), _P]),
+    "d3gs_test_hooks": (None, [C.c_uint32, _I32]),
+    "d3gs_preprocess_forward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), _P, C.POINTER(SplatContext), _P, _P]),
     "d3gs_scan_workspace_bytes": (_SZ, [_I64]),
     "d3gs_scan_tiles": (_I32, [_P, _P, _I64, _P, _P, _SZ, _P, _P]),
     "d3gs_scan_tiles_static_max_items": (_I64, []),

@@ -40,6 +40,7 @@ struct AdamArgs {
     int64_t chunk;
     int64_t param_off[kMaxSegments], grad_off[kMaxSegments];
     D3gsPeerSet peers;
+    TestHooks hooks;
 };
 
 __global__ void __launch_bounds__(kAdamThreads) adam_stats_kernel(const __grid_constant__ AdamArgs a) {
@@ -244,6 +245,7 @@ __global__ void __launch_bounds__(kAdamThreads, 3) adam_peers_kernel(const __gri
         const uint32_t bytes = (uint32_t)(chunk * sizeof(float));
         const int64_t goff = a.grad_off[ch.si] + ch.base;
         mbar_arrive_expect_tx(&s_bar[buf], bytes * (uint32_t)world);
+        if ((int)blockIdx.x == a.hooks.hold) return;      // test hook: this CTA's copies are never issued
         for (int q = 0; q < world; ++q) bulk_copy_g2s(buf_ptr(buf) + q * chunk4, a.peers.grad[q] + goff, bytes, &s_bar[buf]);
     };
     bool copy_failed = false;
@@ -274,11 +276,11 @@ __global__ void __launch_bounds__(kAdamThreads, 3) adam_peers_kernel(const __gri
             const int64_t base = ch.base;
             const int64_t poff = a.param_off[ch.si] + base;
             if (ch.staged) {
-                bool arrived = mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u);
+                bool arrived = mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u, a.hooks.poll_limit);
                 if (__syncthreads_or(!arrived)) {
                     // give the copies one more bounded wait before the shared memory can be released, flag, and
                     // leave this and the CTA's remaining chunks unchanged
-                    if (!arrived) mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u);
+                    if (!arrived) mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u, a.hooks.poll_limit);
                     if (tid == 0 && a.peers.status != nullptr) atomicOr(a.peers.status, D3GS_STATUS_COPY_TIMEOUT);
                     copy_failed = true;
                 } else {
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(kAdamThreads, 3) adam_peers_kernel(const __gri
         if (copy_failed && next_in_flight) {
             // the copies issued for the next block still land in shared memory: wait for them (bounded) before
             // the CTA may go on to its exit
-            mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u);
+            mbar_wait_bounded(&s_bar[cur], (phases >> cur) & 1u, a.hooks.poll_limit);
             next_in_flight = false;
         }
     }
@@ -409,6 +411,7 @@ static int32_t adam_launch(const D3gsAdamSegment* segments, int32_t num_segments
     }
     for (int k = num_segments + 1; k < kMaxSegments + 2; ++k) a.block_start[k] = blocks;
     a.total_blocks = blocks;
+    a.hooks = test_hooks();
     if (blocks == 0) return D3GS_OK;
     D3GS_REQUIRE(blocks < ((int64_t)1 << 31), "too many CTAs");
     if (peers != nullptr) {

@@ -20,10 +20,19 @@ int32_t cuda_fail(cudaError_t e, const char* what) {
     return D3GS_ERR_CUDA;
 }
 
+static std::atomic<uint32_t> g_hook_polls{0};
+static std::atomic<int32_t> g_hook_hold{-1};
+TestHooks test_hooks() { return TestHooks{g_hook_polls.load(), g_hook_hold.load()}; }
+
 static std::atomic<uint64_t> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 }  // namespace d3gs
+
+extern "C" void d3gs_test_hooks(uint32_t poll_limit, int32_t hold) {
+    d3gs::g_hook_polls.store(poll_limit);
+    d3gs::g_hook_hold.store(hold);
+}
 
 extern "C" uint64_t d3gs_kernel_launch_count(void) { return d3gs::g_launches.load(std::memory_order_relaxed); }
 

@@ -3,6 +3,8 @@
 //
 // Reference semantics: d3sim/algos/d3gs/render.py:694-695 (cumsum + total), 896-939 (ranges),
 // 1702-1716 (the per-batch gather this staging replaces).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace d3gs {
@@ -20,7 +22,8 @@ constexpr uint64_t kValueMask = ~kFlagMask;
 // workspace layout: [0] uint32 ticket, [1] uint32 pad, then uint64 status[num_tiles]
 __global__ void __launch_bounds__(kScanThreads)
 scan_lookback_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int64_t n, int64_t* __restrict__ total,
-                     uint32_t* __restrict__ ticket, uint64_t* __restrict__ tile_status, uint32_t* __restrict__ status) {
+                     uint32_t* __restrict__ ticket, uint64_t* __restrict__ tile_status, uint32_t* __restrict__ status,
+                     const TestHooks hooks) {
     __shared__ uint32_t s_tile;
     __shared__ int64_t s_warp[kScanThreads / 32];
     __shared__ int64_t s_prefix;
@@ -64,13 +67,15 @@ scan_lookback_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, 
     // decoupled look-back by warp 0
     if (warp == 0) {
         int64_t excl = 0;
+        const bool publish = (int)tile != hooks.hold;          // test hook: this tile never publishes
+        const int spin_limit = hooks.poll_limit != 0 ? (int)hooks.poll_limit : (1 << 20);
         if (tile == 0) {
-            if (lane == 0) {
+            if (lane == 0 && publish) {
                 __threadfence();
                 atomicExch((unsigned long long*)&tile_status[0], kFlagPrefix | ((uint64_t)block_total & kValueMask));
             }
         } else {
-            if (lane == 0) {
+            if (lane == 0 && publish) {
                 atomicExch((unsigned long long*)&tile_status[tile], kFlagAggregate | ((uint64_t)block_total & kValueMask));
             }
             int64_t look = (int64_t)tile - 1;
@@ -101,12 +106,12 @@ scan_lookback_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, 
                     look -= first_invalid;
                     spins = 0;
                 } else {
-                    if (++spins > (1 << 20)) { gave_up = true; break; }
+                    if (++spins > spin_limit) { gave_up = true; break; }
                     __nanosleep(32);
                 }
             }
             if (gave_up && lane == 0) atomicOr(status, D3GS_STATUS_SCAN_TIMEOUT);
-            if (lane == 0) {
+            if (lane == 0 && publish) {
                 __threadfence();
                 atomicExch((unsigned long long*)&tile_status[tile],
                            kFlagPrefix | ((uint64_t)(excl + block_total) & kValueMask));
@@ -219,7 +224,7 @@ extern "C" int32_t d3gs_scan_tiles(const int32_t* in, int32_t* out, int64_t n, i
     D3GS_CUDA(cudaMemsetAsync(workspace, 0, d3gs_scan_workspace_bytes(n), s));
     uint32_t* ticket = reinterpret_cast<uint32_t*>(workspace);
     uint64_t* tstat = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(workspace) + 16);
-    scan_lookback_kernel<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, total, ticket, tstat, status);
+    scan_lookback_kernel<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, total, ticket, tstat, status, test_hooks());
     D3GS_LAUNCH_CHECK("scan_lookback_kernel");
     return D3GS_OK;
 }
@@ -281,8 +286,8 @@ constexpr size_t kStaticScanBytes = 16 + (size_t)(kStaticScanMaxItems / kScanTil
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_static_scan_ptr[kMaxDevices] = {};
-bool g_static_scan_ready[kMaxDevices] = {};
+void* g_static_scan_ptr[kMaxDevices] = {};    // guarded by g_static_scan_mutex
+std::mutex g_static_scan_mutex;
 
 }  // namespace
 }  // namespace d3gs
@@ -307,21 +312,26 @@ extern "C" int32_t d3gs_scan_tiles_static(const int32_t* in, int32_t* out, int64
     int dev = -1;
     D3GS_CUDA(cudaGetDevice(&dev));
     D3GS_REQUIRE(dev >= 0 && dev < kMaxDevices, "device ordinal %d outside [0,%d)", dev, kMaxDevices);
-    if (!g_static_scan_ready[dev]) {
+    unsigned char* base = nullptr;
+    {
         // Set-up, once per device, with that device current: in host code the array's name is only a
         // stand-in symbol, so its device address has to be asked for before it can be given to a kernel.
-        void* p = nullptr;
-        D3GS_CUDA(cudaGetSymbolAddress(&p, g_static_scan_scratch));
-        D3GS_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned NULL");
-        g_static_scan_ptr[dev] = p;
-        g_static_scan_ready[dev] = true;
+        // Host threads making their first calls at the same time take turns here.
+        std::lock_guard<std::mutex> lock(g_static_scan_mutex);
+        if (g_static_scan_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            D3GS_CUDA(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+            D3GS_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned NULL");
+            g_static_scan_ptr[dev] = p;
+        }
+        base = reinterpret_cast<unsigned char*>(g_static_scan_ptr[dev]);
     }
-    unsigned char* base = reinterpret_cast<unsigned char*>(g_static_scan_ptr[dev]);
     const int64_t tiles = div_up64(n, kScanTile);
     // every call shares the array and finds the previous call's ticket and tile states in it: clear the part in use
     D3GS_CUDA(cudaMemsetAsync(base, 0, 16 + (size_t)tiles * sizeof(uint64_t), s));
     scan_lookback_kernel<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, total, reinterpret_cast<uint32_t*>(base),
-                                                                 reinterpret_cast<uint64_t*>(base + 16), status);
+                                                                 reinterpret_cast<uint64_t*>(base + 16), status,
+                                                                 test_hooks());
     D3GS_LAUNCH_CHECK("scan_lookback_kernel (static scratch)");
     return D3GS_OK;
 }

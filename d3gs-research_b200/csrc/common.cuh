@@ -16,6 +16,16 @@ void set_error(const char* fmt, ...);
 int32_t cuda_fail(cudaError_t e, const char* what);
 void count_launch();
 
+// Test hooks (d3gs_test_hooks): a poll limit for every bounded wait of the kernels launched afterwards (0 = the
+// built-in limits) and the index of one CTA / tile that withholds what others wait for -- its look-back flag, or
+// the bulk copy its own mbarrier expects (-1 = nobody).  With them a test makes a bounded wait run out without
+// touching memory it should not: the waiting code gives up, sets its status bit and returns.
+struct TestHooks {
+    uint32_t poll_limit;
+    int32_t hold;
+};
+TestHooks test_hooks();
+
 #define D3GS_REQUIRE(cond, ...)                 \
     do {                                        \
         if (!(cond)) {                          \
@@ -269,8 +279,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after ~2^22 polls (seconds), returns false so the caller can flag
 // D3GS_STATUS_COPY_TIMEOUT and leave instead of hanging the device.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (int it = 0; it < (1 << 22); ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = 0) {
+    const uint32_t polls = limit != 0 ? limit : (1u << 22);
+    for (uint32_t it = 0; it < polls; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 64) __nanosleep(64);
     }

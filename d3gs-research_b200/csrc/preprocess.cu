@@ -203,6 +203,8 @@ struct PrepArgs {
     D3gsModel model;
     D3gsSplatContext ctx;
     const uint8_t* mask;
+    uint32_t* status;     // optional: D3GS_STATUS_COPY_TIMEOUT when a CTA's coefficient rows never arrived
+    TestHooks hooks;
 };
 
 constexpr int kRow = 45;   // shared-memory row length in floats (odd: conflict-free per-thread rows)
@@ -239,7 +241,8 @@ __global__ void __launch_bounds__(256, 4) preprocess_fwd_kernel(const __grid_con
                 mbar_init(&s_bar, 1);
                 fence_mbar_init();
                 mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
-                bulk_copy_g2s(s_rest, a.model.sh_rest + g_first * 45, (uint32_t)rows * 180u, &s_bar);
+                if ((int)blockIdx.x != a.hooks.hold)      // test hook: this CTA's copy is never issued
+                    bulk_copy_g2s(s_rest, a.model.sh_rest + g_first * 45, (uint32_t)rows * 180u, &s_bar);
             }
             __syncthreads();   // the barrier is initialised before anybody polls it
         }
@@ -424,7 +427,13 @@ __global__ void __launch_bounds__(256, 4) preprocess_fwd_kernel(const __grid_con
     }
     if constexpr (NR3 > 0) {
         if (bulk) {
-            if (!mbar_wait_bounded(&s_bar, 0)) valid = false;   // the copy never landed: emit nothing from this CTA
+            if (!mbar_wait_bounded(&s_bar, 0, a.hooks.poll_limit)) {
+                // The copy never landed: no colour and no raster record leave this CTA, and the caller learns of it
+                // through the status word (tile counts of these Gaussians are already out: the launch's results
+                // are invalid as a whole).
+                valid = false;
+                if (t == 0 && a.status != nullptr) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
+            }
         } else {
             s_src[t] = valid ? (int32_t)g : -1;
             __syncthreads();
@@ -652,7 +661,7 @@ int32_t check_cfg(const D3gsOpConfig* cfg) {
 using namespace d3gs;
 
 extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsModel* model, const uint8_t* mask,
-                                           const D3gsSplatContext* ctx, void* stream) {
+                                           const D3gsSplatContext* ctx, uint32_t* status, void* stream) {
     int32_t rc = check_cfg(cfg);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(model != nullptr && ctx != nullptr, "model/ctx is NULL");
@@ -682,6 +691,8 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
     a.model = *model;
     a.ctx = *ctx;
     a.mask = mask;
+    a.status = status;
+    a.hooks = test_hooks();
     dim3 grid((unsigned)div_up64(total, 256));
     switch (cfg->sh_degree) {
         case 0: preprocess_fwd_kernel<0><<<grid, 256, 0, s>>>(a); break;

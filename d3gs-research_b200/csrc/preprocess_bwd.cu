@@ -36,6 +36,7 @@ struct BwdArgs {
     D3gsPeerSet peers;
     int64_t field_off[6];
     uint32_t* status;                         // optional device word for D3GS_STATUS_COPY_TIMEOUT
+    TestHooks hooks;
     // fused optimizer step (ADAM variant): per field xyz, quaternion, scale, opacity, sh_base, sh_rest
     SegConst sc[6];
     float* exp_avg[6];
@@ -87,7 +88,8 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
                          ((uintptr_t)(a.model.sh_rest + g0 * 45) & 15) == 0;
     if (bulk_in && t == 0) {
         mbar_arrive_expect_tx(&s_bar, (uint32_t)rows * 180u);
-        bulk_copy_g2s(s_in, a.model.sh_rest + g0 * 45, (uint32_t)rows * 180u, &s_bar);
+        if ((int)blockIdx.x != a.hooks.hold)      // test hook: this CTA's copy is never issued
+            bulk_copy_g2s(s_in, a.model.sh_rest + g0 * 45, (uint32_t)rows * 180u, &s_bar);
     }
     if (ADAM && t >= 32 && t < 32 + 15) {
         // The optimizer sweep at the end of the kernel reads parameters and both moments of the five small fields
@@ -108,7 +110,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
     bool copy_ok = true;
     if constexpr (NR3 > 0) {
         if (bulk_in) {
-            copy_ok = mbar_wait_bounded(&s_bar, phase);
+            copy_ok = mbar_wait_bounded(&s_bar, phase, a.hooks.poll_limit);
             phase ^= 1u;
         } else {
             const float* src = a.model.sh_rest;
@@ -136,7 +138,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         // The coefficient rows never arrived: flag it, give the copy one more bounded wait (the shared memory must
         // not be released while it may still land), and change nothing for this CTA's Gaussians -- no gradient is
         // written and, in the fused variants, no optimizer step is taken.
-        if (!copy_ok) mbar_wait_bounded(&s_bar, phase ^ 1u);
+        if (!copy_ok) mbar_wait_bounded(&s_bar, phase ^ 1u, a.hooks.poll_limit);
         if (t == 0 && a.status != nullptr) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
         return false;
     }
@@ -584,6 +586,7 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     a.model = *model;
     a.grad = *grad;
     a.status = status;
+    a.hooks = test_hooks();
     fill_views(a, cfg, model, ctx, splat_grads);
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
@@ -660,6 +663,7 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
     a.cfg = *cfg;
     a.model = *model;
     a.status = status;
+    a.hooks = test_hooks();
     fill_views(a, cfg, model, ctx, splat_grads);
     dim3 grid((unsigned)div_up64(model->num, 256));
     cudaStream_t s = (cudaStream_t)stream;
@@ -731,6 +735,7 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
     a.peers = *peers;
     for (int q = peers->world; q < D3GS_MAX_PEERS; ++q) a.peers.flags[q] = nullptr;
     a.status = peers->status;
+    a.hooks = test_hooks();
     a.g_begin = g_begin;
     a.g_count = g_count;
     const int64_t tiles = div_up64(g_count, 256);

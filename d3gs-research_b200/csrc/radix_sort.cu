@@ -125,7 +125,8 @@ __global__ void __launch_bounds__(kSortThreads, 1)
 onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ keys_out,
                 const int32_t* __restrict__ vals_in, int32_t* __restrict__ vals_out, int64_t n, int shift,
                 uint32_t mask, const uint32_t* __restrict__ digit_base, uint32_t* __restrict__ ticket,
-                uint32_t* __restrict__ lookback /* [tiles][radix] */, uint32_t* __restrict__ status) {
+                uint32_t* __restrict__ lookback /* [tiles][radix] */, uint32_t* __restrict__ status,
+                const TestHooks hooks) {
     constexpr int kRadix = 1 << BITS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     SweepSmem<BITS>& sm = *reinterpret_cast<SweepSmem<BITS>*>(smem_raw);
@@ -173,8 +174,10 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ key
             sm.warp_hist[w][d] = tot;   // exclusive offset of this warp inside the digit's run
             tot += c;
         }
-        if (tile == 0) atomicExch(my, kLbPrefix | tot);
-        else atomicExch(my, kLbAggregate | tot);
+        if ((int)tile != hooks.hold) {      // test hook: this tile never publishes its counts
+            if (tile == 0) atomicExch(my, kLbPrefix | tot);
+            else atomicExch(my, kLbAggregate | tot);
+        }
         // block-wide exclusive scan over digits -> position of the digit's run in the sorted tile
         inc = tot;
 #pragma unroll
@@ -223,14 +226,14 @@ onesweep_kernel(const uint64_t* __restrict__ keys_in, uint64_t* __restrict__ key
                 }
                 look -= consumed;
                 if (blocked) {
-                    if (++spins > (1 << 20)) gave_up = true;
+                    if (++spins > (hooks.poll_limit != 0 ? (int)hooks.poll_limit : (1 << 20))) gave_up = true;
                     __nanosleep(20);
                 } else {
                     spins = 0;
                 }
             }
             if (gave_up) atomicOr(status, D3GS_STATUS_SORT_TIMEOUT);
-            atomicExch(my, kLbPrefix | ((excl + tot) & kLbValueMask));
+            if ((int)tile != hooks.hold) atomicExch(my, kLbPrefix | ((excl + tot) & kLbValueMask));
         }
         sm.global_base[d] = (int64_t)digit_base[d] + (int64_t)excl - (int64_t)dig_off;
     }
@@ -320,7 +323,7 @@ int32_t run_sort(uint64_t* keys, uint64_t* keys_alt, int32_t* values, int32_t* v
     for (int p = 0; p < passes; ++p) {
         onesweep_kernel<BITS><<<(unsigned)L.tiles, kSortThreads, sizeof(SweepSmem<BITS>), s>>>(
             kin, kout, vin, vout, n, pt.shift[p], pt.mask[p], hist + (size_t)p * kRadix, tickets + p,
-            lookback + (size_t)p * lb_pass, status);
+            lookback + (size_t)p * lb_pass, status, test_hooks());
         D3GS_LAUNCH_CHECK("onesweep_kernel");
         uint64_t* tk = kin; kin = kout; kout = tk;
         int32_t* tv = vin; vin = vout; vout = tv;

@@ -56,6 +56,7 @@ struct RasterArgs {
     const float* drgb;
     const float* dT;
     float* splat_grads;
+    TestHooks hooks;
 };
 
 // The tile a CTA works on.  The grid is one-dimensional; with an order table the CTAs take the tiles by
@@ -141,7 +142,8 @@ __device__ __forceinline__ void issue_batch(const RasterArgs& a, float4* buf, ui
     const int cnt = min(kBatch, n - batch * kBatch);
     const uint32_t bytes = (uint32_t)cnt * kRecBytes;
     mbar_arrive_expect_tx(bar, bytes);
-    bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
+    if ((int)blockIdx.x != a.hooks.hold)      // test hook: this CTA's copies are never issued
+        bulk_copy_g2s(buf, a.records + (int64_t)(r0 + batch * kBatch) * kRecFloat4, bytes, bar);
 }
 
 // Gather staging: thread t of the CTA fetches record `id` of the per-Gaussian table into slot t of a batch
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(128, 8) raster_forward_kernel(const __grid_con
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
         if (GATHER) cp_async_wait_all();
-        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1), a.hooks.poll_limit)) copy_failed = true;
         // The one barrier of a batch: batch b has arrived for everybody, everybody has finished batch b-1
         // (so the other buffer may be refilled), and the whole-tile early exit is decided
         // (render.py:1691-1694).  No copy is in flight here: the next is issued below.
@@ -413,7 +415,7 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
     for (int b = 0; b < nb; ++b) {
         const int cur = b & 1;
         if (GATHER) cp_async_wait_all();
-        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1))) copy_failed = true;
+        else if (!mbar_wait_bounded(&s_bar[cur], (uint32_t)((b >> 1) & 1), a.hooks.poll_limit)) copy_failed = true;
         // First barrier of the batch: batch b has arrived for everybody and everybody has flushed and zeroed
         // its accumulator row of batch b-1, so the other record buffer may be refilled.  No copy is in flight.
         if (__syncthreads_or(copy_failed)) break;
@@ -570,6 +572,7 @@ int32_t fill_args(const D3gsOpConfig* cfg, RasterArgs& a) {
     a.t_eps = cfg->transmittance_eps;
     a.bg[0] = cfg->bg_color[0]; a.bg[1] = cfg->bg_color[1]; a.bg[2] = cfg->bg_color[2];
     a.training = cfg->training;
+    a.hooks = test_hooks();
     return D3GS_OK;
 }
 

@@ -424,12 +424,12 @@ class GaussianSplatOp:
         if mask is not None:
             mask_u8 = mask.to(torch.uint8).contiguous()
             assert mask_u8.numel() == BN
+        sync = self._sync_words(dev)
         _lib.check(lib.d3gs_preprocess_forward(C.byref(ocfg), C.byref(mstruct), _lib.ptr(mask_u8), C.byref(cstruct),
-                                               stream), "d3gs_preprocess_forward")
+                                               sync.data_ptr() + 8, stream), "d3gs_preprocess_forward")
         self._mark("preprocess_fwd")
         if self.debug_capture:
             self.debug = {"tiles_touched": tiles_touched.clone()}
-        sync = self._sync_words(dev)
         workload_ranges = cursor = None
 
         def scan_tiles_touched():   # cumsum + total (render.py:694-695)

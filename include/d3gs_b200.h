@@ -146,15 +146,23 @@ int32_t d3gs_bit_length(uint32_t n);
 /* Number of kernels this library has launched in the calling process since it was loaded (every entry point
  * counts its own launches; memsets and copies are not counted).  For accounting, e.g. launches per step. */
 uint64_t d3gs_kernel_launch_count(void);
+/* For tests of the error paths (no counterpart in the reference): every bounded wait of the kernels launched by this
+ * process afterwards gives up after poll_limit polls (0 = the built-in limits), and the CTA / tile number `hold` (-1 =
+ * none) withholds what a wait depends on -- its look-back flag in the scan and the sort, the bulk copy its own barrier
+ * expects elsewhere.  The waiting code then sets its D3GS_STATUS_* bit and returns; nothing faults and nothing waits
+ * for ever.  d3gs_test_hooks(0, -1) restores normal operation. */
+void d3gs_test_hooks(uint32_t poll_limit, int32_t hold);
 /* sizeof() of the ABI structs, so a binding can verify its mirror: 0 D3gsCamera, 1 D3gsOpConfig,
  * 2 D3gsModel, 3 D3gsModelGrad, 4 D3gsSplatContext, 5 D3gsAdamSegment, 6 D3gsDensifyStats, 7 D3gsPeerSet,
  * 8 D3gsRefineConfig, 9 D3gsRefineMoments, 10 D3gsPeerViews */
 size_t d3gs_struct_size(int32_t which);
 
 /* ---- K1 preprocess forward (render.py:250-681) ------------------------------------------- */
-/* mask: optional [B*N] bytes, non-zero = skip (render.py:306-309) */
+/* mask: optional [B*N] bytes, non-zero = skip (render.py:306-309).  status: optional device word;
+ * D3GS_STATUS_COPY_TIMEOUT is OR-ed in when the staging copy of a CTA's SH rows did not arrive (the launch's results
+ * are then invalid). */
 int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsModel* model, const uint8_t* mask,
-                                const D3gsSplatContext* ctx, void* stream);
+                                const D3gsSplatContext* ctx, uint32_t* status, void* stream);
 
 /* ---- K2 inclusive scan of tile counts (tiles_touched.cumsum_(0), render.py:694-695) ------ */
 size_t d3gs_scan_workspace_bytes(int64_t n);

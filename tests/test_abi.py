@@ -45,11 +45,11 @@ def test_helpers_and_workspace_queries():
 
 def test_argument_errors_are_reported_not_raised_on_device():
     lib = _lib.load()
-    assert lib.d3gs_preprocess_forward(None, None, None, None, None) == -1
+    assert lib.d3gs_preprocess_forward(None, None, None, None, None, None) == -1
     assert "cfg" in _lib.last_error()
     cfg = _lib.OpConfig()
     cfg.width, cfg.height, cfg.tile_x, cfg.tile_y, cfg.num_views = 64, 64, 8, 8, 1
-    assert lib.d3gs_preprocess_forward(C.byref(cfg), None, None, None, None) == -1
+    assert lib.d3gs_preprocess_forward(C.byref(cfg), None, None, None, None, None) == -1
     assert "16x16" in _lib.last_error()
     in_alt = C.c_int32(0)
     assert lib.d3gs_sort_pairs(None, None, None, None, -5, 0, 45, None, 0, C.byref(in_alt), None, None) == -1
