@@ -44,14 +44,29 @@ def _scan_static(lib, x):
 def test_static_scratch_scan_matches_workspace_scan_twice_in_a_row(cuda_device):
     lib = _lib.load()
     g = torch.Generator().manual_seed(77)
-    # first call: many tiles; second call: fewer tiles and a ragged tail, reusing the same scratch
-    for n in (3_000_017, 70_001):
+    # many tiles; then fewer tiles and a ragged tail, reusing the same scratch; then more tiles again than the call
+    # before cleared
+    for n in (3_000_017, 70_001, 1_500_003):
         x = torch.randint(0, 40, (n,), generator=g, dtype=torch.int32).to(cuda_device)
         ref, ref_total = _scan_with_workspace(lib, x)
         got, got_total = _scan_static(lib, x)
         assert got_total == ref_total == int(x.sum(dtype=torch.int64))
         assert torch.equal(got, ref)       # integer work: bit-exact
         np.testing.assert_array_equal(got[-5:].cpu().numpy(), np.cumsum(x.cpu().numpy().astype(np.int64))[-5:])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_static_scratch_scan_on_a_second_device(cuda_device):
+    """Every GPU that loads the library holds its own copy of the array; its address is looked up per device."""
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(78)
+    x = torch.randint(0, 40, (200_003,), generator=g, dtype=torch.int32)
+    for dev in (torch.device("cuda", 1), torch.device("cuda", 0)):
+        with torch.cuda.device(dev):
+            xd = x.to(dev)
+            ref, ref_total = _scan_with_workspace(lib, xd)
+            got, got_total = _scan_static(lib, xd)
+            assert got_total == ref_total and torch.equal(got, ref)
 
 
 def test_static_scratch_scan_rejects_sizes_beyond_its_capacity(cuda_device):
