@@ -121,8 +121,8 @@ SIGNATURES = {
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
     "d3gs_bucket_sort_capacity": (_I64, []),
-    "d3gs_bucket_prepare": (_I32, [_P, _P, _I64, _P, _P, _P, _P]),
-    "d3gs_bucket_emit": (_I32, [C.POINTER(OpConfig), _I64, C.POINTER(SplatContext), _P, _P, _P]),
+    "d3gs_bucket_prepare": (_I32, [_P, _P, _I64, _P, _P, _P, _I64, _P]),
+    "d3gs_bucket_emit": (_I32, [C.POINTER(OpConfig), _I64, C.POINTER(SplatContext), _P, _P, _P, _I64, _P]),
     "d3gs_bucket_sort": (_I32, [_P, _P, _I64, _I64, _P, _P, _P]),
     "d3gs_tile_ranges": (_I32, [_P, _I64, _P, _I64, _I32, _P]),
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),

@@ -28,15 +28,20 @@ constexpr uint64_t kPadEntry = ~0ull;       // sorts behind every real entry
 
 __global__ void __launch_bounds__(256)
 bucket_prepare_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ incl, int64_t num_tiles,
-                      int32_t* __restrict__ ranges, int32_t* __restrict__ cursor, int64_t* __restrict__ max_count) {
+                      int32_t* __restrict__ ranges, int32_t* __restrict__ cursor, int64_t* __restrict__ max_count,
+                      int64_t pair_capacity) {
     const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    // A caller that sized the pair buffers before it knew the pair count (from the previous launch) passes their
+    // capacity: when the pairs do not fit, every range is left empty, so that the kernels already queued behind
+    // this one touch nothing, and the caller, who reads the count afterwards, repeats the launch with larger buffers.
+    const bool fits = pair_capacity <= 0 || (int64_t)incl[num_tiles - 1] <= pair_capacity;
     int c = 0;
     if (t < num_tiles) {
         c = counts[t];
         const int end = incl[t], start = end - c;
         // render.py:897: the reference zero-fills the ranges and writes only the tiles that own pairs
-        ranges[t * 2] = c > 0 ? start : 0;
-        ranges[t * 2 + 1] = c > 0 ? end : 0;
+        ranges[t * 2] = c > 0 && fits ? start : 0;
+        ranges[t * 2 + 1] = c > 0 && fits ? end : 0;
         cursor[t] = start;
     }
 #pragma unroll
@@ -55,13 +60,20 @@ __device__ __forceinline__ void cswap(uint64_t& a, uint64_t& b) {
 template <int NT, int VT>
 __global__ void __launch_bounds__(NT)
 tile_sort_kernel(const uint64_t* __restrict__ entries, const int32_t* __restrict__ ranges, int32_t* __restrict__ sorted_values,
-                 uint64_t* __restrict__ sorted_keys, int lo, int hi) {
+                 uint64_t* __restrict__ sorted_keys, int lo, int hi, int pass_longer) {
     extern __shared__ __align__(16) uint64_t s_e[];
     const int tile = blockIdx.x;
     const int r0 = ranges[tile * 2];
     const int n = ranges[tile * 2 + 1] - r0;
-    if (n <= lo || n > hi) return;     // another instance (or nobody, n == 0) handles this tile
     const int t = threadIdx.x;
+    if (n > hi && pass_longer) {
+        // The largest instance launched, and this list is longer than the caller expected when it chose the
+        // instances: hand the indices on in emission order, so that whatever is queued behind reads valid indices;
+        // the caller sees the true length afterwards and repeats the sort.
+        for (int p = t; p < n; p += NT) sorted_values[r0 + p] = (int32_t)(uint32_t)entries[r0 + p];
+        return;
+    }
+    if (n <= lo || n > hi) return;     // another instance (or nobody, n == 0) handles this tile
     auto slot = [](int p) { return p + p / VT; };
 #pragma unroll
     for (int k = 0; k < VT; ++k) {
@@ -128,11 +140,12 @@ tile_sort_kernel(const uint64_t* __restrict__ entries, const int32_t* __restrict
 
 template <int NT, int VT>
 int32_t launch_sort(const uint64_t* entries, const int32_t* ranges, int64_t num_tiles, int32_t* sorted_values,
-                    uint64_t* sorted_keys, int lo, int hi, cudaStream_t s) {
+                    uint64_t* sorted_keys, int lo, int hi, bool pass_longer, cudaStream_t s) {
     const size_t smem = (size_t)(NT * VT + NT) * sizeof(uint64_t);
     if (smem > 48 * 1024)
         D3GS_CUDA(cudaFuncSetAttribute(tile_sort_kernel<NT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tile_sort_kernel<NT, VT><<<(unsigned)num_tiles, NT, smem, s>>>(entries, ranges, sorted_values, sorted_keys, lo, hi);
+    tile_sort_kernel<NT, VT><<<(unsigned)num_tiles, NT, smem, s>>>(entries, ranges, sorted_values, sorted_keys, lo, hi,
+                                                                   pass_longer ? 1 : 0);
     D3GS_LAUNCH_CHECK("tile_sort_kernel");
     return D3GS_OK;
 }
@@ -145,7 +158,8 @@ using namespace d3gs;
 extern "C" int64_t d3gs_bucket_sort_capacity(void) { return kSortCapacity; }
 
 extern "C" int32_t d3gs_bucket_prepare(const int32_t* tile_counts, const int32_t* tile_scan, int64_t num_tiles,
-                                       int32_t* ranges, int32_t* cursor, int64_t* max_count, void* stream) {
+                                       int32_t* ranges, int32_t* cursor, int64_t* max_count, int64_t pair_capacity,
+                                       void* stream) {
     D3GS_REQUIRE(num_tiles >= 0 && num_tiles < ((int64_t)1 << 31), "tile count out of range");
     D3GS_REQUIRE(max_count != nullptr, "max_count is NULL");
     cudaStream_t s = (cudaStream_t)stream;
@@ -153,7 +167,7 @@ extern "C" int32_t d3gs_bucket_prepare(const int32_t* tile_counts, const int32_t
     if (num_tiles == 0) return D3GS_OK;
     D3GS_REQUIRE(tile_counts && tile_scan && ranges && cursor, "NULL argument");
     bucket_prepare_kernel<<<(unsigned)div_up64(num_tiles, 256), 256, 0, s>>>(tile_counts, tile_scan, num_tiles, ranges,
-                                                                            cursor, max_count);
+                                                                            cursor, max_count, pair_capacity);
     D3GS_LAUNCH_CHECK("bucket_prepare_kernel");
     return D3GS_OK;
 }
@@ -172,14 +186,15 @@ extern "C" int32_t d3gs_bucket_sort(const uint64_t* entries, const int32_t* rang
     D3GS_REQUIRE(entries && ranges && sorted_values, "NULL argument");
     cudaStream_t s = (cudaStream_t)stream;
     // three instances by list length; an instance is launched only when some list can fall into its class
-    int32_t rc = launch_sort<128, 4>(entries, ranges, num_tiles, sorted_values, sorted_keys, 0, 512, s);
+    // (the largest one launched also passes through, unsorted, any list longer than max_count promised)
+    int32_t rc = launch_sort<128, 4>(entries, ranges, num_tiles, sorted_values, sorted_keys, 0, 512, max_count <= 512, s);
     if (rc != D3GS_OK) return rc;
     if (max_count > 512) {
-        rc = launch_sort<256, 8>(entries, ranges, num_tiles, sorted_values, sorted_keys, 512, 2048, s);
+        rc = launch_sort<256, 8>(entries, ranges, num_tiles, sorted_values, sorted_keys, 512, 2048, max_count <= 2048, s);
         if (rc != D3GS_OK) return rc;
     }
     if (max_count > 2048) {
-        rc = launch_sort<1024, 16>(entries, ranges, num_tiles, sorted_values, sorted_keys, 2048, kSortCapacity, s);
+        rc = launch_sort<1024, 16>(entries, ranges, num_tiles, sorted_values, sorted_keys, 2048, kSortCapacity, true, s);
         if (rc != D3GS_OK) return rc;
     }
     return D3GS_OK;

@@ -501,6 +501,8 @@ struct DupArgs {
     int32_t* cursor;      // BUCKET: next free position of every tile's range
     uint64_t* entries;    // BUCKET: depth bits << 32 | flat index, one per pair, in the tile's range
     int64_t num;
+    const int64_t* total_pairs;   // BUCKET, optional: the pair count on the device, checked against pair_capacity
+    int64_t pair_capacity;
 };
 
 // BUCKET == false: key = tile << shift | depth bits and value = flat index at the Gaussian's scanned offset
@@ -508,6 +510,8 @@ struct DupArgs {
 // position drawn from the tile's cursor inside the tile's range.
 template <bool BUCKET>
 __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_constant__ DupArgs a) {
+    // entries sized before the pair count was known: write nothing when the pairs do not fit (the caller repeats)
+    if (BUCKET && a.total_pairs != nullptr && *a.total_pairs > a.pair_capacity) return;
     const int64_t total = a.num * a.cfg.num_views;
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     const D3gsOpConfig& cf = a.cfg;
@@ -726,7 +730,7 @@ extern "C" int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, con
 }
 
 extern "C" int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const D3gsSplatContext* ctx, int32_t* cursor,
-                                    uint64_t* entries, void* stream) {
+                                    uint64_t* entries, const int64_t* total_pairs, int64_t pair_capacity, void* stream) {
     int32_t rc = check_cfg(cfg);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(cfg->key_shift_bits == 0 || cfg->key_shift_bits == 32,
@@ -744,6 +748,8 @@ extern "C" int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const 
     a.cursor = cursor;
     a.entries = entries;
     a.num = num;
+    a.total_pairs = pair_capacity > 0 ? total_pairs : nullptr;
+    a.pair_capacity = pair_capacity;
     duplicate_keys_kernel<true><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("duplicate_keys_kernel<bucket>");
     return D3GS_OK;

@@ -144,6 +144,11 @@ def _camera_rows(cameras: BasicPinholeCamera | CameraBundle) -> np.ndarray:
     return cameras.host_params()
 
 
+def _sort_class(longest: int) -> int:
+    """Which instance of the tile sort a list of this length needs (d3gs_bucket_sort: <= 512, <= 2048, larger)."""
+    return 0 if longest <= 512 else (1 if longest <= 2048 else 2)
+
+
 def _pair_capacity(n: int) -> int:
     """Allocation size for a buffer of n (tile, splat) pairs: n + n/8, rounded up to a multiple of 2^20."""
     q = 1 << 20
@@ -240,6 +245,16 @@ class GaussianSplatOp:
         # not fit one CTA's shared memory, and is not used with 32-bit sort keys.
         self.binning = "bucket"
         self.last_binning = ""
+        # Bucket binning only.  True: from the second launch of a shape on, the pair buffers are sized from the
+        # previous launch's pair count (+ 12.5 %, quantised), the binning and raster kernels are queued at once and
+        # check the count on the device, and the host reads the count (one copy on a side stream, as the reference's
+        # one read per forward) while they run; a launch whose count outgrew the buffers, or whose longest list
+        # outgrew the sort classes that were launched, is repeated with the true sizes (``launches_repeated``).
+        # False: the host waits for the count before it launches, like the reference (render.py:695).
+        self.launch_ahead = True
+        self.launches_repeated = 0
+        self._ahead: dict = {}
+        self._readback: dict = {}
         # Optional caller-owned tensors for what a later stage on ANOTHER GPU reads (data-parallel training with
         # the backward fused into the exchange): keys "radii" [N] int32, "cov2d_vecs" [N,3], "sh_to_rgb_ne_0" [N]
         # uint8 (written by forward) and "packed" [N,12] (written by the raster backward); single-view launches.
@@ -268,6 +283,26 @@ class GaussianSplatOp:
             t = torch.zeros(4, dtype=torch.int64, device=device)
             self._sync[device] = t
         return t
+
+    def _read_sync_words_async(self, dev, sync):
+        """Copy the four sync words to pinned host memory on a side stream, ordered after what the current stream
+        has queued so far.  Returns a function that waits for that copy alone and returns the words."""
+        rb = self._readback.get(dev)
+        if rb is None:
+            rb = (torch.empty(4, dtype=torch.int64).pin_memory(), torch.cuda.Stream(dev), torch.cuda.Event(),
+                  torch.cuda.Event())
+            self._readback[dev] = rb
+        host, side, ready, done = rb
+        ready.record(torch.cuda.current_stream(dev))
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            host.copy_(sync, non_blocking=True)
+            done.record(side)
+
+        def wait():
+            done.synchronize()
+            return tuple(int(v) for v in host.tolist())
+        return wait
 
     def check_status(self, device=None) -> None:
         """Read the device status word (one 8-byte copy), clear it and raise if a bounded wait of any kernel
@@ -431,12 +466,50 @@ class GaussianSplatOp:
         if self.debug_capture:
             self.debug = {"tiles_touched": tiles_touched.clone()}
         workload_ranges = cursor = None
+        final_T = torch.empty([B, H, W], dtype=f32, device=dev)
+        n_contrib = torch.empty([B, H, W], dtype=i32, device=dev)
+        out_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
 
         def scan_tiles_touched():   # cumsum + total (render.py:694-695)
             ws = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(BN), dev)
             _lib.check(lib.d3gs_scan_tiles(tiles_touched.data_ptr(), tiles_touched.data_ptr(), BN, sync.data_ptr(),
                                            ws.data_ptr(), ws.numel(), sync.data_ptr() + 8, stream), "d3gs_scan_tiles")
 
+        def bucket_prepare(pair_capacity):
+            _lib.check(lib.d3gs_bucket_prepare(tile_counts.data_ptr(), tile_scan.data_ptr(), num_tiles,
+                                               workload_ranges.data_ptr(), cursor.data_ptr(), sync.data_ptr() + 16,
+                                               pair_capacity, stream), "d3gs_bucket_prepare")
+
+        def bucket_lists(cap, sort_max, checked):
+            """Entries -> sorted lists for pair buffers of ``cap`` entries; ``checked``: the kernels compare the pair
+            count on the device with ``cap`` (the host has not read it yet)."""
+            entries = torch.empty(cap, dtype=torch.int64, device=dev)
+            ids = torch.empty(cap, dtype=i32, device=dev)
+            keys = torch.empty(cap, dtype=torch.int64, device=dev) if self.debug_capture else None
+            _lib.check(lib.d3gs_bucket_emit(C.byref(ocfg), num, C.byref(cstruct), cursor.data_ptr(), entries.data_ptr(),
+                                            sync.data_ptr() if checked else None, cap if checked else 0, stream),
+                       "d3gs_bucket_emit")
+            self._mark("duplicate_keys")
+            _lib.check(lib.d3gs_bucket_sort(entries.data_ptr(), workload_ranges.data_ptr(), num_tiles, sort_max,
+                                            ids.data_ptr(), _lib.ptr(keys), stream), "d3gs_bucket_sort")
+            self._mark("sort")
+            return ids, keys
+
+        def raster(ids):
+            tile_order = torch.empty(num_tiles, dtype=i32, device=dev)
+            _lib.check(lib.d3gs_tile_order(workload_ranges.data_ptr(), num_tiles, tile_order.data_ptr(), stream),
+                       "d3gs_tile_order")
+            self._mark("tile_order")
+            _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), tile_order.data_ptr(),
+                                               records.data_ptr(), ids.data_ptr() if gather else None,
+                                               out_color.data_ptr(), final_T.data_ptr(),
+                                               n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
+            self._mark("raster_fwd")
+            return tile_order
+
+        gaussian_idx_sorted = tile_order = keys = None
+        ahead = None
+        sort_capacity = lib.d3gs_bucket_sort_capacity()
         if use_bucket:
             # the pair count is the total of the per-tile counts; their scan is every tile's range
             tile_scan = torch.empty(num_tiles, dtype=i32, device=dev)
@@ -445,14 +518,21 @@ class GaussianSplatOp:
                                            ws.data_ptr(), ws.numel(), sync.data_ptr() + 8, stream), "d3gs_scan_tiles")
             workload_ranges = torch.empty([num_tiles, 2], dtype=i32, device=dev)
             cursor = torch.empty(num_tiles, dtype=i32, device=dev)
-            _lib.check(lib.d3gs_bucket_prepare(tile_counts.data_ptr(), tile_scan.data_ptr(), num_tiles,
-                                               workload_ranges.data_ptr(), cursor.data_ptr(), sync.data_ptr() + 16,
-                                               stream), "d3gs_bucket_prepare")
+            # Launch ahead of the read-back: buffers sized from the previous launch of the same shape, the kernels
+            # check the count themselves, and the host reads the count while they run (and repeats if it was wrong).
+            ahead = self._ahead.get((dev, B, num, num_tiles)) if (self.launch_ahead and gather) else None
+            bucket_prepare(ahead[0] if ahead else 0)
         else:
             scan_tiles_touched()
         self._mark("scan")
-        # one device->host read per forward, as in the reference (render.py:695)
-        num_rendered, status, longest, _ = (int(v) for v in sync.tolist())
+        if ahead:
+            words = self._read_sync_words_async(dev, sync)
+            gaussian_idx_sorted, keys = bucket_lists(ahead[0], ahead[1], checked=True)
+            tile_order = raster(gaussian_idx_sorted)
+            num_rendered, status, longest, _ = words()
+        else:
+            # one device->host read per forward, as in the reference (render.py:695)
+            num_rendered, status, longest, _ = (int(v) for v in sync.tolist())
         self._mark("host_readback_idle")
         if status != 0:
             sync[1] = 0
@@ -461,14 +541,13 @@ class GaussianSplatOp:
         if num_rendered >= 2 ** 31:
             raise RuntimeError(f"num_rendered {num_rendered} does not fit the int32 offsets")
         self.last_num_rendered = num_rendered
-        final_T = torch.empty([B, H, W], dtype=f32, device=dev)
-        n_contrib = torch.empty([B, H, W], dtype=i32, device=dev)
-        out_color = torch.empty([B, H, W, 3], dtype=f32, device=dev)
         if num_rendered == 0:   # render.py:706-729: outputs are left uninitialised, no context
             return GaussianSplatOutput(custom_features=None, T=final_T, color=self._format_color(out_color, final_T),
                                        depth=None, n_contrib=n_contrib), None
-        if use_bucket and longest > lib.d3gs_bucket_sort_capacity():
+        if use_bucket and longest > sort_capacity:
             use_bucket = False          # a list too long for one CTA's shared memory: radix-sort path for this launch
+            self.launches_repeated += bool(ahead)
+            ahead = None
             scan_tiles_touched()
         self.last_binning = "bucket" if use_bucket else "sort"
         # Pair-sized buffers are allocated with a capacity quantised to 2^20 pairs above 1.125 x the count: the
@@ -476,17 +555,19 @@ class GaussianSplatOp:
         # and fall back to cudaMalloc (a device-wide stall of milliseconds) every few steps.
         cap = _pair_capacity(num_rendered)
         if use_bucket:
-            entries = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
-            gaussian_idx_sorted = torch.empty(cap, dtype=i32, device=dev)[:num_rendered]
-            keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered] if self.debug_capture else None
-            _lib.check(lib.d3gs_bucket_emit(C.byref(ocfg), num, C.byref(cstruct), cursor.data_ptr(), entries.data_ptr(),
-                                            stream), "d3gs_bucket_emit")
-            self._mark("duplicate_keys")
-            _lib.check(lib.d3gs_bucket_sort(entries.data_ptr(), workload_ranges.data_ptr(), num_tiles, longest,
-                                            gaussian_idx_sorted.data_ptr(), _lib.ptr(keys), stream), "d3gs_bucket_sort")
-            self._mark("sort")
+            # classes of the tile sort to launch next time: those the longest list of this launch, grown by a
+            # quarter, falls into
+            self._ahead[(dev, B, num, num_tiles)] = (cap, min(sort_capacity, longest + longest // 4))
+            if ahead and (num_rendered > ahead[0] or _sort_class(longest) > _sort_class(ahead[1])):
+                self.launches_repeated += 1
+                bucket_prepare(0)       # the guess was too small: ranges and cursors again, then the chain below
+                ahead = None
+            if not ahead:
+                gaussian_idx_sorted, keys = bucket_lists(cap, longest, checked=False)
+            gaussian_idx_sorted = gaussian_idx_sorted[:num_rendered]
             if self.debug_capture:
-                self.debug.update(sorted_keys=keys, sorted_values=gaussian_idx_sorted, ranges=workload_ranges)
+                self.debug.update(sorted_keys=keys[:num_rendered], sorted_values=gaussian_idx_sorted,
+                                  ranges=workload_ranges)
         else:
             keys = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
             keys_alt = torch.empty(cap, dtype=torch.int64, device=dev)[:num_rendered]
@@ -523,16 +604,8 @@ class GaussianSplatOp:
                                             float(self._cfg.alpha_eps), records.data_ptr(), stream),
                        "d3gs_pack_splats")
             self._mark("pack_splats")
-        tile_order = torch.empty(num_tiles, dtype=i32, device=dev)
-        _lib.check(lib.d3gs_tile_order(workload_ranges.data_ptr(), num_tiles, tile_order.data_ptr(), stream),
-                   "d3gs_tile_order")
-        self._mark("tile_order")
-        _lib.check(lib.d3gs_raster_forward(C.byref(ocfg), workload_ranges.data_ptr(), tile_order.data_ptr(),
-                                           records.data_ptr(),
-                                           gaussian_idx_sorted.data_ptr() if gather else None,
-                                           out_color.data_ptr(), final_T.data_ptr(),
-                                           n_contrib.data_ptr(), sync.data_ptr() + 8, stream), "d3gs_raster_forward")
-        self._mark("raster_fwd")
+        if not ahead:
+            tile_order = raster(gaussian_idx_sorted)
         # render.py:1824, 1920-1923, 2244-2270: the depth value and the custom features are blended exactly like
         # colour channels (accum += weight * value, never composited or clamped).  Each group of three channels
         # is one more forward pass over the same lists with the values in the records' colour slots.

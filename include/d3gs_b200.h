@@ -218,10 +218,18 @@ int32_t d3gs_tile_ranges(const uint64_t* sorted_keys, int64_t n, int32_t* ranges
  * pairs emitted in index order).  d3gs_bucket_sort returns D3GS_ERR_UNSUPPORTED when max_count exceeds
  * d3gs_bucket_sort_capacity() (16384): take the radix-sort path for that launch.  64-bit sort keys only. */
 int64_t d3gs_bucket_sort_capacity(void);
+/* Launching without waiting for the counts: a caller that sizes entries / sorted_values from the PREVIOUS launch
+ * passes that size as pair_capacity (> 0) to prepare and emit, and total_pairs = the device word d3gs_scan_tiles
+ * wrote.  If the pairs do not fit, prepare leaves every range {0,0} and emit writes nothing, so the sort and the
+ * raster kernels queued behind them touch no pair; the caller reads total and max_count when it likes and repeats
+ * the chain with larger buffers.  A list longer than the classes d3gs_bucket_sort launched for its max_count
+ * argument has its indices passed through in emission order (valid, unsorted): the caller compares the true
+ * max_count with the one it passed and repeats.
+ * pair_capacity 0 (and total_pairs NULL) = sizes are exact, no check. */
 int32_t d3gs_bucket_prepare(const int32_t* tile_counts, const int32_t* tile_scan, int64_t num_tiles, int32_t* ranges,
-                            int32_t* cursor, int64_t* max_count, void* stream);
+                            int32_t* cursor, int64_t* max_count, int64_t pair_capacity, void* stream);
 int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const D3gsSplatContext* ctx, int32_t* cursor,
-                         uint64_t* entries, void* stream);
+                         uint64_t* entries, const int64_t* total_pairs, int64_t pair_capacity, void* stream);
 int32_t d3gs_bucket_sort(const uint64_t* entries, const int32_t* ranges, int64_t num_tiles, int64_t max_count,
                          int32_t* sorted_values, uint64_t* sorted_keys, void* stream);
 

@@ -489,12 +489,21 @@ def test_bucket_sort_every_list_length(cuda_device):
     cursor = torch.empty(len(lengths), dtype=torch.int32, device=dev)
     maxc = torch.zeros(1, dtype=torch.int64, device=dev)
     _lib.check(lib.d3gs_bucket_prepare(d_counts.data_ptr(), d_incl.data_ptr(), len(lengths), ranges.data_ptr(),
-                                       cursor.data_ptr(), maxc.data_ptr(), st), "prepare")
+                                       cursor.data_ptr(), maxc.data_ptr(), 0, st), "prepare")
     assert int(maxc.item()) == cap
     start = incl - counts
     exp_ranges = np.stack([np.where(counts > 0, start, 0), np.where(counts > 0, incl, 0)], axis=1).astype(np.int32)
     np.testing.assert_array_equal(ranges.cpu().numpy(), exp_ranges)
     np.testing.assert_array_equal(cursor.cpu().numpy(), start)
+    # pair buffers sized before the count was known and too small: every range is left empty, the longest list is
+    # still reported; a capacity that holds the pairs changes nothing
+    r2 = torch.full_like(ranges, -1)
+    _lib.check(lib.d3gs_bucket_prepare(d_counts.data_ptr(), d_incl.data_ptr(), len(lengths), r2.data_ptr(),
+                                       cursor.data_ptr(), maxc.data_ptr(), total - 1, st), "prepare (too small)")
+    assert int(maxc.item()) == cap and int(r2.abs().sum().item()) == 0
+    _lib.check(lib.d3gs_bucket_prepare(d_counts.data_ptr(), d_incl.data_ptr(), len(lengths), r2.data_ptr(),
+                                       cursor.data_ptr(), maxc.data_ptr(), total, st), "prepare (fits)")
+    np.testing.assert_array_equal(r2.cpu().numpy(), exp_ranges)
     d_entries = torch.from_numpy(entries.view(np.int64)).to(dev)
     vals = torch.full((total,), -1, dtype=torch.int32, device=dev)
     keys = torch.zeros(total, dtype=torch.int64, device=dev)
@@ -526,6 +535,53 @@ def test_bucket_binning_falls_back_on_long_lists(cuda_device):
     np.testing.assert_array_equal(op.debug["sorted_values"].cpu().numpy(), ref.sorted_ids)
     np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
     np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+
+
+def test_launch_ahead_binning_matches_and_repeats(cuda_device):
+    """From the second launch of a shape on, the bucket path queues binning and rasterisation before the host has
+    read the pair count.  Same lists, ranges and image as the first (waited-for) launch and the oracle -- also when
+    the guess was wrong: buffers too small for the pairs, the tile-sort class of the longest list not launched, and
+    a longest list beyond the sort capacity (radix path)."""
+    # dense enough that some tile list is longer than 512 entries (second sort class)
+    sc = small_scene(n=30000, width=200, height=136, sh_degree=1, seed=9, log_scale=("normal", -2.6, 0.3))
+    op, model, cams, out, ctx, ocfg, osc, ref = _run_forward(sc, cuda_device, EarlyFilterAlgo.OBB_DFVT, binning="bucket")
+    longest = int((ref.ranges[:, 1] - ref.ranges[:, 0]).max())
+    assert 512 < longest <= _lib.load().d3gs_bucket_sort_capacity(), longest
+    (key, guess), = op._ahead.items()
+    assert guess[0] >= ref.num_rendered and guess[1] >= longest
+
+    def same(tag, repeated):
+        o, c = op.forward(model, cams, training=True)
+        torch.cuda.synchronize()
+        assert op.last_binning == "bucket" and op.launches_repeated == repeated, (tag, op.launches_repeated)
+        assert op.last_num_rendered == ref.num_rendered
+        np.testing.assert_array_equal(c.gaussian_idx_sorted.cpu().numpy(), ref.sorted_ids, err_msg=tag)
+        np.testing.assert_array_equal(op.debug["sorted_keys"].cpu().numpy(), ref.sorted_keys.view(np.int64), err_msg=tag)
+        np.testing.assert_array_equal(c.workload_ranges.cpu().numpy(), ref.ranges, err_msg=tag)
+        np.testing.assert_array_equal(o.n_contrib.cpu().numpy(), ref.n_contrib, err_msg=tag)
+        assert torch.equal(o.color, out.color) and torch.equal(o.T, out.T), tag
+
+    same("guess holds", 0)
+    op._ahead[key] = (1024, guess[1])          # fewer entries than pairs: nothing written, launch repeated
+    assert ref.num_rendered > 1024
+    same("pair buffers too small", 1)
+    op._ahead[key] = (guess[0], 100)           # only the first sort class launched: long lists left unsorted, repeated
+    same("sort class missing", 2)
+    same("guess holds again", 2)
+    op.launch_ahead = False
+    same("waited for", 2)
+    # a list beyond the sort capacity, met by a launch that ran ahead: the radix path takes over
+    sc2 = small_scene(n=40000, width=64, height=48, sh_degree=0, seed=41, pos=("uniform", 0.4), log_scale=("normal", -3.0, 0.3))
+    op2, model2, cams2, out2, ctx2, _, _, ref2 = _run_forward(sc2, cuda_device, EarlyFilterAlgo.OBB_DFVT, binning="bucket")
+    assert op2.last_binning == "sort" and not op2._ahead
+    tiles = ref2.ranges.shape[0]
+    op2._ahead[(model2.xyz.device, 1, 40000, tiles)] = (1 << 21, 16384)
+    o2, c2 = op2.forward(model2, cams2, training=True)
+    torch.cuda.synchronize()
+    assert op2.last_binning == "sort" and op2.launches_repeated == 1
+    np.testing.assert_array_equal(c2.gaussian_idx_sorted.cpu().numpy(), ref2.sorted_ids)
+    np.testing.assert_array_equal(o2.n_contrib.cpu().numpy(), ref2.n_contrib)
+    assert torch.equal(o2.color, out2.color)
 
 
 @pytest.mark.parametrize("shape", [(1, 40, 56), (2, 97, 130), (1, 16, 16), (1, 5, 7)])
