@@ -31,7 +31,9 @@ class OpConfig(C.Structure):
                 ("sh_degree", C.c_int32), ("training", C.c_int32), ("clamp_mask_reference_order", C.c_int32),
                 ("fused_activations", C.c_int32),
                 ("bg_color", C.c_float * 3), ("key_shift_bits", C.c_int32), ("depth_32bit_prec", C.c_float), ("anti_aliasing", C.c_int32), ("inv_depth", C.c_int32),
-                ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS)]
+                ("num_views", C.c_int32), ("cameras", Camera * MAX_VIEWS),
+                ("instance_id", C.c_void_p), ("instance2world_T", C.c_void_p), ("num_instance", C.c_int32),
+                ("frame_ids", C.c_int32 * MAX_VIEWS), ("reserved_", C.c_int32)]
 
 
 class Model(C.Structure):
@@ -121,6 +123,8 @@ SIGNATURES = {
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
     "d3gs_bucket_sort_capacity": (_I64, []),
+    "d3gs_simple_knn_workspace_bytes": (C.c_size_t, [_I64, _I32]),
+    "d3gs_simple_knn": (_I32, [_P, _I64, _I64, _I32, _I32, _P, _P, _P, _P, C.c_size_t, _P, _P]),
     "d3gs_bucket_prepare": (_I32, [_P, _P, _I64, _P, _P, _P, _I64, _P]),
     "d3gs_bucket_emit": (_I32, [C.POINTER(OpConfig), _I64, C.POINTER(SplatContext), _P, _P, _P, _I64, _P]),
     "d3gs_bucket_sort": (_I32, [_P, _P, _I64, _I64, _P, _P, _P]),
@@ -128,7 +132,7 @@ SIGNATURES = {
     "d3gs_pack_splats": (_I32, [_P, _I64, C.POINTER(SplatContext), _F, _P, _P]),
     "d3gs_tile_order": (_I32, [_P, _I64, _P, _P]),
     "d3gs_raster_forward": (_I32, [C.POINTER(OpConfig), _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_raster_backward": (_I32, [C.POINTER(OpConfig), _I64, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "d3gs_preprocess_backward": (_I32, [C.POINTER(OpConfig), C.POINTER(Model), C.POINTER(SplatContext), _P,
                                         C.POINTER(ModelGrad), _P, _P]),
     "d3gs_ssim_forward": (_I32, [_P, _P, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P]),

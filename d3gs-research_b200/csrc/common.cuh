@@ -63,6 +63,31 @@ __device__ __forceinline__ float f_fma(float a, float b, float c) { return __fma
 __device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ float f_sqrt(float a) { return __fsqrt_rn(a); }
 
+// Instance rendering (render.py:346-354): the camera of view b in the frame of Gaussian g's object instance,
+// out[k*3 + j] = k-th column of the camera-to-instance rotation, out[9..11] = the camera centre in that frame.
+// cam2instance = inverse(instance2world) @ cam2world with the rigid inverse: R = Ri^T Rc, c = Ri^T (cc - ti); a
+// [4,3] transform T holds Ri^T in rows 0-2 (T[j*3 + m] = Ri[m][j]) and ti in row 3.  Returns false (out untouched)
+// for a Gaussian that belongs to no instance.
+__device__ __forceinline__ bool instance_camera(const D3gsOpConfig& cf, int b, int64_t g, float* out) {
+    const int inst = cf.instance_id[g];
+    if (inst < 0) return false;
+    const float* T = cf.instance2world_T + ((int64_t)cf.frame_ids[b] * cf.num_instance + inst) * 12;
+    const float* Rc = cf.cameras[b].cam2world_T;
+    float t[12];
+#pragma unroll
+    for (int k = 0; k < 12; ++k) t[k] = T[k];
+    const float dc0 = f_sub(Rc[9], t[9]), dc1 = f_sub(Rc[10], t[10]), dc2 = f_sub(Rc[11], t[11]);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+            out[k * 3 + j] = f_add(f_add(f_mul(t[j * 3], Rc[k * 3]), f_mul(t[j * 3 + 1], Rc[k * 3 + 1])),
+                                   f_mul(t[j * 3 + 2], Rc[k * 3 + 2]));
+        out[9 + j] = f_add(f_add(f_mul(t[j * 3], dc0), f_mul(t[j * 3 + 1], dc1)), f_mul(t[j * 3 + 2], dc2));
+    }
+    return true;
+}
+
 // exp(x) of the fused "exponential"/"sigmoid" activations (origin/model.py:453-462): Cephes-style
 // reduction, degree-5 polynomial.
 __device__ __forceinline__ float act_exp(float x) {

@@ -214,8 +214,9 @@ constexpr int kRow = 45;   // shared-memory row length in floats (odd: conflict-
 // loads and evaluated per thread from there: per-thread global loads with a 180-byte stride cost ~22
 // sectors per request.
 // 64 registers (4 CTAs of 256 threads per SM): with 78 the kernel lost a fifth of its throughput
-template <int DEG>
-__global__ void __launch_bounds__(256, 4) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+// INST: instance rendering, a per-Gaussian camera (12 more live registers; an instantiation of its own)
+template <int DEG, bool INST>
+__global__ void __launch_bounds__(256, INST ? 3 : 4) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
     constexpr int NB = (DEG + 1) * (DEG + 1);
     constexpr int NR3 = (NB - 1) * 3;
     __shared__ __align__(128) float s_rest[NR3 > 0 ? 256 * kRow : 4];
@@ -257,6 +258,10 @@ __global__ void __launch_bounds__(256, 4) preprocess_fwd_kernel(const __grid_con
         g = i - (int64_t)b * N;
         const D3gsCamera& cam = cf.cameras[b];
         const float* Rt = cam.cam2world_T;   // Rt[k*3 + j]: k-th column of R_c2w
+        float Ri[12];
+        if constexpr (INST) {
+            if (instance_camera(cf, b, g, Ri)) Rt = Ri;
+        }
         TileGeom tg;
         tg.tiles_x = (cf.width + cf.tile_x - 1) / cf.tile_x;
         tg.tiles_y = (cf.height + cf.tile_y - 1) / cf.tile_y;
@@ -698,11 +703,21 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
     a.status = status;
     a.hooks = test_hooks();
     dim3 grid((unsigned)div_up64(total, 256));
-    switch (cfg->sh_degree) {
-        case 0: preprocess_fwd_kernel<0><<<grid, 256, 0, s>>>(a); break;
-        case 1: preprocess_fwd_kernel<1><<<grid, 256, 0, s>>>(a); break;
-        case 2: preprocess_fwd_kernel<2><<<grid, 256, 0, s>>>(a); break;
-        default: preprocess_fwd_kernel<3><<<grid, 256, 0, s>>>(a); break;
+    if (cfg->instance_id != nullptr) {
+        D3GS_REQUIRE(cfg->instance2world_T != nullptr && cfg->num_instance > 0, "instance rendering needs instance2world_T");
+        switch (cfg->sh_degree) {
+            case 0: preprocess_fwd_kernel<0, true><<<grid, 256, 0, s>>>(a); break;
+            case 1: preprocess_fwd_kernel<1, true><<<grid, 256, 0, s>>>(a); break;
+            case 2: preprocess_fwd_kernel<2, true><<<grid, 256, 0, s>>>(a); break;
+            default: preprocess_fwd_kernel<3, true><<<grid, 256, 0, s>>>(a); break;
+        }
+    } else {
+        switch (cfg->sh_degree) {
+            case 0: preprocess_fwd_kernel<0, false><<<grid, 256, 0, s>>>(a); break;
+            case 1: preprocess_fwd_kernel<1, false><<<grid, 256, 0, s>>>(a); break;
+            case 2: preprocess_fwd_kernel<2, false><<<grid, 256, 0, s>>>(a); break;
+            default: preprocess_fwd_kernel<3, false><<<grid, 256, 0, s>>>(a); break;
+        }
     }
     D3GS_LAUNCH_CHECK("preprocess_fwd_kernel");
     return D3GS_OK;

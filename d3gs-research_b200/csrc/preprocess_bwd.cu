@@ -65,7 +65,7 @@ __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.457045
 //
 // One tile of 256 Gaussians starting at Gaussian g0.  Returns false when the CTA must stop (a staging copy never
 // arrived).  `phase`: parity of the staging barrier, toggled per staged tile.
-template <int DEG, bool MULTI, bool ADAM, bool PEER>
+template <int DEG, bool MULTI, bool ADAM, bool PEER, bool INST = false>
 __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t* s_vis, uint64_t& s_bar, uint32_t& phase,
                                          const int64_t tile) {
     float* s_in = smem;
@@ -190,6 +190,10 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             if (rad_b == 0) continue;
             const D3gsCamera& cam = cf.cameras[b];
             const float* Rt = cam.cam2world_T;
+            float Ri[12];
+            if constexpr (INST) {     // instance rendering: this Gaussian's camera in its object's frame
+                if (instance_camera(cf, b, g, Ri)) Rt = Ri;
+            }
             const float4* sg4 = reinterpret_cast<const float4*>(a.v_grads[b] + g * D3GS_SPLAT_GRAD_FLOATS);
             const float4 gA = sg4[0], gB = sg4[1], gC = sg4[2];
             const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
@@ -506,7 +510,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
 // stores the new parameters into EVERY rank's parameter buffer.  The 236-byte-per-Gaussian parameter gradient
 // never exists: what crosses the links is the rasteriser's 48 bytes per (view, Gaussian) plus 17 bytes of
 // context inbound, and the parameters outbound.  The launches of the ranks are ordered by flags (exchange.cuh).
-template <int DEG, bool MULTI, bool ADAM, bool PEER = false>
+template <int DEG, bool MULTI, bool ADAM, bool PEER = false, bool INST = false>
 __global__ void __launch_bounds__(256, PEER ? 2 : 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint8_t s_vis[256];
@@ -530,7 +534,7 @@ __global__ void __launch_bounds__(256, PEER ? 2 : 3) preprocess_bwd_kernel(const
         exchange_end(a.peers);        // all parameters of every rank's share have arrived when the kernel ends
     } else {
         __syncthreads();
-        bwd_tile<DEG, MULTI, ADAM, PEER>(a, smem, s_vis, s_bar, phase, blockIdx.x);
+        bwd_tile<DEG, MULTI, ADAM, PEER, INST>(a, smem, s_vis, s_bar, phase, blockIdx.x);
     }
 }
 
@@ -594,9 +598,15 @@ extern "C" int32_t d3gs_preprocess_backward(const D3gsOpConfig* cfg, const D3gsM
     const size_t smem = (size_t)256 * kRow * sizeof(float) * (multi ? 2 : 1);
 #define D3GS_LAUNCH_BWD(DEG, MULTI)                                                                              \
     do {                                                                                                         \
-        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI, false>,                                 \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                 \
-        preprocess_bwd_kernel<DEG, MULTI, false><<<grid, 256, smem, s>>>(a);                                     \
+        if (cfg->instance_id != nullptr) {                                                                       \
+            D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI, false, false, true>,                \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));             \
+            preprocess_bwd_kernel<DEG, MULTI, false, false, true><<<grid, 256, smem, s>>>(a);                    \
+        } else {                                                                                                 \
+            D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, MULTI, false>,                             \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));             \
+            preprocess_bwd_kernel<DEG, MULTI, false><<<grid, 256, smem, s>>>(a);                                 \
+        }                                                                                                        \
     } while (0)
     switch (cfg->sh_degree * 2 + (multi ? 1 : 0)) {
         case 0: D3GS_LAUNCH_BWD(0, false); break;
@@ -644,6 +654,7 @@ extern "C" int32_t d3gs_preprocess_backward_adam(const D3gsOpConfig* cfg, const 
     int32_t rc = check_backward_inputs(cfg, model, ctx, splat_grads);
     if (rc != D3GS_OK) return rc;
     D3GS_REQUIRE(segments != nullptr, "segments is NULL");
+    D3GS_REQUIRE(cfg->instance_id == nullptr, "instance rendering: use d3gs_preprocess_backward and d3gs_adam_step");
     D3GS_REQUIRE(cfg->num_views == 1, "the fused backward + Adam handles one view per launch (got %d)", cfg->num_views);
     D3GS_REQUIRE(model->sh_rest != nullptr && model->sh_rest_stride == 45 && model->sh_base_stride == 3,
                  "the fused backward + Adam needs the split degree-3 SH layout (strides 3 and 45)");
@@ -693,6 +704,7 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
     D3GS_REQUIRE(peers->world >= 1 && peers->world <= D3GS_MAX_PEERS && peers->rank >= 0 && peers->rank < peers->world,
                  "bad world / rank");
     D3GS_REQUIRE(cfg->num_views == peers->world, "one view per rank: num_views %d, world %d", cfg->num_views, peers->world);
+    D3GS_REQUIRE(cfg->instance_id == nullptr, "instance rendering: use d3gs_preprocess_backward and d3gs_adam_step");
     D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
     D3GS_REQUIRE(model->sh_rest != nullptr && model->sh_rest_stride == 45 && model->sh_base_stride == 3,
                  "the fused backward + Adam needs the split degree-3 SH layout (strides 3 and 45)");

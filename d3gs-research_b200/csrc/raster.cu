@@ -56,6 +56,7 @@ struct RasterArgs {
     const float* drgb;
     const float* dT;
     float* splat_grads;
+    unsigned long long* atomic_counts;   // instrumented backward only: [0] groups of global adds, [1] warp passes
     TestHooks hooks;
 };
 
@@ -342,7 +343,9 @@ __global__ void __launch_bounds__(128, 8) raster_forward_kernel(const __grid_con
 // four lanes of a group reduce them with a transposing butterfly (8 shuffles) and every lane adds the two
 // components it ends up holding to the record's row in shared memory.
 // 8 CTAs per SM (64 registers): measured faster than 9 / 10 CTAs (56 / 48 registers) and than 6 / 5 (72 / 77)
-template <bool GATHER, bool DIRECT>
+// COUNT (instrumentation, config_def.py:134 measure_atomic_add_count): a.atomic_counts[0] += groups of global adds
+// issued (one per Gaussian a lane group / a tile flush adds to), [1] += warp passes with a valid pixel.
+template <bool GATHER, bool DIRECT, bool COUNT>
 __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_constant__ RasterArgs a) {
     __shared__ __align__(128) float4 s_raw[2][kBatch * kRecFloat4];
     __shared__ __align__(8) uint64_t s_bar[2];
@@ -408,6 +411,7 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
     const int slot = (h2 ? 4 : 0) + (h1 ? 2 : 0);
     f2 T = f2_dup(1.0f);
     bool copy_failed = false;
+    unsigned int n_groups = 0, n_passes = 0;    // COUNT only
     if (!DIRECT) {
 #pragma unroll
         for (int k = 0; k < 9; ++k) s_acc[t][k] = 0.0f;   // row t is zeroed again by its owner after every flush
@@ -511,6 +515,10 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
                 v8 += shfl_x(v8, 2);
                 v8 += shfl_x(v8, 1);
                 const bool gvalid = ((vmask >> (group * 4)) & 0xfu) != 0;
+                if (COUNT) {
+                    n_passes += lane == 0;
+                    if (DIRECT) n_groups += gvalid && (lane & 3) == 0;
+                }
                 if (DIRECT) {
                     // No accumulation in shared memory: a record is touched by one or two groups of the tile on
                     // average, so the group's totals leave as they are.  The four lanes hold (sxx, sxy),
@@ -547,6 +555,7 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
             const float g7 = k1.w * fmaf(2.0f * k1.x, sx, k1.y * sy);
             const float g8 = k1.w * fmaf(2.0f * k1.z, sy, k1.y * sx);
             if (any) {
+                if (COUNT) ++n_groups;
                 float* dst = a.splat_grads + (int64_t)my_id * kGradFloats;
                 red_add_v4(dst, g0, g1, g2, g3);
                 red_add_v4(dst + 4, g4, g5, g6, 0.0f);
@@ -557,6 +566,17 @@ __global__ void __launch_bounds__(128, 8) raster_backward_kernel(const __grid_co
         }
     }
     if (copy_failed && t == 0) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
+    if (COUNT) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            n_groups += __shfl_xor_sync(0xffffffffu, n_groups, o);
+            n_passes += __shfl_xor_sync(0xffffffffu, n_passes, o);
+        }
+        if (lane == 0) {
+            atomicAdd(a.atomic_counts, (unsigned long long)n_groups);
+            atomicAdd(a.atomic_counts + 1, (unsigned long long)n_passes);
+        }
+    }
 }
 
 int32_t fill_args(const D3gsOpConfig* cfg, RasterArgs& a) {
@@ -611,7 +631,8 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
                                         const int32_t* tile_order, const float* records, int32_t mode,
                                         const int32_t* sorted_values, const float* color,
                                         const float* final_T, const int32_t* n_contrib, const float* drgb,
-                                        const float* dT, float* splat_grads, uint32_t* status, void* stream) {
+                                        const float* dT, float* splat_grads, uint64_t* atomic_counts,
+                                        uint32_t* status, void* stream) {
     RasterArgs a = {};
     int32_t rc = fill_args(cfg, a);
     if (rc != D3GS_OK) return rc;
@@ -635,13 +656,23 @@ extern "C" int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, co
     a.dT = dT;
     a.splat_grads = splat_grads;
     const unsigned grid = (unsigned)(a.tiles_x * a.tiles_y * cfg->num_views);
+    a.atomic_counts = reinterpret_cast<unsigned long long*>(atomic_counts);
     const bool records_by_id = (mode & D3GS_RASTER_RECORDS_BY_ID) != 0;
-    if (mode & D3GS_RASTER_DIRECT_ATOMICS) {
-        if (records_by_id) raster_backward_kernel<true, true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
-        else raster_backward_kernel<false, true><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+    const bool direct = (mode & D3GS_RASTER_DIRECT_ATOMICS) != 0;
+    if (atomic_counts != nullptr) {     // the instrumented instances: same arithmetic, plus the two counters
+        if (direct) {
+            if (records_by_id) raster_backward_kernel<true, true, true><<<grid, 128, 0, s>>>(a);
+            else raster_backward_kernel<false, true, true><<<grid, 128, 0, s>>>(a);
+        } else {
+            if (records_by_id) raster_backward_kernel<true, false, true><<<grid, 128, 0, s>>>(a);
+            else raster_backward_kernel<false, false, true><<<grid, 128, 0, s>>>(a);
+        }
+    } else if (direct) {
+        if (records_by_id) raster_backward_kernel<true, true, false><<<grid, 128, 0, s>>>(a);
+        else raster_backward_kernel<false, true, false><<<grid, 128, 0, s>>>(a);
     } else {
-        if (records_by_id) raster_backward_kernel<true, false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
-        else raster_backward_kernel<false, false><<<grid, 128, 0, (cudaStream_t)stream>>>(a);
+        if (records_by_id) raster_backward_kernel<true, false, false><<<grid, 128, 0, s>>>(a);
+        else raster_backward_kernel<false, false, false><<<grid, 128, 0, s>>>(a);
     }
     D3GS_LAUNCH_CHECK("raster_backward_kernel");
     return D3GS_OK;

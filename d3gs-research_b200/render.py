@@ -253,6 +253,9 @@ class GaussianSplatOp:
         # False: the host waits for the count before it launches, like the reference (render.py:695).
         self.launch_ahead = True
         self.launches_repeated = 0
+        # measure_atomic_add_count: groups of global atomic adds of the last raster backward, and more detail
+        self.last_atomic_add_count: int | None = None
+        self.last_atomic_stats: dict = {}
         self._ahead: dict = {}
         self._readback: dict = {}
         # Optional caller-owned tensors for what a later stage on ANOTHER GPU reads (data-parallel training with
@@ -318,7 +321,8 @@ class GaussianSplatOp:
                 raise RuntimeError(f"d3gs_b200 device status {status:#x}: a bounded wait gave up "
                                    "(1 scan, 2 sort, 4 bulk copy); results of the previous call are invalid")
 
-    def _op_config(self, model: GaussianModelOriginBase, cameras, training: bool) -> _lib.OpConfig:
+    def _op_config(self, model: GaussianModelOriginBase, cameras, training: bool,
+                   instance2world_T: torch.Tensor | None = None) -> _lib.OpConfig:
         cfg = self._cfg
         rows = _camera_rows(cameras)
         if rows.shape[0] > _lib.MAX_VIEWS:
@@ -357,6 +361,31 @@ class GaussianSplatOp:
             for k in range(12):
                 cam.cam2world_T[k] = float(rows[b, k])
             cam.fx, cam.fy, cam.cx, cam.cy = (float(v) for v in rows[b, 12:16])
+        if instance2world_T is not None:   # render.py:207-220
+            assert model.instance_id is not None, "instance_id must be provided in model when render with instance"
+            if isinstance(cameras, CameraBundle):
+                assert cameras.frame_ids is not None, "frame_ids must be provided when render with instance"
+                frames = [int(v) for v in cameras.frame_ids.tolist()]
+            else:
+                assert cameras.frame_local_id is not None
+                frames = [int(cameras.frame_local_id)]
+            if instance2world_T.dim() == 3:        # one frame
+                instance2world_T = instance2world_T.unsqueeze(0)
+            assert instance2world_T.dim() == 4 and tuple(instance2world_T.shape[2:]) == (4, 3), \
+                "instance2world_T must be 4D tensor [num_frame, num_instance, 4, 3]"
+            assert max(frames) < instance2world_T.shape[0] and min(frames) >= 0
+            ids = model.instance_id
+            if ids.dtype != torch.int32 or not ids.is_contiguous():
+                ids = ids.to(torch.int32).contiguous()
+            tr = instance2world_T.detach()
+            if tr.dtype != torch.float32 or not tr.is_contiguous():
+                tr = tr.to(torch.float32).contiguous()
+            assert ids.shape[0] == len(model) and ids.device == model.xyz.device and tr.device == model.xyz.device
+            self._instance_keep = (ids, tr)       # the launches read them asynchronously
+            c.instance_id, c.instance2world_T = ids.data_ptr(), tr.data_ptr()
+            c.num_instance = int(tr.shape[1])
+            for b, f in enumerate(frames):
+                c.frame_ids[b] = f
         return c
 
     @staticmethod
@@ -423,13 +452,13 @@ class GaussianSplatOp:
                 custom_features: torch.Tensor | None = None, mask: torch.Tensor | None = None,
                 prep_user_inputs: dict[str, Any] | None = None):
         assert model.act_applied, "model must be activated before render"
-        if instance2world_T is not None or prep_user_inputs is not None:
-            raise NotImplementedError("instance transforms and proxy inputs are not built")
+        if prep_user_inputs is not None:
+            raise NotImplementedError("proxy inputs are not built")
         lib = self._lib
         dev = model.xyz.device
         stream = torch.cuda.current_stream(dev).cuda_stream
         num = len(model)
-        ocfg = self._op_config(model, cameras, training)
+        ocfg = self._op_config(model, cameras, training, instance2world_T)
         B, W, H = ocfg.num_views, ocfg.width, ocfg.height
         BN = B * num
         tiles_x, tiles_y = div_up(W, 16), div_up(H, 16)
@@ -693,13 +722,21 @@ class GaussianSplatOp:
         if direct is None:
             direct = ctx.gaussian_idx_sorted.shape[0] < self.DIRECT_ATOMICS_PAIRS_PER_GAUSSIAN * BN
         mode = (_lib.RASTER_RECORDS_BY_ID if ctx.records_by_id else 0) | (_lib.RASTER_DIRECT_ATOMICS if direct else 0)
+        # config_def.py:134, render.py:1451-1453: count the groups of global atomic adds of this launch
+        counts = torch.zeros(2, dtype=torch.int64, device=dev) if self._cfg.measure_atomic_add_count else None
         _lib.check(lib.d3gs_raster_backward(C.byref(ocfg), num, ctx.workload_ranges.data_ptr(), _lib.ptr(ctx.tile_order),
                                             ctx.splat_records.data_ptr(), mode,
                                             ctx.gaussian_idx_sorted.data_ptr(),
                                             color.data_ptr(), out.T.data_ptr(), out.n_contrib.data_ptr(),
-                                            drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), sync.data_ptr() + 8,
-                                            stream), "d3gs_raster_backward")
+                                            drgb.data_ptr(), _lib.ptr(dT), packed.data_ptr(), _lib.ptr(counts),
+                                            sync.data_ptr() + 8, stream), "d3gs_raster_backward")
         self._mark("raster_bwd")
+        if counts is not None:
+            groups, passes = (int(v) for v in counts.tolist())
+            self.last_atomic_add_count = groups
+            self.last_atomic_stats = dict(atomic_add_groups=groups, warp_passes=passes, direct=bool(direct),
+                                          sort_pairs=int(ctx.gaussian_idx_sorted.shape[0]))
+            print(f"atomic add count: {groups}")     # render.py:2310-2311
         # render.py:1948-1971: the raster backward is linear in the image gradients of all blended channels; the
         # share of every auxiliary group is one more pass with that group's records, whose "colour" gradient is
         # the gradient of the blended values (dz for the depth, dcustom_features for the features)
@@ -732,7 +769,7 @@ class GaussianSplatOp:
                                                 _lib.ptr(ctx.tile_order), recs.data_ptr(), mode,
                                                 ctx.gaussian_idx_sorted.data_ptr(), blend.data_ptr(), out.T.data_ptr(),
                                                 out.n_contrib.data_ptr(), dimg.data_ptr(), None, packed2.data_ptr(),
-                                                sync.data_ptr() + 8, stream), "d3gs_raster_backward(aux)")
+                                                None, sync.data_ptr() + 8, stream), "d3gs_raster_backward(aux)")
             packed[:, 0:4] += packed2[:, 0:4]
             packed[:, 8:10] += packed2[:, 8:10]
             per_splat.append(packed2[:, 4:7])
@@ -768,11 +805,13 @@ class GaussianSplatOp:
         rg = self.rasterize_forward_backward(model, ctx, out, grad, training=True)
         dev = model.xyz.device
         stream = torch.cuda.current_stream(dev).cuda_stream
-        ocfg = self._op_config(model, cameras, True)
+        ocfg = self._op_config(model, cameras, True, instance2world_T)
         B = ocfg.num_views
         num = len(model)
         if adam_segments is not None:
             assert len(adam_segments) == 6 and B == 1
+            assert instance2world_T is None, "the backward fused with Adam does not render instances"
+
             mstruct = self._model_struct(model)
             cstruct = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian,
                                        ctx.cov2d_vecs, ctx.sh_to_rgb_ne_0)
@@ -866,6 +905,7 @@ class _RasterizeGaussians(torch.autograd.Function):
             ctx.model = model
             ctx.cams = cams
         ctx.op = op
+        ctx.instance2world_T = instance2world_T
         ctx.return_uv_grad = uv_grad_holder is not None
         radii = out.radii if out.radii is not None else torch.zeros(0, dtype=torch.int32, device=xyz.device)
         ctx.mark_non_differentiable(out.n_contrib, radii)
@@ -882,7 +922,8 @@ class _RasterizeGaussians(torch.autograd.Function):
         if not drgb.is_contiguous():
             drgb = drgb.contiguous()
         gradient = GaussianSplatGradients(drgb=drgb, dT=dT, ddepth=ddepth, dcustom_features=dcustom_features)
-        gm, duv, dfeat = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad)
+        gm, duv, dfeat = op.backward(ctx.model, ctx.cams, ctx.fwd_ctx, ctx.out, gradient, ctx.return_uv_grad,
+                                     ctx.instance2world_T)
         return (gm.xyz, gm.color_sh, gm.color_sh_base, gm.scale, gm.quaternion_xyzw, gm.opacity, None, None, dfeat,
                 None, None, None, None, None, None, None, None, duv)
 

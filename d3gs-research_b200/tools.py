@@ -170,20 +170,13 @@ def save_3dgs_origin_model(model: GaussianModelOriginBase, ply_path: str) -> Non
         rec.tofile(f)
 
 
-def points_to_gaussian_init_scale(points, chunk: int = 4096):
-    """tools.py:66-71: log of the root mean squared distance to the three nearest neighbours.  The reference
-    uses the simple_knn CUDA extension; this is an exact chunked brute-force search with torch (O(N^2), meant
-    for the few 1e5 points of an SfM initialisation)."""
+def points_to_gaussian_init_scale(points):
+    """tools.py:64-71: log of the root mean squared distance to the three nearest neighbours, for all three axes."""
     import torch
-    n = points.shape[0]
-    out = torch.empty(n, dtype=torch.float32, device=points.device)
-    for i in range(0, n, chunk):
-        d2 = torch.cdist(points[i:i + chunk], points).square_()
-        d2[torch.arange(d2.shape[0], device=points.device), torch.arange(i, i + d2.shape[0], device=points.device)] = float("inf")
-        k = min(3, n - 1)
-        nearest = torch.topk(d2, k, dim=1, largest=False).values if k > 0 else torch.zeros(d2.shape[0], 1, device=points.device)
-        out[i:i + chunk] = nearest.mean(1)
-    return torch.log(torch.sqrt(torch.clamp_min(out, 1e-7)))[..., None].repeat(1, 3)
+    from .ops import simple_knn
+    knn_res = simple_knn(points.contiguous(), min(3, max(points.shape[0] - 1, 1)))
+    dist2 = torch.clamp_min(torch.square(knn_res).mean(1), 0.0000001)
+    return torch.log(torch.sqrt(dist2))[..., None].repeat(1, 3)
 
 
 def init_original_3dgs_model(model: GaussianModelOriginBase, points: np.ndarray, points_rgb: np.ndarray):

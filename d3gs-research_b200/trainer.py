@@ -675,6 +675,44 @@ class SplatTrainer:
         self.apply_gradients(stats, update)
         return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}
 
+    def end_of_iteration(self, cur_step: int, strategy, generator: "torch.Generator | None" = None,
+                         verbose: bool = False) -> list:
+        """The reference trainer's period events for the iteration ``cur_step`` (0-based) that has just finished
+        (d3sim/algos/d3gs/train.py:68-74, 299-320; d3sim/core/train.py:76-87: an event with interval p fires when
+        ``(cur_step + 1) % p == 0``).  ``strategy``: a ``GaussianStrategyOrigin`` whose step counts were already
+        rescaled for the batch size.
+
+        * every ``1000 // batch_size`` iterations the active SH degree goes up by one until it is 3
+          (train.py:299-302); the next forward and backward then evaluate one more band;
+        * every ``refine_every`` iterations with ``refine_start_iter < cur_step + 1 < refine_stop_iter``:
+          densify and prune (train.py:303-316);
+        * every ``reset_opacity_every`` iterations before ``refine_stop_iter``: reset the opacities
+          (train.py:318-320).
+
+        Collective when there are several ranks (every rank calls it with the same ``cur_step``).  Returns the
+        names of the events that fired, in the order the reference registers them."""
+        fired = []
+        step1 = cur_step + 1
+        up_sh = max(1000 // self.batch_size, 1)
+        if step1 % up_sh == 0 and self.model.cur_sh_degree < 3:
+            self.model.cur_sh_degree += 1
+            if self.grad_model is not None:
+                self.grad_model.cur_sh_degree = self.model.cur_sh_degree
+            fired.append("up_sh")
+            if verbose:
+                print(f"Up SH degree to {self.model.cur_sh_degree}")
+        if step1 % max(strategy.refine_every, 1) == 0 and strategy.refine_start_iter < step1 < strategy.refine_stop_iter:
+            self.refine(strategy, step1, generator)
+            fired.append("update_gs")
+            if verbose:
+                print("REFINE GS!!!", len(self.model))
+        if step1 % max(strategy.reset_opacity_every, 1) == 0 and step1 < strategy.refine_stop_iter:
+            self.reset_opacity(strategy)
+            fired.append("reset_opacity")
+            if verbose:
+                print("RESET GS OPACITY!!!", step1)
+        return fired
+
     def _all_cameras(self, cameras, all_cameras):
         from .render import CameraBundle, _camera_rows
         if all_cameras is None:

@@ -82,6 +82,20 @@ typedef struct D3gsOpConfig {
                                                reference, is also the value the sort keys are built from */
     int32_t num_views;                      /* B */
     D3gsCamera cameras[D3GS_MAX_VIEWS];
+    /* Instance rendering (render.py:207-220, 346-354, 3031-3039), read by d3gs_preprocess_forward and
+     * d3gs_preprocess_backward only.  instance_id NULL = off.  A Gaussian g with instance_id[g] >= 0 lives in the
+     * frame of object instance_id[g]; for it view b's camera is taken into that frame, cam2instance =
+     * inverse(instance2world[frame_ids[b]][instance_id[g]]) @ cam2world, and the rest is unchanged (gradients are
+     * those of the Gaussian's parameters in its own frame; the transforms receive none, as in the reference).
+     * instance2world_T: device [num_frame, num_instance, 4, 3] floats, every [4,3] laid out like cam2world_T
+     * (rows 0-2 the transposed rotation, row 3 the translation); rigid transforms (the inverse rotation is the
+     * transpose). */
+    const int32_t* instance_id;             /* device [N] */
+    const float* instance2world_T;
+    int32_t num_instance;
+    int32_t frame_ids[D3GS_MAX_VIEWS];      /* frame of every view (BasicPinholeCamera.frame_local_id /
+                                               CameraBundle.frame_ids) */
+    int32_t reserved_;
 } D3gsOpConfig;
 
 /* Gaussian parameters in the reference model layout (origin/model.py:36-44).  `sh_base` /
@@ -262,13 +276,19 @@ int32_t d3gs_raster_forward(const D3gsOpConfig* cfg, const int32_t* ranges, cons
  * the per-pair records.  D3GS_RASTER_DIRECT_ATOMICS: every group of four lanes adds its sums for a splat to
  * splat_grads directly instead of accumulating them per tile in shared memory first; faster while a splat
  * overlaps few 4x2 pixel blocks of a tile (about three sort pairs per Gaussian or fewer), slower for scenes of
- * large splats.  Same gradients up to the order of the float additions. */
+ * large splats.  Same gradients up to the order of the float additions.
+ * atomic_counts: NULL, or two device uint64 that the call ADDS to (the caller zeroes them) -- the reference's
+ * measure_atomic_add_count (config_def.py:134; render.py:1451-1453, 2145-2148): [0] groups of global atomic adds
+ * issued, one per Gaussian that a reducing lane set (4 lanes = 4x2 pixels with DIRECT_ATOMICS, else a whole tile's
+ * flush) adds to; [1] warp passes that had a valid pixel (in a pass each of the warp's eight lane groups handles
+ * the next splat of its own survivor list).  Non-NULL selects an instrumented instance of the kernel: same
+ * gradients, slower. */
 #define D3GS_RASTER_RECORDS_BY_ID 1
 #define D3GS_RASTER_DIRECT_ATOMICS 2
 int32_t d3gs_raster_backward(const D3gsOpConfig* cfg, int64_t num, const int32_t* ranges, const int32_t* tile_order,
                              const float* records, int32_t mode, const int32_t* sorted_values, const float* color,
                              const float* final_T, const int32_t* n_contrib, const float* drgb, const float* dT,
-                             float* splat_grads, uint32_t* status, void* stream);
+                             float* splat_grads, uint64_t* atomic_counts, uint32_t* status, void* stream);
 
 /* ---- K8 preprocess backward (render.py:2779-3374) ---------------------------------------- */
 /* every gradient element is written (zeros for culled Gaussians); sums over the view batch.  Slot 7 of a
@@ -457,6 +477,17 @@ int32_t d3gs_refine_apply(const D3gsModel* src, const D3gsModel* dst, const D3gs
 /* opacity = logit(min(activated opacity, thresh)) in place; the given Adam moments of opacity are zeroed */
 int32_t d3gs_reset_opacity(float* opacity, int64_t num, float thresh, int32_t fused_activations, float* exp_avg,
                            float* exp_avg_sq, void* stream);
+
+/* ---- k nearest neighbours of a point cloud (d3sim/algos/d3gs/ops.py:14-183 simple_knn) --------------------------
+ * out [n, k] = distances (not squared) from every point to its k nearest OTHER points, ascending; exact.  Used for
+ * the initial scales (origin/model.py:26-28: the mean of the three squared distances).  points: n rows of
+ * point_stride floats (xyz first); points_min / points_max: [3] on the device (the reference computes them with
+ * torch, ops.py:21-22); morton_bits 10 (32-bit codes) or 21 (use_64bit); k in [1, 8].  The workspace holds the
+ * codes, the sort's buffers, the sorted points and the box bounds. */
+size_t d3gs_simple_knn_workspace_bytes(int64_t n, int32_t morton_bits);
+int32_t d3gs_simple_knn(const float* points, int64_t point_stride, int64_t n, int32_t k, int32_t morton_bits,
+                        const float* points_min, const float* points_max, float* out, void* workspace,
+                        size_t workspace_bytes, uint32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -127,6 +127,10 @@ class Scene:
     sh_base: np.ndarray
     sh_rest: np.ndarray          # [N,15,3]
     cams: np.ndarray             # [B,16]
+    # instance rendering (render.py:207-220, 346-354); all three or none
+    instance_id: np.ndarray | None = None          # [N] int32, < 0 = world Gaussian
+    instance2world_T: np.ndarray | None = None     # [num_frame, num_instance, 4, 3]
+    frame_ids: np.ndarray | None = None            # [B] int32
 
     @property
     def n(self):
@@ -142,7 +146,31 @@ def bit_length(n: int) -> int:
     return int(n).bit_length()
 
 
+class _instances:
+    """Switches the C library's instance context on for the calls inside the block."""
+
+    def __init__(self, sc: Scene):
+        self.sc = sc
+
+    def __enter__(self):
+        sc = self.sc
+        if sc.instance_id is not None:
+            self.keep = (np.ascontiguousarray(sc.instance_id, np.int32), _f32(sc.instance2world_T),
+                         np.ascontiguousarray(sc.frame_ids, np.int32))
+            assert self.keep[1].ndim == 4 and self.keep[1].shape[2:] == (4, 3) and self.keep[2].size == sc.b
+            lib().oracle_set_instances(_p(self.keep[0]), _p(self.keep[1]), ctypes.c_int(self.keep[1].shape[1]),
+                                       _p(self.keep[2]), ctypes.c_int(sc.b))
+
+    def __exit__(self, *exc):
+        lib().oracle_set_instances(None, None, ctypes.c_int(0), None, ctypes.c_int(0))
+
+
 def preprocess_fwd(cfg: OpConfig, sc: Scene, mask=None):
+    with _instances(sc):
+        return _preprocess_fwd(cfg, sc, mask)
+
+
+def _preprocess_fwd(cfg: OpConfig, sc: Scene, mask=None):
     BN = sc.b * sc.n
     out = dict(
         tiles_touched=np.zeros(BN, np.int32), radii=np.zeros(BN, np.int32),
@@ -211,7 +239,32 @@ def raster_bwd(cfg: OpConfig, b: int, bn: int, ranges, sorted_ids, prep, color, 
     return dict(duv=duv, dconic=dconic, dopacity=dop, dcolor=dcol)
 
 
+def simple_knn(points, k: int):
+    """[n, k] float32: distances to the k nearest other points, ascending (ops.py:14-183)."""
+    pts = _f32(points)
+    out = np.zeros((pts.shape[0], k), np.float32)
+    lib().oracle_simple_knn(_p(pts), ctypes.c_int64(pts.shape[1]), ctypes.c_int64(pts.shape[0]), ctypes.c_int(k), _p(out))
+    return out
+
+
+def count_accumulations(cfg: OpConfig, b: int, ranges, sorted_ids, prep, nc, block_wh=(16, 2)):
+    """(groups, pixels): (pixel block, splat) pairs with a valid pixel -- what measure_atomic_add_count counts for a
+    kernel whose lanes over ``block_wh`` pixels reduce before one group of global adds -- and valid (pixel, splat)
+    pairs.  (16, 2) is a warp of the reference's 16 x 16 thread block."""
+    out = np.zeros(2, np.int64)
+    cv = cfg.vec()
+    lib().oracle_count_accumulations(_p(cv), ctypes.c_int(b), _p(ranges), _p(sorted_ids), _p(prep["uvs"]),
+                                     _p(prep["conic_opacity"]), _p(nc), ctypes.c_int(block_wh[0]),
+                                     ctypes.c_int(block_wh[1]), _p(out))
+    return int(out[0]), int(out[1])
+
+
 def preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg, dz=None):
+    with _instances(sc):
+        return _preprocess_bwd(cfg, sc, prep, rg, dz)
+
+
+def _preprocess_bwd(cfg: OpConfig, sc: Scene, prep, rg, dz=None):
     n = sc.n
     dz = None if dz is None else _f32(dz)   # [B*N]: d loss / d depth value of every splat (render_depth)
     g = dict(xyz=np.zeros((n, 3), np.float32), quat=np.zeros((n, 4), np.float32),

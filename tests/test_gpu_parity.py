@@ -584,6 +584,48 @@ def test_launch_ahead_binning_matches_and_repeats(cuda_device):
     assert torch.equal(o2.color, out2.color)
 
 
+@pytest.mark.parametrize("direct", [True, False])
+def test_atomic_add_count_matches_the_oracle(cuda_device, direct, capsys):
+    """measure_atomic_add_count (config_def.py:134): the instrumented raster backward counts its groups of global
+    atomic adds.  With direct adds a group is (4 x 2 pixel block, splat) with a valid pixel -- counted exactly by the
+    oracle; with per-tile accumulation it is (tile, splat) with a non-zero sum.  The oracle also gives the count of
+    the reference's own reduction unit (a warp = 16 x 2 pixels).  Gradients are those of the plain kernel."""
+    sc = small_scene(n=6000, width=200, height=136, sh_degree=1, seed=21)
+    grads = {}
+    for measure in (False, True):
+        op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, measure_atomic_add_count=measure)
+        op = d3.GaussianSplatOp(op_cfg)
+        op.raster_grad_direct = direct
+        model = gpu_model(sc, cuda_device)
+        model.act_applied = True
+        cams = gpu_cameras(sc, cuda_device)
+        out, ctx = op.forward(model, cams, training=True)
+        g = torch.Generator(device="cpu").manual_seed(3)
+        drgb = torch.randn(out.color.shape, generator=g).to(cuda_device)
+        rg = op.rasterize_forward_backward(model, ctx, out, GaussianSplatGradients(drgb=drgb, dT=None))
+        torch.cuda.synchronize()
+        grads[measure] = [t.cpu().numpy() for t in (rg.duv, rg.dconic, rg.dopacity, rg.dcolor)]
+    assert "atomic add count:" in capsys.readouterr().out
+    for a, b in zip(grads[False], grads[True]):
+        assert_close(b, a, 1e-4, "instrumented vs plain gradient", floor_frac=1e-3)   # float adds in another order
+    ocfg = oracle_cfg(sc, op_cfg, True)
+    ref = O.forward(ocfg, oracle_scene(sc))
+    nc = out.n_contrib.cpu().numpy()
+    np.testing.assert_array_equal(nc, ref.n_contrib)
+    st = op.last_atomic_stats
+    assert st["direct"] == direct and st["sort_pairs"] == ref.num_rendered
+    groups_42, pixels = O.count_accumulations(ocfg, 1, ref.ranges, ref.sorted_ids, ref.prep, nc, block_wh=(4, 2))
+    groups_warp, _ = O.count_accumulations(ocfg, 1, ref.ranges, ref.sorted_ids, ref.prep, nc, block_wh=(16, 2))
+    groups_tile, _ = O.count_accumulations(ocfg, 1, ref.ranges, ref.sorted_ids, ref.prep, nc, block_wh=(16, 16))
+    assert groups_tile <= groups_warp <= groups_42 <= pixels
+    # a warp pass handles one splat for each of its eight lane groups (every group walks its own survivor list)
+    assert groups_42 / 8 <= st["warp_passes"] <= groups_42
+    if direct:
+        assert op.last_atomic_add_count == groups_42
+    else:   # a sum that cancels to exactly zero is not flushed: at most the oracle's count, and nearly all of it
+        assert 0.999 * groups_tile <= op.last_atomic_add_count <= groups_tile
+
+
 @pytest.mark.parametrize("shape", [(1, 40, 56), (2, 97, 130), (1, 16, 16), (1, 5, 7)])
 def test_l1_dssim_loss_and_gradient(cuda_device, shape):
     b, h, w = shape
@@ -756,3 +798,152 @@ def test_full_size_properties_cfg4_render(cuda_device):
     K, out = _full_size_invariants(cuda_device, "cfg4", training=False)
     assert K > 5_000_000
     assert bool(((out.color >= 0) & (out.color <= 1)).all())
+
+
+@pytest.mark.parametrize("n,k,use_64bit", [(1, 3, False), (3, 3, False), (257, 1, False), (5000, 3, False),
+                                           (20000, 3, True), (20000, 6, False), (4097, 8, True)])
+def test_simple_knn_against_the_oracle(cuda_device, n, k, use_64bit):
+    """d3gs_simple_knn (ops.py:14-183) against the oracle's exhaustive search, bit for bit: the same distance
+    expression in the same order on both sides, and the k smallest values do not depend on the search order.
+    Clustered points (most boxes are culled for most CTAs), a duplicate pair, n not a multiple of the box size, and
+    fewer than k other points (the missing neighbours stay at sqrt(FLT_MAX), as in the reference)."""
+    from d3gs_research_b200.ops import simple_knn
+    rng = np.random.default_rng(n + k)
+    pts = np.concatenate([rng.normal(size=(n - n // 3, 3)) * 3.0,
+                          rng.normal(size=(n // 3, 3)) * 0.02 + np.array([5.0, -2.0, 1.0])]).astype(np.float32)
+    if n > 10:
+        pts[9] = pts[2]
+    # a wider row than xyz: the stride is honoured
+    wide = np.concatenate([pts, rng.normal(size=(n, 2)).astype(np.float32)], axis=1)
+    got = simple_knn(torch.from_numpy(wide).to(cuda_device), k, use_64bit).cpu().numpy()
+    ref = O.simple_knn(wide, k)
+    np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+    if n > 10:
+        assert got[9, 0] == 0.0 and got[2, 0] == 0.0
+
+
+def test_point_cloud_init_scales(cuda_device):
+    """tools.py:64-90: a regular grid has its three nearest neighbours at the grid spacing."""
+    from d3gs_research_b200.tools import init_original_3dgs_model, points_to_gaussian_init_scale
+    pts = np.stack(np.meshgrid(np.arange(4.0), np.arange(4.0), np.arange(4.0), indexing="ij"), -1).reshape(-1, 3) * 0.5
+    s = points_to_gaussian_init_scale(torch.from_numpy(pts.astype(np.float32)).to(cuda_device))
+    assert torch.allclose(s, torch.full_like(s, float(np.log(0.5))), atol=1e-5)
+    m2 = d3.GaussianModelOriginFused.create_flat(64, device=cuda_device)
+    init_original_3dgs_model(m2, pts, np.full((64, 3), 0.5))
+    assert m2.cur_sh_degree == 0 and float(m2.color_sh_base.abs().max()) == 0.0 and float(m2.quaternion_xyzw[:, 3].min()) == 1.0
+    assert abs(float(torch.sigmoid(m2.opacity[0])) - 0.1) < 1e-6
+    assert torch.allclose(m2.scale, torch.full_like(m2.scale, float(np.log(0.5))), atol=1e-5)
+
+
+def test_sh_degree_schedule_steps_match_the_oracle(cuda_device):
+    """train.py:299-302: the active SH degree rises by one every 1000 // batch_size iterations.  A trainer whose
+    batch size makes that period one iteration steps at degree 0, 1, 2, 3; every step's Adam update must be the
+    oracle's for that degree (bands above the active degree get no gradient, their moments only decay)."""
+    from d3gs_research_b200.strategy import GaussianStrategyOrigin
+    from d3gs_research_b200.trainer import SplatTrainer
+    sc = small_scene(n=4000, width=160, height=112, sh_degree=3, seed=23)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
+    osc = oracle_scene(sc)
+    model = gpu_model(sc, cuda_device)
+    model.cur_sh_degree = 0
+    cams = gpu_cameras(sc, cuda_device)
+    target = sc["target"][:1].contiguous()
+    tgt = target.to(cuda_device)
+    fields = ("xyz", "quat", "scale", "opacity", "sh_base", "sh_rest")
+    attr = dict(xyz="xyz", quat="quaternion_xyzw", scale="scale", opacity="opacity", sh_base="color_sh_base", sh_rest="color_sh")
+    tr = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=1)
+    tr.batch_size = 1000          # only the schedule reads it after construction: 1000 // 1000 = every iteration
+    st = GaussianStrategyOrigin(refine_start_iter=10 ** 6)
+    adam_state = {k: (np.zeros_like(getattr(osc, k)), np.zeros_like(getattr(osc, k))) for k in fields}
+    m_views, v_views = tr._field_views(tr.exp_avg), tr._field_views(tr.exp_avg_sq)
+    for step in range(4):
+        assert model.cur_sh_degree == step
+        # both sides start the step from the oracle's state, so that only this step's gradient differs
+        before = {k: getattr(osc, k).copy() for k in fields}
+        with torch.no_grad():
+            for k in fields:
+                getattr(model, attr[k]).copy_(torch.from_numpy(before[k]).to(cuda_device))
+                m_views[attr[k]].copy_(torch.from_numpy(adam_state[k][0]).to(cuda_device))
+                v_views[attr[k]].copy_(torch.from_numpy(adam_state[k][1]).to(cuda_device))
+        ocfg = oracle_cfg(sc, op_cfg, True)
+        ocfg.sh_degree = step
+        ref = O.run_iteration(ocfg, osc, target.numpy(), 0.2, adam_state=adam_state, step=step + 1)
+        if step < 3:     # bands above the active degree: no gradient
+            assert not ref.grads["sh_rest"][:, (step + 1) ** 2 - 1:].any()
+        tr.step(cams, tgt)
+        tr.op.check_status()
+        torch.cuda.synchronize()
+        for k in fields:
+            after = getattr(model, attr[k]).detach().cpu().numpy()
+            assert_update_close(after - before[k], getattr(osc, k) - before[k], ref.grads[k], O.ADAM_LRS[k],
+                                f"degree {step} Adam update {k}", first_step=step == 0, p_before=before[k])
+        fired = tr.end_of_iteration(step, st)
+        assert fired == (["up_sh"] if step < 3 else [])
+    assert model.cur_sh_degree == 3
+
+
+def _rigid_T(rng, angle, shift):
+    """A [4,3] transform in the cam2world_T layout: rows 0-2 the transposed rotation, row 3 the translation."""
+    axis = rng.normal(size=3)
+    axis /= np.linalg.norm(axis)
+    a = rng.uniform(-angle, angle)
+    K = np.array([[0, -axis[2], axis[1]], [axis[2], 0, -axis[0]], [-axis[1], axis[0], 0]])
+    R = np.eye(3) + np.sin(a) * K + (1 - np.cos(a)) * (K @ K)
+    return np.concatenate([R.T, rng.uniform(-shift, shift, size=(1, 3))], axis=0).astype(np.float32)
+
+
+@pytest.mark.parametrize("views", [1, 3])
+def test_instance_rendering_forward_and_backward(cuda_device, views):
+    """instance2world_T (render.py:207-220, 346-354, 3031-3039): Gaussians with instance_id >= 0 are rendered through
+    the camera taken into their object's frame, per view's frame id.  Binning bit-exact, image and the gradients of
+    the Gaussians' own parameters against the oracle; Gaussians of no instance behave as without the argument."""
+    sc = small_scene(n=5000, width=200, height=136, sh_degree=2, seed=31, views=views)
+    rng = np.random.default_rng(8)
+    n = sc["cfg"].n
+    inst = rng.integers(-1, 3, size=n).astype(np.int32)               # -1: world Gaussian; 0..2: an object
+    frames = 4
+    T = np.stack([np.stack([_rigid_T(rng, 0.25, 0.3) for _ in range(3)]) for _ in range(frames)])   # [4,3,4,3]
+    frame_ids = np.array([2, 0, 3][:views], np.int32)
+    op_cfg = d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT)
+    op = d3.GaussianSplatOp(op_cfg)
+    op.debug_capture = True
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    model.instance_id = torch.from_numpy(inst).to(cuda_device)
+    cams = gpu_cameras(sc, cuda_device)
+    if views == 1:
+        cams.frame_local_id = int(frame_ids[0])
+    else:
+        cams.frame_ids = torch.from_numpy(frame_ids).to(cuda_device)
+    T_dev = torch.from_numpy(T).to(cuda_device)
+    out, ctx = op.forward(model, cams, training=True, instance2world_T=T_dev)
+    torch.cuda.synchronize()
+    ocfg = oracle_cfg(sc, op_cfg, True)
+    osc = oracle_scene(sc)
+    osc.instance_id, osc.instance2world_T, osc.frame_ids = inst, T, frame_ids
+    ref = O.forward(ocfg, osc)
+    plain = O.forward(ocfg, oracle_scene(sc))
+    assert (ref.prep["radii"] != plain.prep["radii"]).sum() > 100, "the transforms should move many Gaussians"
+    world = np.tile(inst < 0, views)
+    np.testing.assert_array_equal(ref.prep["radii"][world], plain.prep["radii"][world])
+    np.testing.assert_array_equal(op.debug["tiles_touched"].cpu().numpy(), ref.prep["tiles_touched"])
+    np.testing.assert_array_equal(ctx.radii.cpu().numpy(), ref.prep["radii"])
+    np.testing.assert_array_equal(op.debug["sorted_values"].cpu().numpy(), ref.sorted_ids)
+    np.testing.assert_array_equal(ctx.workload_ranges.cpu().numpy(), ref.ranges)
+    np.testing.assert_array_equal(out.n_contrib.cpu().numpy(), ref.n_contrib)
+    assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
+    g = torch.Generator(device="cpu").manual_seed(5)
+    drgb = torch.randn(out.color.shape, generator=g)
+    O.backward(ocfg, osc, ref, drgb.numpy())
+    gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=drgb.to(cuda_device), dT=None),
+                             return_uv_grad=True, instance2world_T=T_dev)
+    torch.cuda.synchronize()
+    for k, attr in (("xyz", "xyz"), ("quat", "quaternion_xyzw"), ("scale", "scale"), ("opacity", "opacity"),
+                    ("sh_base", "color_sh_base"), ("sh_rest", "color_sh")):
+        assert_close(getattr(gm, attr).cpu().numpy(), ref.grads[k], GRAD_TOL, f"grad {k}", floor_frac=1e-2)
+    # and through the autograd entry point
+    m2 = gpu_model(sc, cuda_device, requires_grad=True)
+    m2.instance_id = model.instance_id
+    out2 = d3.rasterize_gaussians(m2, cams, d3.GaussianSplatOp(op_cfg), training=True, instance2world_T=T_dev)
+    (out2.color * drgb.to(cuda_device)).sum().backward()
+    assert_close(m2.xyz.grad.cpu().numpy(), ref.grads["xyz"], GRAD_TOL, "autograd grad xyz", floor_frac=1e-2)

@@ -24,7 +24,7 @@ def test_config_defaults_follow_reference():
 
 @pytest.mark.parametrize("kw", [dict(transmittance_is_double=True), dict(move_opacity_in_grad_to_prep=True),
                                 dict(sparse_mode=True), dict(tile_size=(8, 8)), dict(tile_size=(16, 8)),
-                                dict(early_filter_algo=d3.EarlyFilterAlgo.ELLIPSE), dict(measure_atomic_add_count=True)])
+                                dict(early_filter_algo=d3.EarlyFilterAlgo.ELLIPSE)])
 def test_unsupported_options_raise_at_construction(kw):
     from d3gs_research_b200.render import GaussianSplatOp
     with pytest.raises(NotImplementedError):
@@ -257,11 +257,39 @@ def test_ply_roundtrip_and_point_cloud_init(tmp_path):
     v = _read_ply_vertices(path)
     assert np.allclose(v["rot_0"], m.quaternion_xyzw[:, 3].numpy()) and np.allclose(v["f_rest_1"], m.color_sh[:, 1, 0].numpy())
     assert np.allclose(v["f_rest_15"], m.color_sh[:, 0, 1].numpy())
-    # point-cloud initialisation: a regular grid has all three nearest neighbours at the grid spacing
+    # point-cloud initialisation needs the neighbour search of the CUDA library: no host fallback
     pts = np.stack(np.meshgrid(np.arange(4.0), np.arange(4.0), np.arange(4.0), indexing="ij"), -1).reshape(-1, 3) * 0.5
-    s = points_to_gaussian_init_scale(torch.from_numpy(pts.astype(np.float32)))
-    assert torch.allclose(s, torch.full_like(s, float(np.log(0.5))), atol=1e-5)
-    m2 = d3.GaussianModelOriginFused.create_flat(64, device="cpu")
-    init_original_3dgs_model(m2, pts, np.full((64, 3), 0.5))
-    assert m2.cur_sh_degree == 0 and float(m2.color_sh_base.abs().max()) == 0.0 and float(m2.quaternion_xyzw[:, 3].min()) == 1.0
-    assert abs(float(torch.sigmoid(m2.opacity[0])) - 0.1) < 1e-6
+    with pytest.raises(RuntimeError, match="GPU"):
+        points_to_gaussian_init_scale(torch.from_numpy(pts.astype(np.float32)))
+
+
+def test_end_of_iteration_fires_like_the_reference_period_events():
+    """train.py:68-74 registers up_sh (1000 // batch), update_gs (refine_every) and reset_opacity
+    (reset_opacity_every); core/train.py:76-87 fires an event when (cur_step + 1) % interval == 0; the handlers'
+    own conditions are train.py:299-320.  Batch size 4: SH degree up after iterations 250, 500, 750; refinement
+    every 25 iterations strictly between 125 and 3750; opacity reset every 750 iterations before 3750."""
+    from types import SimpleNamespace
+    from d3gs_research_b200.strategy import GaussianStrategyOrigin
+    from d3gs_research_b200.trainer import SplatTrainer
+    tr = SplatTrainer.__new__(SplatTrainer)
+    tr.batch_size = 4
+    tr.model = SimpleNamespace(cur_sh_degree=0)
+    tr.grad_model = SimpleNamespace(cur_sh_degree=0)
+    calls = []
+    tr.refine = lambda strategy, step, generator=None: calls.append(("refine", step))
+    tr.reset_opacity = lambda strategy: calls.append(("reset", None))
+    st = GaussianStrategyOrigin()
+    st.rescale_steps_by_batch_size(4)
+    assert (st.refine_every, st.refine_start_iter, st.refine_stop_iter, st.reset_opacity_every) == (25, 125, 3750, 750)
+    fired = {}
+    for cur in range(4000):
+        ev = tr.end_of_iteration(cur, st)
+        if ev:
+            fired[cur + 1] = ev
+    ups = [s for s, ev in fired.items() if "up_sh" in ev]
+    assert ups == [250, 500, 750] and tr.model.cur_sh_degree == 3 and tr.grad_model.cur_sh_degree == 3
+    refines = [s for s, ev in fired.items() if "update_gs" in ev]
+    assert refines == list(range(150, 3750, 25)) and [c[1] for c in calls if c[0] == "refine"] == refines
+    resets = [s for s, ev in fired.items() if "reset_opacity" in ev]
+    assert resets == [750, 1500, 2250, 3000]
+    assert fired[750] == ["up_sh", "update_gs", "reset_opacity"]      # the reference's registration order

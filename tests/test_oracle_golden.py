@@ -97,3 +97,16 @@ def test_sort_is_stable_and_ranges_cover_tiles():
             assert r[t, 0] == idx[0] and r[t, 1] == idx[-1] + 1
         else:
             assert tuple(r[t]) == (0, 0)
+
+
+def test_oracle_simple_knn_against_sklearn():
+    """The reference checks simple_knn against sklearn's NearestNeighbors (ops.py:186-206); so does the oracle."""
+    from sklearn.neighbors import NearestNeighbors
+    rng = np.random.default_rng(11)
+    pts = np.concatenate([rng.normal(size=(1500, 3)), rng.normal(size=(500, 3)) * 0.05 + 2.0]).astype(np.float32)
+    pts[7] = pts[3]                                    # a duplicate: its nearest other point is at distance 0
+    for k in (1, 3, 6):
+        got = O.simple_knn(pts, k)
+        dist, _ = NearestNeighbors(n_neighbors=k + 1, algorithm="brute").fit(pts.astype(np.float64)).kneighbors(pts.astype(np.float64))
+        np.testing.assert_allclose(got, dist[:, 1:], rtol=2e-5, atol=1e-7)
+        assert (np.diff(got, axis=1) >= 0).all() and got[7, 0] == 0.0 and got[3, 0] == 0.0
