@@ -65,6 +65,22 @@ __constant__ float kC3[7] = {-0.5900435899266435f, 2.890611442640554f, -0.457045
 //
 // One tile of 256 Gaussians starting at Gaussian g0.  Returns false when the CTA must stop (a staging copy never
 // arrived).  `phase`: parity of the staging barrier, toggled per staged tile.
+// what one view contributes for one Gaussian: the rasteriser's packed gradient row and the context it left
+struct ViewIn {
+    float4 gA, gB, gC;
+    float ca, cb, cc;
+    uint32_t ne0;
+};
+__device__ __forceinline__ ViewIn load_view(const BwdArgs& a, int b, int64_t g) {
+    ViewIn v;
+    const float4* sg4 = reinterpret_cast<const float4*>(a.v_grads[b] + g * D3GS_SPLAT_GRAD_FLOATS);
+    v.gA = sg4[0]; v.gB = sg4[1]; v.gC = sg4[2];
+    const float* cv = a.v_cov2d[b] + g * 3;
+    v.ca = cv[0]; v.cb = cv[1]; v.cc = cv[2];
+    v.ne0 = a.v_ne0[b][g];
+    return v;
+}
+
 template <int DEG, bool MULTI, bool ADAM, bool PEER, bool INST = false>
 __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t* s_vis, uint64_t& s_bar, uint32_t& phase,
                                          const int64_t tile) {
@@ -78,9 +94,27 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
     const int64_t g0 = a.g_begin + tile * 256;
     const int64_t g = g0 + t;
 
-    bool any_view = false;
-    if (g < range_end)
-        for (int b = 0; b < cf.num_views; ++b) any_view |= a.v_radii[b][g] != 0;
+    // Which views see this Gaussian, as a bit mask, and its largest radius.  All the views' radii are asked for
+    // before any is used: with the views on other GPUs every load is a round trip over NVLink, and eight in a row
+    // would cost eight of them.
+    uint32_t vis = 0;
+    int radmax = 0;
+    if (g < range_end) {
+        if constexpr (MULTI) {
+            int rad[D3GS_MAX_VIEWS];
+#pragma unroll
+            for (int b = 0; b < D3GS_MAX_VIEWS; ++b) rad[b] = b < cf.num_views ? a.v_radii[b][g] : 0;
+#pragma unroll
+            for (int b = 0; b < D3GS_MAX_VIEWS; ++b) {
+                vis |= rad[b] != 0 ? 1u << b : 0u;
+                radmax = max(radmax, rad[b]);
+            }
+        } else {
+            radmax = a.v_radii[0][g];
+            vis = radmax != 0 ? 1u : 0u;
+        }
+    }
+    const bool any_view = vis != 0;
     s_vis[t] = any_view ? 1 : 0;
     const int rows = (int)min((int64_t)256, range_end - g0);
     // contiguous degree-3 layout: the CTA's rows are one 16-byte aligned span -> one bulk async copy
@@ -185,17 +219,28 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         // of a Gaussian sees every view's duv and radius here, so the statistics come out already summed over ranks
         float st_len = 0.f, st_cnt = 0.f, st_rad = 0.f;
 
-        for (int b = 0; b < cf.num_views; ++b) {
-            const int rad_b = a.v_radii[b][g];
-            if (rad_b == 0) continue;
+        // The views that see the Gaussian, one after the other; the next view's inputs (48 bytes of raster gradient,
+        // the 2D covariance, the clamp bits) are requested before the current view's arithmetic starts.
+        uint32_t rem = vis;
+        int b = __ffs((int)rem) - 1;
+        ViewIn cur = load_view(a, b, g);
+        while (true) {
+            int b_next = -1;
+            ViewIn nxt = cur;
+            if constexpr (MULTI) {
+                rem &= rem - 1;
+                if (rem != 0) {
+                    b_next = __ffs((int)rem) - 1;
+                    nxt = load_view(a, b_next, g);
+                }
+            }
             const D3gsCamera& cam = cf.cameras[b];
             const float* Rt = cam.cam2world_T;
             float Ri[12];
             if constexpr (INST) {     // instance rendering: this Gaussian's camera in its object's frame
                 if (instance_camera(cf, b, g, Ri)) Rt = Ri;
             }
-            const float4* sg4 = reinterpret_cast<const float4*>(a.v_grads[b] + g * D3GS_SPLAT_GRAD_FLOATS);
-            const float4 gA = sg4[0], gB = sg4[1], gC = sg4[2];
+            const float4 gA = cur.gA, gB = cur.gB, gC = cur.gC;
             const float d0 = px - Rt[9], d1 = py - Rt[10], d2 = pz - Rt[11];
             const float pc0 = Rt[0] * d0 + Rt[1] * d1 + Rt[2] * d2;
             const float pc1 = Rt[3] * d0 + Rt[4] * d1 + Rt[5] * d2;
@@ -214,8 +259,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
                 T1[j] = J11 * Rt[3 + j] + J12 * Rt[6 + j];
             }
             // conic -> cov2d (gs3d.py:559-588)
-            const float* cv = a.v_cov2d[b] + g * 3;
-            const float ca = cv[0], cb = cv[1], cc = cv[2];
+            const float ca = cur.ca, cb = cur.cb, cc = cur.cc;
             const float g0c = gA.x, g1c = gA.y, g2c = gA.z;
             const float det = ca * cc - cb * cb;
             const float d2i = 1.0f / (det * det + 1e-8f);
@@ -269,7 +313,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
                 const float ax = gC.x * (0.5f * (float)a.stats.width * lb), ay = gC.y * (0.5f * (float)a.stats.height * lb);
                 st_len += sqrtf(ax * ax + ay * ay);
                 st_cnt += 1.0f;
-                st_rad = fmaxf(st_rad, (float)rad_b / (float)max(a.stats.width, a.stats.height));
+                st_rad = (float)radmax / (float)max(a.stats.width, a.stats.height);
             }
             // pinhole (camera.py:335-371)
             const float du = gC.x * cam.fx, dv = gC.y * cam.fy;
@@ -287,7 +331,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             const float dni = 1.0f / dn;
             const float x = d0 * dni, y = d1 * dni, zz_ = d2 * dni;
             float cg[3] = {gB.x, gB.y, gB.z};
-            const uint8_t m = a.v_ne0[b][g];
+            const uint32_t m = cur.ne0;
             if (cf.clamp_mask_reference_order) {   // bit k gates channel k (render.py:3344-3350)
                 if (m & 1) cg[0] = 0.f;
                 if (m & 2) cg[1] = 0.f;
@@ -350,6 +394,9 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             axyz[0] += dxyz[0] + (ddx - x * dd) * dni;
             axyz[1] += dxyz[1] + (ddy - y * dd) * dni;
             axyz[2] += dxyz[2] + (ddz - zz_ * dd) * dni;
+            if (b_next < 0) break;
+            cur = nxt;
+            b = b_next;
         }
         // Sigma = M M^T (gs3d.py:387-418): dM = 2 dSigma M (dSigma symmetric), ds_j = <dM[:,j], R[:,j]>
         float dM[3][3];
