@@ -73,6 +73,18 @@ def sharded_update(grad_flat: torch.Tensor, param_flat: torch.Tensor, grad_shard
     torch.distributed.all_gather_into_tensor(param_flat, param_flat[lo:hi], group=group)
 
 
+def check_same_count(n: int, device, group=None) -> None:
+    """Data parallel with replicated Gaussians: every rank must hold the same number of them before the first
+    exchange (the buffers the ranks share are cut by index).  Collective; raises on EVERY rank when they differ."""
+    dist = torch.distributed
+    t = torch.tensor([n, -n], dtype=torch.int64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    lo, hi = int(t[0].item()), -int(t[1].item())
+    if lo != hi:
+        raise RuntimeError(f"data-parallel ranks hold different Gaussian counts (between {lo} and {hi}; this rank {n}): "
+                           "the replicas must be identical before the first gradient exchange")
+
+
 class _DeviceSpan:
     """Lets torch alias raw device memory (``torch.as_tensor`` reads ``__cuda_array_interface__``)."""
 
@@ -243,6 +255,8 @@ class SplatTrainer:
             self.rank = torch.distributed.get_rank(process_group)
         self.sharded = (self.world > 1) if shard_optimizer is None else (bool(shard_optimizer) and self.world > 1)
         n, dev = len(model), model.xyz.device
+        if self.world > 1:
+            check_same_count(n, dev, process_group)
         layout, total = flat_layout(n)
         self.flat_total = total
         self.shard_len, padded = shard_layout(total, self.world) if self.sharded else (total, total)

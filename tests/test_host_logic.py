@@ -293,3 +293,34 @@ def test_end_of_iteration_fires_like_the_reference_period_events():
     resets = [s for s, ev in fired.items() if "reset_opacity" in ev]
     assert resets == [750, 1500, 2250, 3000]
     assert fired[750] == ["up_sh", "update_gs", "reset_opacity"]      # the reference's registration order
+
+
+def _count_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from d3gs_research_b200.trainer import check_same_count
+    check_same_count(1000, torch.device("cpu"))                 # equal counts pass
+    try:
+        check_same_count(1000 + 4 * rank, torch.device("cpu"))  # rank 1 holds four more
+        q.put((rank, "no error"))
+    except RuntimeError as e:
+        q.put((rank, "between 1000 and 1004" in str(e)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_gaussian_counts_are_refused_gloo():
+    """The host check before the first exchange: all ranks raise, with the range of counts in the message."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_count_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=180) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True), (1, True)], got
