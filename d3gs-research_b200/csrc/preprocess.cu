@@ -7,6 +7,8 @@
 //
 // Reference semantics: d3sim/algos/d3gs/render.py:250-681 (proxy branch 421-476, 569-619),
 // 739-840, 1017-1327; math from d3sim/csrc/gs3d.py and d3sim/csrc/camera.py:307-333.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace d3gs {
@@ -88,15 +90,61 @@ __device__ __forceinline__ bool aabb_overlap_obb(float minx, float miny, float m
 }
 
 // The tiles that the early filter keeps (render.py:1017-1327) intersected with the 3-sigma rect
-// (render.py:594, 814-817).  filter: 0 NONE, 1 AABB, 3 OBB; OBB_DFVT (4) is mapped to OBB by the host (same
+// (render.py:594, 814-817).  filter: 0 NONE, 1 AABB, 2 ELLIPSE, 3 OBB; OBB_DFVT (4) is mapped to OBB by the host (same
 // tile set by construction of the traversal).  The walk covers the box [bmin, bmax) row by row: the rect
 // itself for NONE, the bounding box of the alpha >= alpha_eps ellipse otherwise.
-struct TileWalk {
+// ELL: the walk can also evaluate the exact ellipse test (filter 2); it then keeps the conic and the bound, four
+// more live registers, which is why the kernels that never need it are instantiated without.
+struct EllipseState {
+    float cx, cy, cz, bound;
+};
+struct NoEllipseState {};
+
+// gs3d.py:1149-1178, 1210-1229 (the _v2 forms, offsets taken relative to the centre): where the ellipse
+// cx dx^2 + 2 cy dx dy + cz dy^2 = -bound crosses the horizontal line y (the two x) or the vertical line x (the two y);
+// (-1, -1) when it does not
+__device__ __forceinline__ void ellipse_cross_y(const EllipseState& e, float y, float u, float v, float* r) {
+    y -= v;
+    const float val = -e.bound * e.cx - e.cx * e.cz * y * y + e.cy * e.cy * y * y;
+    const float sq = f_sqrt(fmaxf(0.0f, val));
+    r[0] = val >= 0.0f ? u + (-e.cy * y - sq) / e.cx : -1.0f;
+    r[1] = val >= 0.0f ? u + (-e.cy * y + sq) / e.cx : -1.0f;
+}
+__device__ __forceinline__ void ellipse_cross_x(const EllipseState& e, float x, float u, float v, float* r) {
+    x -= u;
+    const float val = -e.bound * e.cz - e.cx * e.cz * x * x + e.cy * e.cy * x * x;
+    const float sq = f_sqrt(fmaxf(0.0f, val));
+    r[0] = val >= 0.0f ? v + (-e.cy * x - sq) / e.cz : -1.0f;
+    r[1] = val >= 0.0f ? v + (-e.cy * x + sq) / e.cz : -1.0f;
+}
+// gs3d.py:1078-1117: an edge of the box is crossed, or the ellipse covers the box, or the box holds the centre
+__device__ __forceinline__ bool ellipse_overlaps_box(const EllipseState& e, float px0, float py0, float px1, float py1,
+                                                     float u, float v) {
+    float x0[2], x1[2], y0[2], y1[2];
+    ellipse_cross_x(e, px0, u, v, x0);
+    ellipse_cross_x(e, px1, u, v, x1);
+    ellipse_cross_y(e, py0, u, v, y0);
+    ellipse_cross_y(e, py1, u, v, y1);
+    bool hit = (x0[0] >= py0 && x0[0] <= py1) || (x0[1] >= py0 && x0[1] <= py1);
+    hit |= (x1[0] >= py0 && x1[0] <= py1) || (x1[1] >= py0 && x1[1] <= py1);
+    hit |= (y0[0] >= px0 && y0[0] <= px1) || (y0[1] >= px0 && y0[1] <= px1);
+    hit |= (y1[0] >= px0 && y1[0] <= px1) || (y1[1] >= px0 && y1[1] <= px1);
+    bool cover = x0[0] <= py0 && x0[1] >= py1;
+    cover &= x1[0] <= py0 && x1[1] >= py1;
+    cover &= y0[0] <= px0 && y0[1] >= px1;
+    cover &= y1[0] <= px0 && y1[1] >= px1;
+    const bool centre = px0 <= u && px1 >= u && py0 <= v && py1 >= v;
+    return hit || cover || centre;
+}
+
+template <bool ELL>
+struct TileWalkT {
     int filter, tile_px;
     float ts;
     int rmin[2], rmax[2], bmin[2], bmax[2];
     float half[2], ox, oy;
     Obb obb;
+    typename std::conditional<ELL, EllipseState, NoEllipseState>::type ell;
 
     __device__ __forceinline__ void init(int filter_, const TileGeom& tg, int tile_px_, float alpha_eps, float u, float v,
                                          float ca, float cb, float cc, float opacity, const int* rmin_, const int* rmax_) {
@@ -116,6 +164,12 @@ struct TileWalk {
         bmax[1] = clampi(f2i_sat(ceilf(div_ts(v + half[1], tg))), 0, tg.tiles_y);
         ox = u - (float)bmin[0] * tg.ts;
         oy = v - (float)bmin[1] * tg.ts;
+        if constexpr (ELL) {
+            if (filter == 2) {
+                ell.cx = ca; ell.cy = cb; ell.cz = cc; ell.bound = bound;
+                return;
+            }
+        }
         obb = ellipse_bound_obb(ca, cb, cc, bound);
     }
     __device__ __forceinline__ int width() const { return max(bmax[0] - bmin[0], 0); }
@@ -129,6 +183,9 @@ struct TileWalk {
             bool xo = (ox - half[0]) <= px1 && (ox + half[0]) >= px0;
             bool yo = (oy - half[1]) <= py1 && (oy + half[1]) >= py0;
             ok = xo && yo;
+        } else if (ELL && filter == 2) {
+            if constexpr (ELL) ok = ellipse_overlaps_box(ell, px0, py0, px1, py1, ox, oy);   // render.py:1277-1297
+            else ok = false;
         } else {
             ok = aabb_overlap_obb(px0, py0, px1, py1, obb, ox, oy);
         }
@@ -215,8 +272,9 @@ constexpr int kRow = 45;   // shared-memory row length in floats (odd: conflict-
 // sectors per request.
 // 64 registers (4 CTAs of 256 threads per SM): with 78 the kernel lost a fifth of its throughput
 // INST: instance rendering, a per-Gaussian camera (12 more live registers; an instantiation of its own)
-template <int DEG, bool INST>
-__global__ void __launch_bounds__(256, INST ? 3 : 4) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+template <int DEG, bool INST, bool ELL>
+__global__ void __launch_bounds__(256, (INST || ELL) ? 3 : 4) preprocess_fwd_kernel(const __grid_constant__ PrepArgs a) {
+    using TileWalk = TileWalkT<ELL>;
     constexpr int NB = (DEG + 1) * (DEG + 1);
     constexpr int NR3 = (NB - 1) * 3;
     __shared__ __align__(128) float s_rest[NR3 > 0 ? 256 * kRow : 4];
@@ -513,8 +571,9 @@ struct DupArgs {
 // BUCKET == false: key = tile << shift | depth bits and value = flat index at the Gaussian's scanned offset
 // (render.py:739-840).  BUCKET == true: the pair becomes one 8-byte entry, depth bits << 32 | flat index, at a
 // position drawn from the tile's cursor inside the tile's range.
-template <bool BUCKET>
+template <bool BUCKET, bool ELL>
 __global__ void __launch_bounds__(256) duplicate_keys_kernel(const __grid_constant__ DupArgs a) {
+    using TileWalk = TileWalkT<ELL>;
     // entries sized before the pair count was known: write nothing when the pairs do not fit (the caller repeats)
     if (BUCKET && a.total_pairs != nullptr && *a.total_pairs > a.pair_capacity) return;
     const int64_t total = a.num * a.cfg.num_views;
@@ -651,9 +710,8 @@ int32_t check_cfg(const D3gsOpConfig* cfg) {
     D3GS_REQUIRE(cfg->num_views >= 1 && cfg->num_views <= D3GS_MAX_VIEWS, "num_views %d outside [1,%d]",
                  cfg->num_views, D3GS_MAX_VIEWS);
     D3GS_REQUIRE(cfg->sh_degree >= 0 && cfg->sh_degree <= 3, "sh_degree %d outside [0,3]", cfg->sh_degree);
-    D3GS_REQUIRE(cfg->early_filter_algo == 0 || cfg->early_filter_algo == 1 || cfg->early_filter_algo == 3 ||
-                     cfg->early_filter_algo == 4,
-                 "early_filter_algo %d unsupported (NONE=0, AABB=1, OBB=3, OBB_DFVT=4)", cfg->early_filter_algo);
+    D3GS_REQUIRE(cfg->early_filter_algo >= 0 && cfg->early_filter_algo <= 4,
+                 "early_filter_algo %d unsupported (NONE=0, AABB=1, ELLIPSE=2, OBB=3, OBB_DFVT=4)", cfg->early_filter_algo);
     D3GS_REQUIRE(cfg->key_shift_bits == 0 || cfg->key_shift_bits == 32 || cfg->key_shift_bits == 18,
                  "key_shift_bits must be 32 (64-bit keys) or 18 (32-bit keys), got %d", cfg->key_shift_bits);
     if (cfg->key_shift_bits == 18) {
@@ -703,22 +761,27 @@ extern "C" int32_t d3gs_preprocess_forward(const D3gsOpConfig* cfg, const D3gsMo
     a.status = status;
     a.hooks = test_hooks();
     dim3 grid((unsigned)div_up64(total, 256));
-    if (cfg->instance_id != nullptr) {
+    if (cfg->instance_id != nullptr)
         D3GS_REQUIRE(cfg->instance2world_T != nullptr && cfg->num_instance > 0, "instance rendering needs instance2world_T");
-        switch (cfg->sh_degree) {
-            case 0: preprocess_fwd_kernel<0, true><<<grid, 256, 0, s>>>(a); break;
-            case 1: preprocess_fwd_kernel<1, true><<<grid, 256, 0, s>>>(a); break;
-            case 2: preprocess_fwd_kernel<2, true><<<grid, 256, 0, s>>>(a); break;
-            default: preprocess_fwd_kernel<3, true><<<grid, 256, 0, s>>>(a); break;
-        }
-    } else {
-        switch (cfg->sh_degree) {
-            case 0: preprocess_fwd_kernel<0, false><<<grid, 256, 0, s>>>(a); break;
-            case 1: preprocess_fwd_kernel<1, false><<<grid, 256, 0, s>>>(a); break;
-            case 2: preprocess_fwd_kernel<2, false><<<grid, 256, 0, s>>>(a); break;
-            default: preprocess_fwd_kernel<3, false><<<grid, 256, 0, s>>>(a); break;
-        }
+    // instances of their own for instance rendering and for the exact ellipse filter (both keep more state live)
+#define D3GS_LAUNCH_PREP(DEG)                                                                           \
+    do {                                                                                                \
+        if (cfg->instance_id != nullptr) {                                                              \
+            if (ellipse) preprocess_fwd_kernel<DEG, true, true><<<grid, 256, 0, s>>>(a);                \
+            else preprocess_fwd_kernel<DEG, true, false><<<grid, 256, 0, s>>>(a);                       \
+        } else {                                                                                        \
+            if (ellipse) preprocess_fwd_kernel<DEG, false, true><<<grid, 256, 0, s>>>(a);               \
+            else preprocess_fwd_kernel<DEG, false, false><<<grid, 256, 0, s>>>(a);                      \
+        }                                                                                               \
+    } while (0)
+    const bool ellipse = a.cfg.early_filter_algo == 2;
+    switch (cfg->sh_degree) {
+        case 0: D3GS_LAUNCH_PREP(0); break;
+        case 1: D3GS_LAUNCH_PREP(1); break;
+        case 2: D3GS_LAUNCH_PREP(2); break;
+        default: D3GS_LAUNCH_PREP(3); break;
     }
+#undef D3GS_LAUNCH_PREP
     D3GS_LAUNCH_CHECK("preprocess_fwd_kernel");
     return D3GS_OK;
 }
@@ -739,7 +802,10 @@ extern "C" int32_t d3gs_duplicate_keys(const D3gsOpConfig* cfg, int64_t num, con
     a.keys = keys;
     a.values = values;
     a.num = num;
-    duplicate_keys_kernel<false><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    if (a.cfg.early_filter_algo == 2)
+        duplicate_keys_kernel<false, true><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    else
+        duplicate_keys_kernel<false, false><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("duplicate_keys_kernel");
     return D3GS_OK;
 }
@@ -765,7 +831,10 @@ extern "C" int32_t d3gs_bucket_emit(const D3gsOpConfig* cfg, int64_t num, const 
     a.num = num;
     a.total_pairs = pair_capacity > 0 ? total_pairs : nullptr;
     a.pair_capacity = pair_capacity;
-    duplicate_keys_kernel<true><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    if (a.cfg.early_filter_algo == 2)
+        duplicate_keys_kernel<true, true><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
+    else
+        duplicate_keys_kernel<true, false><<<(unsigned)div_up64(total, 256), 256, 0, (cudaStream_t)stream>>>(a);
     D3GS_LAUNCH_CHECK("duplicate_keys_kernel<bucket>");
     return D3GS_OK;
 }

@@ -64,7 +64,7 @@ typedef struct D3gsOpConfig {
     float alpha_eps;                        /* 1/255 */
     float transmittance_eps;                /* 1e-4 */
     float scale_global;                     /* inference only */
-    int32_t early_filter_algo;              /* EarlyFilterAlgo: 0 NONE, 1 AABB, 3 OBB, 4 OBB_DFVT */
+    int32_t early_filter_algo;              /* EarlyFilterAlgo: 0 NONE, 1 AABB, 2 ELLIPSE, 3 OBB, 4 OBB_DFVT */
     int32_t sh_degree;                      /* active degree 0..3 (model.cur_sh_degree) */
     int32_t training;
     int32_t clamp_mask_reference_order;     /* 1: gate dcolor like render.py:3344-3350 */

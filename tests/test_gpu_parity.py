@@ -38,8 +38,8 @@ def _run_forward(sc, device, early_filter, training=True, binning="sort", **cfg_
     return op, model, cams, out, ctx, ocfg, osc, ref
 
 
-@pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB,
-                                          EarlyFilterAlgo.OBB_DFVT])
+@pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.ELLIPSE,
+                                          EarlyFilterAlgo.OBB, EarlyFilterAlgo.OBB_DFVT])
 @pytest.mark.parametrize("sh_degree,views", [(3, 1), (0, 1), (2, 3)])
 @pytest.mark.parametrize("binning", ["sort", "bucket"])
 def test_binning_bit_exact(cuda_device, early_filter, sh_degree, views, binning):
@@ -95,7 +95,8 @@ def test_binning_bit_exact_32bit_keys(cuda_device, views):
     assert_close(out.color.cpu().numpy(), ref.color, IMG_TOL, "color")
 
 
-@pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.OBB_DFVT])
+@pytest.mark.parametrize("early_filter", [EarlyFilterAlgo.NONE, EarlyFilterAlgo.AABB, EarlyFilterAlgo.ELLIPSE,
+                                          EarlyFilterAlgo.OBB_DFVT])
 @pytest.mark.parametrize("binning", ["sort", "bucket"])
 def test_binning_bit_exact_large_gaussians(cuda_device, early_filter, binning):
     """Gaussians that cover hundreds of tiles take the warp-cooperative paths of the tile count and of the key

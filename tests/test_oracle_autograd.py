@@ -10,7 +10,8 @@ from parity_utils import oracle_scene, small_scene
 
 
 @pytest.mark.parametrize("deg,early_filter,ref_order,aa", [(0, 0, True, False), (3, 0, True, False), (3, 3, True, False),
-                                                             (2, 1, False, False), (1, 0, True, True), (3, 4, True, True)])
+                                                             (2, 1, False, False), (1, 0, True, True), (3, 4, True, True),
+                                                             (2, 2, True, False)])
 def test_oracle_matches_dense_autograd(deg, early_filter, ref_order, aa):
     """aa: enable_anti_aliasing, the opacity compensation of render.py:449-462 and its gradient (3295-3309)."""
     W, H = 48, 40
@@ -128,3 +129,22 @@ def test_oracle_custom_features_match_dense_autograd():
     for k in ("xyz", "quat", "scale", "opacity"):
         ref = params[k].grad.numpy()
         assert np.abs(res.grads[k] - ref).max() / np.abs(ref).max() < 2e-4, k
+
+
+def test_early_filters_drop_only_tiles_that_contribute_nothing():
+    """The filters (render.py:1017-1327) only remove (tile, splat) pairs in which no pixel reaches alpha_eps, so the
+    image is the unfiltered one bit for bit; the exact ellipse test (ELLIPSE) keeps no more pairs than its
+    bounding boxes (AABB, OBB) do."""
+    sc = small_scene(n=3000, width=200, height=136, sh_degree=1, seed=6, log_scale=("normal", -2.2, 0.7))
+    osc = oracle_scene(sc)
+    res = {f: O.forward(O.OpConfig(width=200, height=136, sh_degree=1, early_filter=f), osc) for f in (0, 1, 2, 3)}
+    for f in (1, 2, 3):
+        np.testing.assert_array_equal(res[f].color.view(np.uint32), res[0].color.view(np.uint32))
+        np.testing.assert_array_equal(res[f].T.view(np.uint32), res[0].T.view(np.uint32))
+    k = {f: r.num_rendered for f, r in res.items()}
+    assert k[2] <= k[3] <= k[0] and k[2] <= k[1] <= k[0] and k[2] < 0.9 * k[0], k
+    # pair by pair: what ELLIPSE keeps, both boxes keep
+    for other in (1, 3):
+        kept = set(zip((res[2].sorted_keys >> np.uint64(32)).tolist(), res[2].sorted_ids.tolist()))
+        box = set(zip((res[other].sorted_keys >> np.uint64(32)).tolist(), res[other].sorted_ids.tolist()))
+        assert kept <= box, other
