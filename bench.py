@@ -243,6 +243,9 @@ def algorithmic_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, train
         # single-rank fused path: the per-unit figures of the two stages it replaces, so that the iteration total
         # stays comparable between update paths (see moved_bytes for what the launch itself has to move)
         "preprocess_bwd_adam": (53 + 36) * V + 4 * N + 236 * V + 236 * N + 1652 * N + 12 * N + 24 * N,
+        # data parallel, backward fused into the exchange: per rank, what the replicated pipeline would move for
+        # it -- the backward of its own view and Adam over all Gaussians (the same figure as the single-rank launch)
+        "preprocess_bwd_adam_peers": (53 + 36) * V + 4 * N + 236 * V + 236 * N + 1652 * N + 12 * N + 24 * N,
         "densify_stats": 0,
     }
     return float(table.get(stage, 0.0))
@@ -283,8 +286,8 @@ def moved_bytes(stage: str, N: int, V: int, K: int, P: int, Tn: int, training: b
 # A full-size launch is too large to capture under a 40-pass replay, so the figure is scaled to the bench's
 # workload by the ratio of algorithmic bytes (traffic of these kernels grows with the units processed).
 NCU_SMALL_CASE = dict(N=750000, V=574917, K=1068256, P=2073600, Tn=8160)
-NCU_SMALL_TRAFFIC = {"raster_bwd": 151.38e6, "raster_fwd": 43.82e6, "adam_stats": 1244.93e6, "preprocess_bwd": 351.21e6,
-                     "preprocess_fwd": 252.27e6, "preprocess_bwd_adam": 1103.29e6, "l1_dssim": 224.19e6, "pack_splats": 35.39e6, "duplicate_keys": 21.03e6}
+NCU_SMALL_TRAFFIC = {"raster_bwd": 152.06e6, "raster_fwd": 42.86e6, "adam_stats": 1244.93e6, "preprocess_bwd": 351.21e6,
+                     "preprocess_fwd": 253.40e6, "preprocess_bwd_adam": 1104.75e6, "l1_dssim": 224.19e6, "pack_splats": 35.39e6, "duplicate_keys": 21.03e6}
 
 
 def ncu_traffic(stage: str, N: int, V: int, K: int, P: int, Tn: int):
