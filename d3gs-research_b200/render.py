@@ -948,8 +948,12 @@ def rasterize_gaussians(model: GaussianModelOriginBase, cameras: BasicPinholeCam
 def rasterize_gaussians_dynamic(model, cameras, op: GaussianSplatOp, training=False, uv_grad_holder=None,
                                 instance2world_T=None, custom_features=None, prep_input_tensors=None,
                                 prep_inputs=None, mask=None) -> GaussianSplatOutput:
-    """render.py:3840-3891.  The proxy extension inputs are not built; without them this is
-    ``rasterize_gaussians``."""
+    """render.py:3840-3891: the entry point of models whose parameters carry user-defined (proxy) fields.  The proxy
+    extension inputs are user code spliced into JIT kernels in the reference and are not built; without them this
+    is ``rasterize_gaussians`` with the reference's two preconditions."""
+    assert op._cfg.use_proxy_model, "only v2 (proxy) is supported"                      # render.py:3852
+    if instance2world_T is not None:
+        assert isinstance(cameras, CameraBundle) and cameras.frame_ids is not None      # render.py:3859-3860
     if prep_input_tensors is not None or prep_inputs is not None:
         raise NotImplementedError("user-defined proxy inputs are not built")
     return rasterize_gaussians(model, cameras, op, training, uv_grad_holder, instance2world_T, custom_features, mask)

@@ -951,3 +951,16 @@ def test_instance_rendering_forward_and_backward(cuda_device, views):
     out2 = d3.rasterize_gaussians(m2, cams, d3.GaussianSplatOp(op_cfg), training=True, instance2world_T=T_dev)
     (out2.color * drgb.to(cuda_device)).sum().backward()
     assert_close(m2.xyz.grad.cpu().numpy(), ref.grads["xyz"], GRAD_TOL, "autograd grad xyz", floor_frac=1e-2)
+    # render.py:3840-3891: the "dynamic" entry point is the same call for a model without proxy fields; it wants a
+    # camera bundle with frame ids when instances are rendered, and refuses user-defined proxy inputs
+    op3 = d3.GaussianSplatOp(op_cfg)
+    if views > 1:
+        out3 = d3.rasterize_gaussians_dynamic(model, cams, op3, training=True, instance2world_T=T_dev)
+        assert torch.equal(out3.color, out.color) and torch.equal(out3.n_contrib, out.n_contrib)
+    else:
+        with pytest.raises(AssertionError):
+            d3.rasterize_gaussians_dynamic(model, cams, op3, training=True, instance2world_T=T_dev)
+        out3 = d3.rasterize_gaussians_dynamic(model, cams, op3, training=True)
+        assert out3.color.shape == out.color.shape
+    with pytest.raises(NotImplementedError):
+        d3.rasterize_gaussians_dynamic(model, cams, op3, prep_inputs={"x": 1})
