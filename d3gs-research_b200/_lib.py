@@ -123,6 +123,12 @@ SIGNATURES = {
     "d3gs_sort_workspace_bytes": (_SZ, [_I64, _I32, _I32]),
     "d3gs_sort_pairs": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, C.POINTER(_I32), _P, _P]),
     "d3gs_bucket_sort_capacity": (_I64, []),
+    "d3gs_sparse_flags": (_I32, [_P, _I64, _I32, _I32, _P, _P]),
+    "d3gs_sparse_compact": (_I32, [C.POINTER(SplatContext), _I64, _I32, _P, C.POINTER(SplatContext), _P, _P, _P]),
+    "d3gs_sparse_remap": (_I32, [_P, _I64, _P, _P]),
+    "d3gs_sparse_expand": (_I32, [_I64, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "d3gs_flagged_indices": (_I32, [_P, _P, _I64, _P, _P]),
+    "d3gs_gather_rows": (_I32, [_P, _I32, _P, _I64, _P, _P]),
     "d3gs_simple_knn_workspace_bytes": (C.c_size_t, [_I64, _I32]),
     "d3gs_simple_knn": (_I32, [_P, _I64, _I64, _I32, _I32, _P, _P, _P, _P, C.c_size_t, _P, _P]),
     "d3gs_bucket_prepare": (_I32, [_P, _P, _I64, _P, _P, _P, _I64, _P]),

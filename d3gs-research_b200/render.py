@@ -53,6 +53,10 @@ class GaussianSplatOpContext:
     # for every pass (records with those values in the colour slots, their [B,H,W,3] blend)
     aux_passes: list | None = None
     num_custom_feat: int = 0
+    # sparse_mode: the per-item tensors above hold the kept items only; which Gaussian / view each is, and N
+    sparse_gaussian_ids: torch.Tensor | None = None
+    sparse_batch_ids: torch.Tensor | None = None
+    num_gaussians: int = 0
 
 
 @dataclasses.dataclass
@@ -683,8 +687,50 @@ class GaussianSplatOp:
                                      sh_to_rgb_ne_0=sh_ne0, splat_records=records, tile_order=tile_order,
                                      records_by_id=gather,
                                      raster_color=out_color if output.color is not out_color else None,
-                                     aux_passes=aux_passes, num_custom_feat=nfeat)
+                                     aux_passes=aux_passes, num_custom_feat=nfeat, num_gaussians=num)
+        if self._cfg.sparse_mode:
+            self._compact_context(output, ctx, B, num, stream)
         return output, ctx
+
+    def _compact_context(self, output: GaussianSplatOutput, ctx: GaussianSplatOpContext, B: int, num: int, stream) -> None:
+        """sparse_mode (render.py:235-238, 478-499, 622-637): what is kept for the backward holds the visible
+        (view, Gaussian) items only, in flat-index order; ``output.sparse_gaussian_ids`` / ``sparse_batch_ids`` name
+        them and ``output.radii`` is compact too.  One more device->host read (the kept count, render.py:635)."""
+        lib = self._lib
+        assert ctx.records_by_id and not ctx.aux_passes, "sparse mode: no depth / custom-feature passes, gathered records"
+        dev = ctx.radii.device
+        BN = B * num
+        i32, f32 = torch.int32, torch.float32
+        flags = torch.empty(BN, dtype=i32, device=dev)
+        _lib.check(lib.d3gs_sparse_flags(ctx.radii.data_ptr(), num, B, 0, flags.data_ptr(), stream), "d3gs_sparse_flags")
+        scan = torch.empty(BN, dtype=i32, device=dev)
+        total = torch.zeros(1, dtype=torch.int64, device=dev)
+        ws = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(BN), dev)
+        _lib.check(lib.d3gs_scan_tiles(flags.data_ptr(), scan.data_ptr(), BN, total.data_ptr(), ws.data_ptr(), ws.numel(),
+                                       self._sync_words(dev).data_ptr() + 8, stream), "d3gs_scan_tiles")
+        kept = int(total.item())
+        new = dict(radii=torch.empty(kept, dtype=i32, device=dev), depths=torch.empty(kept, dtype=f32, device=dev),
+                   uvs=torch.empty([kept, 2], dtype=f32, device=dev),
+                   conic_opacity=torch.empty([kept, 4], dtype=f32, device=dev),
+                   rgb_gaussian=torch.empty([kept, 3], dtype=f32, device=dev),
+                   cov2d_vecs=torch.empty([kept, 3], dtype=f32, device=dev),
+                   sh_to_rgb_ne_0=torch.empty([kept], dtype=torch.uint8, device=dev),
+                   splat_records=torch.empty([kept, 12], dtype=f32, device=dev))
+        gids = torch.empty(kept, dtype=i32, device=dev)
+        bids = torch.empty(kept, dtype=i32, device=dev)
+        dense = self._ctx_struct(None, ctx.radii, ctx.depths, ctx.uvs, ctx.conic_opacity, ctx.rgb_gaussian, ctx.cov2d_vecs,
+                                 ctx.sh_to_rgb_ne_0, None, ctx.splat_records)
+        comp = self._ctx_struct(None, new["radii"], new["depths"], new["uvs"], new["conic_opacity"], new["rgb_gaussian"],
+                                new["cov2d_vecs"], new["sh_to_rgb_ne_0"], None, new["splat_records"])
+        _lib.check(lib.d3gs_sparse_compact(C.byref(dense), num, B, scan.data_ptr(), C.byref(comp), gids.data_ptr(),
+                                           bids.data_ptr(), stream), "d3gs_sparse_compact")
+        ids = ctx.gaussian_idx_sorted
+        _lib.check(lib.d3gs_sparse_remap(ids.data_ptr(), ids.shape[0], scan.data_ptr(), stream), "d3gs_sparse_remap")
+        for k, v in new.items():
+            setattr(ctx, k, v)
+        ctx.sparse_gaussian_ids, ctx.sparse_batch_ids = gids, bids
+        output.radii = new["radii"]
+        output.sparse_gaussian_ids, output.sparse_batch_ids = gids, bids
 
     # ---- raster backward (render.py:1329-2316 with grad) -----------------------------------------
     def rasterize_forward_backward(self, model, ctx: GaussianSplatOpContext, out: GaussianSplatOutput,
@@ -710,7 +756,10 @@ class GaussianSplatOp:
             packed = self.external["packed"]
             assert packed.shape == (BN, 12) and packed.is_contiguous()
         else:
-            packed = torch.empty([BN, 12], dtype=torch.float32, device=dev)
+            # sparse mode: the kept items are not a whole number of Gaussians per view, so the entry point's own
+            # zero fill (num * B rows) may stop short of the last rows
+            alloc = torch.zeros if ctx.sparse_gaussian_ids is not None else torch.empty
+            packed = alloc([BN, 12], dtype=torch.float32, device=dev)
         ocfg = _lib.OpConfig()
         ocfg.width, ocfg.height, ocfg.tile_x, ocfg.tile_y = W, H, 16, 16
         ocfg.alpha_eps, ocfg.transmittance_eps = self._cfg.alpha_eps, self._cfg.transmittance_eps
@@ -808,6 +857,24 @@ class GaussianSplatOp:
         ocfg = self._op_config(model, cameras, True, instance2world_T)
         B = ocfg.num_views
         num = len(model)
+        sparse = ctx.sparse_gaussian_ids is not None
+        if sparse:
+            # render.py:2857-2903: spread the kept rows over dense arrays of what the preprocess backward reads, run
+            # it, then hand out the gradient rows of the Gaussians that some view saw
+            assert adam_segments is None and grad_out is None, "sparse mode returns a compact gradient model"
+            kept = ctx.sparse_gaussian_ids.shape[0]
+            d_radii = torch.empty(B * num, dtype=torch.int32, device=dev)
+            d_cov2d = torch.empty([B * num, 3], dtype=torch.float32, device=dev)
+            d_ne0 = torch.empty(B * num, dtype=torch.uint8, device=dev)
+            d_packed = torch.empty([B * num, 12], dtype=torch.float32, device=dev)
+            _lib.check(lib.d3gs_sparse_expand(kept, num, B, ctx.sparse_gaussian_ids.data_ptr(), ctx.sparse_batch_ids.data_ptr(),
+                                              ctx.radii.data_ptr(), ctx.cov2d_vecs.data_ptr(), ctx.sh_to_rgb_ne_0.data_ptr(),
+                                              rg.packed.data_ptr(), d_radii.data_ptr(), d_cov2d.data_ptr(), d_ne0.data_ptr(),
+                                              d_packed.data_ptr(), stream), "d3gs_sparse_expand")
+            compact_rg, compact_ctx = rg, ctx
+            ctx = dataclasses.replace(ctx, radii=d_radii, cov2d_vecs=d_cov2d, sh_to_rgb_ne_0=d_ne0, depths=None, uvs=None,
+                                      conic_opacity=None, rgb_gaussian=None)
+            rg = dataclasses.replace(rg, packed=d_packed)
         if adam_segments is not None:
             assert len(adam_segments) == 6 and B == 1
             assert instance2world_T is None, "the backward fused with Adam does not render instances"
@@ -852,6 +919,37 @@ class GaussianSplatOp:
                                                 rg.packed.data_ptr(), C.byref(g), self._sync_words(dev).data_ptr() + 8,
                                                 stream), "d3gs_preprocess_backward")
         self._mark("preprocess_bwd")
+        if sparse:
+            if B == 1:      # render.py:2904-2905: one view, the kept items are the Gaussians
+                unique = compact_ctx.sparse_gaussian_ids
+            else:           # render.py:2864-2903 collects them through a hash table; here: ascending
+                flags = torch.empty(num, dtype=torch.int32, device=dev)
+                _lib.check(lib.d3gs_sparse_flags(d_radii.data_ptr(), num, B, 1, flags.data_ptr(), stream), "d3gs_sparse_flags")
+                scan = torch.empty(num, dtype=torch.int32, device=dev)
+                total = torch.zeros(1, dtype=torch.int64, device=dev)
+                ws = self._ws.get("scan", lib.d3gs_scan_workspace_bytes(num), dev)
+                _lib.check(lib.d3gs_scan_tiles(flags.data_ptr(), scan.data_ptr(), num, total.data_ptr(), ws.data_ptr(),
+                                               ws.numel(), self._sync_words(dev).data_ptr() + 8, stream), "d3gs_scan_tiles")
+                unique = torch.empty(int(total.item()), dtype=torch.int32, device=dev)
+                _lib.check(lib.d3gs_flagged_indices(flags.data_ptr(), scan.data_ptr(), num, unique.data_ptr(), stream),
+                           "d3gs_flagged_indices")
+            rows = unique.shape[0]
+            t = {}
+            for name, v in grad_out.get_all_tensor_fields().items():
+                if not v.is_floating_point():
+                    continue
+                per = v[0].numel() if v.dim() > 1 else 1
+                dst = torch.empty((rows,) + tuple(v.shape[1:]), dtype=v.dtype, device=dev)
+                src = v if v.is_contiguous() else v.contiguous()
+                _lib.check(lib.d3gs_gather_rows(src.data_ptr(), per, unique.data_ptr(), rows, dst.data_ptr(), stream),
+                           "d3gs_gather_rows")
+                t[name] = dst
+            if grad_out.color_sh_base is None:
+                t["color_sh_base"] = None
+            grad_sparse = type(model)(**t, cur_sh_degree=model.cur_sh_degree, act_applied=True)
+            grad_sparse.sparse_gaussian_ids = unique       # not in the reference: which Gaussian every row belongs to
+            duv = compact_rg.packed[:, 8:10]
+            return grad_sparse, ((duv.view(1, -1, 2) if B == 1 else duv) if return_uv_grad else None), rg.dcustom_features
         if return_uv_grad:
             # [B,N,2] strided view of the packed array (the reference returns duv.view(B,-1,2), render.py:3373)
             return grad_out, rg.packed.view(B, -1, 12)[:, :, 8:10], rg.dcustom_features

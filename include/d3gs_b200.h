@@ -478,6 +478,34 @@ int32_t d3gs_refine_apply(const D3gsModel* src, const D3gsModel* dst, const D3gs
 int32_t d3gs_reset_opacity(float* opacity, int64_t num, float thresh, int32_t fused_activations, float* exp_avg,
                            float* exp_avg_sq, void* stream);
 
+/* ---- sparse_mode (config_def.py:119; render.py:235-238, 478-499, 622-637, 2860-2903) ---------------------------------
+ * The tensors kept between forward and backward hold the visible (view, Gaussian) items only, in flat-index order
+ * (the reference: in the arrival order of an atomic counter), with gaussian_ids / batch_ids naming every kept item
+ * (GaussianSplatOutput.sparse_gaussian_ids / sparse_batch_ids).  Forward, after the dense pipeline:
+ *   d3gs_sparse_flags(radii, N, B, 0, flags)            flags[i] = radii[i] != 0 over the B*N items
+ *   d3gs_scan_tiles(flags -> scan, total = kept)        (one read of `kept`, like render.py:635)
+ *   d3gs_sparse_compact(dense ctx, N, B, scan, compact ctx, gaussian_ids, batch_ids)   radii, depths, uvs,
+ *       conic_opacity, rgb_gaussian and, where both contexts hold them, cov2d_vecs, sh_to_rgb_ne_0, records
+ *   d3gs_sparse_remap(sorted_values, K, scan)           sorted indices -> rows of the compact tensors
+ * The raster kernels then run on the compact records unchanged.  Backward: d3gs_raster_backward on the compact
+ * tensors, d3gs_sparse_expand (rows back to zero-filled dense radii / cov2d_vecs / sh_to_rgb_ne_0 / splat_grads),
+ * d3gs_preprocess_backward on those, then the gradient rows of the Gaussians some view saw:
+ *   d3gs_sparse_flags(dense radii, N, B, 1, flags) ; scan ; d3gs_flagged_indices -> unique ids (ascending) ;
+ *   d3gs_gather_rows per gradient tensor. */
+int32_t d3gs_sparse_flags(const int32_t* radii, int64_t num, int32_t views, int32_t per_gaussian, int32_t* flags,
+                          void* stream);
+int32_t d3gs_sparse_compact(const D3gsSplatContext* dense, int64_t num, int32_t views, const int32_t* scan,
+                            const D3gsSplatContext* compact, int32_t* gaussian_ids, int32_t* batch_ids, void* stream);
+int32_t d3gs_sparse_remap(int32_t* sorted_values, int64_t n, const int32_t* scan, void* stream);
+int32_t d3gs_sparse_expand(int64_t kept, int64_t num, int32_t views, const int32_t* gaussian_ids,
+                           const int32_t* batch_ids, const int32_t* radii, const float* cov2d_vecs,
+                           const uint8_t* sh_to_rgb_ne_0, const float* splat_grads, int32_t* dense_radii,
+                           float* dense_cov2d_vecs, uint8_t* dense_sh_to_rgb_ne_0, float* dense_splat_grads,
+                           void* stream);
+int32_t d3gs_flagged_indices(const int32_t* flags, const int32_t* scan, int64_t count, int32_t* out, void* stream);
+int32_t d3gs_gather_rows(const float* src, int32_t row_floats, const int32_t* index, int64_t rows, float* dst,
+                         void* stream);
+
 /* ---- k nearest neighbours of a point cloud (d3sim/algos/d3gs/ops.py:14-183 simple_knn) --------------------------
  * out [n, k] = distances (not squared) from every point to its k nearest OTHER points, ascending; exact.  Used for
  * the initial scales (origin/model.py:26-28: the mean of the three squared distances).  points: n rows of

@@ -964,3 +964,45 @@ def test_instance_rendering_forward_and_backward(cuda_device, views):
         assert out3.color.shape == out.color.shape
     with pytest.raises(NotImplementedError):
         d3.rasterize_gaussians_dynamic(model, cams, op3, prep_inputs={"x": 1})
+
+
+@pytest.mark.parametrize("views", [1, 3])
+def test_sparse_mode_matches_dense(cuda_device, views):
+    """sparse_mode (config_def.py:119; render.py:235-238, 478-499, 2860-2903): the tensors kept for the backward and
+    the returned gradient model hold the visible items / the Gaussians some view saw; values are the dense ones."""
+    sc = small_scene(n=5000, width=200, height=136, sh_degree=2, seed=37, views=views)
+    model = gpu_model(sc, cuda_device)
+    model.act_applied = True
+    cams = gpu_cameras(sc, cuda_device)
+    n = sc["cfg"].n
+    res = {}
+    for sparse in (False, True):
+        op = d3.GaussianSplatOp(d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, sparse_mode=sparse))
+        out, ctx = op.forward(model, cams, training=True)
+        g = torch.Generator(device="cpu").manual_seed(5)
+        drgb = torch.randn(out.color.shape, generator=g).to(cuda_device)
+        gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=drgb, dT=None), return_uv_grad=True)
+        torch.cuda.synchronize()
+        res[sparse] = (out, ctx, gm, duv)
+    (od, cd, gd, duvd), (os_, cs, gs, duvs) = res[False], res[True]
+    assert torch.equal(os_.color, od.color) and torch.equal(os_.T, od.T) and torch.equal(os_.n_contrib, od.n_contrib)
+    flat = torch.nonzero(cd.radii != 0).flatten()
+    assert 100 < flat.numel() < views * n
+    assert torch.equal(os_.sparse_gaussian_ids.long(), flat % n) and torch.equal(os_.sparse_batch_ids.long(), flat // n)
+    assert os_.radii.shape[0] == flat.numel() and torch.equal(os_.radii, cd.radii[flat])
+    for name in ("depths", "uvs", "conic_opacity", "rgb_gaussian", "cov2d_vecs", "sh_to_rgb_ne_0", "splat_records"):
+        assert torch.equal(getattr(cs, name), getattr(cd, name)[flat]), name
+    # the sorted lists are the dense ones with the indices renumbered
+    assert torch.equal(flat[cs.gaussian_idx_sorted.long()], cd.gaussian_idx_sorted.long())
+    assert torch.equal(cs.workload_ranges, cd.workload_ranges)
+    # gradients: rows of the Gaussians some view saw, ascending; everything else is zero in the dense model
+    seen = torch.nonzero((cd.radii.view(views, n) != 0).any(0)).flatten()
+    assert torch.equal(gs.sparse_gaussian_ids.long(), seen) and len(gs) == seen.numel()
+    for attr in ("xyz", "quaternion_xyzw", "scale", "opacity", "color_sh_base", "color_sh"):
+        dense = getattr(gd, attr)
+        assert_close(getattr(gs, attr).cpu().numpy(), dense[seen].cpu().numpy(), 1e-4, f"sparse grad {attr}", floor_frac=1e-3)
+        rest = torch.ones(n, dtype=torch.bool, device=cuda_device)
+        rest[seen] = False
+        assert not dense[rest].any()
+    got = duvs.reshape(-1, 2).cpu().numpy()
+    assert_close(got, duvd.reshape(-1, 2)[flat].cpu().numpy(), 1e-4, "sparse duv", floor_frac=1e-3)

@@ -23,7 +23,7 @@ def test_config_defaults_follow_reference():
 
 
 @pytest.mark.parametrize("kw", [dict(transmittance_is_double=True), dict(move_opacity_in_grad_to_prep=True),
-                                dict(sparse_mode=True), dict(tile_size=(8, 8)), dict(tile_size=(16, 8))])
+                                dict(tile_size=(8, 8)), dict(tile_size=(16, 8))])
 def test_unsupported_options_raise_at_construction(kw):
     from d3gs_research_b200.render import GaussianSplatOp
     with pytest.raises(NotImplementedError):
