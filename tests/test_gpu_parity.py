@@ -975,10 +975,12 @@ def test_sparse_mode_matches_dense(cuda_device, views):
     model.act_applied = True
     cams = gpu_cameras(sc, cuda_device)
     n = sc["cfg"].n
+    # the scene's Gaussians all lie in view: a mask (render.py:270-272, non-zero = skip) takes a third of the items out
+    mask = (torch.rand(views * n, generator=torch.Generator().manual_seed(2)) < 0.33).to(cuda_device)
     res = {}
     for sparse in (False, True):
         op = d3.GaussianSplatOp(d3.GaussianSplatConfig(early_filter_algo=EarlyFilterAlgo.OBB_DFVT, sparse_mode=sparse))
-        out, ctx = op.forward(model, cams, training=True)
+        out, ctx = op.forward(model, cams, training=True, mask=mask)
         g = torch.Generator(device="cpu").manual_seed(5)
         drgb = torch.randn(out.color.shape, generator=g).to(cuda_device)
         gm, duv, _ = op.backward(model, cams, ctx, out, GaussianSplatGradients(drgb=drgb, dT=None), return_uv_grad=True)
@@ -1000,9 +1002,10 @@ def test_sparse_mode_matches_dense(cuda_device, views):
     assert torch.equal(gs.sparse_gaussian_ids.long(), seen) and len(gs) == seen.numel()
     for attr in ("xyz", "quaternion_xyzw", "scale", "opacity", "color_sh_base", "color_sh"):
         dense = getattr(gd, attr)
-        assert_close(getattr(gs, attr).cpu().numpy(), dense[seen].cpu().numpy(), 1e-4, f"sparse grad {attr}", floor_frac=1e-3)
+        # the float atomics of the raster backward add in another order: not bit-equal
+        assert_close(getattr(gs, attr).cpu().numpy(), dense[seen].cpu().numpy(), GRAD_TOL, f"sparse grad {attr}", floor_frac=1e-2)
         rest = torch.ones(n, dtype=torch.bool, device=cuda_device)
         rest[seen] = False
         assert not dense[rest].any()
     got = duvs.reshape(-1, 2).cpu().numpy()
-    assert_close(got, duvd.reshape(-1, 2)[flat].cpu().numpy(), 1e-4, "sparse duv", floor_frac=1e-3)
+    assert_close(got, duvd.reshape(-1, 2)[flat].cpu().numpy(), GRAD_TOL, "sparse duv", floor_frac=1e-2)
