@@ -313,15 +313,15 @@ def load_peak():
 
 def roofline_block(stage_ms: dict, ms_per_step: float, N, V, K, P, Tn, training=True, with_traffic=True) -> dict:
     """Roofline of the stage with the largest share and of the whole step.  ``frac`` counts the bytes the launch
-    itself has to move; ``frac_survey_bytes`` the per-stage figures of the unfused pipeline (for a fused launch the
+    itself has to move; ``frac_unfused_bytes`` the per-stage figures of the unfused pipeline (for a fused launch the
     sum of the stages it replaces, which can exceed 1: those bytes are saved, not moved)."""
     peak, peak_kind = load_peak()
     kernel_stages = {k: v for k, v in stage_ms.items() if k not in COMM_STAGES and v > 0}
     dom = max(kernel_stages, key=kernel_stages.get)
     sec = kernel_stages[dom] * 1e-3
     moved = moved_bytes(dom, N, V, K, P, Tn, training)
-    survey = algorithmic_bytes(dom, N, V, K, P, Tn, training)
-    it_survey = sum(algorithmic_bytes(s, N, V, K, P, Tn, training) for s in kernel_stages)
+    unfused = algorithmic_bytes(dom, N, V, K, P, Tn, training)
+    it_unfused = sum(algorithmic_bytes(s, N, V, K, P, Tn, training) for s in kernel_stages)
     it_moved = sum(moved_bytes(s, N, V, K, P, Tn, training) for s in kernel_stages)
     step_sec = ms_per_step * 1e-3
     per_stage = {s: round(moved_bytes(s, N, V, K, P, Tn, training) / (t * 1e-3) / 1e9 / peak, 4)
@@ -332,11 +332,11 @@ def roofline_block(stage_ms: dict, ms_per_step: float, N, V, K, P, Tn, training=
             "traffic_source": "ncu dram bytes of the 750k-Gaussian case scaled by the bytes moved" if with_traffic else None,
             "peak_kind": peak_kind,
             "algorithmic_bytes_per_launch": moved,
-            "survey_bytes_per_launch": survey,
-            "frac_survey_bytes": survey / sec / 1e9 / peak,
+            "unfused_bytes_per_launch": unfused,
+            "frac_unfused_bytes": unfused / sec / 1e9 / peak,
             "stage_frac": per_stage,
-            "iteration": {"algorithmic_bytes": it_survey, "achieved": it_survey / step_sec / 1e9,
-                          "frac": it_survey / step_sec / 1e9 / peak,
+            "iteration": {"algorithmic_bytes": it_unfused, "achieved": it_unfused / step_sec / 1e9,
+                          "frac": it_unfused / step_sec / 1e9 / peak,
                           "moved_bytes": it_moved, "frac_moved_bytes": it_moved / step_sec / 1e9 / peak}}
 
 
