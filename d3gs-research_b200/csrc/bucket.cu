@@ -58,11 +58,9 @@ __device__ __forceinline__ void cswap(uint64_t& a, uint64_t& b) {
 // One CTA sorts one tile's list of n <= NT * VT entries.  Shared-memory slots are padded by one per VT entries
 // so that the per-thread runs (VT consecutive entries) start in different banks.
 template <int NT, int VT>
-__global__ void __launch_bounds__(NT)
-tile_sort_kernel(const uint64_t* __restrict__ entries, const int32_t* __restrict__ ranges, int32_t* __restrict__ sorted_values,
-                 uint64_t* __restrict__ sorted_keys, int lo, int hi, int pass_longer) {
-    extern __shared__ __align__(16) uint64_t s_e[];
-    const int tile = blockIdx.x;
+__device__ __forceinline__ void sort_one_tile(uint64_t* s_e, const int tile, const uint64_t* __restrict__ entries,
+                                              const int32_t* __restrict__ ranges, int32_t* __restrict__ sorted_values,
+                                              uint64_t* __restrict__ sorted_keys, int lo, int hi, int pass_longer) {
     const int r0 = ranges[tile * 2];
     const int n = ranges[tile * 2 + 1] - r0;
     const int t = threadIdx.x;
@@ -138,14 +136,35 @@ tile_sort_kernel(const uint64_t* __restrict__ entries, const int32_t* __restrict
     }
 }
 
+// The grid may be smaller than the number of tiles: a CTA then takes every gridDim.x-th tile.  The instance for the
+// longest lists holds 136 KB of shared memory, one CTA per SM; launched with one CTA per tile it spent 33 us on a
+// scene where no list needed it (8160 CTAs that leave at once, 148 at a time), so it gets two CTAs per SM's worth.
+template <int NT, int VT>
+__global__ void __launch_bounds__(NT)
+tile_sort_kernel(const uint64_t* __restrict__ entries, const int32_t* __restrict__ ranges, int num_tiles,
+                 int32_t* __restrict__ sorted_values, uint64_t* __restrict__ sorted_keys, int lo, int hi, int pass_longer) {
+    extern __shared__ __align__(16) uint64_t s_e[];
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        sort_one_tile<NT, VT>(s_e, tile, entries, ranges, sorted_values, sorted_keys, lo, hi, pass_longer);
+        __syncthreads();      // the next tile reuses the shared memory
+    }
+}
+
 template <int NT, int VT>
 int32_t launch_sort(const uint64_t* entries, const int32_t* ranges, int64_t num_tiles, int32_t* sorted_values,
                     uint64_t* sorted_keys, int lo, int hi, bool pass_longer, cudaStream_t s) {
     const size_t smem = (size_t)(NT * VT + NT) * sizeof(uint64_t);
     if (smem > 48 * 1024)
         D3GS_CUDA(cudaFuncSetAttribute(tile_sort_kernel<NT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    tile_sort_kernel<NT, VT><<<(unsigned)num_tiles, NT, smem, s>>>(entries, ranges, sorted_values, sorted_keys, lo, hi,
-                                                                   pass_longer ? 1 : 0);
+    int64_t grid = num_tiles;
+    if (NT >= 1024) {
+        int dev = 0, sms = 0;
+        D3GS_CUDA(cudaGetDevice(&dev));
+        D3GS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        grid = grid < 2 * (int64_t)sms ? grid : 2 * (int64_t)sms;
+    }
+    tile_sort_kernel<NT, VT><<<(unsigned)grid, NT, smem, s>>>(entries, ranges, (int)num_tiles, sorted_values, sorted_keys,
+                                                              lo, hi, pass_longer ? 1 : 0);
     D3GS_LAUNCH_CHECK("tile_sort_kernel");
     return D3GS_OK;
 }

@@ -133,49 +133,71 @@ __global__ void __launch_bounds__(kThreads) ssim_forward_kernel(const __grid_con
             float xv[16], yv[16];
             unpack16(&s_x[c][row][st * kStrip], xv);
             unpack16(&s_y[c][row][st * kStrip], yv);
-            float acc[kStrip][5];
+            // the five maps as two packed pairs and a scalar: (x, y), (x^2, y^2), x y -- one issue slot per pair
+            // (packed fp32 of sm_100, each half rounded like the scalar fma)
+            float2 a01[kStrip], a23[kStrip];
+            float a4[kStrip];
 #pragma unroll
-            for (int o = 0; o < kStrip; ++o)
-#pragma unroll
-                for (int m = 0; m < 5; ++m) acc[o][m] = 0.0f;
+            for (int o = 0; o < kStrip; ++o) {
+                a01[o] = make_float2(0.0f, 0.0f);
+                a23[o] = make_float2(0.0f, 0.0f);
+                a4[o] = 0.0f;
+            }
 #pragma unroll
             for (int i = 0; i < kTaps; ++i) {
-                const float x = xv[i], y = yv[i], xx = x * x, yy = y * y, xy = x * y;
+                const float2 p = make_float2(xv[i], yv[i]);
+                const float2 q = __fmul2_rn(p, p);
+                const float xy = p.x * p.y;
 #pragma unroll
                 for (int o = 0; o < kStrip; ++o) {
                     const int j = i - o;
                     if (j >= 0 && j < kWin) {
                         const float w = a.win.g[j];
-                        acc[o][0] += x * w; acc[o][1] += y * w; acc[o][2] += xx * w; acc[o][3] += yy * w; acc[o][4] += xy * w;
+                        const float2 ww = make_float2(w, w);
+                        a01[o] = __ffma2_rn(p, ww, a01[o]);
+                        a23[o] = __ffma2_rn(q, ww, a23[o]);
+                        a4[o] = fmaf(xy, w, a4[o]);
                     }
                 }
             }
-#pragma unroll
-            for (int m = 0; m < 5; ++m)
-                *reinterpret_cast<float4*>(&s_h[m][row][st * kStrip]) = make_float4(acc[0][m], acc[1][m], acc[2][m], acc[3][m]);
+            *reinterpret_cast<float4*>(&s_h[0][row][st * kStrip]) = make_float4(a01[0].x, a01[1].x, a01[2].x, a01[3].x);
+            *reinterpret_cast<float4*>(&s_h[1][row][st * kStrip]) = make_float4(a01[0].y, a01[1].y, a01[2].y, a01[3].y);
+            *reinterpret_cast<float4*>(&s_h[2][row][st * kStrip]) = make_float4(a23[0].x, a23[1].x, a23[2].x, a23[3].x);
+            *reinterpret_cast<float4*>(&s_h[3][row][st * kStrip]) = make_float4(a23[0].y, a23[1].y, a23[2].y, a23[3].y);
+            *reinterpret_cast<float4*>(&s_h[4][row][st * kStrip]) = make_float4(a4[0], a4[1], a4[2], a4[3]);
         }
         __syncthreads();
         {   // vertical: 32 columns x 4 strips of 4 rows = one item per thread
             const int col = t & 31, st = t >> 5;
-            float acc[kStrip][5];
+            float2 a01[kStrip], a23[kStrip];
+            float a4[kStrip];
 #pragma unroll
-            for (int o = 0; o < kStrip; ++o)
-#pragma unroll
-                for (int m = 0; m < 5; ++m) acc[o][m] = 0.0f;
+            for (int o = 0; o < kStrip; ++o) {
+                a01[o] = make_float2(0.0f, 0.0f);
+                a23[o] = make_float2(0.0f, 0.0f);
+                a4[o] = 0.0f;
+            }
 #pragma unroll
             for (int i = 0; i < kTaps; ++i) {
-                float v[5];
-#pragma unroll
-                for (int m = 0; m < 5; ++m) v[m] = s_h[m][st * kStrip + i][col];
+                const float2 v01 = make_float2(s_h[0][st * kStrip + i][col], s_h[1][st * kStrip + i][col]);
+                const float2 v23 = make_float2(s_h[2][st * kStrip + i][col], s_h[3][st * kStrip + i][col]);
+                const float v4 = s_h[4][st * kStrip + i][col];
 #pragma unroll
                 for (int o = 0; o < kStrip; ++o) {
                     const int j = i - o;
                     if (j >= 0 && j < kWin) {
                         const float w = a.win.g[j];
-#pragma unroll
-                        for (int m = 0; m < 5; ++m) acc[o][m] += v[m] * w;
+                        const float2 ww = make_float2(w, w);
+                        a01[o] = __ffma2_rn(v01, ww, a01[o]);
+                        a23[o] = __ffma2_rn(v23, ww, a23[o]);
+                        a4[o] = fmaf(v4, w, a4[o]);
                     }
                 }
+            }
+            float acc[kStrip][5];
+#pragma unroll
+            for (int o = 0; o < kStrip; ++o) {
+                acc[o][0] = a01[o].x; acc[o][1] = a01[o].y; acc[o][2] = a23[o].x; acc[o][3] = a23[o].y; acc[o][4] = a4[o];
             }
             const int px = bx + col;
 #pragma unroll
@@ -262,19 +284,34 @@ __global__ void __launch_bounds__(kThreads) ssim_backward_kernel(const __grid_co
         float(*s_cur)[kHY][kSX] = s_m;
         for (int item = t; item < kHY * (kTX / kStrip); item += kThreads) {
             const int row = item >> 3, st = item & 7;
+            {   // maps 0 and 1 as one packed pair, map 2 alone
+                float v0[16], v1[16], v2[16];
+                unpack16(&s_cur[0][row][st * kStrip], v0);
+                unpack16(&s_cur[1][row][st * kStrip], v1);
+                unpack16(&s_cur[2][row][st * kStrip], v2);
+                float2 a01[kStrip];
+                float a2[kStrip];
 #pragma unroll
-            for (int m = 0; m < 3; ++m) {
-                float v[16];
-                unpack16(&s_cur[m][row][st * kStrip], v);
-                float acc[kStrip] = {0.f, 0.f, 0.f, 0.f};
+                for (int o = 0; o < kStrip; ++o) {
+                    a01[o] = make_float2(0.0f, 0.0f);
+                    a2[o] = 0.0f;
+                }
 #pragma unroll
-                for (int i = 0; i < kTaps; ++i)
+                for (int i = 0; i < kTaps; ++i) {
+                    const float2 p = make_float2(v0[i], v1[i]);
 #pragma unroll
                     for (int o = 0; o < kStrip; ++o) {
                         const int j = i - o;
-                        if (j >= 0 && j < kWin) acc[o] += v[i] * a.win.g[j];
+                        if (j >= 0 && j < kWin) {
+                            const float w = a.win.g[j];
+                            a01[o] = __ffma2_rn(p, make_float2(w, w), a01[o]);
+                            a2[o] = fmaf(v2[i], w, a2[o]);
+                        }
                     }
-                *reinterpret_cast<float4*>(&s_h[m][row][st * kStrip]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                }
+                *reinterpret_cast<float4*>(&s_h[0][row][st * kStrip]) = make_float4(a01[0].x, a01[1].x, a01[2].x, a01[3].x);
+                *reinterpret_cast<float4*>(&s_h[1][row][st * kStrip]) = make_float4(a01[0].y, a01[1].y, a01[2].y, a01[3].y);
+                *reinterpret_cast<float4*>(&s_h[2][row][st * kStrip]) = make_float4(a2[0], a2[1], a2[2], a2[3]);
             }
         }
         __syncthreads();
@@ -291,7 +328,9 @@ __global__ void __launch_bounds__(kThreads) ssim_backward_kernel(const __grid_co
                     const int j = i - o;
                     if (j >= 0 && j < kWin) {
                         const float w = a.win.g[j];
-                        acc[o][0] += v0 * w; acc[o][1] += v1 * w; acc[o][2] += v2 * w;
+                        const float2 r = __ffma2_rn(make_float2(v0, v1), make_float2(w, w), make_float2(acc[o][0], acc[o][1]));
+                        acc[o][0] = r.x; acc[o][1] = r.y;
+                        acc[o][2] = fmaf(v2, w, acc[o][2]);
                     }
                 }
             }

@@ -588,9 +588,14 @@ class GaussianSplatOp:
         # and fall back to cudaMalloc (a device-wide stall of milliseconds) every few steps.
         cap = _pair_capacity(num_rendered)
         if use_bucket:
-            # classes of the tile sort to launch next time: those the longest list of this launch, grown by a
-            # quarter, falls into
-            self._ahead[(dev, B, num, num_tiles)] = (cap, min(sort_capacity, longest + longest // 4))
+            # Instances of the tile sort to launch next time: those this launch's longest list needs -- no margin, an
+            # instance nobody needs costs 20-30 us, a wrong guess one repeated launch -- but sticky: once a longer
+            # list has been met the guess only comes down when the lists have shrunk to half of it, so that a
+            # longest list hovering around an instance boundary does not repeat every other step.
+            sort_guess = longest
+            if ahead and longest > ahead[1] // 2:
+                sort_guess = max(longest, ahead[1])
+            self._ahead[(dev, B, num, num_tiles)] = (cap, min(sort_capacity, sort_guess))
             if ahead and (num_rendered > ahead[0] or _sort_class(longest) > _sort_class(ahead[1])):
                 self.launches_repeated += 1
                 bucket_prepare(0)       # the guess was too small: ranges and cursors again, then the chain below
