@@ -81,18 +81,6 @@ __device__ __forceinline__ ViewIn load_view(const BwdArgs& a, int b, int64_t g) 
     return v;
 }
 
-// the first view at or after `from` that sees Gaussian g (-1: none); keeps the largest radius met
-__device__ __forceinline__ int next_view(const BwdArgs& a, int64_t g, int from, int views, int& radmax) {
-    for (int b = from; b < views; ++b) {
-        const int r = a.v_radii[b][g];
-        if (r != 0) {
-            radmax = max(radmax, r);
-            return b;
-        }
-    }
-    return -1;
-}
-
 template <int DEG, bool MULTI, bool ADAM, bool PEER, bool INST = false>
 __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t* s_vis, uint64_t& s_bar, uint32_t& phase,
                                          const int64_t tile) {
@@ -106,16 +94,14 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
     const int64_t g0 = a.g_begin + tile * 256;
     const int64_t g = g0 + t;
 
-    // Which views see this Gaussian, as a bit mask, and its largest radius; a view batch on this GPU asks for all
-    // the views' radii before any is used.  PEER (the views live on other GPUs): measured, the mask and the
-    // one-view-ahead requests below made the launch SLOWER (1.44 -> 1.61 ms at 8 GPUs, 1.18 -> 1.26 at 4; more live
-    // registers, 540 bytes of spills), so that instance walks the views the plain way: radius, test, loads, arithmetic.
+    // Which views see this Gaussian, as a bit mask, and its largest radius.  All the views' radii are asked for
+    // before any is used: with the views on other GPUs every load is a round trip over NVLink, and eight in a row
+    // would cost eight of them.  (A/B on one 8-GPU box, two runs each: this and the one-view-ahead requests below
+    // against the plain walk -- radius, test, loads, arithmetic per view -- 1.56 against 1.66 ms for the launch.)
     uint32_t vis = 0;
     int radmax = 0;
     if (g < range_end) {
-        if constexpr (PEER) {
-            for (int b = 0; b < cf.num_views; ++b) vis |= a.v_radii[b][g] != 0 ? 1u : 0u;
-        } else if constexpr (MULTI) {
+        if constexpr (MULTI) {
             int rad[D3GS_MAX_VIEWS];
 #pragma unroll
             for (int b = 0; b < D3GS_MAX_VIEWS; ++b) rad[b] = b < cf.num_views ? a.v_radii[b][g] : 0;
@@ -237,17 +223,12 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         // The views that see the Gaussian, one after the other; the next view's inputs (48 bytes of raster gradient,
         // the 2D covariance, the clamp bits) are requested before the current view's arithmetic starts.
         uint32_t rem = vis;
-        int b = 0;
-        if constexpr (PEER) {
-            b = next_view(a, g, 0, cf.num_views, radmax);
-        } else {
-            b = __ffs((int)rem) - 1;
-        }
+        int b = __ffs((int)rem) - 1;
         ViewIn cur = load_view(a, b, g);
         while (true) {
             int b_next = -1;
             ViewIn nxt = cur;
-            if constexpr (MULTI && !PEER) {
+            if constexpr (MULTI) {
                 rem &= rem - 1;
                 if (rem != 0) {
                     b_next = __ffs((int)rem) - 1;
@@ -414,14 +395,8 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             axyz[0] += dxyz[0] + (ddx - x * dd) * dni;
             axyz[1] += dxyz[1] + (ddy - y * dd) * dni;
             axyz[2] += dxyz[2] + (ddz - zz_ * dd) * dni;
-            if constexpr (PEER) {
-                b_next = next_view(a, g, b + 1, cf.num_views, radmax);
-                if (b_next < 0) break;
-                cur = load_view(a, b_next, g);
-            } else {
-                if (b_next < 0) break;
-                cur = nxt;
-            }
+            if (b_next < 0) break;
+            cur = nxt;
             b = b_next;
         }
         // Sigma = M M^T (gs3d.py:387-418): dM = 2 dSigma M (dSigma symmetric), ds_j = <dM[:,j], R[:,j]>
