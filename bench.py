@@ -53,6 +53,8 @@ def parse():
     ap.add_argument("--config", default="cfg3")
     ap.add_argument("--n", type=int, default=0, help="override the Gaussian count (profiling on small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--peer-lanes", type=int, default=0, choices=[0, 1, 2, 4],
+                    help="N>1, fused exchange: lanes that share one Gaussian in the exchange launch (0 = the library's choice)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "symm", "symm-nomc", "ipc", "nccl"],
                     help="N>1: how gradients are summed and parameters broadcast.  fused (the default when symmetric "
                          "memory can be set up): one launch does the preprocess backward of all ranks' views from their "
@@ -482,6 +484,7 @@ def bench_train(args):
                            fuse_backward_adam=False if (args.separate_adam or world > 1 or not do_update) else None)
     trainer.op.raster_grad_direct = {"auto": None, "direct": True, "shared": False}[args.raster_grad_mode]
     trainer.op.binning = args.binning
+    trainer.peer_lanes = args.peer_lanes
     fx, fy, cx, cy = sc["intrinsics"]
     cam = d3.BasicPinholeCamera.from_params(sc["cam2worlds"][rank % len(sc["cam2worlds"])], fx, fy, cx, cy, W, H)
     # the cameras of all ranks of this step's batch, in rank order (a training loop knows the batch it draws)

@@ -81,7 +81,7 @@ class PeerSet(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("grad", C.c_void_p * MAX_PEERS),
                 ("param", C.c_void_p * MAX_PEERS), ("status", C.c_void_p), ("grad_mc", C.c_void_p),
                 ("param_mc", C.c_void_p), ("flags", C.c_void_p * MAX_PEERS), ("epoch", C.c_uint32),
-                ("wait_limit", C.c_uint32)]
+                ("wait_limit", C.c_uint32), ("lanes_per_gaussian", C.c_int32), ("reserved_", C.c_int32)]
 
 
 class PeerViews(C.Structure):

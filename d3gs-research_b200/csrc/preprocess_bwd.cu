@@ -81,18 +81,33 @@ __device__ __forceinline__ ViewIn load_view(const BwdArgs& a, int b, int64_t g) 
     return v;
 }
 
-template <int DEG, bool MULTI, bool ADAM, bool PEER, bool INST = false>
+template <int DEG, bool MULTI, bool ADAM, bool PEER, bool INST = false, int Q = 1>
 __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t* s_vis, uint64_t& s_bar, uint32_t& phase,
                                          const int64_t tile) {
+    // PEER with Q = 2 or 4: Q lanes per Gaussian, lane vq taking the views b with b % Q == vq, so that the round
+    // trips to the other GPUs for several of a Gaussian's views are in flight together (one lane per Gaussian walks
+    // them one after the other, one view ahead); a tile is then 256 / Q Gaussians, every lane accumulates its views'
+    // SH-gradient row in a plane of its own (summed when the optimizer sweep reads them) and the scalar sums are
+    // reduced over the Q lanes.  Lanes without a view idle through the per-view arithmetic, so Q pays only when
+    // there are several views per lane to wait for.
+    static_assert(Q == 1 || (PEER && (Q == 2 || Q == 4)), "several lanes per Gaussian only in the peer launch");
+    constexpr int kQuad = Q;
+    constexpr int kTileG = 256 / kQuad;           // Gaussians per tile
+    // floats between the lanes' planes of gradient rows: 32 / Q more than the rows take, so that the lanes of a
+    // Gaussian (same row, same element) and the Gaussians of a warp fall into 32 different banks
+    constexpr int kPlane = kTileG * kRow + (Q > 1 ? 32 / Q : 0);
     float* s_in = smem;
-    float* s_out = MULTI ? smem + 256 * kRow : smem;
+    float* s_out = MULTI ? smem + kTileG * kRow : smem;
     const int t = threadIdx.x;
+    const int gi = t / Q;                          // this thread's Gaussian within the tile
+    const int vq = t % Q;
+    const unsigned qmask = Q > 1 ? (((1u << Q) - 1u) << (t & 31 & ~(Q - 1))) : 0xffffffffu;   // lanes sharing this Gaussian
     const D3gsOpConfig& cf = a.cfg;
     constexpr int NB = (DEG + 1) * (DEG + 1);
     constexpr int NR3 = (NB - 1) * 3;
     const int64_t range_end = a.g_begin + a.g_count;
-    const int64_t g0 = a.g_begin + tile * 256;
-    const int64_t g = g0 + t;
+    const int64_t g0 = a.g_begin + tile * kTileG;
+    const int64_t g = g0 + gi;
 
     // Which views see this Gaussian, as a bit mask, and its largest radius.  All the views' radii are asked for
     // before any is used: with the views on other GPUs every load is a round trip over NVLink, and eight in a row
@@ -104,7 +119,8 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         if constexpr (MULTI) {
             int rad[D3GS_MAX_VIEWS];
 #pragma unroll
-            for (int b = 0; b < D3GS_MAX_VIEWS; ++b) rad[b] = b < cf.num_views ? a.v_radii[b][g] : 0;
+            for (int b = 0; b < D3GS_MAX_VIEWS; ++b)
+                rad[b] = (b < cf.num_views && (b & (Q - 1)) == vq) ? a.v_radii[b][g] : 0;
 #pragma unroll
             for (int b = 0; b < D3GS_MAX_VIEWS; ++b) {
                 vis |= rad[b] != 0 ? 1u << b : 0u;
@@ -115,9 +131,14 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             vis = radmax != 0 ? 1u : 0u;
         }
     }
-    const bool any_view = vis != 0;
-    s_vis[t] = any_view ? 1 : 0;
-    const int rows = (int)min((int64_t)256, range_end - g0);
+    bool any_view = vis != 0;       // Q > 1: some lane of the Gaussian has a view that sees it
+    if constexpr (Q > 1) {
+        any_view = __ballot_sync(0xffffffffu, any_view) & qmask;
+        if (vq == 0) s_vis[gi] = any_view ? 1 : 0;
+    } else {
+        s_vis[t] = any_view ? 1 : 0;
+    }
+    const int rows = (int)min((int64_t)kTileG, range_end - g0);
     // contiguous degree-3 layout: the CTA's rows are one 16-byte aligned span -> one bulk async copy
     const bool bulk_in = NR3 > 0 && a.model.sh_rest_stride == 45 && (rows & 3) == 0 &&
                          ((uintptr_t)(a.model.sh_rest + g0 * 45) & 15) == 0;
@@ -151,14 +172,14 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             const float* src = a.model.sh_rest;
             const int64_t stride = a.model.sh_rest_stride;
             constexpr int kU = NR3 % 9 == 0 ? 9 : 3;
-            for (int f0 = t; f0 < 256 * NR3; f0 += 256 * kU) {
+            for (int f0 = t; f0 < kTileG * NR3; f0 += 256 * kU) {
                 float tmp[kU];
                 int dst[kU];
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
                     const int f = f0 + u * 256;
                     const int row = f / NR3, k = f - row * NR3;
-                    const bool ok = f < 256 * NR3 && s_vis[row];
+                    const bool ok = f < kTileG * NR3 && s_vis[row];
                     dst[u] = ok ? row * kRow + k : -1;
                     tmp[u] = ok ? src[(g0 + row) * stride + k] : 0.0f;
                 }
@@ -177,8 +198,8 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         if (t == 0 && a.status != nullptr) atomicOr(a.status, D3GS_STATUS_COPY_TIMEOUT);
         return false;
     }
-    float* my_in = s_in + t * kRow;
-    float* my_out = s_out + t * kRow;
+    float* my_in = s_in + gi * kRow;
+    float* my_out = s_out + vq * kPlane + gi * kRow;
 
     float axyz[3] = {0.f, 0.f, 0.f}, aq[4] = {0.f, 0.f, 0.f, 0.f}, as[3] = {0.f, 0.f, 0.f}, ao = 0.f;
     float abase[3] = {0.f, 0.f, 0.f};
@@ -224,8 +245,9 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         // the 2D covariance, the clamp bits) are requested before the current view's arithmetic starts.
         uint32_t rem = vis;
         int b = __ffs((int)rem) - 1;
-        ViewIn cur = load_view(a, b, g);
-        while (true) {
+        ViewIn cur = {};
+        if (Q == 1 || vis != 0) cur = load_view(a, b, g);
+        while (Q == 1 || vis != 0) {
             int b_next = -1;
             ViewIn nxt = cur;
             if constexpr (MULTI) {
@@ -399,6 +421,22 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             cur = nxt;
             b = b_next;
         }
+        if constexpr (Q > 1) {     // the lanes' sums for this Gaussian
+#pragma unroll
+            for (int o = 1; o < Q; o <<= 1) {
+#pragma unroll
+                for (int r = 0; r < 3; ++r) {
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) dSacc[r][c] += __shfl_xor_sync(qmask, dSacc[r][c], o);
+                    axyz[r] += __shfl_xor_sync(qmask, axyz[r], o);
+                    abase[r] += __shfl_xor_sync(qmask, abase[r], o);
+                }
+                ao += __shfl_xor_sync(qmask, ao, o);
+                st_len += __shfl_xor_sync(qmask, st_len, o);
+                st_cnt += __shfl_xor_sync(qmask, st_cnt, o);
+                st_rad = fmaxf(st_rad, __shfl_xor_sync(qmask, st_rad, o));
+            }
+        }
         // Sigma = M M^T (gs3d.py:387-418): dM = 2 dSigma M (dSigma symmetric), ds_j = <dM[:,j], R[:,j]>
         float dM[3][3];
 #pragma unroll
@@ -424,7 +462,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         aq[0] = (dq[0] - qx * dot) * qni; aq[1] = (dq[1] - qy * dot) * qni;
         aq[2] = (dq[2] - qz * dot) * qni; aq[3] = (dq[3] - qw * dot) * qni;
         if (fused) ao = ao * opac * (1.0f - opac);   // sigmoid_grad_out: g * out * (1 - out)
-        if (PEER && a.has_stats) {
+        if (PEER && a.has_stats && vq == 0) {
             a.stats.duv_ndc_length[g] += st_len;
             a.stats.count[g] += st_cnt;
             if (a.stats.need_max_radii) a.stats.max_radii[g] = fmaxf(a.stats.max_radii[g], st_rad);
@@ -436,18 +474,22 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
         // thread), exactly like the stand-alone optimizer kernel but with the gradient coming from shared
         // memory.  The parameters are updated in place: a CTA reads and writes only its own Gaussians'.
         if (!PEER && a.has_stats && g < range_end) stats_update(a.stats, g);
-        // [xyz 768 | quaternion 1024 | scale 768 | opacity 256 | sh_base 768]
-        float* s_small = smem + (MULTI ? 2 : 1) * 256 * kRow;
-        s_small[t * 3] = axyz[0]; s_small[t * 3 + 1] = axyz[1]; s_small[t * 3 + 2] = axyz[2];
-        *reinterpret_cast<float4*>(s_small + 768 + t * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
-        s_small[1792 + t * 3] = as[0]; s_small[1792 + t * 3 + 1] = as[1]; s_small[1792 + t * 3 + 2] = as[2];
-        s_small[2560 + t] = ao;
-        s_small[2816 + t * 3] = abase[0]; s_small[2816 + t * 3 + 1] = abase[1]; s_small[2816 + t * 3 + 2] = abase[2];
+        // per tile of T Gaussians: [xyz 3T | quaternion 4T | scale 3T | opacity T | sh_base 3T], behind the SH rows
+        // (PEER: behind the coefficient rows and the four gradient planes)
+        float* s_small = smem + kTileG * kRow + (MULTI ? kQuad * kPlane : 0);
+        if (vq == 0) {
+            s_small[gi * 3] = axyz[0]; s_small[gi * 3 + 1] = axyz[1]; s_small[gi * 3 + 2] = axyz[2];
+            *reinterpret_cast<float4*>(s_small + 3 * kTileG + gi * 4) = make_float4(aq[0], aq[1], aq[2], aq[3]);
+            s_small[7 * kTileG + gi * 3] = as[0]; s_small[7 * kTileG + gi * 3 + 1] = as[1]; s_small[7 * kTileG + gi * 3 + 2] = as[2];
+            s_small[10 * kTileG + gi] = ao;
+            s_small[11 * kTileG + gi * 3] = abase[0]; s_small[11 * kTileG + gi * 3 + 1] = abase[1];
+            s_small[11 * kTileG + gi * 3 + 2] = abase[2];
+        }
         __syncthreads();
         const float* params[6] = {a.model.xyz, a.model.quaternion_xyzw, a.model.scale, a.model.opacity,
                                   a.model.sh_base, a.model.sh_rest};
         const int per[6] = {3, 4, 3, 1, 3, 45};
-        const int soff[6] = {0, 768, 1792, 2560, 2816, -1};
+        const int soff[6] = {0, 3 * kTileG, 7 * kTileG, 10 * kTileG, 11 * kTileG, -1};
 #pragma unroll
         for (int fld = 0; fld < 6; ++fld) {
             const int count = rows * per[fld];
@@ -475,6 +517,13 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
                         const int q = q0 + u * 256;
                         if (q < count / 4) {
                             float4 gr = reinterpret_cast<const float4*>(gs)[q];
+                            if (Q > 1 && fld == 5) {     // the lanes' planes of SH-gradient rows
+#pragma unroll
+                                for (int pl = 1; pl < kQuad; ++pl) {
+                                    const float4 o4 = reinterpret_cast<const float4*>(gs + pl * kPlane)[q];
+                                    gr.x += o4.x; gr.y += o4.y; gr.z += o4.z; gr.w += o4.w;
+                                }
+                            }
                             if (fld == 5 && NR3 < 45) {   // coefficients above the active degree have no gradient
                                 const int k0 = (q * 4) % 45;
                                 if (k0 >= NR3) gr.x = 0.0f;
@@ -501,6 +550,10 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
             } else {
                 for (int f = t; f < count; f += 256) {
                     float gr = gs[f];
+                    if (Q > 1 && fld == 5) {
+#pragma unroll
+                        for (int pl = 1; pl < kQuad; ++pl) gr += gs[pl * kPlane + f];
+                    }
                     if (fld == 5 && NR3 < 45 && f % 45 >= NR3) gr = 0.0f;
                     float p = pp[f], m = pm[f], v = pv[f];
                     adam_update(gr, p, m, v, c);
@@ -558,7 +611,7 @@ __device__ __forceinline__ bool bwd_tile(const BwdArgs& a, float* smem, uint8_t*
 // stores the new parameters into EVERY rank's parameter buffer.  The 236-byte-per-Gaussian parameter gradient
 // never exists: what crosses the links is the rasteriser's 48 bytes per (view, Gaussian) plus 17 bytes of
 // context inbound, and the parameters outbound.  The launches of the ranks are ordered by flags (exchange.cuh).
-template <int DEG, bool MULTI, bool ADAM, bool PEER = false, bool INST = false>
+template <int DEG, bool MULTI, bool ADAM, bool PEER = false, bool INST = false, int Q = 1>
 __global__ void __launch_bounds__(256, PEER ? 2 : 3) preprocess_bwd_kernel(const __grid_constant__ BwdArgs a) {
     extern __shared__ __align__(16) float smem[];
     __shared__ uint8_t s_vis[256];
@@ -572,10 +625,11 @@ __global__ void __launch_bounds__(256, PEER ? 2 : 3) preprocess_bwd_kernel(const
         // a resident grid that strides over the tiles: the flag exchange and the system-wide fence at the end are
         // paid once per CTA
         const bool ready = exchange_begin(a.peers);   // every rank's raster gradients are complete (contains a barrier)
-        const int64_t num_tiles = (a.g_count + 255) / 256;
+        constexpr int kTileG = 256 / Q;
+        const int64_t num_tiles = (a.g_count + kTileG - 1) / kTileG;
         if (ready) {      // else a rank never announced its gradients: change nothing
             for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                if (!bwd_tile<DEG, MULTI, ADAM, PEER>(a, smem, s_vis, s_bar, phase, tile)) break;
+                if (!bwd_tile<DEG, MULTI, ADAM, PEER, INST, Q>(a, smem, s_vis, s_bar, phase, tile)) break;
                 __syncthreads();      // the next tile reuses the shared memory
             }
         }
@@ -798,7 +852,12 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
     a.hooks = test_hooks();
     a.g_begin = g_begin;
     a.g_count = g_count;
-    const int64_t tiles = div_up64(g_count, 256);
+    // lanes per Gaussian: 0 = chosen here from the number of views a lane would have to wait for
+    int lanes = peers->lanes_per_gaussian;
+    D3GS_REQUIRE(lanes == 0 || lanes == 1 || lanes == 2 || lanes == 4, "lanes_per_gaussian must be 0, 1, 2 or 4 (got %d)", lanes);
+    if (lanes == 0) lanes = peers->world >= 8 ? 4 : 1;
+    const int tile_g = 256 / lanes;
+    const int64_t tiles = div_up64(g_count, tile_g);
     // every rank launches, even with an empty share: the flag exchange needs all ranks
     int dev = 0, sms = 0;
     D3GS_CUDA(cudaGetDevice(&dev));
@@ -806,12 +865,20 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
     int64_t grid = tiles < (int64_t)sms * 2 ? tiles : (int64_t)sms * 2;
     if (grid < 1) grid = 1;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)256 * (2 * kRow + 14) * sizeof(float);   // SH rows in, gradient rows, small fields
+    // SH rows in, one (padded) plane of gradient rows per lane of a Gaussian, small fields
+    const size_t smem = (size_t)(tile_g * kRow + lanes * (tile_g * kRow + (lanes > 1 ? 32 / lanes : 0)) + tile_g * 14) *
+                        sizeof(float);
+#define D3GS_LAUNCH_BWD_PEER_Q(DEG, QQ)                                                                         \
+    do {                                                                                                        \
+        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, true, true, true, false, QQ>,                 \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
+        preprocess_bwd_kernel<DEG, true, true, true, false, QQ><<<(unsigned)grid, 256, smem, s>>>(a);           \
+    } while (0)
 #define D3GS_LAUNCH_BWD_PEER(DEG)                                                                               \
     do {                                                                                                        \
-        D3GS_CUDA(cudaFuncSetAttribute(preprocess_bwd_kernel<DEG, true, true, true>,                            \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                \
-        preprocess_bwd_kernel<DEG, true, true, true><<<(unsigned)grid, 256, smem, s>>>(a);                      \
+        if (lanes == 4) D3GS_LAUNCH_BWD_PEER_Q(DEG, 4);                                                         \
+        else if (lanes == 2) D3GS_LAUNCH_BWD_PEER_Q(DEG, 2);                                                    \
+        else D3GS_LAUNCH_BWD_PEER_Q(DEG, 1);                                                                    \
     } while (0)
     switch (cfg->sh_degree) {
         case 0: D3GS_LAUNCH_BWD_PEER(0); break;
@@ -820,6 +887,7 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
         default: D3GS_LAUNCH_BWD_PEER(3); break;
     }
 #undef D3GS_LAUNCH_BWD_PEER
+#undef D3GS_LAUNCH_BWD_PEER_Q
     D3GS_LAUNCH_CHECK("preprocess_bwd_kernel<peers>");
     return D3GS_OK;
 }

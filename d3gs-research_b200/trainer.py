@@ -309,6 +309,7 @@ class SplatTrainer:
         self._peerset = None
         self._epoch = 0
         self.peer_wait_limit = 0      # polls before a flag wait inside the exchange kernel gives up; 0 = default
+        self.peer_lanes = 0           # fused exchange: lanes that share one Gaussian (1, 2, 4; 0 = the library's choice)
         self.fused_exchange = False
         self.peer_views = None
         if self.peer_param is not None:
@@ -764,6 +765,7 @@ class SplatTrainer:
         self._epoch += 1
         self._peerset.epoch = self._epoch
         self._peerset.wait_limit = int(self.peer_wait_limit)
+        self._peerset.lanes_per_gaussian = int(self.peer_lanes)
         self.op.backward_adam_peers(model, bundle, self._views_struct, self.g_begin, self.g_count,
                                     self._fused_segments(), self._peerset, st)
         return {"out": out, "loss": loss, "num_rendered": self.op.last_num_rendered}

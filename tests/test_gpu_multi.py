@@ -34,7 +34,10 @@ pytestmark = pytest.mark.gpu
 PATHS = (("fused", dict(peer_update="symm", fuse_exchange=True)),
          ("symm-mc", dict(peer_update="symm", multicast=None, fuse_exchange=False)),
          ("symm", dict(peer_update="symm", multicast=False, fuse_exchange=False)),
-         ("ipc", dict(peer_update="ipc")), ("nccl", dict(peer_update=False)), ("replicated", dict(shard_optimizer=False)))
+         ("ipc", dict(peer_update="ipc")), ("nccl", dict(peer_update=False)), ("replicated", dict(shard_optimizer=False)),
+         # the fused launch with two and with four lanes per Gaussian (each lane takes every 2nd / 4th view)
+         ("fused-2", dict(peer_update="symm", fuse_exchange=True, _lanes=2)),
+         ("fused-4", dict(peer_update="symm", fuse_exchange=True, _lanes=4)))
 
 
 def _worker(rank, world, port, q):
@@ -81,11 +84,14 @@ def _worker(rank, world, port, q):
         results = {}
         for name, kw in PATHS:
             model = gpu_model(sc, dev)
+            kw = dict(kw)
+            lanes = kw.pop("_lanes", 0)
             tr = SplatTrainer(model, op_cfg, lambda_dssim=0.2, batch_size=world, **kw)
+            tr.peer_lanes = lanes
             check(tr.sharded == (name != "replicated"), f"{name}: sharded = {tr.sharded}")
-            check(tr.exchange == {"fused": "symm", "symm-mc": "symm", "symm": "symm", "ipc": "ipc"}.get(name, "nccl"),
-                  f"{name}: exchange = {tr.exchange}")
-            check(tr.fused_exchange == (name == "fused"), f"{name}: fused_exchange = {tr.fused_exchange}")
+            check(tr.exchange == {"fused": "symm", "fused-2": "symm", "fused-4": "symm", "symm-mc": "symm", "symm": "symm",
+                                  "ipc": "ipc"}.get(name, "nccl"), f"{name}: exchange = {tr.exchange}")
+            check(tr.fused_exchange == name.startswith("fused"), f"{name}: fused_exchange = {tr.fused_exchange}")
             all_cams = [d3.BasicPinholeCamera.from_params(m, fx, fy, cx, cy, 160, 112) for m in sc["cam2worlds"]]
             if name == "symm-mc" and not tr.multicast:
                 notes.append("no multicast mapping on this box: symm-mc ran with plain peer accesses")
@@ -114,7 +120,7 @@ def _worker(rank, world, port, q):
             torch.cuda.synchronize()
             dist.barrier()
             # (a) fixed gradients (the fused path has no gradient buffer to put them in)
-            if name != "fused":
+            if not name.startswith("fused"):
                 for t in range(3):
                     gen = torch.Generator().manual_seed(1000 * t + rank)
                     tr.grad_flat[:tr.flat_total].copy_(torch.randn(tr.flat_total, generator=gen))
@@ -137,7 +143,7 @@ def _worker(rank, world, port, q):
         init = gpu_model(sc, dev).flat[:results["ipc"][0].numel()]
         ok = True
         for name, _ in PATHS:
-            if name in ("ipc", "fused"):      # fused: no fixed-gradient updates, so a different state; it has (c)
+            if name == "ipc" or name.startswith("fused"):   # fused: no fixed-gradient updates, a different state; it has (c)
                 continue
             exact = bool(torch.equal(results["ipc"][0], results[name][0]))               # (a) exact
             counts = bool(torch.equal(results["ipc"][2], results[name][2]))             # visibility counts
