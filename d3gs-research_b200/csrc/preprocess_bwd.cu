@@ -855,7 +855,9 @@ extern "C" int32_t d3gs_preprocess_backward_adam_peers(const D3gsOpConfig* cfg, 
     // lanes per Gaussian: 0 = chosen here from the number of views a lane would have to wait for
     int lanes = peers->lanes_per_gaussian;
     D3GS_REQUIRE(lanes == 0 || lanes == 1 || lanes == 2 || lanes == 4, "lanes_per_gaussian must be 0, 1, 2 or 4 (got %d)", lanes);
-    if (lanes == 0) lanes = peers->world >= 8 ? 4 : 1;
+    // measured (cfg3, one box each): 8 ranks 3.61 / 3.47 / 3.45 ms per step with 1 / 2 / 4 lanes, 4 ranks 3.22 / 3.18 / 3.24,
+    // 2 ranks 3.06 / - / 4.12
+    if (lanes == 0) lanes = peers->world >= 8 ? 4 : (peers->world >= 4 ? 2 : 1);
     const int tile_g = 256 / lanes;
     const int64_t tiles = div_up64(g_count, tile_g);
     // every rank launches, even with an empty share: the flag exchange needs all ranks

@@ -401,7 +401,7 @@ typedef struct D3gsPeerSet {
     uint32_t wait_limit;
     /* d3gs_preprocess_backward_adam_peers only: lanes that share one Gaussian, each taking every
      * lanes_per_gaussian-th view, so that the loads from several ranks are in flight together: 1, 2 or 4;
-     * 0 = chosen by the library (4 from eight ranks on, else 1) */
+     * 0 = chosen by the library (4 from eight ranks on, 2 from four, else 1) */
     int32_t lanes_per_gaussian;
     int32_t reserved_;
 } D3gsPeerSet;
